@@ -1,0 +1,369 @@
+"""Throughput benchmark: GPT-2 124M training with Distributed Shampoo.
+
+Metric: training tokens per second (whole job) and milliseconds per step, on N GPUs of one
+node.  Model and optimizer follow the reference benchmark configuration: 12 layers,
+d_model 768, 12 heads, MLP 3072, vocabulary 50257, sequence 1024, batch 16 per GPU, bf16
+autocast, fp32 Kronecker factors, max_preconditioner_dim 2048, precondition_frequency 100,
+AdaGrad grafting.  Data is synthetic (uniform token ids) and weights are randomly initialised.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5                  # this framework
+    python bench.py --impl reference --gpus 1 --steps 20 --warmup 5 # unmodified reference
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+The step counter of the optimizer is preset to ``start_preconditioning_step - 1`` (in both
+arms) so that the first warm-up step performs the root-inverse refresh and every timed step
+runs the preconditioned path; further refreshes fall in the timed region whenever the step
+count crosses a multiple of ``precondition_frequency``.
+
+Rank 0 prints one JSON line.  ``value`` is timed on the device with CUDA events around the K
+steps (inputs already on the device); ``e2e`` repeats the K steps through the public API with a
+pinned-host -> device copy of each step's tokens and a device -> host read of each step's loss
+inside the timed region.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+REF_DIR = os.path.join(REPO, "baseline", "_ref")
+
+SEQ = 1024
+BATCH_PER_GPU = 16
+VOCAB = 50257
+MAX_PRECOND_DIM = 2048
+PRECOND_FREQ = 100
+
+
+def parse_args() -> argparse.Namespace:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--backend", choices=["auto", "native", "torch"], default="native")
+    ap.add_argument("--gemm-mode", choices=["tf32x3", "tf32"], default="tf32x3")
+    ap.add_argument("--layers", type=int, default=12, help="debug only; the reported config needs 12")
+    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="debug only; the reported config needs 16")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = (
+        "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.proc: subprocess.Popen | None = None
+        self.lines: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self) -> None:
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def make_gpt2(n_layer: int):
+    """Plain-PyTorch GPT-2 124M (pre-LN, learned positions, tied embedding), defined here so that
+    the reference arm imports nothing from this repository's package."""
+    import math
+
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    d_model, n_head, d_mlp, n_ctx = 768, 12, 3072, 1024
+
+    class Block(nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.ln_1 = nn.LayerNorm(d_model)
+            self.attn_qkv = nn.Linear(d_model, 3 * d_model)
+            self.attn_proj = nn.Linear(d_model, d_model)
+            self.ln_2 = nn.LayerNorm(d_model)
+            self.mlp_fc = nn.Linear(d_model, d_mlp)
+            self.mlp_proj = nn.Linear(d_mlp, d_model)
+
+        def forward(self, x):
+            B, T, C = x.shape
+            q, k, v = self.attn_qkv(self.ln_1(x)).split(C, dim=2)
+            q, k, v = (t.view(B, T, n_head, C // n_head).transpose(1, 2) for t in (q, k, v))
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            x = x + self.attn_proj(a.transpose(1, 2).reshape(B, T, C))
+            return x + self.mlp_proj(F.gelu(self.mlp_fc(self.ln_2(x)), approximate="tanh"))
+
+    class GPT2(nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.wte = nn.Embedding(VOCAB, d_model)
+            self.wpe = nn.Embedding(n_ctx, d_model)
+            self.blocks = nn.ModuleList(Block() for _ in range(n_layer))
+            self.ln_f = nn.LayerNorm(d_model)
+            for m in self.modules():
+                if isinstance(m, (nn.Linear, nn.Embedding)):
+                    nn.init.normal_(m.weight, mean=0.0, std=0.02)
+                if isinstance(m, nn.Linear):
+                    nn.init.zeros_(m.bias)
+            for name, p in self.named_parameters():
+                if name.endswith("proj.weight"):
+                    nn.init.normal_(p, mean=0.0, std=0.02 / math.sqrt(2 * n_layer))
+
+        def forward(self, idx, targets):
+            x = self.wte(idx) + self.wpe(torch.arange(idx.shape[1], device=idx.device))
+            for blk in self.blocks:
+                x = blk(x)
+            logits = F.linear(self.ln_f(x), self.wte.weight)
+            return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))
+
+    return GPT2()
+
+
+def build_optimizer(impl: str, model, world: int, args):
+    import torch
+
+    if impl == "reference":
+        sys.path.insert(0, REF_DIR)
+        import distributed_shampoo as lib  # the unmodified reference, installed under baseline/_ref
+
+        assert os.path.realpath(lib.__file__).startswith(os.path.realpath(REF_DIR)), lib.__file__
+        extra = {}
+    else:
+        import optimizers_b200 as lib
+
+        extra = {"native_runtime_config": lib.NativeRuntimeConfig(backend=args.backend, gemm_mode=args.gemm_mode)}
+    if world > 1:
+        dist_cfg = lib.DDPDistributedConfig(communication_dtype=torch.bfloat16, num_trainers_per_group=world)
+    else:
+        dist_cfg = lib.DefaultSingleDeviceDistributedConfig
+    opt = lib.DistributedShampoo(
+        model.parameters(),
+        lr=1e-3,
+        betas=(0.9, 1.0),
+        epsilon=1e-12,
+        max_preconditioner_dim=MAX_PRECOND_DIM,
+        precondition_frequency=PRECOND_FREQ,
+        start_preconditioning_step=PRECOND_FREQ,
+        grafting_config=lib.AdaGradPreconditionerConfig(epsilon=1e-10),
+        distributed_config=dist_cfg,
+        **extra,
+    )
+    # Resume-style preset of the shared step counter (a CPU tensor aliased under every parameter).
+    for state in opt.state.values():
+        if "step" in state:
+            state["step"].fill_(PRECOND_FREQ - 1)
+            break
+    return opt
+
+
+def count_native_launches(opt) -> int:
+    total = 0
+    for rec in getattr(opt, "_per_group_state_lists", []):
+        eng = rec.get("native_engine") if isinstance(rec, dict) else None
+        if eng is not None:
+            total += eng.launches_per_step
+    return total
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference" and not os.path.isdir(os.path.join(REF_DIR, "distributed_shampoo")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing; install the reference with pip --target baseline/_ref"}))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # Convenience: re-launch under torchrun when called as plain `python bench.py --gpus N`.
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__), *sys.argv[1:]]
+            raise SystemExit(subprocess.call(cmd))
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    if args.impl == "ours":
+        sys.path.insert(0, REPO)
+    torch.manual_seed(1234)
+    torch.backends.cuda.matmul.allow_tf32 = False  # optimizer math of the reference stays fp32
+    model = make_gpt2(args.layers).to(dev)
+    train_model = model
+    if world > 1:
+        train_model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
+    opt = build_optimizer(args.impl, model, world, args)
+    if hasattr(opt, "train"):
+        opt.train()
+
+    B = args.batch
+    gen = torch.Generator().manual_seed(100 + rank)
+    n_batches = 8
+    host_tokens = [torch.randint(0, VOCAB, (B, SEQ + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev_tokens = [t.to(dev) for t in host_tokens]
+
+    def train_step(tokens: torch.Tensor) -> torch.Tensor:
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = train_model(tokens[:, :-1], tokens[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (untimed); the first step performs the root-inverse refresh
+    refresh_ms = None
+    for i in range(max(args.warmup, 1)):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        train_step(dev_tokens[i % n_batches])
+        torch.cuda.synchronize()
+        if i == 0:
+            refresh_ms = (time.perf_counter() - t0) * 1e3
+
+    # ---- device-timed region: K steps, inputs resident on the device
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        train_step(dev_tokens[i % n_batches])
+    stop.record()
+    barrier()
+    dev_ms = start.elapsed_time(stop)
+
+    # ---- end-to-end region: pinned host tokens in, loss out, every step
+    barrier()
+    h2d = d2h = 0
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall = time.perf_counter()
+    e_start.record()
+    last = 0.0
+    for i in range(args.steps):
+        src = host_tokens[i % n_batches]
+        tokens = src.to(dev, non_blocking=True)
+        h2d += src.numel() * src.element_size()
+        loss = train_step(tokens)
+        last = loss.item()
+        d2h += loss.element_size()
+    e_stop.record()
+    barrier()
+    e2e_ms = max(e_start.elapsed_time(e_stop), (time.perf_counter() - t_wall) * 1e3 if world == 1 else 0.0)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    times = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = times.tolist()
+
+    tokens_per_step = B * SEQ * world
+    value = tokens_per_step * args.steps / (dev_ms / 1e3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    launches = count_native_launches(opt) * args.steps if args.impl == "ours" else 0
+    if rank == 0:
+        out = {
+            "metric": "train tokens/sec (GPT-2 124M, Distributed Shampoo)",
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic uniform token ids, random-init weights",
+            "impl": args.impl,
+            "config": {
+                "model": f"gpt2-124m ({args.layers} layers, d_model 768, 12 heads, mlp 3072, vocab 50257)",
+                "global_batch": B * world,
+                "seq_len": SEQ,
+                "parallelism": f"dp{world}" if world > 1 else "single",
+                "optimizer": "DistributedShampoo max_preconditioner_dim=2048 precondition_frequency=100 AdaGrad grafting, fp32 factors",
+                "gemm_mode": args.gemm_mode if args.impl == "ours" else "fp32 (cuBLAS)",
+                "l2_policy": "working set (params, grads, optimizer state, activations: several GB) exceeds the 126 MB L2",
+                "step_counter_preset": PRECOND_FREQ - 1,
+            },
+            "refresh_step_ms": refresh_ms,
+            "final_loss": last,
+            "clocks": clocks,
+            "e2e": {
+                "value": e2e_value,
+                "unit": "tokens/s",
+                "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": h2d // max(args.steps, 1),
+                "d2h_bytes_per_step": d2h // max(args.steps, 1),
+            },
+            "gpu_launches": launches,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

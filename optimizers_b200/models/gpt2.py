@@ -1,0 +1,75 @@
+"""GPT-2 style decoder (pre-LN, learned positions, tied input/output embedding) used by the
+examples and the throughput benchmark.  Defaults are the 124M configuration: 12 layers,
+d_model 768, 12 heads, MLP 3072, vocabulary 50257, context 1024."""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class GPT2Config:
+    vocab_size: int = 50257
+    n_ctx: int = 1024
+    n_layer: int = 12
+    n_head: int = 12
+    d_model: int = 768
+    d_mlp: int = 3072
+
+
+class _Block(nn.Module):
+    def __init__(self, cfg: GPT2Config) -> None:
+        super().__init__()
+        self.n_head = cfg.n_head
+        self.ln_1 = nn.LayerNorm(cfg.d_model)
+        self.attn_qkv = nn.Linear(cfg.d_model, 3 * cfg.d_model)
+        self.attn_proj = nn.Linear(cfg.d_model, cfg.d_model)
+        self.ln_2 = nn.LayerNorm(cfg.d_model)
+        self.mlp_fc = nn.Linear(cfg.d_model, cfg.d_mlp)
+        self.mlp_proj = nn.Linear(cfg.d_mlp, cfg.d_model)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        B, T, C = x.shape
+        q, k, v = self.attn_qkv(self.ln_1(x)).split(C, dim=2)
+        shape = (B, T, self.n_head, C // self.n_head)
+        q, k, v = (t.view(shape).transpose(1, 2) for t in (q, k, v))
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.attn_proj(a.transpose(1, 2).reshape(B, T, C))
+        return x + self.mlp_proj(F.gelu(self.mlp_fc(self.ln_2(x)), approximate="tanh"))
+
+
+class GPT2(nn.Module):
+    def __init__(self, cfg: GPT2Config | None = None) -> None:
+        super().__init__()
+        self.cfg = cfg = cfg or GPT2Config()
+        self.wte = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        self.wpe = nn.Embedding(cfg.n_ctx, cfg.d_model)
+        self.blocks = nn.ModuleList(_Block(cfg) for _ in range(cfg.n_layer))
+        self.ln_f = nn.LayerNorm(cfg.d_model)
+        self.apply(self._init)
+        for name, p in self.named_parameters():
+            if name.endswith("proj.weight"):
+                nn.init.normal_(p, mean=0.0, std=0.02 / math.sqrt(2 * cfg.n_layer))
+
+    @staticmethod
+    def _init(m: nn.Module) -> None:
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, mean=0.0, std=0.02)
+        if isinstance(m, nn.Linear) and m.bias is not None:
+            nn.init.zeros_(m.bias)
+
+    def forward(self, idx: torch.Tensor, targets: torch.Tensor | None = None):
+        B, T = idx.shape
+        pos = torch.arange(T, device=idx.device)
+        x = self.wte(idx) + self.wpe(pos)
+        for blk in self.blocks:
+            x = blk(x)
+        logits = F.linear(self.ln_f(x), self.wte.weight)
+        if targets is None:
+            return logits
+        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.view(-1))

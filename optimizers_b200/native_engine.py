@@ -1,0 +1,408 @@
+"""Native sm_100a execution of one parameter group's optimizer step.
+
+The torch step walks Python lists of per-block tensors and launches several kernels per block.
+The native engine instead keeps a *device block table* for the group and runs the whole step as
+a fixed, short sequence of grouped launches:
+
+    grad_prologue        one pass over the gradients (L2, tf32 operand splits in both
+                         orientations, filtered-gradient EMA, grafting second moment and norm)
+    grouped SYRK         every factor of every block:  F <- beta2 F + w X X^T, written straight
+                         into the (packed) factor state by the tensor-core kernel's epilogue
+    [refresh]            at amortised steps: inverse roots, then their operand mirrors
+    grouped GEMM x2      T^T = R^(-1/p) G^T and P = L^(-1/p) T with the Frobenius norm of P
+                         accumulated in the epilogue
+    direction_epilogue   grafting rescale, weight decay, momentum, -lr, primal averaging, update
+
+The checkpointed state tensors are exactly those the preconditioner lists allocated; the engine
+adds scratch operands and full (unpacked, split) mirrors of the inverse roots, which are rebuilt
+from the state after every refresh and after ``load_state_dict``.
+
+Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 with every dim preconditioned,
+root-inverse Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting, any weight decay type,
+classic momentum, GPA / Schedule-Free, single-device and DDP distributors.  Anything else makes
+``build_native_engine`` return ``None`` (torch step) or raise with ``backend="native"``.
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Any
+
+import torch
+from torch import Tensor
+
+from optimizers_b200.config import (
+    AdaGradPreconditionerConfig,
+    BETA3,
+    BETAS,
+    ClassicMomentumConfig,
+    DDPDistributedConfig,
+    DISTRIBUTED_CONFIG,
+    DISTRIBUTOR,
+    FILTERED_GRAD_LIST,
+    GRAFTING_CONFIG,
+    GRAFTING_PRECONDITIONER_LIST,
+    ITERATE_AVERAGING_CONFIG,
+    LR_CPU_PINNED,
+    MASKED_BLOCKED_GRADS,
+    MOMENTUM_BUFFER_LIST,
+    NativeRuntimeConfig,
+    PARAMS,
+    PRECONDITIONER_CONFIG,
+    PreconditionerValueError,
+    RootInvShampooPreconditionerConfig,
+    SGDPreconditionerConfig,
+    SHAMPOO_PRECONDITIONER_LIST,
+    SingleDeviceDistributedConfig,
+    TRAIN_MODE,
+    WEIGHT_BUFFER_LIST,
+    WeightDecayType,
+)
+from optimizers_b200.utils.blocking import compress_list, generate_pairwise_indices
+
+logger: logging.Logger = logging.getLogger(__name__)
+
+_GRAFT_NONE, _GRAFT_SGD, _GRAFT_ADAGRAD = 0, 1, 2
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
+    pc = group[PRECONDITIONER_CONFIG]
+    if type(pc) is not RootInvShampooPreconditionerConfig:
+        return f"preconditioner config {type(pc).__name__} has no native step yet"
+    if pc.factor_matrix_dtype != torch.float32 or pc.inv_factor_matrix_dtype != torch.float32:
+        return "factor matrices must be fp32"
+    gc = group[GRAFTING_CONFIG]
+    if gc is not None and not isinstance(gc, (SGDPreconditionerConfig, AdaGradPreconditionerConfig)):
+        return f"grafting config {type(gc).__name__} has no native step"
+    dc = group[DISTRIBUTED_CONFIG]
+    if type(dc) is not SingleDeviceDistributedConfig:
+        return f"distributed config {type(dc).__name__} has no native step yet"
+    for p in group[PARAMS]:
+        if p.dtype != torch.float32 or not p.is_contiguous() or type(p.data) is not Tensor:
+            return "parameters must be plain contiguous fp32 tensors"
+    plist = rec[SHAMPOO_PRECONDITIONER_LIST]
+    for block, sel in zip(
+        rec[DISTRIBUTOR].local_blocked_params, plist._local_preconditioned_dims_selector_list, strict=True
+    ):
+        if block.dim() > 2:
+            return f"block of order {block.dim()} has no native step yet"
+        if not all(sel):
+            return "blocks with unpreconditioned dims have no native step yet"
+        if block.numel() == 0:
+            return "empty blocks"
+    return None
+
+
+def build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig):
+    reason = _why_not_covered(rec, group)
+    if reason is None and torch.cuda.get_device_capability(group[PARAMS][0].device)[0] != 10:
+        reason = "device is not sm_100"
+    if reason is not None:
+        if cfg.backend == "native":
+            raise RuntimeError(f"native backend requested but {reason}")
+        logger.info("Parameter group uses the torch step: %s.", reason)
+        return None
+    return NativeGroupEngine(optimizer, rec, group, cfg)
+
+
+class _Block:
+    """Host-side record of one local block: views, state, scratch operands."""
+
+    __slots__ = (
+        "index", "param_view", "grad_slot", "grad_offset", "m", "n", "n_pad", "m_pad", "order", "factors",
+        "m1", "v", "mom", "z", "g_hi", "g_lo", "gt_hi", "gt_lo", "f_hi", "f_lo", "tt_hi", "tt_lo", "p",
+        "inv_hi", "inv_lo",
+    )
+
+
+class NativeGroupEngine:
+    def __init__(self, optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig) -> None:
+        from optimizers_b200.ops import build
+
+        self._ext = build.load()
+        self._optimizer = optimizer
+        self._rec = rec
+        self._group = group
+        self._cfg = cfg
+        self._split = cfg.gemm_mode == "tf32x3"
+        self._dist = rec[DISTRIBUTOR]
+        self._device = group[PARAMS][0].device
+        self._plist = rec[SHAMPOO_PRECONDITIONER_LIST]
+        self._glist = rec[GRAFTING_PRECONDITIONER_LIST]
+        self._packing = group[PRECONDITIONER_CONFIG].use_symmetric_packing
+        self.launches_per_step = 0
+
+        gc = group[GRAFTING_CONFIG]
+        if gc is None:
+            self._graft_kind = _GRAFT_NONE
+        elif isinstance(gc, SGDPreconditionerConfig):
+            self._graft_kind = _GRAFT_SGD
+        else:
+            self._graft_kind = _GRAFT_ADAGRAD
+
+        self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
+        self._build_blocks()
+        n_ptrs = max(len(group[PARAMS]), 1)
+        # Two pinned staging buffers, used alternately, so that a pointer table still being
+        # copied by the device is never overwritten by the host.
+        self._grad_ptrs_host = [torch.zeros(n_ptrs, dtype=torch.int64).pin_memory() for _ in range(2)]
+        self._grad_ptrs_flip = 0
+        self._grad_ptrs_dev = torch.zeros(n_ptrs, dtype=torch.int64, device=self._device)
+        self._last_ptrs: list[int] | None = None
+        self._active: tuple[bool, ...] | None = None
+        self._plans_for: tuple[bool, ...] | None = None
+        self.refresh_inverse_mirrors()
+
+    # ------------------------------------------------------------------------------------------
+    # Set-up
+    # ------------------------------------------------------------------------------------------
+    def _build_blocks(self) -> None:
+        rec, dist = self._rec, self._dist
+        dev = self._device
+        params = self._group[PARAMS]
+        param_pos = {id(p): i for i, p in enumerate(params)}
+        blocks: list[_Block] = []
+        factors_list = self._plist._local_kronecker_factors_unwrapped
+        m1s = rec.get(FILTERED_GRAD_LIST)
+        moms = rec.get(MOMENTUM_BUFFER_LIST)
+        zs = rec.get(WEIGHT_BUFFER_LIST)
+        vs = self._glist._local_preconditioner_list if self._graft_kind == _GRAFT_ADAGRAD else None
+        self._norms = torch.zeros(max(len(dist.local_blocked_params), 1), 2, dtype=torch.float32, device=dev)
+
+        def zeros(*shape: int) -> Tensor:
+            return torch.zeros(*shape, dtype=torch.float32, device=dev)
+
+        for i, (view, info) in enumerate(zip(dist.local_blocked_params, dist.local_block_info_list, strict=True)):
+            b = _Block()
+            b.index = i
+            b.param_view = view
+            p = info.param
+            b.grad_slot = param_pos[id(p)]
+            b.grad_offset = (view.data_ptr() - p.data_ptr()) // 4
+            b.order = view.dim()
+            if view.dim() == 1:
+                b.m, b.n = 1, view.shape[0]
+            else:
+                b.m, b.n = view.shape
+            b.n_pad, b.m_pad = _pad4(b.n), _pad4(b.m)
+            b.factors = factors_list[i]
+            b.m1 = m1s[i] if m1s is not None else None
+            b.v = vs[i] if vs is not None else None
+            b.mom = moms[i] if moms is not None else None
+            b.z = zs[i] if zs is not None else None
+            two_d = b.order == 2
+            b.g_hi = zeros(b.m, b.n_pad) if two_d else None
+            b.g_lo = zeros(b.m, b.n_pad) if two_d and self._split else None
+            b.gt_hi = zeros(b.n, b.m_pad)
+            b.gt_lo = zeros(b.n, b.m_pad) if self._split else None
+            b.f_hi = zeros(b.m, b.n_pad)
+            b.f_lo = zeros(b.m, b.n_pad) if self._split else None
+            b.tt_hi = zeros(b.n, b.m_pad) if two_d else None
+            b.tt_lo = zeros(b.n, b.m_pad) if two_d and self._split else None
+            b.p = zeros(b.m, b.n)
+            dims = (b.m, b.n) if two_d else (b.n,)
+            b.inv_hi = [zeros(d, _pad4(d)) for d in dims]
+            b.inv_lo = [zeros(d, _pad4(d)) if self._split else None for d in dims]
+            blocks.append(b)
+        self._blocks = blocks
+
+    def _send_ptr(self, b: _Block) -> int:
+        return 0
+
+    def _build_plans(self, active: tuple[bool, ...]) -> None:
+        """(Re)build the block table and the three GEMM plans for the active blocks."""
+        ext = self._ext
+        blocks = [b for b, on in zip(self._blocks, active, strict=True) if on]
+        self._active_blocks = blocks
+        if not blocks:
+            self._table = None
+            return
+        F = ext
+        specs = []
+        for b in blocks:
+            specs.append(
+                (
+                    b.param_view, b.grad_offset, b.grad_slot, b.m, b.n, b.n_pad, b.m_pad, b.m1, b.v, b.mom, b.z,
+                    b.g_hi, b.g_lo, b.gt_hi, b.gt_lo, b.f_hi, b.f_lo, b.p, self._norms[b.index], self._send_ptr(b),
+                )
+            )
+        self._table = ext.build_block_table(specs)
+
+        def op(t: Tensor, rows: int, k: int) -> Tensor:
+            return t[:, :k] if t.shape[1] != k else t
+
+        syrk, gemm1, gemm2 = [], [], []
+        pack_flag = F.FLAG_PACKED_C if self._packing else 0
+        for b in blocks:
+            fm = b.factors.factor_matrices
+            two_d = b.order == 2
+            if two_d:
+                a_hi, a_lo = op(b.g_hi, b.m, b.n), (op(b.g_lo, b.m, b.n) if self._split else None)
+                syrk.append((a_hi, a_lo, a_hi, a_lo, fm[0], None, None, None, b.m, 0, pack_flag, self._packing))
+            t_hi, t_lo = op(b.gt_hi, b.n, b.m), (op(b.gt_lo, b.n, b.m) if self._split else None)
+            syrk.append((t_hi, t_lo, t_hi, t_lo, fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
+
+            f_hi, f_lo = op(b.f_hi, b.m, b.n), (op(b.f_lo, b.m, b.n) if self._split else None)
+            sumsq = self._norms[b.index, 1:2]
+            if two_d:
+                r_hi, r_lo = op(b.inv_hi[1], b.n, b.n), (op(b.inv_lo[1], b.n, b.n) if self._split else None)
+                l_hi, l_lo = op(b.inv_hi[0], b.m, b.m), (op(b.inv_lo[0], b.m, b.m) if self._split else None)
+                if self._split:
+                    gemm1.append(
+                        (r_hi, r_lo, f_hi, f_lo, None, b.tt_hi, b.tt_lo, None, 0, b.m_pad, F.FLAG_NO_C | F.FLAG_SPLIT_OUT, False)
+                    )
+                else:
+                    gemm1.append((r_hi, None, f_hi, None, b.tt_hi, None, None, None, b.m_pad, 0, 0, False))
+                tt_hi, tt_lo = op(b.tt_hi, b.n, b.m), (op(b.tt_lo, b.n, b.m) if self._split else None)
+                gemm2.append((l_hi, l_lo, tt_hi, tt_lo, b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
+            else:
+                r_hi, r_lo = op(b.inv_hi[0], b.n, b.n), (op(b.inv_lo[0], b.n, b.n) if self._split else None)
+                gemm2.append((f_hi, f_lo, r_hi, r_lo, b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
+        self._syrk_plan = ext.build_gemm_plan(syrk)
+        self._gemm1_plan = ext.build_gemm_plan(gemm1) if gemm1 else None
+        self._gemm2_plan = ext.build_gemm_plan(gemm2)
+
+    def refresh_inverse_mirrors(self, blocks: list[_Block] | None = None) -> None:
+        """Rebuild the full (hi, lo) operand copies of the inverse roots from the state tensors."""
+        for b in self._blocks if blocks is None else blocks:
+            for k, inv in enumerate(b.factors.get_unpacked_inv_factor_matrices()):
+                d = inv.shape[0]
+                if self._split:
+                    self._ext.tf32_split(inv, b.inv_hi[k][:, :d], b.inv_lo[k][:, :d])
+                else:
+                    b.inv_hi[k][:, :d].copy_(inv)
+
+    # ------------------------------------------------------------------------------------------
+    # Hooks called by the optimizer
+    # ------------------------------------------------------------------------------------------
+    def on_selector_change(self, selector: tuple[bool, ...]) -> None:
+        self._active = tuple(selector)
+
+    def on_state_loaded(self) -> None:
+        self.refresh_inverse_mirrors()
+
+    def collect_gradients(self) -> tuple[int, ...]:
+        """Native twin of ``merge_and_block_gradients``: records which parameters have a usable
+        gradient, refreshes the distributor's selectors, and stages the gradient base pointers.
+        No per-block views are created.  Returns the pointers (empty when nothing has a gradient)."""
+        dist = self._dist
+        ptrs: list[int] = []
+        selector: list[bool] = []
+        any_grad = False
+        for p, count in zip(self._group[PARAMS], dist._global_num_blocks_per_param, strict=True):
+            g = p.grad
+            usable = g is not None and g.numel() > 0
+            if usable:
+                if g.dtype != torch.float32 or not g.is_contiguous():
+                    raise RuntimeError("the native step needs contiguous fp32 gradients")
+                if self._optimizer._runtime_config.eager_nan_check:
+                    assert torch.isfinite(g).all(), (
+                        f"Encountered gradient containing NaN/Inf in parameter with shape {g.shape}. Check your model for numerical instability or consider gradient clipping."
+                    )
+                ptrs.append(g.data_ptr())
+                any_grad = True
+            else:
+                ptrs.append(0)
+            selector.extend([usable] * count)
+        dist._global_grad_selector = tuple(selector)
+        dist._refresh_local_selection()
+        if ptrs != self._last_ptrs:
+            self._grad_ptrs_flip ^= 1
+            staging = self._grad_ptrs_host[self._grad_ptrs_flip]
+            staging[: len(ptrs)] = torch.tensor(ptrs, dtype=torch.int64)
+            self._grad_ptrs_dev.copy_(staging, non_blocking=True)
+            self._last_ptrs = ptrs
+        local_any = any_grad and any(dist.local_grad_selector)
+        return tuple(ptrs) if local_any else ()
+
+    # ------------------------------------------------------------------------------------------
+    # The step
+    # ------------------------------------------------------------------------------------------
+    def check_status(self) -> None:
+        """Read the device status word (one synchronisation) and raise on kernel-reported errors."""
+        code = int(self._status.item())
+        if code & 1:
+            raise RuntimeError("grouped GEMM pipeline wait timed out (device-side bounded wait expired)")
+        if code & 2:
+            self._status.zero_()
+            raise PreconditionerValueError("Encountered NaN/Inf in a gradient passed to the optimizer.")
+
+    def step(
+        self, group, step, lr, beta1, beta3, weight_decay, peak_lr, weight_decay_type, has_grafting, refresh,
+        use_bias_correction, graft_only, primal, classic, mu_y, mu_x, momentum, dampening, nesterov,
+    ) -> None:
+        rec, ext = self._rec, self._ext
+        if not rec[MASKED_BLOCKED_GRADS]:
+            self._dist.update_params(blocked_search_directions=())
+            return
+        active = self._active if self._active is not None else (True,) * len(self._blocks)
+        if self._plans_for != active:
+            self._build_plans(active)
+            self._plans_for = active
+        t = int(step.item())
+        launches = 0
+
+        plist, glist = self._plist, self._glist
+        plist._refresh_bias_correction(step)
+        bc1 = 1.0 - beta3 * beta1 ** (t - 1) if (beta1 != 0.0 and use_bias_correction) else 1.0
+        g_beta2 = g_weight = 1.0
+        g_bc2, g_eps = 1.0, 0.0
+        if self._graft_kind == _GRAFT_ADAGRAD:
+            g_beta2, g_weight, g_eps = glist._beta2, glist._weighting_factor, glist._epsilon
+            if glist._use_bias_correction and g_beta2 < 1.0:
+                glist._bias_correction2 = torch.tensor(1.0) - g_beta2**step
+            g_bc2 = float(glist._bias_correction2)
+        l2 = weight_decay if (weight_decay_type == WeightDecayType.L2) else 0.0
+
+        self._norms.zero_()
+        blocks_t, tiles_t, n_tiles = self._table
+        ext.grad_prologue(
+            blocks_t, tiles_t, n_tiles, self._grad_ptrs_dev, l2, beta1, beta3, bc1, self._graft_kind,
+            g_beta2, g_weight, g_bc2, g_eps, self._split, self._status,
+        )
+        launches += 2
+        ext.run_gemm_plan(*self._syrk_plan, plist._weighting_factor, plist._beta2, self._split, self._status)
+        launches += 1
+
+        if refresh:
+            for b in self._active_blocks:
+                b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
+            self.refresh_inverse_mirrors(self._active_blocks)
+            self.check_status()
+
+        if not graft_only:
+            if self._gemm1_plan is not None:
+                ext.run_gemm_plan(*self._gemm1_plan, 1.0, 0.0, self._split, self._status)
+                launches += 1
+            ext.run_gemm_plan(*self._gemm2_plan, 1.0, 0.0, self._split, self._status)
+            launches += 1
+
+        alpha = 0.0
+        if weight_decay != 0.0 and weight_decay_type != WeightDecayType.L2:
+            if weight_decay_type == WeightDecayType.DECOUPLED:
+                alpha = weight_decay
+            elif weight_decay_type == WeightDecayType.CORRECTED:
+                alpha = weight_decay * rec[LR_CPU_PINNED].item() / peak_lr
+            else:
+                alpha = weight_decay / peak_lr
+        if primal and not rec[TRAIN_MODE]:
+            raise RuntimeError(
+                "Called _apply_in_place_primal_averaging when not in train mode. Call optimizer.train() before calling optimizer.step()!"
+            )
+        ext.direction_epilogue(
+            blocks_t, tiles_t, n_tiles, lr, graft_only, self._graft_kind if has_grafting else _GRAFT_NONE, g_bc2,
+            g_eps, alpha, primal, mu_y, mu_x, classic, momentum, dampening, nesterov, self._send_dtype(), self._split,
+        )
+        launches += 1
+        self.launches_per_step = launches
+        self._after_epilogue()
+
+    def _send_dtype(self) -> int:
+        return 0
+
+    def _after_epilogue(self) -> None:
+        """Single device: the epilogue already updated the parameters."""

@@ -1,0 +1,342 @@
+// Python bindings of the sm_100a kernels.  Host-side work here is plan construction: TMA tensor
+// maps, problem tables and tile lists are encoded once (when a parameter group is set up or its
+// gradient selector changes) and uploaded; each step then only launches kernels.
+#include <torch/extension.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <optional>
+#include <vector>
+
+#include "block_kernels.cuh"
+#include "flat_kernels.cuh"
+#include "grouped_gemm.cuh"
+
+namespace py = pybind11;
+using namespace ob200;
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    TORCH_CHECK(err == cudaSuccess && sym != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
+    fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+// Tensor map of a K-major fp32 operand: `t` is a 2-D view [rows, K] whose last stride is 1.
+CUtensorMap encode_operand(const torch::Tensor& t, int box_rows) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.dim() == 2, "operand must be a 2-D fp32 CUDA tensor");
+  TORCH_CHECK(t.stride(1) == 1, "operand must be contiguous along K");
+  TORCH_CHECK((t.stride(0) * 4) % 16 == 0, "operand row pitch must be a multiple of 16 bytes, got ", t.stride(0), " elements");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, "operand base must be 16-byte aligned");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(t.size(1)), static_cast<cuuint64_t>(t.size(0))};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(t.stride(0)) * 4};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUresult res = get_encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, t.data_ptr(), dims, strides, box,
+                                 elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(res == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", static_cast<int>(res));
+  return map;
+}
+
+float* fptr(const std::optional<torch::Tensor>& t) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32, "expected an fp32 CUDA tensor");
+  return t->data_ptr<float>();
+}
+
+torch::Tensor upload_bytes(const void* src, size_t bytes, const torch::Device& device) {
+  auto host = torch::empty({static_cast<int64_t>(std::max<size_t>(bytes, 1))}, torch::dtype(torch::kUInt8));
+  std::memcpy(host.data_ptr(), src, bytes);
+  return host.to(device);
+}
+
+// One GEMM problem as given from Python.
+struct GemmSpec {
+  torch::Tensor a_hi, b_hi;
+  std::optional<torch::Tensor> a_lo, b_lo, c, d_hi, d_lo, sumsq;
+  int64_t ldc = 0, ldd = 0, flags = 0;
+  bool upper_tiles_only = false;  // symmetric result: schedule only tiles on or above the diagonal
+};
+
+// Returns (problem table bytes, tile list bytes, number of tiles), the first two on the device.
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vector<py::tuple>& specs) {
+  TORCH_CHECK(!specs.empty(), "empty GEMM plan");
+  std::vector<GemmProblem> problems(specs.size());
+  std::vector<GemmTile> tiles;
+  struct Order {
+    int problem;
+    int K;
+  };
+  std::vector<Order> order;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 12, "GEMM spec must have 12 fields");
+    GemmSpec g;
+    g.a_hi = s[0].cast<torch::Tensor>();
+    g.a_lo = s[1].cast<std::optional<torch::Tensor>>();
+    g.b_hi = s[2].cast<torch::Tensor>();
+    g.b_lo = s[3].cast<std::optional<torch::Tensor>>();
+    g.c = s[4].cast<std::optional<torch::Tensor>>();
+    g.d_hi = s[5].cast<std::optional<torch::Tensor>>();
+    g.d_lo = s[6].cast<std::optional<torch::Tensor>>();
+    g.sumsq = s[7].cast<std::optional<torch::Tensor>>();
+    g.ldc = s[8].cast<int64_t>();
+    g.ldd = s[9].cast<int64_t>();
+    g.flags = s[10].cast<int64_t>();
+    g.upper_tiles_only = s[11].cast<bool>();
+    device = g.a_hi.device();
+
+    GemmProblem& p = problems[i];
+    std::memset(&p, 0, sizeof(p));
+    p.M = static_cast<int>(g.a_hi.size(0));
+    p.N = static_cast<int>(g.b_hi.size(0));
+    p.K = static_cast<int>(g.a_hi.size(1));
+    TORCH_CHECK(g.b_hi.size(1) == p.K, "A and B must agree on K");
+    p.a_hi = encode_operand(g.a_hi, kBM);
+    p.b_hi = encode_operand(g.b_hi, kBN);
+    p.a_lo = g.a_lo.has_value() ? encode_operand(*g.a_lo, kBM) : p.a_hi;
+    p.b_lo = g.b_lo.has_value() ? encode_operand(*g.b_lo, kBN) : p.b_hi;
+    p.c = fptr(g.c);
+    p.d_hi = fptr(g.d_hi);
+    p.d_lo = fptr(g.d_lo);
+    p.sumsq = fptr(g.sumsq);
+    p.ldc = static_cast<int>(g.ldc);
+    p.ldd = static_cast<int>(g.ldd);
+    p.flags = static_cast<int>(g.flags);
+    if (p.flags & kFlagPackedC) TORCH_CHECK(p.M == p.N && g.upper_tiles_only, "packed output needs a square upper-tile problem");
+    if (!(p.flags & kFlagNoC)) TORCH_CHECK(p.c != nullptr, "C is required unless kFlagNoC is set");
+    if (p.flags & kFlagSplitOut) TORCH_CHECK(p.d_hi != nullptr && p.d_lo != nullptr, "split output needs d_hi and d_lo");
+    if (p.flags & kFlagSumSq) TORCH_CHECK(p.sumsq != nullptr, "sumsq output missing");
+    order.push_back({static_cast<int>(i), p.K});
+  }
+  // Longest K loops first so the persistent CTAs finish together.
+  std::stable_sort(order.begin(), order.end(), [](const Order& x, const Order& y) { return x.K > y.K; });
+  for (const Order& o : order) {
+    const GemmProblem& p = problems[o.problem];
+    const bool upper = specs[o.problem][11].cast<bool>();
+    for (int m0 = 0; m0 < p.M; m0 += kBM) {
+      for (int n0 = upper ? m0 : 0; n0 < p.N; n0 += kBN) {
+        tiles.push_back({o.problem, m0, n0, 0});
+      }
+    }
+  }
+  auto d_problems = upload_bytes(problems.data(), problems.size() * sizeof(GemmProblem), device);
+  auto d_tiles = upload_bytes(tiles.data(), tiles.size() * sizeof(GemmTile), device);
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(d_problems.data_ptr()) % 128 == 0, "problem table must be 128-byte aligned");
+  return {d_problems, d_tiles, static_cast<int64_t>(tiles.size())};
+}
+
+void run_gemm_plan(const torch::Tensor& problems, const torch::Tensor& tiles, int64_t num_tiles, double alpha,
+                   double beta, bool split, torch::Tensor status) {
+  c10::cuda::CUDAGuard guard(problems.device());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  launch_grouped_gemm(reinterpret_cast<const GemmProblem*>(problems.data_ptr()),
+                      reinterpret_cast<const GemmTile*>(tiles.data_ptr()), static_cast<int>(num_tiles),
+                      static_cast<float>(alpha), static_cast<float>(beta), split, status.data_ptr<int>(), sms,
+                      at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// Block table.  Each spec: (param_view, grad_offset, grad_slot, m, n, n_pad, m_pad, m1, v, mom, z,
+//                           g_hi, g_lo, gt_hi, gt_lo, f_hi, f_lo, p, norms, send_ptr)
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::vector<py::tuple>& specs) {
+  std::vector<BlockDesc> blocks(specs.size());
+  std::vector<TileRef> tiles;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 20, "block spec must have 20 fields");
+    BlockDesc& b = blocks[i];
+    std::memset(&b, 0, sizeof(b));
+    auto param = s[0].cast<torch::Tensor>();
+    TORCH_CHECK(param.is_cuda() && param.scalar_type() == torch::kFloat32, "parameter blocks must be fp32 CUDA tensors");
+    device = param.device();
+    b.param = param.data_ptr<float>();
+    b.grad_offset = s[1].cast<int64_t>();
+    b.grad_slot = s[2].cast<int>();
+    b.m = s[3].cast<int>();
+    b.n = s[4].cast<int>();
+    b.n_pad = s[5].cast<int>();
+    b.m_pad = s[6].cast<int>();
+    if (param.dim() == 2) {
+      TORCH_CHECK(param.stride(1) == 1, "parameter block must be contiguous along its last dim");
+      b.param_pitch = param.stride(0);
+    } else {
+      TORCH_CHECK(param.dim() == 1 && param.stride(0) == 1 && b.m == 1, "1-D blocks are presented as 1 x n");
+      b.param_pitch = b.n;
+    }
+    auto opt = [&](int k) { return fptr(s[k].cast<std::optional<torch::Tensor>>()); };
+    b.m1 = opt(7);
+    b.v = opt(8);
+    b.mom = opt(9);
+    b.z = opt(10);
+    b.g_hi = opt(11);
+    b.g_lo = opt(12);
+    b.gt_hi = opt(13);
+    b.gt_lo = opt(14);
+    b.f_hi = opt(15);
+    b.f_lo = opt(16);
+    b.p = opt(17);
+    b.norms = opt(18);
+    b.send = reinterpret_cast<void*>(s[19].cast<int64_t>());
+    const int tm = (b.m + 31) / 32, tn = (b.n + 31) / 32;
+    for (int ti = 0; ti < tm; ++ti)
+      for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});
+  }
+  auto d_blocks = upload_bytes(blocks.data(), blocks.size() * sizeof(BlockDesc), device);
+  auto d_tiles = upload_bytes(tiles.data(), tiles.size() * sizeof(TileRef), device);
+  return {d_blocks, d_tiles, static_cast<int64_t>(tiles.size())};
+}
+
+void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles,
+                   const torch::Tensor& grad_ptrs, double l2_weight_decay, double beta1, double beta3,
+                   double bias_correction1, int64_t graft_kind, double graft_beta2, double graft_weight,
+                   double graft_bc2, double graft_eps, bool write_split, torch::Tensor status) {
+  c10::cuda::CUDAGuard guard(blocks.device());
+  PrologueArgs a;
+  a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
+  a.tiles = reinterpret_cast<const TileRef*>(tiles.data_ptr());
+  a.num_tiles = static_cast<int>(num_tiles);
+  a.grad_ptrs = reinterpret_cast<const float* const*>(grad_ptrs.data_ptr<int64_t>());
+  a.l2_weight_decay = static_cast<float>(l2_weight_decay);
+  a.beta1 = static_cast<float>(beta1);
+  a.beta3 = static_cast<float>(beta3);
+  a.bias_correction1 = static_cast<float>(bias_correction1);
+  a.graft_kind = static_cast<int>(graft_kind);
+  a.graft_beta2 = static_cast<float>(graft_beta2);
+  a.graft_weight = static_cast<float>(graft_weight);
+  a.graft_bias_correction2 = static_cast<float>(graft_bc2);
+  a.graft_epsilon = static_cast<float>(graft_eps);
+  a.write_split = write_split ? 1 : 0;
+  a.status = status.data_ptr<int>();
+  launch_grad_prologue(a, at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles,
+                        const torch::Tensor& lr, bool graft_only, int64_t graft_kind, double graft_bc2,
+                        double graft_eps, double wd_alpha, bool primal_averaging, const torch::Tensor& mu_y,
+                        const torch::Tensor& mu_x, bool classic_momentum, double momentum, double dampening,
+                        bool nesterov, int64_t send_dtype, bool split_input) {
+  c10::cuda::CUDAGuard guard(blocks.device());
+  EpilogueArgs a;
+  a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
+  a.tiles = reinterpret_cast<const TileRef*>(tiles.data_ptr());
+  a.num_tiles = static_cast<int>(num_tiles);
+  a.lr = lr.data_ptr<float>();
+  a.graft_only = graft_only ? 1 : 0;
+  a.graft_kind = static_cast<int>(graft_kind);
+  a.graft_bias_correction2 = static_cast<float>(graft_bc2);
+  a.graft_epsilon = static_cast<float>(graft_eps);
+  a.wd_alpha = static_cast<float>(wd_alpha);
+  a.primal_averaging = primal_averaging ? 1 : 0;
+  a.mu_y = mu_y.data_ptr<float>();
+  a.mu_x = mu_x.data_ptr<float>();
+  a.classic_momentum = classic_momentum ? 1 : 0;
+  a.momentum = static_cast<float>(momentum);
+  a.dampening = static_cast<float>(dampening);
+  a.nesterov = nesterov ? 1 : 0;
+  a.send_dtype = static_cast<int>(send_dtype);
+  a.split_input = split_input ? 1 : 0;
+  launch_direction_epilogue(a, at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void tf32_split(const torch::Tensor& src, torch::Tensor hi, torch::Tensor lo) {
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1);
+  TORCH_CHECK(hi.dim() == 2 && lo.dim() == 2 && hi.stride(1) == 1 && lo.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(src.device());
+  launch_tf32_split(src.data_ptr<float>(), src.stride(0), hi.data_ptr<float>(), lo.data_ptr<float>(), hi.stride(0),
+                    static_cast<int>(src.size(0)), static_cast<int>(src.size(1)), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void gpa_adamw_step(const torch::Tensor& table, int64_t total_chunks, const torch::Tensor& chunk_map, double lr,
+                    double beta1, double beta2, double eps, double bias_correction1, double bias_correction2,
+                    double weight_decay, bool wd_on_y, double avg_coeff, double train_interp_coeff) {
+  c10::cuda::CUDAGuard guard(table.device());
+  launch_gpa_adamw(reinterpret_cast<const GpaTensorDesc*>(table.data_ptr()),
+                   reinterpret_cast<const int2*>(chunk_map.data_ptr()), static_cast<int>(total_chunks),
+                   static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2), static_cast<float>(eps),
+                   static_cast<float>(bias_correction1), static_cast<float>(bias_correction2),
+                   static_cast<float>(weight_decay), wd_on_y, static_cast<float>(avg_coeff),
+                   static_cast<float>(train_interp_coeff), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void gpa_lerp(const torch::Tensor& table, int64_t total_chunks, const torch::Tensor& chunk_map, double weight) {
+  c10::cuda::CUDAGuard guard(table.device());
+  launch_gpa_lerp(reinterpret_cast<const GpaTensorDesc*>(table.data_ptr()), reinterpret_cast<const int2*>(chunk_map.data_ptr()),
+                  static_cast<int>(total_chunks), static_cast<float>(weight), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// Table for the GPA-AdamW kernels.  Each spec: (param, grad, z, exp_avg, exp_avg_sq); params may be
+// fp32, bf16 or fp16 (grad of the same dtype); state is fp32.
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gpa_table(const std::vector<py::tuple>& specs) {
+  std::vector<GpaTensorDesc> descs(specs.size());
+  std::vector<int2> chunks;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    auto p = s[0].cast<torch::Tensor>();
+    auto g = s[1].cast<std::optional<torch::Tensor>>();
+    auto z = s[2].cast<torch::Tensor>();
+    auto m = s[3].cast<torch::Tensor>();
+    auto v = s[4].cast<torch::Tensor>();
+    TORCH_CHECK(p.is_cuda() && p.is_contiguous() && z.is_contiguous() && m.is_contiguous() && v.is_contiguous());
+    device = p.device();
+    GpaTensorDesc& d = descs[i];
+    d.param = p.data_ptr();
+    d.grad = g.has_value() ? g->data_ptr() : nullptr;
+    if (g.has_value()) TORCH_CHECK(g->is_contiguous() && g->scalar_type() == p.scalar_type());
+    d.z = z.data_ptr<float>();
+    d.m = m.data_ptr<float>();
+    d.v = v.data_ptr<float>();
+    d.numel = p.numel();
+    d.dtype = p.scalar_type() == torch::kFloat32 ? 0 : (p.scalar_type() == torch::kBFloat16 ? 1 : 2);
+    TORCH_CHECK(p.scalar_type() == torch::kFloat32 || p.scalar_type() == torch::kBFloat16 || p.scalar_type() == torch::kFloat16);
+    const int64_t n_chunks = (d.numel + kGpaChunk - 1) / kGpaChunk;
+    for (int64_t c = 0; c < n_chunks; ++c) chunks.push_back(make_int2(static_cast<int>(i), static_cast<int>(c)));
+  }
+  auto d_descs = upload_bytes(descs.data(), descs.size() * sizeof(GpaTensorDesc), device);
+  auto d_chunks = upload_bytes(chunks.data(), chunks.size() * sizeof(int2), device);
+  return {d_descs, d_chunks, static_cast<int64_t>(chunks.size())};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.attr("FLAG_PACKED_C") = kFlagPackedC;
+  m.attr("FLAG_SPLIT_OUT") = kFlagSplitOut;
+  m.attr("FLAG_SUMSQ") = kFlagSumSq;
+  m.attr("FLAG_NO_C") = kFlagNoC;
+  m.def("build_gemm_plan", &build_gemm_plan);
+  m.def("run_gemm_plan", &run_gemm_plan);
+  m.def("build_block_table", &build_block_table);
+  m.def("grad_prologue", &grad_prologue);
+  m.def("direction_epilogue", &direction_epilogue);
+  m.def("tf32_split", &tf32_split);
+  m.def("build_gpa_table", &build_gpa_table);
+  m.def("gpa_adamw_step", &gpa_adamw_step);
+  m.def("gpa_lerp", &gpa_lerp);
+}

@@ -1,0 +1,93 @@
+// Grouped per-block kernels of the optimizer step: one launch covers every block of a
+// parameter group through a device block table.
+//
+//   grad_prologue       one read of the gradient produces everything the step needs from it:
+//                       L2-regularised gradient, its tf32 (hi, lo) split in both orientations
+//                       (the K-major operands of the factor Gram GEMMs), the filtered-gradient
+//                       EMA and its bias-corrected, split form (operand of the preconditioner
+//                       GEMMs), the diagonal second moment of the grafting method, the squared
+//                       norm of the grafting direction, and a non-finite status flag.
+//   direction_epilogue  grafting rescale, weight decay, classic momentum, multiplication by -lr,
+//                       primal averaging and the parameter update (or the cast into the
+//                       all-gather send buffer) in one pass.
+//
+// They replace the chains of torch._foreach_* launches of the reference
+// (distributed_shampoo/distributed_shampoo.py:1110-1139, :1170-1199, :1232-1293, :1358-1381,
+// :1484; preconditioner/adagrad_preconditioner_list.py:122-162;
+// distributor/shampoo_distributor.py:361-365).
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace ob200 {
+
+// One 2-D block (m x n).  1-D blocks are presented as 1 x n.
+struct BlockDesc {
+  float* param;        // view into the parameter; element (i, j) at param[i * param_pitch + j]
+  long long param_pitch;
+  long long grad_offset;  // element offset of the block inside its parameter's gradient
+  int grad_slot;          // index into the per-step gradient pointer array
+  int m, n;
+  int n_pad, m_pad;       // row pitches of the row-major / transposed split arrays
+  float* m1;              // filtered gradient EMA [m, n] (null if beta1 == 0)
+  float* v;               // diagonal second moment [m, n] (null unless AdaGrad-family grafting)
+  float* mom;             // classic momentum buffer [m, n] (null if unused)
+  float* z;               // primal-averaging weight buffer [m, n] (null if unused)
+  float* g_hi;            // [m, n_pad]  (null if dim 0 has no factor)
+  float* g_lo;
+  float* gt_hi;           // [n, m_pad]  (null if dim 1 has no factor)
+  float* gt_lo;
+  float* f_hi;            // filtered gradient, bias corrected, [m, n_pad]
+  float* f_lo;
+  float* p;               // search direction [m, n] (output of the preconditioner GEMMs)
+  float* norms;           // [2]: squared norm of the grafting direction, of the Shampoo direction
+  void* send;             // all-gather send slot in the communication dtype (null: update params)
+};
+
+struct TileRef {
+  int block;
+  int ti;  // 32-row tile index
+  int tj;  // 32-column tile index
+  int pad_;
+};
+
+enum GraftKind : int { kGraftNone = 0, kGraftSGD = 1, kGraftAdaGrad = 2 };
+
+struct PrologueArgs {
+  const BlockDesc* blocks;
+  const TileRef* tiles;
+  int num_tiles;
+  const float* const* grad_ptrs;  // per gradient slot: base pointer of the parameter's gradient
+  float l2_weight_decay;          // 0 unless WeightDecayType.L2
+  float beta1, beta3;
+  float bias_correction1;         // 1 - beta3 * beta1^(t-1), or 1
+  int graft_kind;
+  float graft_beta2, graft_weight, graft_bias_correction2, graft_epsilon;
+  int write_split;                // 0: store raw fp32 into the *_hi arrays and skip *_lo (tf32 mode)
+  int* status;                    // bit 1 set when a gradient holds NaN/Inf
+};
+
+struct EpilogueArgs {
+  const BlockDesc* blocks;
+  const TileRef* tiles;
+  int num_tiles;
+  const float* lr;                // device scalar
+  int graft_only;                 // direction = grafting direction (before start_preconditioning_step)
+  int graft_kind;
+  float graft_bias_correction2, graft_epsilon;
+  float wd_alpha;                 // decoupled-style weight decay coefficient (0: none)
+  int primal_averaging;
+  const float* mu_y;              // train interpolation coefficient (device scalar)
+  const float* mu_x;              // eval interpolation coefficient (device scalar)
+  int classic_momentum;
+  float momentum, dampening;
+  int nesterov;
+  int send_dtype;                 // 0 fp32, 1 bf16, 2 fp16 (only with BlockDesc::send)
+  int split_input;                // f given as (hi, lo) pair (1) or raw in f_hi (0)
+};
+
+void launch_grad_prologue(const PrologueArgs& args, cudaStream_t stream);
+void launch_direction_epilogue(const EpilogueArgs& args, cudaStream_t stream);
+
+}  // namespace ob200

@@ -1,0 +1,165 @@
+// See flat_kernels.cuh.
+#include "flat_kernels.cuh"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace ob200 {
+
+namespace {
+
+// torch.lerp semantics: the formula switches at weight 0.5 to stay monotone.
+__device__ __forceinline__ float lerpf(float a, float b, float w) {
+  const float d = b - a;
+  return w < 0.5f ? a + w * d : b - d * (1.f - w);
+}
+
+template <typename T>
+__device__ __forceinline__ float load_as_float(const void* base, long long i);
+template <>
+__device__ __forceinline__ float load_as_float<float>(const void* base, long long i) {
+  return static_cast<const float*>(base)[i];
+}
+template <>
+__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const void* base, long long i) {
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
+}
+template <>
+__device__ __forceinline__ float load_as_float<__half>(const void* base, long long i) {
+  return __half2float(static_cast<const __half*>(base)[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_from_float(void* base, long long i, float x);
+template <>
+__device__ __forceinline__ void store_from_float<float>(void* base, long long i, float x) {
+  static_cast<float*>(base)[i] = x;
+}
+template <>
+__device__ __forceinline__ void store_from_float<__nv_bfloat16>(void* base, long long i, float x) {
+  static_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(x);
+}
+template <>
+__device__ __forceinline__ void store_from_float<__half>(void* base, long long i, float x) {
+  static_cast<__half*>(base)[i] = __float2half_rn(x);
+}
+
+__global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict__ src, long long src_pitch,
+                                                         float* __restrict__ hi, float* __restrict__ lo,
+                                                         long long dst_pitch, int rows, int cols) {
+  const long long total = static_cast<long long>(rows) * cols;
+  for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int i = static_cast<int>(e / cols), j = static_cast<int>(e % cols);
+    const float x = src[i * src_pitch + j];
+    const float h = tf32_round(x);
+    hi[i * dst_pitch + j] = h;
+    lo[i * dst_pitch + j] = x - h;
+  }
+}
+
+struct GpaScalars {
+  float lr, beta1, beta2, eps, bc1, bc2, wd, avg_coeff, mu_y;
+  int wd_on_y;
+};
+
+template <typename T>
+__device__ __forceinline__ void gpa_chunk(const GpaTensorDesc& d, long long begin, long long end, const GpaScalars& s) {
+  const float y_step = s.lr * (s.mu_y * (1.f - s.avg_coeff) - 1.f);
+  const float shrink = 1.f - s.lr * s.wd;
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const float g = load_as_float<T>(d.grad, i);
+    float y = load_as_float<T>(d.param, i);
+    float z = d.z[i];
+    const float m = lerpf(d.m[i], g, 1.f - s.beta1);
+    const float v = s.beta2 * d.v[i] + (1.f - s.beta2) * g * g;
+    d.m[i] = m;
+    d.v[i] = v;
+    const float gn = (m / s.bc1) / (sqrtf(v / s.bc2) + s.eps);
+    if (s.wd != 0.f) {
+      if (s.wd_on_y) {
+        y *= shrink;
+      } else {
+        z *= shrink;
+      }
+    }
+    y = lerpf(y, z, s.avg_coeff);
+    y += y_step * gn;
+    z -= s.lr * gn;
+    store_from_float<T>(d.param, i, y);
+    d.z[i] = z;
+  }
+}
+
+__global__ void __launch_bounds__(256) gpa_adamw_kernel(const GpaTensorDesc* __restrict__ table,
+                                                        const int2* __restrict__ chunks, int num_chunks, GpaScalars s) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const GpaTensorDesc d = table[ref.x];
+    if (d.grad == nullptr) continue;
+    const long long begin = static_cast<long long>(ref.y) * kGpaChunk;
+    const long long end = begin + kGpaChunk < d.numel ? begin + kGpaChunk : d.numel;
+    if (d.dtype == 0) {
+      gpa_chunk<float>(d, begin, end, s);
+    } else if (d.dtype == 1) {
+      gpa_chunk<__nv_bfloat16>(d, begin, end, s);
+    } else {
+      gpa_chunk<__half>(d, begin, end, s);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void lerp_chunk(const GpaTensorDesc& d, long long begin, long long end, float w) {
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    store_from_float<T>(d.param, i, lerpf(load_as_float<T>(d.param, i), d.z[i], w));
+  }
+}
+
+__global__ void __launch_bounds__(256) gpa_lerp_kernel(const GpaTensorDesc* __restrict__ table,
+                                                       const int2* __restrict__ chunks, int num_chunks, float w) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const GpaTensorDesc d = table[ref.x];
+    const long long begin = static_cast<long long>(ref.y) * kGpaChunk;
+    const long long end = begin + kGpaChunk < d.numel ? begin + kGpaChunk : d.numel;
+    if (d.dtype == 0) {
+      lerp_chunk<float>(d, begin, end, w);
+    } else if (d.dtype == 1) {
+      lerp_chunk<__nv_bfloat16>(d, begin, end, w);
+    } else {
+      lerp_chunk<__half>(d, begin, end, w);
+    }
+  }
+}
+
+int grid_for(long long work_items) {
+  const long long cap = 148 * 8;
+  return static_cast<int>(work_items < cap ? (work_items > 0 ? work_items : 1) : cap);
+}
+
+}  // namespace
+
+void launch_tf32_split(const float* src, long long src_pitch, float* hi, float* lo, long long dst_pitch, int rows,
+                       int cols, cudaStream_t stream) {
+  const long long total = static_cast<long long>(rows) * cols;
+  if (total == 0) return;
+  tf32_split_kernel<<<grid_for((total + 255) / 256), 256, 0, stream>>>(src, src_pitch, hi, lo, dst_pitch, rows, cols);
+}
+
+void launch_gpa_adamw(const GpaTensorDesc* table, const int2* chunks, int num_chunks, float lr, float beta1,
+                      float beta2, float eps, float bias_correction1, float bias_correction2, float weight_decay,
+                      bool wd_on_y, float avg_coeff, float train_interp_coeff, cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  GpaScalars s{lr, beta1, beta2, eps, bias_correction1, bias_correction2, weight_decay, avg_coeff, train_interp_coeff,
+               wd_on_y ? 1 : 0};
+  gpa_adamw_kernel<<<grid_for(num_chunks), 256, 0, stream>>>(table, chunks, num_chunks, s);
+}
+
+void launch_gpa_lerp(const GpaTensorDesc* table, const int2* chunks, int num_chunks, float weight,
+                     cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  gpa_lerp_kernel<<<grid_for(num_chunks), 256, 0, stream>>>(table, chunks, num_chunks, weight);
+}
+
+}  // namespace ob200

@@ -1,0 +1,38 @@
+// Kernels over flat (contiguous) tensors: the tf32 (hi, lo) operand split, and the fused
+// GPA-AdamW update and train/eval interpolation as single multi-tensor launches.
+//
+// gpa_adamw: one read and one write of p, z, m, v and one read of g per element, instead of the
+// nine-plus pointwise launches and three temporaries per parameter of the reference loop
+// (gpa/gpa_adamw.py:455-497); gpa_lerp replaces the per-parameter lerp_ of train()/eval()
+// (gpa/gpa_adamw.py:307-357).
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace ob200 {
+
+constexpr int kGpaChunk = 4096;  // elements handled by one CTA iteration
+
+struct GpaTensorDesc {
+  void* param;       // fp32 / bf16 / fp16
+  const void* grad;  // same dtype as param; null when the parameter has no gradient
+  float* z;
+  float* m;
+  float* v;
+  long long numel;
+  int dtype;  // 0 fp32, 1 bf16, 2 fp16
+  int pad_;
+};
+
+void launch_tf32_split(const float* src, long long src_pitch, float* hi, float* lo, long long dst_pitch, int rows,
+                       int cols, cudaStream_t stream);
+
+void launch_gpa_adamw(const GpaTensorDesc* table, const int2* chunks, int num_chunks, float lr, float beta1,
+                      float beta2, float eps, float bias_correction1, float bias_correction2, float weight_decay,
+                      bool wd_on_y, float avg_coeff, float train_interp_coeff, cudaStream_t stream);
+
+void launch_gpa_lerp(const GpaTensorDesc* table, const int2* chunks, int num_chunks, float weight,
+                     cudaStream_t stream);
+
+}  // namespace ob200

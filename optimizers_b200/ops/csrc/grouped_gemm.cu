@@ -1,0 +1,263 @@
+// Grouped TN GEMM kernel for sm_100a (tcgen05 + TMEM + TMA).  See grouped_gemm.cuh for the
+// contract.  Replaces, as one launch over a problem table, the per-block cuBLAS calls behind
+// torch.tensordot in the reference (distributed_shampoo/preconditioner/
+// shampoo_preconditioner_list.py:1499-1507 factor Gram matrices, :1563-1578 preconditioner
+// application) together with the packing / EMA / norm kernels around them (:1525-1539).
+#include "grouped_gemm.cuh"
+#include "ptx.cuh"
+
+namespace ob200 {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr int kTileBytesA = kBM * kBK * 4;  // 16 KiB
+constexpr int kTileBytesB = kBN * kBK * 4;  // 16 KiB
+constexpr int kStagePitch = 33;             // floats per staged row: conflict-free transposition
+constexpr int kAccumCols = 2 * kBN;         // two accumulator buffers
+constexpr uint32_t kIdesc = make_idesc(/*tf32*/ 2, kBM, kBN);
+
+template <int kSplit>
+struct Cfg {
+  static constexpr int kStageBytes = (kTileBytesA + kTileBytesB) * (kSplit ? 2 : 1);
+  static constexpr int kStages = kSplit ? 3 : 6;
+  static constexpr int kStagingBytes = kEpilogueWarps * 32 * kStagePitch * 4;
+  static constexpr int kBarrierBytes = 256;
+  // 1024 B of slack so the stage buffers can be aligned for the 128-byte swizzle.
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
+};
+
+template <int kSplit>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __restrict__ tiles, int num_tiles,
+                    float alpha, float beta, int* __restrict__ status) {
+  using C = Cfg<kSplit>;
+  constexpr int kStages = C::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  float* staging = reinterpret_cast<float*>(smem + kStages * C::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes + C::kStagingBytes);
+  uint64_t* full_bar = bars;                 // [kStages]
+  uint64_t* empty_bar = bars + kStages;      // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], kEpilogueWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kAccumCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const GemmTile tile = tiles[t];
+        const GemmProblem* p = &problems[tile.problem];
+        const int num_kb = (p->K + kBK - 1) / kBK;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* s = stage_base + stage * C::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+          tma_load_2d(s, &p->a_hi, &full_bar[stage], kb * kBK, tile.m0);
+          tma_load_2d(s + kTileBytesA, &p->b_hi, &full_bar[stage], kb * kBK, tile.n0);
+          if (kSplit) {
+            tma_load_2d(s + kTileBytesA + kTileBytesB, &p->a_lo, &full_bar[stage], kb * kBK, tile.m0);
+            tma_load_2d(s + 2 * kTileBytesA + kTileBytesB, &p->b_lo, &full_bar[stage], kb * kBK, tile.n0);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const GemmTile tile = tiles[t];
+        const int num_kb = (problems[tile.problem].K + kBK - 1) / kBK;
+        const int buf = it & 1;
+        if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t s = smem_u32(stage_base + stage * C::kStageBytes);
+          const uint64_t a_hi = make_kmajor_sw128_desc(s);
+          const uint64_t b_hi = make_kmajor_sw128_desc(s + kTileBytesA);
+          const uint64_t a_lo = make_kmajor_sw128_desc(s + kTileBytesA + kTileBytesB);
+          const uint64_t b_lo = make_kmajor_sw128_desc(s + 2 * kTileBytesA + kTileBytesB);
+#pragma unroll
+          for (int k = 0; k < kBK / 8; ++k) {
+            // Advancing the start address by 32 bytes (encoded >> 4) walks the K steps inside
+            // the 128-byte swizzle row.
+            const uint64_t koff = static_cast<uint64_t>(k * 2);
+            if (kSplit) {
+              umma_tf32(d_tmem, a_lo + koff, b_hi + koff, kIdesc, (kb | k) != 0);
+              umma_tf32(d_tmem, a_hi + koff, b_lo + koff, kIdesc, 1);
+              umma_tf32(d_tmem, a_hi + koff, b_hi + koff, kIdesc, 1);
+            } else {
+              umma_tf32(d_tmem, a_hi + koff, b_hi + koff, kIdesc, (kb | k) != 0);
+            }
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    float* st = staging + (warp - 2) * 32 * kStagePitch;
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      const GemmTile tile = tiles[t];
+      const GemmProblem* p = &problems[tile.problem];
+      const int M = p->M, N = p->N, flags = p->flags;
+      float* __restrict__ Cp = p->c;
+      float* __restrict__ Dhi = p->d_hi;
+      float* __restrict__ Dlo = p->d_lo;
+      const int ldc = p->ldc, ldd = p->ldd;
+      const int buf = it & 1;
+      if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag)) break;
+      tc_fence_after_sync();
+      const int row0 = tile.m0 + q * 32;
+      float sq = 0.f;
+      if (row0 < M) {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          const int col0 = tile.n0 + c * 32;
+          if (col0 >= N) break;
+          if ((flags & kFlagPackedC) && col0 + 31 < row0) continue;  // chunk strictly below the diagonal
+          float v[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kBN + c * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) st[lane * kStagePitch + j] = v[j];
+          __syncwarp();
+          const int col = col0 + lane;
+          if (col < N) {
+            const int rows = min(32, M - row0);
+            for (int rr = 0; rr < rows; ++rr) {
+              const int row = row0 + rr;
+              float val = alpha * st[rr * kStagePitch + lane];
+              if (flags & kFlagPackedC) {
+                if (col < row) continue;
+                const long long off =
+                    static_cast<long long>(row) * N - (static_cast<long long>(row) * (row - 1)) / 2 + (col - row);
+                if (beta != 0.f) val += beta * Cp[off];
+                Cp[off] = val;
+              } else if (!(flags & kFlagNoC)) {
+                const long long off = static_cast<long long>(row) * ldc + col;
+                if (beta != 0.f) val += beta * Cp[off];
+                Cp[off] = val;
+              }
+              if (flags & kFlagSplitOut) {
+                const long long off = static_cast<long long>(row) * ldd + col;
+                const float hi = tf32_round(val);
+                Dhi[off] = hi;
+                Dlo[off] = val - hi;
+              }
+              sq += val * val;
+            }
+          }
+          __syncwarp();
+        }
+      }
+      tc_fence_before_sync();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (flags & kFlagSumSq) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0 && sq != 0.f) atomicAdd(p->sumsq, sq);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(status, kErrPipelineTimeout);
+    // Give copies that are still in flight time to land before the CTA's shared memory goes away.
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kAccumCols);
+  }
+}
+
+template <int kSplit>
+void launch_impl(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
+                 int* status, int max_ctas, cudaStream_t stream) {
+  using C = Cfg<kSplit>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(grouped_gemm_kernel<kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    configured = true;
+  }
+  const int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
+  grouped_gemm_kernel<kSplit><<<grid, kThreads, C::kSmemBytes, stream>>>(problems, tiles, num_tiles, alpha, beta,
+                                                                        status);
+}
+
+}  // namespace
+
+void launch_grouped_gemm(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
+                         bool split, int* status, int max_ctas, cudaStream_t stream) {
+  if (num_tiles <= 0) return;
+  if (split) {
+    launch_impl<1>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream);
+  } else {
+    launch_impl<0>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream);
+  }
+}
+
+}  // namespace ob200

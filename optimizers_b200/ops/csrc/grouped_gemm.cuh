@@ -1,0 +1,66 @@
+// Grouped "TN" GEMM on the 5th-generation tensor cores:  C_g = beta * C_g + alpha * A_g * B_g^T
+// for a table of independent problems, where A_g is [M,K] and B_g is [N,K], both K-major fp32.
+//
+// Two accuracy modes.  kSplit == 1: each operand arrives as a (hi, lo) pair with
+// hi = tf32_round(x), lo = x - hi, and every K step issues three tf32 products
+// (hi*hi + hi*lo + lo*hi) into the same fp32 TMEM accumulator, which restores fp32-grade
+// accuracy.  kSplit == 0: one tf32 product on the raw fp32 operands.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles of 128 x 32 fp32 with 128-byte swizzle
+//   warp 1      MMA issuer: tcgen05.mma 128x128x8 kind::tf32, accumulators in TMEM, two
+//               accumulator buffers so the epilogue of one tile overlaps the next tile's MMAs
+//   warps 2..5  epilogue: tcgen05.ld, transpose through shared memory, then coalesced global
+//               access with the fused options below.
+//
+// Epilogue options per problem (flags):
+//   kFlagPackedC    C is the row-major packed upper triangle of a symmetric N x N matrix; only
+//                   entries with col >= row are touched (the tile list then holds only tiles
+//                   on or above the diagonal)
+//   kFlagSplitOut   additionally write the result as a (hi, lo) tf32 pair into d_hi/d_lo
+//                   (row pitch ldd) so it can feed the next GEMM of a chain
+//   kFlagSumSq      add the sum of squares of the results to *sumsq (Frobenius norm partials)
+//   kFlagNoC        do not write C (only the split / sumsq outputs)
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+
+namespace ob200 {
+
+constexpr int kFlagPackedC = 1;
+constexpr int kFlagSplitOut = 2;
+constexpr int kFlagSumSq = 4;
+constexpr int kFlagNoC = 8;
+
+constexpr int kErrPipelineTimeout = 1;  // a bounded mbarrier wait expired
+
+struct alignas(128) GemmProblem {
+  CUtensorMap a_hi, a_lo, b_hi, b_lo;  // 2-D maps: dim0 = K (contiguous), dim1 = rows
+  float* c;
+  float* d_hi;
+  float* d_lo;
+  float* sumsq;
+  int M, N, K;
+  int ldc;  // row pitch of C in elements (full mode); N in packed mode
+  int ldd;  // row pitch of d_hi / d_lo
+  int flags;
+  int pad_[2];
+};
+
+struct GemmTile {
+  int problem;
+  int m0;  // first row of the tile
+  int n0;  // first column of the tile
+  int pad_;
+};
+
+constexpr int kBM = 128;
+constexpr int kBN = 128;
+constexpr int kBK = 32;  // fp32 elements = 128 bytes = one swizzle row
+
+// Host-side launch.  `status` is a device int the kernel writes a non-zero error code to.
+void launch_grouped_gemm(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
+                         bool split, int* status, int max_ctas, cudaStream_t stream);
+
+}  // namespace ob200

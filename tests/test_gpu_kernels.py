@@ -1,0 +1,222 @@
+"""GPU numerics of the sm_100a kernels against plain PyTorch fp32/fp64 references."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from optimizers_b200.ops import build
+
+    return build.load()
+
+
+def _pad4(n):
+    return (n + 3) // 4 * 4
+
+
+def _split(ext, x):
+    rows, k = x.shape
+    hi = torch.zeros(rows, _pad4(k), device=x.device)
+    lo = torch.zeros_like(hi)
+    ext.tf32_split(x, hi[:, :k], lo[:, :k])
+    return hi[:, :k], lo[:, :k]
+
+
+def _packed(full):
+    d = full.shape[0]
+    r, c = torch.triu_indices(d, d, device=full.device)
+    return full[r, c].contiguous()
+
+
+@pytest.mark.parametrize("split", [True, False])
+@pytest.mark.parametrize(
+    "M,N,K", [(128, 128, 32), (128, 128, 256), (256, 384, 100), (1, 200, 200), (37, 5, 7), (300, 129, 1000), (513, 64, 36)]
+)
+def test_grouped_gemm_full(ext, split, M, N, K):
+    torch.manual_seed(M * 7 + N * 3 + K)
+    dev = torch.device("cuda")
+    A = torch.randn(M, K, device=dev)
+    B = torch.randn(N, K, device=dev)
+    C0 = torch.randn(M, N, device=dev)
+    C = C0.clone()
+    a_hi, a_lo = _split(ext, A)
+    b_hi, b_lo = _split(ext, B)
+    if not split:
+        # raw operands in padded storage
+        a_hi = torch.zeros(M, _pad4(K), device=dev)[:, :K].copy_(A)
+        b_hi = torch.zeros(N, _pad4(K), device=dev)[:, :K].copy_(B)
+        a_lo = b_lo = None
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    sumsq = torch.zeros(1, device=dev)
+    plan = ext.build_gemm_plan([(a_hi, a_lo, b_hi, b_lo, C, None, None, sumsq, N, 0, ext.FLAG_SUMSQ, False)])
+    ext.run_gemm_plan(*plan, 0.5, 2.0, split, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = 2.0 * C0.double() + 0.5 * (A.double() @ B.double().T)
+    scale = math.sqrt(K)
+    tol = 2e-5 * scale if split else 4e-3 * scale
+    assert (C.double() - ref).abs().max().item() < tol
+    assert abs(sumsq.item() - (ref**2).sum().item()) <= 1e-2 * (ref**2).sum().item() + 1e-3
+
+
+@pytest.mark.parametrize("split", [True, False])
+@pytest.mark.parametrize("d,K", [(128, 64), (200, 300), (384, 32), (5, 3), (129, 1024)])
+def test_grouped_syrk_packed_ema(ext, split, d, K):
+    torch.manual_seed(d + K)
+    dev = torch.device("cuda")
+    X = torch.randn(d, K, device=dev)
+    F0 = torch.randn(d, d, device=dev)
+    F0 = F0 @ F0.T
+    Fp = _packed(F0)
+    x_hi, x_lo = _split(ext, X)
+    if not split:
+        x_hi = torch.zeros(d, _pad4(K), device=dev)[:, :K].copy_(X)
+        x_lo = None
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    plan = ext.build_gemm_plan([(x_hi, x_lo, x_hi, x_lo, Fp, None, None, None, d, 0, ext.FLAG_PACKED_C, True)])
+    ext.run_gemm_plan(*plan, 0.25, 0.9, split, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = _packed((0.9 * F0.double() + 0.25 * (X.double() @ X.double().T)).float())
+    # tensor-core fp32 accumulation truncates, so the error grows with the magnitude of the sums
+    tol = (2e-5 if split else 4e-3) * math.sqrt(K) + 3e-5 * ref.abs().max().item()
+    assert (Fp - ref).abs().max().item() < tol
+
+
+def test_grouped_gemm_many_problems_and_split_out(ext):
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    specs, checks = [], []
+    for i, (M, N, K) in enumerate([(130, 70, 90), (64, 64, 64), (400, 300, 200), (17, 257, 33)] * 3):
+        A, B = torch.randn(M, K, device=dev), torch.randn(N, K, device=dev)
+        a_hi, a_lo = _split(ext, A)
+        b_hi, b_lo = _split(ext, B)
+        d_hi = torch.zeros(M, _pad4(N), device=dev)
+        d_lo = torch.zeros_like(d_hi)
+        specs.append((a_hi, a_lo, b_hi, b_lo, None, d_hi, d_lo, None, 0, _pad4(N), ext.FLAG_NO_C | ext.FLAG_SPLIT_OUT, False))
+        checks.append((A, B, d_hi, d_lo, N, K))
+    plan = ext.build_gemm_plan(specs)
+    ext.run_gemm_plan(*plan, 1.0, 0.0, True, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    for A, B, d_hi, d_lo, N, K in checks:
+        ref = A.double() @ B.double().T
+        got = d_hi[:, :N].double() + d_lo[:, :N].double()
+        assert (got - ref).abs().max().item() < 2e-5 * math.sqrt(K)
+        # hi must be representable in tf32: the 13 low mantissa bits are zero
+        assert (d_hi.view(torch.int32) & 0x1FFF).abs().max().item() == 0
+
+
+def _mlp(dev):
+    torch.manual_seed(0)
+    return torch.nn.Sequential(
+        torch.nn.Linear(96, 200), torch.nn.ReLU(), torch.nn.Linear(200, 72), torch.nn.ReLU(), torch.nn.Linear(72, 10)
+    ).to(dev)
+
+
+def _train(backend, steps, **kw):
+    from optimizers_b200 import DistributedShampoo, NativeRuntimeConfig
+
+    dev = torch.device("cuda")
+    model = _mlp(dev)
+    opt = DistributedShampoo(
+        model.parameters(), native_runtime_config=NativeRuntimeConfig(backend=backend), **kw
+    )
+    if hasattr(opt, "train"):
+        opt.train()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    losses = []
+    for _ in range(steps):
+        x = torch.randn(64, 96, device=dev, generator=g)
+        y = torch.randint(0, 10, (64,), device=dev, generator=g)
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(model(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    return model, opt, losses
+
+
+def _configs():
+    from optimizers_b200 import (
+        AdaGradPreconditionerConfig,
+        AdamPreconditionerConfig,
+        ClassicMomentumConfig,
+        GeneralizedPrimalAveragingConfig,
+        RootInvShampooPreconditionerConfig,
+        SGDPreconditionerConfig,
+        WeightDecayType,
+    )
+
+    base = dict(lr=1e-2, betas=(0.9, 0.999), epsilon=1e-8, max_preconditioner_dim=64, precondition_frequency=3, start_preconditioning_step=3)
+    return {
+        "adam_graft": dict(base, grafting_config=AdamPreconditionerConfig(beta2=0.999, epsilon=1e-8)),
+        "adagrad_graft_wd": dict(base, grafting_config=AdaGradPreconditionerConfig(), weight_decay=1e-2),
+        "sgd_graft_l2_momentum": dict(
+            base, grafting_config=SGDPreconditionerConfig(), weight_decay=1e-3, weight_decay_type=WeightDecayType.L2,
+            iterate_averaging_config=ClassicMomentumConfig(momentum=0.5, use_nesterov=True),
+        ),
+        "no_graft_unpacked_beta3": dict(
+            base, beta3=0.8, preconditioner_config=RootInvShampooPreconditionerConfig(use_symmetric_packing=False)
+        ),
+        "gpa": dict(
+            base, grafting_config=AdamPreconditionerConfig(), weight_decay=1e-2,
+            iterate_averaging_config=GeneralizedPrimalAveragingConfig(eval_interp_coeff=0.9, train_interp_coeff=0.7),
+        ),
+    }
+
+
+@pytest.mark.parametrize("name", ["adam_graft", "adagrad_graft_wd", "sgd_graft_l2_momentum", "no_graft_unpacked_beta3", "gpa"])
+def test_native_engine_matches_torch_step(name):
+    kw = _configs()[name]
+    m_ref, o_ref, l_ref = _train("torch", 8, **kw)
+    m_nat, o_nat, l_nat = _train("native", 8, **kw)
+    for rec in o_nat._per_group_state_lists:
+        assert rec["native_engine"] is not None
+        rec["native_engine"].check_status()
+    for a, b in zip(l_ref, l_nat):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (l_ref, l_nat)
+    for p, q in zip(m_ref.parameters(), m_nat.parameters()):
+        assert torch.allclose(p, q, rtol=5e-3, atol=5e-4), (p - q).abs().max()
+    # optimizer state trees agree as well (factor matrices are the sensitive part)
+    s_ref, s_nat = o_ref.state_dict()["state"], o_nat.state_dict()["state"]
+
+    def walk(a, b, path=""):
+        if isinstance(a, dict):
+            assert a.keys() == b.keys(), path
+            for k in a:
+                walk(a[k], b[k], f"{path}/{k}")
+        elif isinstance(a, torch.Tensor) and a.is_floating_point() and a.numel():
+            denom = a.abs().max().item() + 1e-12
+            assert (a - b).abs().max().item() / denom < 2e-2, path
+
+    walk(s_ref, s_nat)
+
+
+def test_gpa_adamw_kernel_matches_torch_loop():
+    from optimizers_b200.gpa_adamw import GPAAdamW
+
+    dev = torch.device("cuda")
+    results = []
+    for native in (False, True):
+        torch.manual_seed(0)
+        model = _mlp(dev)
+        opt = GPAAdamW(model.parameters(), lr=1e-2, weight_decay=1e-2, use_native_kernels=native)
+        opt.train()
+        g = torch.Generator(device="cuda").manual_seed(1)
+        for _ in range(6):
+            x = torch.randn(32, 96, device=dev, generator=g)
+            y = torch.randint(0, 10, (32,), device=dev, generator=g)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+        opt.eval()
+        results.append([p.detach().clone() for p in model.parameters()])
+    for a, b in zip(*results):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
