@@ -51,6 +51,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--backend", choices=["auto", "native", "torch"], default="native")
     ap.add_argument("--gemm-mode", choices=["tf32x3", "tf32"], default="tf32x3")
+    ap.add_argument("--comm", choices=["p2p", "nccl"], default="p2p", help="multi-GPU path of this framework")
     ap.add_argument("--layers", type=int, default=12, help="debug only; the reported config needs 12")
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="debug only; the reported config needs 16")
     return ap.parse_args()
@@ -182,7 +183,13 @@ def build_optimizer(impl: str, model, world: int, args):
     else:
         import optimizers_b200 as lib
 
-        extra = {"native_runtime_config": lib.NativeRuntimeConfig(backend=args.backend, gemm_mode=args.gemm_mode)}
+        fused = world > 1 and args.comm == "p2p" and args.backend != "torch"
+        extra = {
+            "native_runtime_config": lib.NativeRuntimeConfig(
+                backend=args.backend, gemm_mode=args.gemm_mode, comm_path="p2p" if fused else "nccl",
+                fuse_gradient_reduction=fused,
+            )
+        }
     if world > 1:
         dist_cfg = lib.DDPDistributedConfig(communication_dtype=torch.bfloat16, num_trainers_per_group=world)
     else:
@@ -247,8 +254,14 @@ def main() -> None:
     torch.backends.cuda.matmul.allow_tf32 = False  # optimizer math of the reference stays fp32
     model = make_gpt2(args.layers).to(dev)
     train_model = model
-    if world > 1:
+    # This framework's p2p path reduces the gradients inside the optimizer's prologue kernel
+    # (owners pull their blocks from peer memory), so the model is not wrapped in DDP there.
+    fused_comm = args.impl == "ours" and world > 1 and args.comm == "p2p" and args.backend != "torch"
+    if world > 1 and not fused_comm:
         train_model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
+    elif world > 1:
+        for p in model.parameters():
+            dist.broadcast(p.data, src=0)
     opt = build_optimizer(args.impl, model, world, args)
     if hasattr(opt, "train"):
         opt.train()
@@ -264,7 +277,7 @@ def main() -> None:
             loss = train_model(tokens[:, :-1], tokens[:, 1:])
         loss.backward()
         opt.step()
-        opt.zero_grad(set_to_none=True)
+        opt.zero_grad(set_to_none=not fused_comm)
         return loss
 
     def barrier() -> None:
@@ -343,6 +356,7 @@ def main() -> None:
                 "global_batch": B * world,
                 "seq_len": SEQ,
                 "parallelism": f"dp{world}" if world > 1 else "single",
+                "comm": ("p2p fused reduce-scatter + all-gather kernels" if fused_comm else "nccl") if world > 1 else "none",
                 "optimizer": "DistributedShampoo max_preconditioner_dim=2048 precondition_frequency=100 AdaGrad grafting, fp32 factors",
                 "gemm_mode": args.gemm_mode if args.impl == "ours" else "fp32 (cuBLAS)",
                 "l2_policy": "working set (params, grads, optimizer state, activations: several GB) exceeds the 126 MB L2",

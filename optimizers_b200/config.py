@@ -710,12 +710,20 @@ class NativeRuntimeConfig:
     gemm_mode: ``"tf32x3"`` splits fp32 operands into two tf32 terms and issues three tensor-core
                products (fp32-grade accuracy); ``"tf32"`` issues one.
     comm_path: ``"nccl"`` uses ``torch.distributed`` collectives; ``"p2p"`` lets the kernels
-               load/store peer memory directly over NVLink.
+               load/store peer memory directly over NVLink: the direction epilogue stores each
+               block's search direction into every peer's gather buffer (all-gather fused into
+               the producing kernel).
+    fuse_gradient_reduction: with ``comm_path="p2p"`` and the DDP distributor, gradients are
+               accumulated by autograd straight into peer-addressable memory and each block's
+               owner sums its peers' gradient blocks inside the prologue kernel (reduce-scatter
+               fused into the factor update).  The model must then NOT be wrapped in
+               ``DistributedDataParallel`` and ``zero_grad(set_to_none=False)`` must be used.
     """
 
     backend: str = "auto"
     gemm_mode: str = "tf32x3"
     comm_path: str = "nccl"
+    fuse_gradient_reduction: bool = False
 
     def __post_init__(self) -> None:
         if self.backend not in ("auto", "torch", "native"):
@@ -724,6 +732,8 @@ class NativeRuntimeConfig:
             raise ValueError(f"Invalid gemm_mode {self.gemm_mode!r}. Must be tf32x3 or tf32.")
         if self.comm_path not in ("nccl", "p2p"):
             raise ValueError(f"Invalid comm_path {self.comm_path!r}. Must be nccl or p2p.")
+        if self.fuse_gradient_reduction and self.comm_path != "p2p":
+            raise ValueError("fuse_gradient_reduction=True requires comm_path='p2p'.")
 
 
 DefaultNativeRuntimeConfig = NativeRuntimeConfig()

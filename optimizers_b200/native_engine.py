@@ -19,7 +19,8 @@ from the state after every refresh and after ``load_state_dict``.
 
 Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 with every dim preconditioned,
 root-inverse Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting, any weight decay type,
-classic momentum, GPA / Schedule-Free, single-device and DDP distributors.  Anything else makes
+classic momentum, GPA / Schedule-Free, single-device and DDP distributors (NCCL all-gather, or
+peer-to-peer stores and loads over NVLink with ``comm_path="p2p"``).  Anything else makes
 ``build_native_engine`` return ``None`` (torch step) or raise with ``backend="native"``.
 """
 
@@ -79,8 +80,13 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     if gc is not None and not isinstance(gc, (SGDPreconditionerConfig, AdaGradPreconditionerConfig)):
         return f"grafting config {type(gc).__name__} has no native step"
     dc = group[DISTRIBUTED_CONFIG]
-    if type(dc) is not SingleDeviceDistributedConfig:
+    if type(dc) not in (SingleDeviceDistributedConfig, DDPDistributedConfig):
         return f"distributed config {type(dc).__name__} has no native step yet"
+    if isinstance(dc, DDPDistributedConfig):
+        if dc.communicate_params:
+            return "communicate_params=True has no native step yet"
+        if dc.communication_dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            return f"communication dtype {dc.communication_dtype} has no native step"
     for p in group[PARAMS]:
         if p.dtype != torch.float32 or not p.is_contiguous() or type(p.data) is not Tensor:
             return "parameters must be plain contiguous fp32 tensors"
@@ -94,6 +100,8 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
             return "blocks with unpreconditioned dims have no native step yet"
         if block.numel() == 0:
             return "empty blocks"
+    if any(b.dim() > 2 or b.numel() == 0 for b in rec[DISTRIBUTOR]._global_blocked_params):
+        return "a block of another rank has no native step"
     return None
 
 
@@ -145,13 +153,28 @@ class NativeGroupEngine:
             self._graft_kind = _GRAFT_ADAGRAD
 
         self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
+        self._ddp = isinstance(group[DISTRIBUTED_CONFIG], DDPDistributedConfig)
+        self._p2p = self._ddp and cfg.comm_path == "p2p"
+        self._pull = self._p2p and cfg.fuse_gradient_reduction
+        self._comm_dtype_code = 0
+        self._gather_table = None
+        self._gather_for: tuple[bool, ...] | None = None
+        self._barrier_seq = 0
+        if self._ddp:
+            cd = group[DISTRIBUTED_CONFIG].communication_dtype
+            self._comm_dtype_code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[cd]
+            sel = self._dist._distributor_selector
+            self._local_slot_offsets = compress_list(self._dist._global_block_byte_offsets, sel)
+        if self._p2p:
+            self._setup_peer_memory()
         self._build_blocks()
         n_ptrs = max(len(group[PARAMS]), 1)
         # Two pinned staging buffers, used alternately, so that a pointer table still being
         # copied by the device is never overwritten by the host.
         self._grad_ptrs_host = [torch.zeros(n_ptrs, dtype=torch.int64).pin_memory() for _ in range(2)]
         self._grad_ptrs_flip = 0
-        self._grad_ptrs_dev = torch.zeros(n_ptrs, dtype=torch.int64, device=self._device)
+        if not self._pull:
+            self._grad_ptrs_dev = torch.zeros(n_ptrs, dtype=torch.int64, device=self._device)
         self._last_ptrs: list[int] | None = None
         self._active: tuple[bool, ...] | None = None
         self._plans_for: tuple[bool, ...] | None = None
@@ -211,7 +234,56 @@ class NativeGroupEngine:
         self._blocks = blocks
 
     def _send_ptr(self, b: _Block) -> int:
-        return 0
+        if not self._ddp or self._p2p:
+            return 0
+        return self._dist._local_dist_blocked_buffers[b.index].data_ptr()
+
+    def _slot_offset(self, b: _Block) -> int:
+        return int(self._local_slot_offsets[b.index]) if self._ddp else 0
+
+    def _setup_peer_memory(self) -> None:
+        """Allocate the peer-addressable arena: gather buffer (same layout as the distributor's),
+        two flag arrays for the cross-rank barriers, and, when the gradient reduction is fused,
+        one fp32 gradient arena that autograd accumulates into."""
+        from optimizers_b200.parallel.symm_arena import SymmetricArena
+
+        dist_ = self._dist
+        world = dist_._group_size
+        if world > 8:
+            raise RuntimeError("comm_path='p2p' needs all ranks of a group on one NVLink domain (at most 8)")
+        regions = {"gather": dist_._global_dist_buffer.numel(), "flags": 2 * 32 * 4}
+        params = self._group[PARAMS]
+        if self._pull:
+            if dist_._group_size != dist_._global_size:
+                raise RuntimeError("fuse_gradient_reduction needs num_trainers_per_group == world size")
+            regions["grads"] = sum(p.numel() for p in params) * 4
+        self._arena = SymmetricArena(regions, self._device, dist_._dist_group)
+        self._flags = self._arena.region("flags").view(torch.int32)
+        self._flag_bases = [
+            torch.tensor([a + k * 128 for a in self._arena.peer_addresses("flags")], dtype=torch.int64, device=self._device)
+            for k in range(2)
+        ]
+        self._gather_local = self._arena.region("gather", dist_._global_dist_buffer.numel())
+        self._gather_bases = self._arena.peer_addresses("gather")
+        if self._pull:
+            flat = self._arena.region("grads", regions["grads"]).view(torch.float32)
+            bases = self._arena.peer_addresses("grads")
+            table, cursor = [], 0
+            self._grad_views = []
+            for p in params:
+                view = flat[cursor : cursor + p.numel()].view(p.shape)
+                p.grad = view
+                self._grad_views.append(view)
+                table.extend(b + cursor * 4 for b in bases)
+                cursor += p.numel()
+            self._grad_ptrs_dev = torch.tensor(table, dtype=torch.int64, device=self._device)
+
+    def _peer_barrier(self, which: int) -> None:
+        self._barrier_seq += 1
+        self._ext.peer_barrier(
+            self._flags[which * 32 : which * 32 + 32], self._flag_bases[which], self._arena.rank, self._arena.world,
+            self._barrier_seq, self._status,
+        )
 
     def _build_plans(self, active: tuple[bool, ...]) -> None:
         """(Re)build the block table and the three GEMM plans for the active blocks."""
@@ -228,6 +300,7 @@ class NativeGroupEngine:
                 (
                     b.param_view, b.grad_offset, b.grad_slot, b.m, b.n, b.n_pad, b.m_pad, b.m1, b.v, b.mom, b.z,
                     b.g_hi, b.g_lo, b.gt_hi, b.gt_lo, b.f_hi, b.f_lo, b.p, self._norms[b.index], self._send_ptr(b),
+                    self._slot_offset(b),
                 )
             )
         self._table = ext.build_block_table(specs)
@@ -290,6 +363,17 @@ class NativeGroupEngine:
         gradient, refreshes the distributor's selectors, and stages the gradient base pointers.
         No per-block views are created.  Returns the pointers (empty when nothing has a gradient)."""
         dist = self._dist
+        if self._pull:
+            # Gradients live in the peer-addressable arena; every parameter takes part every step.
+            for p, view in zip(self._group[PARAMS], self._grad_views, strict=True):
+                if p.grad is None or p.grad.data_ptr() != view.data_ptr():
+                    raise RuntimeError(
+                        "fuse_gradient_reduction=True: a parameter's .grad no longer is its view of the shared "
+                        "gradient arena; call optimizer.zero_grad(set_to_none=False) (never set grads to None)."
+                    )
+            dist._global_grad_selector = (True,) * len(dist._global_blocked_params)
+            dist._refresh_local_selection()
+            return (1,)
         ptrs: list[int] = []
         selector: list[bool] = []
         any_grad = False
@@ -319,6 +403,11 @@ class NativeGroupEngine:
         local_any = any_grad and any(dist.local_grad_selector)
         return tuple(ptrs) if local_any else ()
 
+    def zero_grad(self) -> None:
+        """Zero the shared gradient arena in one memset (fused-reduction mode)."""
+        if self._pull:
+            self._arena.region("grads").zero_()
+
     # ------------------------------------------------------------------------------------------
     # The step
     # ------------------------------------------------------------------------------------------
@@ -327,6 +416,8 @@ class NativeGroupEngine:
         code = int(self._status.item())
         if code & 1:
             raise RuntimeError("grouped GEMM pipeline wait timed out (device-side bounded wait expired)")
+        if code & 4:
+            raise RuntimeError("a peer rank did not reach the cross-rank barrier in time (bounded device-side wait expired)")
         if code & 2:
             self._status.zero_()
             raise PreconditionerValueError("Encountered NaN/Inf in a gradient passed to the optimizer.")
@@ -336,13 +427,19 @@ class NativeGroupEngine:
         use_bias_correction, graft_only, primal, classic, mu_y, mu_x, momentum, dampening, nesterov,
     ) -> None:
         rec, ext = self._rec, self._ext
-        if not rec[MASKED_BLOCKED_GRADS]:
-            self._dist.update_params(blocked_search_directions=())
-            return
         active = self._active if self._active is not None else (True,) * len(self._blocks)
         if self._plans_for != active:
             self._build_plans(active)
             self._plans_for = active
+        if not rec[MASKED_BLOCKED_GRADS] or self._table is None:
+            # Nothing to compute here; other ranks may still need this rank in their collective.
+            self.launches_per_step = 0
+            self._finish_update()
+            return
+        if self._p2p:
+            # Every rank has finished its backward pass (its gradients are complete) and has applied
+            # the previous step's directions (its gather buffer may be overwritten).
+            self._peer_barrier(0)
         t = int(step.item())
         launches = 0
 
@@ -363,6 +460,7 @@ class NativeGroupEngine:
         ext.grad_prologue(
             blocks_t, tiles_t, n_tiles, self._grad_ptrs_dev, l2, beta1, beta3, bc1, self._graft_kind,
             g_beta2, g_weight, g_bc2, g_eps, self._split, self._status,
+            self._arena.world if self._pull else 0, 1.0 / self._arena.world if self._pull else 1.0,
         )
         launches += 2
         ext.run_gemm_plan(*self._syrk_plan, plist._weighting_factor, plist._beta2, self._split, self._status)
@@ -395,14 +493,40 @@ class NativeGroupEngine:
             )
         ext.direction_epilogue(
             blocks_t, tiles_t, n_tiles, lr, graft_only, self._graft_kind if has_grafting else _GRAFT_NONE, g_bc2,
-            g_eps, alpha, primal, mu_y, mu_x, classic, momentum, dampening, nesterov, self._send_dtype(), self._split,
+            g_eps, alpha, primal, mu_y, mu_x, classic, momentum, dampening, nesterov, self._comm_dtype_code, self._split,
+            self._gather_bases if self._p2p else [],
         )
         launches += 1
         self.launches_per_step = launches
-        self._after_epilogue()
+        self._finish_update()
 
-    def _send_dtype(self) -> int:
-        return 0
-
-    def _after_epilogue(self) -> None:
-        """Single device: the epilogue already updated the parameters."""
+    def _finish_update(self) -> None:
+        """Deliver the search directions.  Single device: the epilogue already updated the
+        parameters.  DDP: all-gather (NCCL), or a cross-rank barrier after the epilogue's peer
+        stores (p2p); then one grouped kernel adds every block's direction to the parameters."""
+        if not self._ddp:
+            return
+        dist_ = self._dist
+        if self._p2p:
+            if self.launches_per_step == 0:
+                self._peer_barrier(0)
+            self._peer_barrier(1)
+            self.launches_per_step += 1
+            recv = self._gather_local
+        else:
+            dist_._all_gather()
+            recv = dist_._global_dist_buffer
+        sel = dist_._global_grad_selector
+        if self._gather_for != sel:
+            specs = []
+            base = recv.data_ptr()
+            for view, off, on in zip(dist_._global_blocked_params, dist_._global_block_byte_offsets, sel, strict=True):
+                if not on:
+                    continue
+                m, n = (1, view.shape[0]) if view.dim() == 1 else view.shape
+                specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 12 + (base + off, off))
+            self._gather_table = self._ext.build_block_table(specs) if specs else None
+            self._gather_for = sel
+        if self._gather_table is not None:
+            self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code)
+            self.launches_per_step += 1

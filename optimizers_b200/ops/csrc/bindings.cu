@@ -157,14 +157,14 @@ void run_gemm_plan(const torch::Tensor& problems, const torch::Tensor& tiles, in
 }
 
 // Block table.  Each spec: (param_view, grad_offset, grad_slot, m, n, n_pad, m_pad, m1, v, mom, z,
-//                           g_hi, g_lo, gt_hi, gt_lo, f_hi, f_lo, p, norms, send_ptr)
+//                           g_hi, g_lo, gt_hi, gt_lo, f_hi, f_lo, p, norms, send_ptr, slot_offset)
 std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::vector<py::tuple>& specs) {
   std::vector<BlockDesc> blocks(specs.size());
   std::vector<TileRef> tiles;
   torch::Device device(torch::kCPU);
   for (size_t i = 0; i < specs.size(); ++i) {
     const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 20, "block spec must have 20 fields");
+    TORCH_CHECK(s.size() == 21, "block spec must have 21 fields");
     BlockDesc& b = blocks[i];
     std::memset(&b, 0, sizeof(b));
     auto param = s[0].cast<torch::Tensor>();
@@ -198,6 +198,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
     b.p = opt(17);
     b.norms = opt(18);
     b.send = reinterpret_cast<void*>(s[19].cast<int64_t>());
+    b.slot_offset = s[20].cast<int64_t>();
     const int tm = (b.m + 31) / 32, tn = (b.n + 31) / 32;
     for (int ti = 0; ti < tm; ++ti)
       for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});
@@ -210,7 +211,8 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
 void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles,
                    const torch::Tensor& grad_ptrs, double l2_weight_decay, double beta1, double beta3,
                    double bias_correction1, int64_t graft_kind, double graft_beta2, double graft_weight,
-                   double graft_bc2, double graft_eps, bool write_split, torch::Tensor status) {
+                   double graft_bc2, double graft_eps, bool write_split, torch::Tensor status,
+                   int64_t num_grad_peers, double grad_scale) {
   c10::cuda::CUDAGuard guard(blocks.device());
   PrologueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
@@ -228,6 +230,8 @@ void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int6
   a.graft_epsilon = static_cast<float>(graft_eps);
   a.write_split = write_split ? 1 : 0;
   a.status = status.data_ptr<int>();
+  a.num_grad_peers = static_cast<int>(num_grad_peers);
+  a.grad_scale = static_cast<float>(grad_scale);
   launch_grad_prologue(a, at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
@@ -236,7 +240,7 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
                         const torch::Tensor& lr, bool graft_only, int64_t graft_kind, double graft_bc2,
                         double graft_eps, double wd_alpha, bool primal_averaging, const torch::Tensor& mu_y,
                         const torch::Tensor& mu_x, bool classic_momentum, double momentum, double dampening,
-                        bool nesterov, int64_t send_dtype, bool split_input) {
+                        bool nesterov, int64_t send_dtype, bool split_input, const std::vector<int64_t>& peer_bases) {
   c10::cuda::CUDAGuard guard(blocks.device());
   EpilogueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
@@ -257,7 +261,29 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
   a.nesterov = nesterov ? 1 : 0;
   a.send_dtype = static_cast<int>(send_dtype);
   a.split_input = split_input ? 1 : 0;
+  TORCH_CHECK(peer_bases.size() <= 8, "at most 8 peers");
+  a.num_push_peers = static_cast<int>(peer_bases.size());
+  for (size_t r = 0; r < 8; ++r) a.peer_base[r] = r < peer_bases.size() ? static_cast<unsigned long long>(peer_bases[r]) : 0ull;
   launch_direction_epilogue(a, at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype) {
+  c10::cuda::CUDAGuard guard(blocks.device());
+  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()),
+                        reinterpret_cast<const TileRef*>(tiles.data_ptr()), static_cast<int>(num_tiles),
+                        static_cast<int>(dtype), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void peer_barrier(torch::Tensor local_flags, const torch::Tensor& peer_flag_bases, int64_t my_rank, int64_t world,
+                  int64_t seq, torch::Tensor status) {
+  c10::cuda::CUDAGuard guard(local_flags.device());
+  TORCH_CHECK(world <= 32, "peer barrier supports up to 32 ranks");
+  launch_peer_barrier(local_flags.data_ptr<int>(),
+                      reinterpret_cast<const unsigned long long*>(peer_flag_bases.data_ptr<int64_t>()),
+                      static_cast<int>(my_rank), static_cast<int>(world), static_cast<int>(seq),
+                      status.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -335,6 +361,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_block_table", &build_block_table);
   m.def("grad_prologue", &grad_prologue);
   m.def("direction_epilogue", &direction_epilogue);
+  m.def("gathered_apply", &gathered_apply);
+  m.def("peer_barrier", &peer_barrier);
   m.def("tf32_split", &tf32_split);
   m.def("build_gpa_table", &build_gpa_table);
   m.def("gpa_adamw_step", &gpa_adamw_step);

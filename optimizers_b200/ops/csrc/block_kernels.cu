@@ -31,7 +31,8 @@ __global__ void __launch_bounds__(256) grad_prologue_kernel(PrologueArgs a) {
   for (int t = blockIdx.x; t < a.num_tiles; t += gridDim.x) {
     const TileRef ref = a.tiles[t];
     const BlockDesc& b = a.blocks[ref.block];
-    const float* __restrict__ grad = a.grad_ptrs[b.grad_slot] + b.grad_offset;
+    const int n_src = a.num_grad_peers > 0 ? a.num_grad_peers : 1;
+    const float* const* srcs = a.grad_ptrs + static_cast<long long>(b.grad_slot) * n_src;
     const int i0 = ref.ti * kTile, j0 = ref.tj * kTile;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int j = j0 + tx;
@@ -46,7 +47,17 @@ __global__ void __launch_bounds__(256) grad_prologue_kernel(PrologueArgs a) {
       float hi = 0.f, lo = 0.f;
       if (i < b.m && j < b.n) {
         const long long e = static_cast<long long>(i) * b.n + j;           // contiguous state index
-        float g = grad[static_cast<long long>(i) * b.param_pitch + j];
+        const long long ge = b.grad_offset + static_cast<long long>(i) * b.param_pitch + j;
+        float g;
+        if (a.num_grad_peers > 0) {
+          // Plain (coherent) loads: the sources are other GPUs' memory written by their last
+          // backward pass; fixed rank order keeps the sum identical on every owner.
+          g = 0.f;
+          for (int r = 0; r < n_src; ++r) g += *reinterpret_cast<const volatile float*>(srcs[r] + ge);
+          g *= a.grad_scale;
+        } else {
+          g = srcs[0][ge];
+        }
         if (a.l2_weight_decay != 0.f) g += a.l2_weight_decay * b.param[static_cast<long long>(i) * b.param_pitch + j];
         bad |= !isfinite(g);
         if (a.write_split) {
@@ -191,7 +202,18 @@ __global__ void __launch_bounds__(256) direction_epilogue_kernel(EpilogueArgs a)
         b.z[e] = z + p;
         p = (1.f - mu_x * mu_y) * p + (1.f - mu_x) * gap;
       }
-      if (b.send != nullptr) {
+      if (a.num_push_peers > 0) {
+        for (int r = 0; r < a.num_push_peers; ++r) {
+          void* dst = reinterpret_cast<void*>(a.peer_base[r] + b.slot_offset);
+          if (a.send_dtype == 1) {
+            store_send<__nv_bfloat16>(dst, e, p);
+          } else if (a.send_dtype == 2) {
+            store_send<__half>(dst, e, p);
+          } else {
+            store_send<float>(dst, e, p);
+          }
+        }
+      } else if (b.send != nullptr) {
         if (a.send_dtype == 1) {
           store_send<__nv_bfloat16>(b.send, e, p);
         } else if (a.send_dtype == 2) {
@@ -204,6 +226,74 @@ __global__ void __launch_bounds__(256) direction_epilogue_kernel(EpilogueArgs a)
       }
     }
   }
+}
+
+template <typename T>
+__device__ __forceinline__ float load_recv(const void* base, long long idx);
+template <>
+__device__ __forceinline__ float load_recv<float>(const void* base, long long idx) {
+  return static_cast<const float*>(base)[idx];
+}
+template <>
+__device__ __forceinline__ float load_recv<__nv_bfloat16>(const void* base, long long idx) {
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
+}
+template <>
+__device__ __forceinline__ float load_recv<__half>(const void* base, long long idx) {
+  return __half2float(static_cast<const __half*>(base)[idx]);
+}
+
+// Every rank applies every block's gathered search direction: param += cast(slot).
+__global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __restrict__ blocks,
+                                                             const TileRef* __restrict__ tiles, int num_tiles,
+                                                             int dtype) {
+  for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const TileRef ref = tiles[t];
+    const BlockDesc& b = blocks[ref.block];
+    const int i0 = ref.ti * kTile, j0 = ref.tj * kTile;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int j = j0 + tx;
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r) {
+      const int i = i0 + ty + r * 8;
+      if (i >= b.m || j >= b.n) continue;
+      const long long e = static_cast<long long>(i) * b.n + j;
+      const long long pe = static_cast<long long>(i) * b.param_pitch + j;
+      float d;
+      if (dtype == 1) {
+        d = load_recv<__nv_bfloat16>(b.send, e);
+      } else if (dtype == 2) {
+        d = load_recv<__half>(b.send, e);
+      } else {
+        d = load_recv<float>(b.send, e);
+      }
+      b.param[pe] += d;
+    }
+  }
+}
+
+__global__ void peer_barrier_kernel(int* local_flags, const unsigned long long* peer_flag_bases, int my_rank,
+                                    int world, int seq, int* status) {
+  // Everything this rank wrote before the barrier (earlier kernels of the stream) must be
+  // visible to the peers that observe the flag.
+  __threadfence_system();
+  const int r = threadIdx.x;
+  if (r < world) {
+    int* remote = reinterpret_cast<int*>(peer_flag_bases[r]) + my_rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
+    const unsigned long long t0 = globaltimer_ns();
+    int seen;
+    do {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(local_flags + r) : "memory");
+      if (seen >= seq) break;
+      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+        atomicOr(status, kErrPeerTimeout);
+        break;
+      }
+      __nanosleep(100);
+    } while (true);
+  }
+  __threadfence_system();
 }
 
 int grid_for(int num_tiles) {
@@ -222,6 +312,17 @@ void launch_grad_prologue(const PrologueArgs& args, cudaStream_t stream) {
 void launch_direction_epilogue(const EpilogueArgs& args, cudaStream_t stream) {
   if (args.num_tiles <= 0) return;
   direction_epilogue_kernel<<<grid_for(args.num_tiles), 256, 0, stream>>>(args);
+}
+
+void launch_peer_barrier(int* local_flags, const unsigned long long* peer_flag_bases, int my_rank, int world,
+                         int seq, int* status, cudaStream_t stream) {
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(local_flags, peer_flag_bases, my_rank, world, seq, status);
+}
+
+void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype,
+                           cudaStream_t stream) {
+  if (num_tiles <= 0) return;
+  gathered_apply_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, dtype);
 }
 
 }  // namespace ob200

@@ -43,6 +43,7 @@ struct BlockDesc {
   float* p;               // search direction [m, n] (output of the preconditioner GEMMs)
   float* norms;           // [2]: squared norm of the grafting direction, of the Shampoo direction
   void* send;             // all-gather send slot in the communication dtype (null: update params)
+  long long slot_offset;  // byte offset of the block's slot inside the gather buffer (peer push)
 };
 
 struct TileRef {
@@ -58,7 +59,11 @@ struct PrologueArgs {
   const BlockDesc* blocks;
   const TileRef* tiles;
   int num_tiles;
-  const float* const* grad_ptrs;  // per gradient slot: base pointer of the parameter's gradient
+  const float* const* grad_ptrs;  // [slot * max(num_grad_peers, 1) + r]: gradient base pointers
+  int num_grad_peers;             // 0: local gradient; G > 0: the gradient is the scaled sum of G
+                                  // ranks' gradients, loaded from peer memory over NVLink in rank
+                                  // order (reduce-scatter fused into the owner's prologue)
+  float grad_scale;               // 1 / G for a mean
   float l2_weight_decay;          // 0 unless WeightDecayType.L2
   float beta1, beta3;
   float bias_correction1;         // 1 - beta3 * beta1^(t-1), or 1
@@ -85,9 +90,26 @@ struct EpilogueArgs {
   int nesterov;
   int send_dtype;                 // 0 fp32, 1 bf16, 2 fp16 (only with BlockDesc::send)
   int split_input;                // f given as (hi, lo) pair (1) or raw in f_hi (0)
+  int num_push_peers;             // G > 0: store the direction into the gather buffer of all G ranks
+                                  // (all-gather fused into the epilogue); 0: BlockDesc::send or params
+  unsigned long long peer_base[8];  // gather-buffer base address on each rank (this rank included)
 };
+
+constexpr int kErrPeerTimeout = 4;  // a bounded wait on a peer's flag expired
+
+// Cross-rank barrier over peer memory: writes `seq` into slot `my_rank` of every peer's flag
+// array, then waits (bounded) until every slot of the local flag array has reached `seq`.
+void launch_peer_barrier(int* local_flags, const unsigned long long* peer_flag_bases, int my_rank, int world,
+                         int seq, int* status, cudaStream_t stream);
 
 void launch_grad_prologue(const PrologueArgs& args, cudaStream_t stream);
 void launch_direction_epilogue(const EpilogueArgs& args, cudaStream_t stream);
+
+// gathered_apply: after the all-gather every rank adds each block's direction, read from its
+// slot of the receive buffer in the communication dtype (BlockDesc::send points at the slot),
+// to the parameter block.  One grouped launch replaces the reference's _foreach_add_ over views
+// of the gather buffer (distributed_shampoo/distributor/shampoo_ddp_distributor.py:330-360).
+void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype,
+                           cudaStream_t stream);
 
 }  // namespace ob200

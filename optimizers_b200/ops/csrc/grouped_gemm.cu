@@ -181,27 +181,45 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
           const int col = col0 + lane;
           if (col < N) {
             const int rows = min(32, M - row0);
-            for (int rr = 0; rr < rows; ++rr) {
+            const bool packed = (flags & kFlagPackedC) != 0;
+            const bool write_c = packed || !(flags & kFlagNoC);
+            // All loads of the old values first, then the stores: the loads are independent
+            // and overlap instead of each waiting behind the previous store.  Offsets advance
+            // incrementally: one row down is +ldc, or +(N - row - 1) in the packed triangle.
+            const long long off0 =
+                packed ? static_cast<long long>(row0) * N - (static_cast<long long>(row0) * (row0 - 1)) / 2 + (col - row0)
+                       : static_cast<long long>(row0) * ldc + col;
+            float old[32];
+            if (write_c && beta != 0.f) {
+              long long o = off0;
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) {
+                const int row = row0 + rr;
+                const bool live = rr < rows && (!packed || col >= row);
+                old[rr] = live ? Cp[o] : 0.f;
+                o += packed ? (N - row - 1) : ldc;
+              }
+            } else {
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) old[rr] = 0.f;
+            }
+            long long o = off0;
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr) {
               const int row = row0 + rr;
-              float val = alpha * st[rr * kStagePitch + lane];
-              if (flags & kFlagPackedC) {
-                if (col < row) continue;
-                const long long off =
-                    static_cast<long long>(row) * N - (static_cast<long long>(row) * (row - 1)) / 2 + (col - row);
-                if (beta != 0.f) val += beta * Cp[off];
-                Cp[off] = val;
-              } else if (!(flags & kFlagNoC)) {
-                const long long off = static_cast<long long>(row) * ldc + col;
-                if (beta != 0.f) val += beta * Cp[off];
-                Cp[off] = val;
+              const bool live = rr < rows && (!packed || col >= row);
+              if (live) {
+                const float val = alpha * st[rr * kStagePitch + lane] + beta * old[rr];
+                if (write_c) Cp[o] = val;
+                if (flags & kFlagSplitOut) {
+                  const long long od = static_cast<long long>(row) * ldd + col;
+                  const float hi = tf32_round(val);
+                  Dhi[od] = hi;
+                  Dlo[od] = val - hi;
+                }
+                sq += val * val;
               }
-              if (flags & kFlagSplitOut) {
-                const long long off = static_cast<long long>(row) * ldd + col;
-                const float hi = tf32_round(val);
-                Dhi[off] = hi;
-                Dlo[off] = val - hi;
-              }
-              sq += val * val;
+              o += packed ? (N - row - 1) : ldc;
             }
           }
           __syncwarp();

@@ -1,0 +1,71 @@
+"""Worker for the multi-GPU tests: trains a small MLP with the native DDP engine and writes the
+final parameters of rank 0.  Launched by test_gpu_multi.py through torch.distributed.run."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main() -> None:
+    mode, out = sys.argv[1], sys.argv[2]
+    from optimizers_b200 import (
+        AdamPreconditionerConfig,
+        DDPDistributedConfig,
+        DistributedShampoo,
+        NativeRuntimeConfig,
+    )
+
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(
+        torch.nn.Linear(96, 200), torch.nn.ReLU(), torch.nn.Linear(200, 72), torch.nn.ReLU(), torch.nn.Linear(72, 10)
+    ).to(dev)
+    fused = mode == "p2p_pull"
+    train_model = model if fused else torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index])
+    native = NativeRuntimeConfig(
+        backend="torch" if mode == "torch" else "native",
+        comm_path="p2p" if mode.startswith("p2p") else "nccl",
+        fuse_gradient_reduction=fused,
+    )
+    opt = DistributedShampoo(
+        model.parameters(), lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64,
+        precondition_frequency=3, start_preconditioning_step=3, weight_decay=1e-2,
+        grafting_config=AdamPreconditionerConfig(),
+        distributed_config=DDPDistributedConfig(communication_dtype=torch.float32, num_trainers_per_group=world),
+        native_runtime_config=native,
+    )
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for _ in range(8):
+        x = torch.randn(64, 96, device=dev, generator=g)
+        y = torch.randint(0, 10, (64,), device=dev, generator=g)
+        shard = slice(rank * 64 // world, (rank + 1) * 64 // world)
+        opt.zero_grad(set_to_none=not fused)
+        torch.nn.functional.cross_entropy(train_model(x[shard]), y[shard]).backward()
+        opt.step()
+    for rec in opt._per_group_state_lists:
+        if rec.get("native_engine") is not None:
+            rec["native_engine"].check_status()
+        else:
+            assert mode == "torch"
+    torch.cuda.synchronize()
+    params = [p.detach().cpu() for p in model.parameters()]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, params)
+    if rank == 0:
+        for other in gathered[1:]:
+            for a, b in zip(gathered[0], other):
+                assert torch.equal(a, b), "ranks diverged"
+        torch.save(params, out)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -84,7 +84,7 @@ def test_grouped_syrk_packed_ema(ext, split, d, K):
     assert status.item() == 0
     ref = _packed((0.9 * F0.double() + 0.25 * (X.double() @ X.double().T)).float())
     # tensor-core fp32 accumulation truncates, so the error grows with the magnitude of the sums
-    tol = (2e-5 if split else 4e-3) * math.sqrt(K) + 3e-5 * ref.abs().max().item()
+    tol = (2e-5 if split else 4e-3) * math.sqrt(K) + (3e-5 if split else 2e-3) * ref.abs().max().item()
     assert (Fp - ref).abs().max().item() < tol
 
 
@@ -154,7 +154,7 @@ def _configs():
         WeightDecayType,
     )
 
-    base = dict(lr=1e-2, betas=(0.9, 0.999), epsilon=1e-8, max_preconditioner_dim=64, precondition_frequency=3, start_preconditioning_step=3)
+    base = dict(lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64, precondition_frequency=3, start_preconditioning_step=3)
     return {
         "adam_graft": dict(base, grafting_config=AdamPreconditionerConfig(beta2=0.999, epsilon=1e-8)),
         "adagrad_graft_wd": dict(base, grafting_config=AdaGradPreconditionerConfig(), weight_decay=1e-2),
