@@ -467,10 +467,7 @@ class NativeGroupEngine:
         launches += 1
 
         if refresh:
-            for b in self._active_blocks:
-                b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
-            self.refresh_inverse_mirrors(self._active_blocks)
-            self.check_status()
+            self._refresh(self._active_blocks)
 
         if not graft_only:
             if self._gemm1_plan is not None:
@@ -499,6 +496,21 @@ class NativeGroupEngine:
         launches += 1
         self.launches_per_step = launches
         self._finish_update()
+
+    def _refresh(self, blocks: list[_Block]) -> None:
+        """Amortised computation for the given blocks: batched native path for the eigen root
+        inverse, the per-factor torch path for every other matrix-function config."""
+        from optimizers_b200.matrix import batched
+
+        plist = self._plist
+        cfg = self._group[PRECONDITIONER_CONFIG].amortized_computation_config
+        if batched.eigen_refresh_supported(cfg):
+            batched.batched_eigen_refresh(self._ext, blocks, plist._bias_correction2, self._split, self._status)
+        else:
+            for b in blocks:
+                b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
+        self.refresh_inverse_mirrors(blocks)
+        self.check_status()
 
     def _finish_update(self) -> None:
         """Deliver the search directions.  Single device: the epilogue already updated the
