@@ -76,16 +76,10 @@ class DDPDistributor(DistributorInterface):
         super().__init__(param_group, runtime_config)
         cfg: DDPDistributedConfig = param_group[DISTRIBUTED_CONFIG]
         self._global_masked_blocked_params: tuple[Tensor, ...] = self._global_blocked_params
-        self._global_size: int = dist.get_world_size(group=dist_group)
-        if cfg.num_trainers_per_group == -1:
-            logger.info(
-                f"Note that distributed_config.num_trainers_per_group={cfg.num_trainers_per_group}! Defaulting to world size {self._global_size}."
-            )
-        self._group_size: int = cfg.num_trainers_per_group if cfg.num_trainers_per_group != -1 else self._global_size
         self._communicate_params: bool = cfg.communicate_params
         self._communication_dtype: torch.dtype = cfg.communication_dtype
-        # Collective: every rank creates every sub-group and keeps its own.
-        self._dist_group: dist.ProcessGroup = dist.new_subgroups(group_size=self._group_size, group=dist_group)[0]
+        self._block_id_rank: int | None = None
+        self._resolve_group(cfg, dist_group)
         self._group_rank: int = dist.get_rank(group=self._dist_group)
 
         # Ownership is decided on meta tensors in the communication dtype: no memory, exact sizes.
@@ -100,6 +94,21 @@ class DDPDistributor(DistributorInterface):
         self._local_grad_selector = (True,) * len(self._local_blocked_params)
         self._construct_distributed_buffers(self._buffer_size_ranks, cfg.communication_dtype, self._group_rank)
 
+    def _resolve_group(self, cfg: DDPDistributedConfig, dist_group: dist.ProcessGroup | None) -> None:
+        """Decide which ranks share the work of this parameter group.  Sets ``_dist_group`` (the
+        all-gather group), ``_group_size``, ``_global_size`` and ``_owner_mesh_rows`` (the
+        replicate x shard arrangement used to place state DTensors on their owners)."""
+        self._global_size: int = dist.get_world_size(group=dist_group)
+        if cfg.num_trainers_per_group == -1:
+            logger.info(
+                f"Note that distributed_config.num_trainers_per_group={cfg.num_trainers_per_group}! Defaulting to world size {self._global_size}."
+            )
+        self._group_size: int = cfg.num_trainers_per_group if cfg.num_trainers_per_group != -1 else self._global_size
+        # Collective: every rank creates every sub-group and keeps its own.
+        self._dist_group: dist.ProcessGroup = dist.new_subgroups(group_size=self._group_size, group=dist_group)[0]
+        ranks = dist.get_process_group_ranks(group=self._dist_group)
+        self._owner_mesh_rows: tuple[tuple[int, ...], ...] = tuple(batched(ranks, self._group_size))
+
     # -- parameters may be DTensors (composable replicate()) ------------------------------------
     @torch.no_grad()
     def _get_params_or_grads(self, get_grad: bool = False) -> Iterable[Tensor | None]:
@@ -113,10 +122,7 @@ class DDPDistributor(DistributorInterface):
     def _allocate_zeros_distributed_tensor(
         self, size: tuple[int, ...], dtype: torch.dtype, device: torch.device, group_source_rank: int
     ) -> Tensor:
-        ranks = dist.get_process_group_ranks(group=self._dist_group)
-        return allocate_zeros_on_owner(
-            size, dtype, device, tuple(batched(ranks, self._group_size)), group_source_rank
-        )
+        return allocate_zeros_on_owner(size, dtype, device, self._owner_mesh_rows, group_source_rank)
 
     @torch.no_grad()
     def _construct_local_block_info_list(
@@ -134,7 +140,9 @@ class DDPDistributor(DistributorInterface):
                 infos.append(
                     DTensorBlockInfo(
                         param=p,
-                        composable_block_ids=self._construct_composable_block_ids(param_index, block_index),
+                        composable_block_ids=self._construct_composable_block_ids(
+                            param_index, block_index, self._block_id_rank
+                        ),
                         allocate_zeros_tensor=partial(
                             self._allocate_zeros_distributed_tensor, group_source_rank=owner
                         ),
