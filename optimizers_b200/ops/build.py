@@ -21,7 +21,7 @@ _NAME = "optimizers_b200_C"
 _SO = _HERE / f"{_NAME}.so"
 _module: ModuleType | None = None
 
-SOURCES = ["bindings.cu", "grouped_gemm.cu", "block_kernels.cu", "flat_kernels.cu"]
+SOURCES = ["bindings.cu", "grouped_gemm.cu", "block_kernels.cu", "flat_kernels.cu", "two_sided_apply.cu"]
 NVCC_FLAGS = [
     "-gencode",
     "arch=compute_100a,code=sm_100a",
@@ -36,7 +36,7 @@ def _stale() -> bool:
     if not _SO.exists():
         return True
     built = _SO.stat().st_mtime
-    return any(p.stat().st_mtime > built for p in _CSRC.iterdir() if p.suffix in (".cu", ".cuh"))
+    return any(p.stat().st_mtime > built for p in _CSRC.iterdir() if p.suffix in (".cu", ".cuh", ".h"))
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:

@@ -16,6 +16,7 @@
 #include "block_kernels.cuh"
 #include "flat_kernels.cuh"
 #include "grouped_gemm.cuh"
+#include "two_sided_apply.h"
 
 namespace py = pybind11;
 using namespace ob200;
@@ -287,6 +288,22 @@ void peer_barrier(torch::Tensor local_flags, const torch::Tensor& peer_flag_base
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// Exact-fp32 P = L G R for one block; the m x n intermediate comes from torch's allocator.
+torch::Tensor two_sided_apply(const torch::Tensor& L, const torch::Tensor& G, const torch::Tensor& R) {
+  TORCH_CHECK(L.is_cuda() && G.is_cuda() && R.is_cuda(), "operands must be CUDA tensors");
+  TORCH_CHECK(L.scalar_type() == torch::kFloat32 && G.scalar_type() == torch::kFloat32 && R.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(L.is_contiguous() && G.is_contiguous() && R.is_contiguous() && G.dim() == 2);
+  const int m = static_cast<int>(G.size(0)), n = static_cast<int>(G.size(1));
+  TORCH_CHECK(L.size(0) == m && L.size(1) == m && R.size(0) == n && R.size(1) == n, "shape mismatch");
+  c10::cuda::CUDAGuard guard(G.device());
+  auto scratch = torch::empty_like(G);
+  auto P = torch::empty_like(G);
+  launch_two_sided_apply(L.data_ptr<float>(), G.data_ptr<float>(), R.data_ptr<float>(), P.data_ptr<float>(),
+                         scratch.data_ptr<float>(), m, n, at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return P;
+}
+
 void tf32_split(const torch::Tensor& src, torch::Tensor hi, torch::Tensor lo) {
   TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1);
   TORCH_CHECK(hi.dim() == 2 && lo.dim() == 2 && hi.stride(1) == 1 && lo.stride(1) == 1);
@@ -363,6 +380,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("direction_epilogue", &direction_epilogue);
   m.def("gathered_apply", &gathered_apply);
   m.def("peer_barrier", &peer_barrier);
+  m.def("two_sided_apply", &two_sided_apply);
   m.def("tf32_split", &tf32_split);
   m.def("build_gpa_table", &build_gpa_table);
   m.def("gpa_adamw_step", &gpa_adamw_step);
