@@ -83,18 +83,21 @@ def allocate_zeros_on_owner(
 
 def create_hybrid_shard_process_groups(device_mesh: DeviceMesh, dist_group_size: int) -> dist.ProcessGroup:
     """Communication group of the hybrid-shard distributors: the replicate dim of ``device_mesh``
-    (all ranks holding the same shard) cut into consecutive groups of ``dist_group_size``.  Every
-    rank builds every group's mesh (process-group creation is collective) and keeps its own."""
-    names = device_mesh.mesh_dim_names
-    assert names is not None, "DeviceMesh must have mesh_dim_names"
+    (all ranks holding the same shard) cut into consecutive groups of ``dist_group_size``.
+
+    Process-group creation is collective, so every rank builds the (replicate x shard) mesh of
+    every shard position, in the same order, and keeps the group of its own.  The meshes are
+    cached under exactly the arguments ``allocate_zeros_on_owner`` uses later, which therefore
+    never creates a group on a subset of ranks."""
+    assert device_mesh.mesh_dim_names is not None, "DeviceMesh must have mesh_dim_names"
     mine: dist.ProcessGroup | None = None
     for same_shard_ranks in device_mesh.mesh.T:
         sub = get_device_mesh(
             device_type=device_mesh.device_type,
             mesh=tuple(map(tuple, same_shard_ranks.view(-1, dist_group_size).tolist())),
-            mesh_dim_names=names,
+            mesh_dim_names=("replicate", "shard"),
         )
         if dist.get_rank() in same_shard_ranks:
-            mine = sub.get_group(names[1])
+            mine = sub.get_group("shard")
     assert mine is not None
     return mine
