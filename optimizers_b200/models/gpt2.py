@@ -72,4 +72,4 @@ class GPT2(nn.Module):
         logits = F.linear(self.ln_f(x), self.wte.weight)
         if targets is None:
             return logits
-        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.view(-1))
+        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))

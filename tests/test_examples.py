@@ -1,0 +1,51 @@
+"""Smoke tests of the example entry points on CPU."""
+
+import pytest
+import torch
+
+from optimizers_b200.examples import gpa_example, train
+from optimizers_b200.examples.loss_metrics import LossMetrics
+from optimizers_b200.examples.parallelism import STRATEGIES, SingleGPUStrategy
+from optimizers_b200.examples.resolvers import resolve_fsdp_param_strategy, resolve_torch_dtype, resolve_weight_decay_type
+
+
+@pytest.mark.parametrize(
+    "argv",
+    [
+        ["--model", "convnet", "--optimizer", "shampoo"],
+        ["--model", "mlp", "--optimizer", "muon"],
+        ["--model", "gpt2", "--small", "--optimizer", "soap", "--seq-len", "16"],
+        ["--model", "llama", "--small", "--optimizer", "gpa_adamw", "--seq-len", "16"],
+        ["--model", "convnet", "--optimizer", "adamw"],
+    ],
+)
+def test_train_cli_runs(argv):
+    loss = train.main(argv + ["--steps", "2", "--batch-size", "4", "--device", "cpu"])
+    assert loss == loss and loss > 0
+
+
+def test_gpa_example_improves_eval_loss():
+    first, last = gpa_example.main(["--steps", "20", "--device", "cpu", "--eval-interp-coeff", "0.9"])
+    assert last < first
+
+
+def test_loss_metrics_window_and_lifetime():
+    m = LossMetrics(window_size=2)
+    for v in (1.0, 2.0, 6.0):
+        m.update(torch.tensor(v))
+    assert float(m.window_loss) == pytest.approx(4.0) and float(m.lifetime_loss) == pytest.approx(3.0)
+    m.log(); m.update_global_metrics(); m.log_global_metrics(); m.flush()
+
+
+def test_resolvers_and_strategies():
+    assert resolve_torch_dtype("bfloat16") is torch.bfloat16 and resolve_torch_dtype("torch.float32") is torch.float32
+    assert resolve_fsdp_param_strategy("round_robin").name == "ROUND_ROBIN"
+    assert resolve_weight_decay_type("l2").name == "L2"
+    for bad in (resolve_torch_dtype, resolve_fsdp_param_strategy, resolve_weight_decay_type):
+        with pytest.raises(ValueError):
+            bad("nope")
+    assert set(STRATEGIES) == {"none", "ddp", "ddp_fused", "fsdp", "hsdp", "fully_shard", "hybrid_shard"}
+    model = torch.nn.Linear(2, 2)
+    wrapped = SingleGPUStrategy().wrap_model(model, 0, "gloo")
+    assert wrapped.model is model and wrapped.distributed_config is None
+    assert STRATEGIES["hsdp"]().requires_device_mesh and STRATEGIES["ddp"]().requires_distributed
