@@ -21,7 +21,7 @@ def main(argv=None) -> tuple[float, float]:
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--batch-size", type=int, default=64)
-    ap.add_argument("--lr", type=float, default=1e-3)
+    ap.add_argument("--lr", type=float, default=1e-4)
     ap.add_argument("--weight-decay", type=float, default=0.0)
     ap.add_argument("--train-interp-coeff", type=float, default=0.7)
     ap.add_argument("--eval-interp-coeff", type=float, default=0.9967)

@@ -25,7 +25,7 @@ def test_train_cli_runs(argv):
 
 
 def test_gpa_example_improves_eval_loss():
-    first, last = gpa_example.main(["--steps", "20", "--device", "cpu", "--eval-interp-coeff", "0.9"])
+    first, last = gpa_example.main(["--steps", "40", "--device", "cpu", "--eval-interp-coeff", "0.9"])
     assert last < first
 
 
