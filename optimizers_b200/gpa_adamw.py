@@ -196,6 +196,22 @@ class GPAAdamW(Optimizer):
                 continue
             mu_y = group[TRAIN_INTERP_COEFF]
             weight = (1 - mu_y) if to_train else (1 - 1 / mu_y)
+            with_z = [p for p in group[PARAMS] if p in self.state and Z_BUFFER in self.state[p]]
+            zs = [self.state[p][Z_BUFFER] for p in with_z]
+            if with_z and self._use_native is not False and all(
+                p.is_cuda and p.is_contiguous() and z.dtype == torch.float32 and z.is_contiguous() and type(p.data) is torch.Tensor
+                and p.dtype in (torch.float32, torch.bfloat16, torch.float16)
+                for p, z in zip(with_z, zs)
+            ) and torch.cuda.get_device_capability(with_z[0].device)[0] == 10:
+                # One grouped launch: p <- lerp(p, z, weight) for every parameter of the group.
+                from optimizers_b200.ops import build
+
+                ext = build.load()
+                table, chunks, n_chunks = ext.build_gpa_table([(p, None, z, z, z) for p, z in zip(with_z, zs)])
+                ext.gpa_lerp(table, n_chunks, chunks, weight)
+                self.native_launches += 1
+                mode.fill_(to_train)
+                continue
             for p in group[PARAMS]:
                 state = self.state.get(p) if p in self.state else None
                 if state and Z_BUFFER in state:

@@ -195,3 +195,247 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
             last_error.setdefault(id(it.block), None)
     for b in blocks:
         b.factors.note_refresh_outcome(last_error.get(id(b)))
+
+
+# ----------------------------------------------------------------------------------------------
+# Coupled Newton inverse root, all factors at once, on the grouped tensor-core GEMM
+# ----------------------------------------------------------------------------------------------
+def newton_refresh_supported(cfg: Any) -> bool:
+    from optimizers_b200.config import CoupledNewtonConfig
+
+    return isinstance(cfg, CoupledNewtonConfig)
+
+
+class _NewtonItem:
+    """Iteration buffers of one factor.  Every matrix is kept as a (hi, lo) tf32 pair in padded
+    storage so that it can be an operand of the next grouped GEMM; ``X`` and ``M`` ping-pong."""
+
+    __slots__ = ("block", "k", "d", "root", "A", "X", "M", "Mp", "pw", "err", "converged", "last_err", "iters")
+
+
+def _pair(d: int, device: torch.device, split: bool) -> tuple[Tensor, Tensor | None]:
+    ld = _pad4(d)
+    hi = torch.zeros(d, ld, device=device)
+    return hi, (torch.zeros(d, ld, device=device) if split else None)
+
+
+def _v(p: tuple[Tensor, Tensor | None], d: int) -> tuple[Tensor, Tensor | None]:
+    return p[0][:, :d], (p[1][:, :d] if p[1] is not None else None)
+
+
+def _power_chain(p: int) -> list[tuple[int, int, int]]:
+    """Multiplication schedule for M_p^p as ``(result exponent, left exponent, right exponent)``
+    triples: repeated squaring, then products of the squares that make up ``p``."""
+    steps: list[tuple[int, int, int]] = []
+    e = 1
+    squares = [1]
+    while e * 2 <= p:
+        steps.append((e * 2, e, e))
+        e *= 2
+        squares.append(e)
+    acc = None
+    for s in reversed(squares):
+        if p & s:
+            if acc is None:
+                acc = s
+            else:
+                steps.append((acc + s, acc, s))
+                acc += s
+    return steps
+
+
+def batched_newton_refresh(
+    ext: Any, blocks: list[Any], bias_correction2: Tensor | float, split: bool, status: Tensor, check_every: int = 4
+) -> None:
+    """Coupled Newton iteration for ``(F/bc2 + eps I)^(-1/p)`` of every factor of ``blocks``.
+
+    Per iteration and factor: ``M_p = (1-a) I + a M`` (a = -1/p; grouped pointwise kernel that also
+    splits the operand), ``X <- X M_p``, ``M <- M_p^p M`` (grouped tcgen05 GEMMs whose epilogues
+    write the split result).  All matrices are polynomials in the same symmetric matrix, hence
+    symmetric and commuting, which is what lets the K-major "TN" kernel compute plain products.
+    ``max|M - I|`` is reduced on the device; the host reads the error vector every
+    ``check_every`` iterations and drops converged factors from the launch tables.  A factor stops
+    when its error is below the configured tolerance, when the iteration limit is reached
+    (warning, as in the reference), or when the error stalls above the tolerance at the
+    rounding floor of the tensor-core accumulation (error below 1e-3 and not improved by 10 %
+    between two checks)."""
+    if not blocks:
+        return
+    device = blocks[0].inv_hi[0].device
+    cfg = blocks[0].factors.amortized_computation_config
+    max_iterations, tolerance = cfg.max_iterations, cfg.tolerance
+
+    items: list[_NewtonItem] = []
+    for b in blocks:
+        kf = b.factors
+        for k, factor in enumerate(kf.factor_matrices):
+            root = Fraction(kf.roots[k])
+            if root.denominator != 1:
+                raise ValueError(f"root.denominator={root.denominator} must be equal to 1 to use coupled inverse Newton iteration!")
+            A = kf.unpack(factor / bias_correction2)
+            if kf.use_trace_scaling:
+                A = A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent)
+            it = _NewtonItem()
+            it.block, it.k, it.d, it.root, it.A = b, k, A.shape[0], root.numerator, A
+            it.converged, it.last_err, it.iters = False, float("inf"), 0
+            items.append(it)
+    finite = torch.stack([torch.isfinite(it.A).all() for it in items]).cpu().tolist()
+    for it, ok in zip(items, finite):
+        if not ok:
+            index = it.block.factors.factor_matrix_indices[it.k]
+            raise PreconditionerValueError(f"Encountered nan/inf values in factor matrix {index}!")
+
+    # Initial iterates: z = (p+1) / (2 ||A||_F), X = z^(1/p) I, M = z A  (no host synchronisation).
+    errs = torch.zeros(len(items), device=device)
+    for n, it in enumerate(items):
+        d, p = it.d, it.root
+        eps = it.block.factors.epsilon
+        A_r = it.A.clone()
+        A_r.diagonal().add_(eps)
+        z = (p + 1) / (2 * torch.linalg.norm(A_r))
+        it.X = [_pair(d, device, split), _pair(d, device, split)]
+        it.M = [_pair(d, device, split), _pair(d, device, split)]
+        it.Mp = _pair(d, device, split)
+        it.pw = {}
+        x0 = torch.zeros(d, d, device=device)
+        x0.diagonal().fill_(1.0)
+        x0 *= z ** (1.0 / p)
+        m0 = A_r * z
+        for src, dst in ((x0, it.X[0]), (m0, it.M[0])):
+            hi, lo = _v(dst, d)
+            if split:
+                ext.tf32_split(src, hi, lo)
+            else:
+                hi.copy_(src)
+        it.err = errs[n : n + 1]
+    return _newton_iterate(ext, items, errs, split, status, max_iterations, tolerance, check_every, blocks)
+
+
+_NEWTON_CHUNK_ELEMS = 64 * 1024 * 1024  # sum of d^2 iterated together (16 arrays of that size are live)
+
+
+def _newton_iterate(ext, items, errs, split, status, max_iterations, tolerance, check_every, blocks) -> None:
+    failures: dict[int, Exception] = {}
+    by_root: dict[int, list[_NewtonItem]] = {}
+    for it in items:
+        by_root.setdefault(it.root, []).append(it)
+    for p, group in by_root.items():
+        chunk: list[_NewtonItem] = []
+        size = 0
+        for it in sorted(group, key=lambda x: -x.d):
+            if chunk and size + it.d * it.d > _NEWTON_CHUNK_ELEMS:
+                _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures)
+                chunk, size = [], 0
+            chunk.append(it)
+            size += it.d * it.d
+        if chunk:
+            _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures)
+
+    # results -> packed checkpoint state; one finiteness read
+    good = [it for it in items if id(it) not in failures]
+    flags = []
+    for it in good:
+        kf = it.block.factors
+        hi, lo = _v(it.X, it.d)
+        full = hi + lo if lo is not None else hi
+        state = kf.inv_factor_matrices[it.k]
+        state.copy_(kf.pack(full).to(dtype=state.dtype))
+        flags.append(torch.isfinite(state).all())
+    if flags:
+        for it, ok in zip(good, torch.stack(flags).cpu().tolist()):
+            if not ok:
+                index = it.block.factors.factor_matrix_indices[it.k]
+                raise PreconditionerValueError(f"Encountered nan or inf values in matrices of factor matrix {index}!")
+    last_error: dict[int, Exception | None] = {}
+    for it in items:
+        err = failures.get(id(it))
+        if err is not None:
+            logger.warning(
+                f"Matrix computation failed for factor matrix {it.block.factors.factor_matrix_indices[it.k]} with exception={err!r}. Using previous preconditioner and continuing..."
+            )
+            last_error[id(it.block)] = err
+        else:
+            last_error.setdefault(id(it.block), None)
+    for b in blocks:
+        b.factors.note_refresh_outcome(last_error.get(id(b)))
+
+
+def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures) -> None:
+    device = errs.device
+    alpha = -1.0 / p
+    chain = _power_chain(p)
+    for it in chunk:
+        d = it.d
+        it.pw = {e: _pair(d, device, split) for e, _, _ in chain}
+        # full-precision copies of M (source of the affine step and of the error measure)
+        it.A = [torch.zeros(d, _pad4(d), device=device), torch.zeros(d, _pad4(d), device=device)]
+        hi, lo = _v(it.M[0], d)
+        it.A[0][:, :d].copy_(hi + lo if lo is not None else hi)
+
+    def gemm(a, b, out, d, c_full=None):
+        a_hi, a_lo = _v(a, d)
+        b_hi, b_lo = _v(b, d)
+        if split:
+            flags = ext.FLAG_SPLIT_OUT | (0 if c_full is not None else ext.FLAG_NO_C)
+            return (a_hi, a_lo, b_hi, b_lo, c_full, out[0], out[1], None, out[0].stride(0), out[0].stride(0), flags, False)
+        # single-pass mode: the plain result is the operand of the next product
+        return (a_hi, None, b_hi, None, out[0], None, None, None, out[0].stride(0), 0, 0, False)
+
+    def build(active, cur):
+        nxt = cur ^ 1
+        full_m = lambda it, which: it.A[which][:, : it.d] if split else it.M[which][0][:, : it.d]  # noqa: E731
+        affine = ext.build_mat_table([(full_m(it, cur), *_v(it.Mp, it.d), None) for it in active])
+        stages = [[gemm(it.X[cur], it.Mp, it.X[nxt], it.d) for it in active]]
+        for n, (e, l, r) in enumerate(chain):
+            specs = [gemm(it.Mp if l == 1 else it.pw[l], it.Mp if r == 1 else it.pw[r], it.pw[e], it.d) for it in active]
+            if n == 0:
+                stages[0] = stages[0] + specs  # independent of X <- X M_p: same launch
+            else:
+                stages.append(specs)
+        last = []
+        for it in active:
+            top = it.Mp if p == 1 else it.pw[p]
+            c_full = it.A[nxt] if split else None
+            last.append(gemm(top, it.M[cur], it.M[nxt], it.d, c_full=c_full))
+        stages.append(last)
+        plans = [ext.build_gemm_plan(s) for s in stages]
+        err_src = [(full_m(it, nxt), None, None, it.err) for it in active]
+        return affine, plans, ext.build_mat_table(err_src)
+
+    active = list(chunk)
+    cur = 0
+    tables = {}
+    iteration = 0
+    while active:
+        if cur not in tables:
+            tables[cur] = build(active, cur)
+        affine, plans, err_table = tables[cur]
+        ext.affine_identity_split(*affine, alpha, 1.0 - alpha)
+        for plan in plans:
+            ext.run_gemm_plan(*plan, 1.0, 0.0, split, status)
+        iteration += 1
+        cur ^= 1
+        if iteration % check_every and iteration < max_iterations:
+            continue
+        errs.zero_()
+        ext.identity_error(*err_table)
+        values = torch.stack([it.err[0] for it in active]).cpu().tolist()  # the only host read of the loop
+        still = []
+        for it, e in zip(active, values):
+            it.iters = iteration
+            stalled = e < 1e-3 and e > 0.9 * it.last_err
+            if e != e or e == float("inf"):
+                failures[id(it)] = ArithmeticError("coupled Newton iteration produced NaN/Inf")
+            elif e <= tolerance or stalled or iteration >= max_iterations:
+                if e > tolerance and iteration >= max_iterations:
+                    logger.warning("Newton did not converge and reached maximum number of iterations!")
+            else:
+                it.last_err = e
+                still.append(it)
+                continue
+            it.X = it.X[cur]  # the iterate that was current when the factor stopped
+        if len(still) != len(active):
+            tables = {}
+        active = still
+    for it in chunk:  # release iteration buffers
+        it.M = it.Mp = it.pw = it.A = None

@@ -17,8 +17,12 @@ The checkpointed state tensors are exactly those the preconditioner lists alloca
 adds scratch operands and full (unpacked, split) mirrors of the inverse roots, which are rebuilt
 from the state after every refresh and after ``load_state_dict``.
 
+The eigenvalue-corrected variant (SOAP) replaces the two apply GEMMs by project -> scale ->
+unproject (``_soap_step``) and updates its second moment in the epilogue of the projection GEMM.
+
 Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 with every dim preconditioned,
-root-inverse Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting, any weight decay type,
+root-inverse or eigenvalue-corrected Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting,
+any weight decay type,
 classic momentum, GPA / Schedule-Free, single-device and DDP distributors (NCCL all-gather, or
 peer-to-peer stores and loads over NVLink with ``comm_path="p2p"``).  Anything else makes
 ``build_native_engine`` return ``None`` (torch step) or raise with ``backend="native"``.
@@ -40,6 +44,7 @@ from optimizers_b200.config import (
     DDPDistributedConfig,
     DISTRIBUTED_CONFIG,
     DISTRIBUTOR,
+    EigenvalueCorrectedShampooPreconditionerConfig,
     FILTERED_GRAD_LIST,
     GRAFTING_CONFIG,
     GRAFTING_PRECONDITIONER_LIST,
@@ -72,10 +77,18 @@ def _pad4(n: int) -> int:
 
 def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     pc = group[PRECONDITIONER_CONFIG]
-    if type(pc) is not RootInvShampooPreconditionerConfig:
+    if type(pc) is RootInvShampooPreconditionerConfig:
+        if pc.factor_matrix_dtype != torch.float32 or pc.inv_factor_matrix_dtype != torch.float32:
+            return "factor matrices must be fp32"
+    elif type(pc) is EigenvalueCorrectedShampooPreconditionerConfig:
+        dtypes = (pc.factor_matrix_dtype, pc.factor_matrix_eigenvectors_dtype, pc.corrected_eigenvalues_dtype)
+        if any(d != torch.float32 for d in dtypes):
+            return "factor matrices, eigenvectors and corrected eigenvalues must be fp32"
+        roots = {kf.roots[0] for kf in rec[SHAMPOO_PRECONDITIONER_LIST]._local_kronecker_factors_unwrapped}
+        if len(roots) > 1:
+            return "eigenvalue-corrected Shampoo with different roots per tensor order has no native step yet"
+    else:
         return f"preconditioner config {type(pc).__name__} has no native step yet"
-    if pc.factor_matrix_dtype != torch.float32 or pc.inv_factor_matrix_dtype != torch.float32:
-        return "factor matrices must be fp32"
     gc = group[GRAFTING_CONFIG]
     if gc is not None and not isinstance(gc, (SGDPreconditionerConfig, AdaGradPreconditionerConfig)):
         return f"grafting config {type(gc).__name__} has no native step"
@@ -123,7 +136,7 @@ class _Block:
     __slots__ = (
         "index", "param_view", "grad_slot", "grad_offset", "m", "n", "n_pad", "m_pad", "order", "factors",
         "m1", "v", "mom", "z", "g_hi", "g_lo", "gt_hi", "gt_lo", "f_hi", "f_lo", "tt_hi", "tt_lo", "p",
-        "inv_hi", "inv_lo",
+        "inv_hi", "inv_lo", "ev", "qt_hi", "qt_lo", "t2_hi", "t2_lo",
     )
 
 
@@ -142,6 +155,7 @@ class NativeGroupEngine:
         self._plist = rec[SHAMPOO_PRECONDITIONER_LIST]
         self._glist = rec[GRAFTING_PRECONDITIONER_LIST]
         self._packing = group[PRECONDITIONER_CONFIG].use_symmetric_packing
+        self._soap = type(group[PRECONDITIONER_CONFIG]) is EigenvalueCorrectedShampooPreconditionerConfig
         self.launches_per_step = 0
 
         gc = group[GRAFTING_CONFIG]
@@ -218,8 +232,9 @@ class NativeGroupEngine:
             b.mom = moms[i] if moms is not None else None
             b.z = zs[i] if zs is not None else None
             two_d = b.order == 2
-            b.g_hi = zeros(b.m, b.n_pad) if two_d else None
-            b.g_lo = zeros(b.m, b.n_pad) if two_d and self._split else None
+            need_g = two_d or self._soap
+            b.g_hi = zeros(b.m, b.n_pad) if need_g else None
+            b.g_lo = zeros(b.m, b.n_pad) if need_g and self._split else None
             b.gt_hi = zeros(b.n, b.m_pad)
             b.gt_lo = zeros(b.n, b.m_pad) if self._split else None
             b.f_hi = zeros(b.m, b.n_pad)
@@ -230,6 +245,14 @@ class NativeGroupEngine:
             dims = (b.m, b.n) if two_d else (b.n,)
             b.inv_hi = [zeros(d, _pad4(d)) for d in dims]
             b.inv_lo = [zeros(d, _pad4(d)) if self._split else None for d in dims]
+            b.ev = b.qt_hi = b.qt_lo = b.t2_hi = b.t2_lo = None
+            if self._soap:
+                # inv_hi/inv_lo hold the eigenvector matrices Q_k, qt_* their transposes.
+                b.ev = b.factors.corrected_eigenvalues
+                b.qt_hi = [zeros(d, _pad4(d)) for d in dims]
+                b.qt_lo = [zeros(d, _pad4(d)) if self._split else None for d in dims]
+                b.t2_hi = zeros(b.n, b.m_pad) if two_d else None
+                b.t2_lo = zeros(b.n, b.m_pad) if two_d and self._split else None
             blocks.append(b)
         self._blocks = blocks
 
@@ -300,10 +323,13 @@ class NativeGroupEngine:
                 (
                     b.param_view, b.grad_offset, b.grad_slot, b.m, b.n, b.n_pad, b.m_pad, b.m1, b.v, b.mom, b.z,
                     b.g_hi, b.g_lo, b.gt_hi, b.gt_lo, b.f_hi, b.f_lo, b.p, self._norms[b.index], self._send_ptr(b),
-                    self._slot_offset(b),
+                    self._slot_offset(b), b.ev,
                 )
             )
         self._table = ext.build_block_table(specs)
+        if self._soap:
+            self._build_soap_plans(blocks)
+            return
 
         def op(t: Tensor, rows: int, k: int) -> Tensor:
             return t[:, :k] if t.shape[1] != k else t
@@ -339,8 +365,75 @@ class NativeGroupEngine:
         self._gemm1_plan = ext.build_gemm_plan(gemm1) if gemm1 else None
         self._gemm2_plan = ext.build_gemm_plan(gemm2)
 
+    def _build_soap_plans(self, blocks: list[_Block]) -> None:
+        """GEMM plans of the eigenvalue-corrected step.  With Qt the transposed eigenvector
+        mirrors, a 2-D block is projected as T^T = Q_R^T X^T, X~ = Q_L^T T and unprojected as
+        U^T = Q_R S^T, P = Q_L U; a 1-D block (1 x n) uses the column side only.
+
+        ``_soap_plans``: ``a`` first projection stage of the raw and of the filtered gradient,
+        ``v`` second stage of the raw gradient with the squared-EMA epilogue into the corrected
+        eigenvalues, ``f`` second stage of the filtered gradient into ``p``, ``u1``/``u2`` the
+        unprojection of the scaled direction (``u2`` accumulates the norm)."""
+        ext, split = self._ext, self._split
+        F = ext
+
+        def pair(hi: Tensor, lo: Tensor | None, k: int) -> tuple[Tensor, Tensor | None]:
+            return hi[:, :k], (lo[:, :k] if lo is not None else None)
+
+        def chained(a, b, out_hi, out_lo):
+            """Product whose result is only an operand of the next product."""
+            if split:
+                return (*_ab(a, b), None, out_hi, out_lo, None, 0, out_hi.stride(0), F.FLAG_NO_C | F.FLAG_SPLIT_OUT, False)
+            return (*_ab(a, b), out_hi, None, None, None, out_hi.stride(0), 0, 0, False)
+
+        def _ab(a, b):
+            return (a[0], a[1], b[0], b[1])
+
+        syrk, st_a, st_v, st_f, st_u1, st_u2 = [], [], [], [], [], []
+        pack_flag = F.FLAG_PACKED_C if self._packing else 0
+        for b in blocks:
+            fm = b.factors.factor_matrices
+            two_d = b.order == 2
+            g = pair(b.g_hi, b.g_lo, b.n)
+            gt = pair(b.gt_hi, b.gt_lo, b.m)
+            f = pair(b.f_hi, b.f_lo, b.n)
+            sumsq = self._norms[b.index, 1:2]
+            if two_d:
+                syrk.append((*_ab(g, g), fm[0], None, None, None, b.m, 0, pack_flag, self._packing))
+            syrk.append((*_ab(gt, gt), fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
+            r = 1 if two_d else 0
+            qr, qrt = pair(b.inv_hi[r], b.inv_lo[r], b.n), pair(b.qt_hi[r], b.qt_lo[r], b.n)
+            if two_d:
+                ql, qlt = pair(b.inv_hi[0], b.inv_lo[0], b.m), pair(b.qt_hi[0], b.qt_lo[0], b.m)
+                t2, tt = pair(b.t2_hi, b.t2_lo, b.m), pair(b.tt_hi, b.tt_lo, b.m)
+                st_a.append(chained(qrt, g, b.t2_hi, b.t2_lo))
+                st_a.append(chained(qrt, f, b.tt_hi, b.tt_lo))
+                st_v.append((*_ab(qlt, t2), b.ev, None, None, None, b.n, 0, F.FLAG_SQUARE_ACC, False))
+                st_f.append((*_ab(qlt, tt), b.p, None, None, None, b.n, 0, 0, False))
+                st_u1.append(chained(qr, f, b.tt_hi, b.tt_lo))
+                st_u2.append((*_ab(ql, tt), b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
+            else:
+                st_v.append((*_ab(g, qrt), b.ev, None, None, None, b.n, 0, F.FLAG_SQUARE_ACC, False))
+                st_f.append((*_ab(f, qrt), b.p, None, None, None, b.n, 0, 0, False))
+                st_u2.append((*_ab(f, qr), b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
+        self._syrk_plan = ext.build_gemm_plan(syrk)
+        mk = lambda specs: ext.build_gemm_plan(specs) if specs else None  # noqa: E731
+        self._soap_plans = {"a": mk(st_a), "v": mk(st_v), "f": mk(st_f), "u1": mk(st_u1), "u2": mk(st_u2)}
+
     def refresh_inverse_mirrors(self, blocks: list[_Block] | None = None) -> None:
-        """Rebuild the full (hi, lo) operand copies of the inverse roots from the state tensors."""
+        """Rebuild the full (hi, lo) operand copies of the inverse roots (or, for the
+        eigenvalue-corrected variant, of the eigenvector matrices and their transposes) from the
+        state tensors."""
+        if self._soap:
+            for b in self._blocks if blocks is None else blocks:
+                for k, Q in enumerate(b.factors.factor_matrices_eigenvectors):
+                    d = Q.shape[0]
+                    for src, hi, lo in ((Q, b.inv_hi[k], b.inv_lo[k]), (Q.T.contiguous(), b.qt_hi[k], b.qt_lo[k])):
+                        if self._split:
+                            self._ext.tf32_split(src.contiguous(), hi[:, :d], lo[:, :d])
+                        else:
+                            hi[:, :d].copy_(src)
+            return
         for b in self._blocks if blocks is None else blocks:
             for k, inv in enumerate(b.factors.get_unpacked_inv_factor_matrices()):
                 d = inv.shape[0]
@@ -357,6 +450,22 @@ class NativeGroupEngine:
 
     def on_state_loaded(self) -> None:
         self.refresh_inverse_mirrors()
+
+    def mode_switch(self, coeff: float) -> bool:
+        """W <- W + coeff (Z - W) on every local block in one grouped launch (train()/eval() of the
+        primal-averaging schemes).  Returns False when the switch has to travel through the
+        distributor's collective instead (DDP)."""
+        if self._ddp:
+            return False
+        if getattr(self, "_full_table", None) is None:
+            specs = [
+                (b.param_view, 0, 0, b.m, b.n, b.n_pad, b.m_pad, None, None, None, b.z) + (None,) * 8 + (0, 0, None)
+                for b in self._blocks
+            ]
+            self._full_table = self._ext.build_block_table(specs) if specs else ()
+        if self._full_table:
+            self._ext.mode_switch(*self._full_table, coeff, 0)
+        return True
 
     def collect_gradients(self) -> tuple[int, ...]:
         """Native twin of ``merge_and_block_gradients``: records which parameters have a usable
@@ -469,7 +578,9 @@ class NativeGroupEngine:
         if refresh:
             self._refresh(self._active_blocks)
 
-        if not graft_only:
+        if self._soap:
+            launches += self._soap_step(plist, graft_only)
+        elif not graft_only:
             if self._gemm1_plan is not None:
                 ext.run_gemm_plan(*self._gemm1_plan, 1.0, 0.0, self._split, self._status)
                 launches += 1
@@ -497,6 +608,29 @@ class NativeGroupEngine:
         self.launches_per_step = launches
         self._finish_update()
 
+    def _soap_step(self, plist: Any, graft_only: bool) -> int:
+        """Second-moment update in the eigenbasis (every step) and, unless only the grafting
+        direction is needed, project -> scale -> unproject of the filtered gradient."""
+        ext, plans, split = self._ext, self._soap_plans, self._split
+        run = lambda key, alpha=1.0, beta=0.0: ext.run_gemm_plan(*plans[key], alpha, beta, split, self._status)  # noqa: E731
+        launches = 0
+        if plans["a"] is not None:
+            run("a")
+            launches += 1
+        run("v", plist._weighting_factor, plist._beta2)
+        launches += 1
+        if graft_only:
+            return launches
+        run("f")
+        blocks_t, tiles_t, n_tiles = self._table
+        root = self._active_blocks[0].factors.roots[0]
+        ext.eig_scale(blocks_t, tiles_t, n_tiles, float(plist._bias_correction2), 1.0 / root, plist._epsilon, split)
+        if plans["u1"] is not None:
+            run("u1")
+            launches += 1
+        run("u2")
+        return launches + 3
+
     def _refresh(self, blocks: list[_Block]) -> None:
         """Amortised computation for the given blocks: batched native path for the eigen root
         inverse, the per-factor torch path for every other matrix-function config."""
@@ -504,8 +638,13 @@ class NativeGroupEngine:
 
         plist = self._plist
         cfg = self._group[PRECONDITIONER_CONFIG].amortized_computation_config
-        if batched.eigen_refresh_supported(cfg):
+        if self._soap:
+            for b in blocks:
+                b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
+        elif batched.eigen_refresh_supported(cfg):
             batched.batched_eigen_refresh(self._ext, blocks, plist._bias_correction2, self._split, self._status)
+        elif batched.newton_refresh_supported(cfg):
+            batched.batched_newton_refresh(self._ext, blocks, plist._bias_correction2, self._split, self._status)
         else:
             for b in blocks:
                 b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
@@ -536,7 +675,7 @@ class NativeGroupEngine:
                 if not on:
                     continue
                 m, n = (1, view.shape[0]) if view.dim() == 1 else view.shape
-                specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 12 + (base + off, off))
+                specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 12 + (base + off, off, None))
             self._gather_table = self._ext.build_block_table(specs) if specs else None
             self._gather_for = sel
         if self._gather_table is not None:

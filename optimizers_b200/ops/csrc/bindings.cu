@@ -158,14 +158,14 @@ void run_gemm_plan(const torch::Tensor& problems, const torch::Tensor& tiles, in
 }
 
 // Block table.  Each spec: (param_view, grad_offset, grad_slot, m, n, n_pad, m_pad, m1, v, mom, z,
-//                           g_hi, g_lo, gt_hi, gt_lo, f_hi, f_lo, p, norms, send_ptr, slot_offset)
+//                           g_hi, g_lo, gt_hi, gt_lo, f_hi, f_lo, p, norms, send_ptr, slot_offset, ev)
 std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::vector<py::tuple>& specs) {
   std::vector<BlockDesc> blocks(specs.size());
   std::vector<TileRef> tiles;
   torch::Device device(torch::kCPU);
   for (size_t i = 0; i < specs.size(); ++i) {
     const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 21, "block spec must have 21 fields");
+    TORCH_CHECK(s.size() == 22, "block spec must have 22 fields");
     BlockDesc& b = blocks[i];
     std::memset(&b, 0, sizeof(b));
     auto param = s[0].cast<torch::Tensor>();
@@ -200,6 +200,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
     b.norms = opt(18);
     b.send = reinterpret_cast<void*>(s[19].cast<int64_t>());
     b.slot_offset = s[20].cast<int64_t>();
+    b.ev = opt(21);
     const int tm = (b.m + 31) / 32, tn = (b.n + 31) / 32;
     for (int ti = 0; ti < tm; ++ti)
       for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});
@@ -277,6 +278,23 @@ void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+void eig_scale(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double bc2, double inv_root,
+               double eps, bool write_split) {
+  c10::cuda::CUDAGuard guard(blocks.device());
+  launch_eig_scale(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), reinterpret_cast<const TileRef*>(tiles.data_ptr()),
+                   static_cast<int>(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
+                   static_cast<float>(eps), write_split ? 1 : 0, at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void mode_switch(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double coeff, int64_t send_dtype) {
+  c10::cuda::CUDAGuard guard(blocks.device());
+  launch_mode_switch(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), reinterpret_cast<const TileRef*>(tiles.data_ptr()),
+                     static_cast<int>(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
+                     at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 void peer_barrier(torch::Tensor local_flags, const torch::Tensor& peer_flag_bases, int64_t my_rank, int64_t world,
                   int64_t seq, torch::Tensor status) {
   c10::cuda::CUDAGuard guard(local_flags.device());
@@ -285,6 +303,55 @@ void peer_barrier(torch::Tensor local_flags, const torch::Tensor& peer_flag_base
                       reinterpret_cast<const unsigned long long*>(peer_flag_bases.data_ptr<int64_t>()),
                       static_cast<int>(my_rank), static_cast<int>(world), static_cast<int>(seq),
                       status.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// Table for the grouped square-matrix passes.  Each spec: (src, dst_hi | None, dst_lo | None, err | None).
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_mat_table(const std::vector<py::tuple>& specs) {
+  std::vector<MatOp> ops(specs.size());
+  std::vector<int2> chunks;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    auto src = s[0].cast<torch::Tensor>();
+    TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1 && src.size(0) == src.size(1));
+    device = src.device();
+    MatOp& op = ops[i];
+    std::memset(&op, 0, sizeof(op));
+    op.src = src.data_ptr<float>();
+    op.d = static_cast<int>(src.size(0));
+    op.ld_src = static_cast<int>(src.stride(0));
+    auto hi = s[1].cast<std::optional<torch::Tensor>>();
+    auto lo = s[2].cast<std::optional<torch::Tensor>>();
+    if (hi.has_value()) {
+      TORCH_CHECK(hi->dim() == 2 && hi->stride(1) == 1);
+      op.dst_hi = hi->data_ptr<float>();
+      op.ld_dst = static_cast<int>(hi->stride(0));
+    }
+    if (lo.has_value()) {
+      TORCH_CHECK(hi.has_value() && lo->stride(0) == hi->stride(0));
+      op.dst_lo = lo->data_ptr<float>();
+    }
+    op.err = fptr(s[3].cast<std::optional<torch::Tensor>>());
+    for (int r = 0; r < (op.d + kMatRowsPerChunk - 1) / kMatRowsPerChunk; ++r) chunks.push_back(make_int2(static_cast<int>(i), r));
+  }
+  auto d_ops = upload_bytes(ops.data(), ops.size() * sizeof(MatOp), device);
+  auto d_chunks = upload_bytes(chunks.data(), chunks.size() * sizeof(int2), device);
+  return {d_ops, d_chunks, static_cast<int64_t>(chunks.size())};
+}
+
+void affine_identity_split(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks, double a, double b) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_affine_identity_split(reinterpret_cast<const MatOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
+                               static_cast<int>(num_chunks), static_cast<float>(a), static_cast<float>(b),
+                               at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void identity_error(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_identity_error(reinterpret_cast<const MatOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
+                        static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -380,6 +447,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("direction_epilogue", &direction_epilogue);
   m.def("gathered_apply", &gathered_apply);
   m.def("peer_barrier", &peer_barrier);
+  m.def("eig_scale", &eig_scale);
+  m.def("mode_switch", &mode_switch);
+  m.attr("FLAG_SQUARE_ACC") = kFlagSquareAcc;
+  m.def("build_mat_table", &build_mat_table);
+  m.def("affine_identity_split", &affine_identity_split);
+  m.def("identity_error", &identity_error);
   m.def("two_sided_apply", &two_sided_apply);
   m.def("tf32_split", &tf32_split);
   m.def("build_gpa_table", &build_gpa_table);

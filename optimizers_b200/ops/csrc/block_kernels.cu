@@ -272,6 +272,64 @@ __global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __
   }
 }
 
+__global__ void __launch_bounds__(256) eig_scale_kernel(const BlockDesc* __restrict__ blocks,
+                                                        const TileRef* __restrict__ tiles, int num_tiles, float bc2,
+                                                        float inv_root, float eps, int write_split) {
+  for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const TileRef ref = tiles[t];
+    const BlockDesc& b = blocks[ref.block];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int j = ref.tj * kTile + tx;
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r) {
+      const int i = ref.ti * kTile + ty + r * 8;
+      if (i >= b.m || j >= b.n) continue;
+      const long long e = static_cast<long long>(i) * b.n + j;
+      const float denom = powf(b.ev[e] / bc2, inv_root) + eps;
+      const float s = b.p[e] / denom;
+      const long long o = static_cast<long long>(i) * b.n_pad + j;
+      if (write_split) {
+        const float h = tf32_round(s);
+        b.f_hi[o] = h;
+        b.f_lo[o] = s - h;
+      } else {
+        b.f_hi[o] = s;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) mode_switch_kernel(const BlockDesc* __restrict__ blocks,
+                                                          const TileRef* __restrict__ tiles, int num_tiles, float coeff,
+                                                          int send_dtype) {
+  for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const TileRef ref = tiles[t];
+    const BlockDesc& b = blocks[ref.block];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int j = ref.tj * kTile + tx;
+#pragma unroll
+    for (int r = 0; r < kRowsPerThread; ++r) {
+      const int i = ref.ti * kTile + ty + r * 8;
+      if (i >= b.m || j >= b.n) continue;
+      const long long e = static_cast<long long>(i) * b.n + j;
+      const long long pe = static_cast<long long>(i) * b.param_pitch + j;
+      const float w = b.param[pe];
+      const float delta = (b.z[e] - w) * coeff;
+      if (b.send != nullptr) {
+        if (send_dtype == 1) {
+          store_send<__nv_bfloat16>(b.send, e, delta);
+        } else if (send_dtype == 2) {
+          store_send<__half>(b.send, e, delta);
+        } else {
+          store_send<float>(b.send, e, delta);
+        }
+      } else {
+        b.param[pe] = w + delta;
+      }
+    }
+  }
+}
+
 __global__ void peer_barrier_kernel(int* local_flags, const unsigned long long* peer_flag_bases, int my_rank,
                                     int world, int seq, int* status) {
   // Everything this rank wrote before the barrier (earlier kernels of the stream) must be
@@ -312,6 +370,19 @@ void launch_grad_prologue(const PrologueArgs& args, cudaStream_t stream) {
 void launch_direction_epilogue(const EpilogueArgs& args, cudaStream_t stream) {
   if (args.num_tiles <= 0) return;
   direction_epilogue_kernel<<<grid_for(args.num_tiles), 256, 0, stream>>>(args);
+}
+
+void launch_eig_scale(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, float bias_correction2,
+                      float inv_root, float epsilon, int write_split, cudaStream_t stream) {
+  if (num_tiles <= 0) return;
+  eig_scale_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, bias_correction2, inv_root,
+                                                            epsilon, write_split);
+}
+
+void launch_mode_switch(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, float coeff, int send_dtype,
+                        cudaStream_t stream) {
+  if (num_tiles <= 0) return;
+  mode_switch_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, coeff, send_dtype);
 }
 
 void launch_peer_barrier(int* local_flags, const unsigned long long* peer_flag_bases, int my_rank, int world,

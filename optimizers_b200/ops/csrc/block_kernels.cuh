@@ -44,6 +44,7 @@ struct BlockDesc {
   float* norms;           // [2]: squared norm of the grafting direction, of the Shampoo direction
   void* send;             // all-gather send slot in the communication dtype (null: update params)
   long long slot_offset;  // byte offset of the block's slot inside the gather buffer (peer push)
+  float* ev;              // eigenvalue-corrected second moment [m, n] (null unless SOAP)
 };
 
 struct TileRef {
@@ -94,6 +95,18 @@ struct EpilogueArgs {
                                   // (all-gather fused into the epilogue); 0: BlockDesc::send or params
   unsigned long long peer_base[8];  // gather-buffer base address on each rank (this rank included)
 };
+
+// eig_scale: S = P / ((ev / bc2)^(1/root) + eps) on the projected filtered gradient held in
+// BlockDesc::p, written as the (hi, lo) operand pair into f_hi / f_lo for the unprojection GEMMs
+// (reference: shampoo_preconditioner_list.py:1920-1942).
+void launch_eig_scale(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, float bias_correction2,
+                      float inv_root, float epsilon, int write_split, cudaStream_t stream);
+
+// mode_switch: W <- W + c (Z - W) for every block, the train()/eval() switch of the primal
+// averaging schemes; with BlockDesc::send the delta goes to the gather buffer instead
+// (reference: distributed_shampoo.py:1749-1757, :1783-1794).
+void launch_mode_switch(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, float coeff, int send_dtype,
+                        cudaStream_t stream);
 
 constexpr int kErrPeerTimeout = 4;  // a bounded wait on a peer's flag expired
 

@@ -58,6 +58,62 @@ __global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict
   }
 }
 
+__global__ void __launch_bounds__(256) affine_identity_split_kernel(const MatOp* __restrict__ ops,
+                                                                    const int2* __restrict__ chunks, int num_chunks,
+                                                                    float a, float b) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const MatOp op = ops[ref.x];
+    const int row0 = ref.y * kMatRowsPerChunk;
+    const int rows = min(kMatRowsPerChunk, op.d - row0);
+    for (int e = threadIdx.x; e < rows * op.d; e += blockDim.x) {
+      const int i = row0 + e / op.d, j = e % op.d;
+      float x = a * op.src[static_cast<long long>(i) * op.ld_src + j];
+      if (i == j) x += b;
+      const long long o = static_cast<long long>(i) * op.ld_dst + j;
+      if (op.dst_lo != nullptr) {
+        const float h = tf32_round(x);
+        op.dst_hi[o] = h;
+        op.dst_lo[o] = x - h;
+      } else {
+        op.dst_hi[o] = x;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) identity_error_kernel(const MatOp* __restrict__ ops,
+                                                             const int2* __restrict__ chunks, int num_chunks) {
+  __shared__ float red[8];
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const MatOp op = ops[ref.x];
+    const int row0 = ref.y * kMatRowsPerChunk;
+    const int rows = min(kMatRowsPerChunk, op.d - row0);
+    float worst = 0.f;
+    for (int e = threadIdx.x; e < rows * op.d; e += blockDim.x) {
+      const int i = row0 + e / op.d, j = e % op.d;
+      const float x = op.src[static_cast<long long>(i) * op.ld_src + j] - (i == j ? 1.f : 0.f);
+      const float ax = fabsf(x);
+      worst = (ax > worst || ax != ax) ? ax : worst;  // NaN propagates
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, worst, o);
+      worst = (other > worst || other != other) ? other : worst;
+    }
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = worst;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float w = 0.f;
+      for (int k = 0; k < 8; ++k) w = (red[k] > w || red[k] != red[k]) ? red[k] : w;
+      // Non-negative floats (and +NaN, which has the largest bit pattern) order like their bits.
+      atomicMax(reinterpret_cast<int*>(op.err), __float_as_int(w));
+    }
+    __syncthreads();
+  }
+}
+
 struct GpaScalars {
   float lr, beta1, beta2, eps, bc1, bc2, wd, avg_coeff, mu_y;
   int wd_on_y;
@@ -139,6 +195,17 @@ int grid_for(long long work_items) {
 }
 
 }  // namespace
+
+void launch_affine_identity_split(const MatOp* ops, const int2* chunks, int num_chunks, float a, float b,
+                                  cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  affine_identity_split_kernel<<<grid_for(num_chunks), 256, 0, stream>>>(ops, chunks, num_chunks, a, b);
+}
+
+void launch_identity_error(const MatOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  identity_error_kernel<<<grid_for(num_chunks), 256, 0, stream>>>(ops, chunks, num_chunks);
+}
 
 void launch_tf32_split(const float* src, long long src_pitch, float* hi, float* lo, long long dst_pitch, int rows,
                        int cols, cudaStream_t stream) {

@@ -25,6 +25,28 @@ struct GpaTensorDesc {
   int pad_;
 };
 
+// One square matrix of a grouped pointwise pass over many matrices of different sizes.
+struct MatOp {
+  const float* src;  // d x d, row pitch ld_src
+  float* dst_hi;     // d x d, row pitch ld_dst (tf32-rounded part, or the plain result when dst_lo is null)
+  float* dst_lo;     // residual part, may be null
+  float* err;        // one float per matrix (identity_error)
+  int d, ld_src, ld_dst, pad_;
+};
+
+constexpr int kMatRowsPerChunk = 8;
+
+// dst = a * src + b * I for every matrix of the table, written as a (hi, lo) tf32 pair: the
+// M_p = (1 - alpha) I + alpha M step of the coupled Newton iteration (reference:
+// distributed_shampoo/preconditioner/matrix_functions.py:423-428), fused with the operand split.
+void launch_affine_identity_split(const MatOp* ops, const int2* chunks, int num_chunks, float a, float b,
+                                  cudaStream_t stream);
+
+// err = max |src - I| per matrix (err must be zeroed first): the convergence measure of the
+// coupled iterations, kept on the device (reference: torch.dist(M, I, p=inf) read by the host every
+// iteration, matrix_functions.py:423).
+void launch_identity_error(const MatOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream);
+
 void launch_tf32_split(const float* src, long long src_pitch, float* hi, float* lo, long long dst_pitch, int rows,
                        int cols, cudaStream_t stream);
 

@@ -209,7 +209,9 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
               const int row = row0 + rr;
               const bool live = rr < rows && (!packed || col >= row);
               if (live) {
-                const float val = alpha * st[rr * kStagePitch + lane] + beta * old[rr];
+                float acc = st[rr * kStagePitch + lane];
+                if (flags & kFlagSquareAcc) acc *= acc;
+                const float val = alpha * acc + beta * old[rr];
                 if (write_c) Cp[o] = val;
                 if (flags & kFlagSplitOut) {
                   const long long od = static_cast<long long>(row) * ldd + col;

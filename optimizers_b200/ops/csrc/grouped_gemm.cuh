@@ -21,6 +21,8 @@
 //                   (row pitch ldd) so it can feed the next GEMM of a chain
 //   kFlagSumSq      add the sum of squares of the results to *sumsq (Frobenius norm partials)
 //   kFlagNoC        do not write C (only the split / sumsq outputs)
+//   kFlagSquareAcc  the accumulator is squared before alpha/beta are applied: with C the running
+//                   second moment V this is V <- beta2 V + w (Q_L^T G Q_R)^2 fused into the projection
 #pragma once
 
 #include <cstdint>
@@ -32,6 +34,7 @@ constexpr int kFlagPackedC = 1;
 constexpr int kFlagSplitOut = 2;
 constexpr int kFlagSumSq = 4;
 constexpr int kFlagNoC = 8;
+constexpr int kFlagSquareAcc = 16;  // C = beta * C + alpha * acc^2 (second moment in the eigenbasis)
 
 constexpr int kErrPipelineTimeout = 1;  // a bounded mbarrier wait expired
 

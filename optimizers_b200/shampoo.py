@@ -801,6 +801,11 @@ class DistributedShampoo(Optimizer):
             if not _is_primal_averaging(cfg) or bool(rec[TRAIN_MODE]) == to_train:
                 continue
             mu_y, _ = self._get_train_and_eval_interp_coeffs(cfg, None, rec)
+            engine = rec.get(NATIVE_ENGINE)
+            coeff = (1 - cfg.train_interp_coeff) if to_train else (1 - 1 / cfg.train_interp_coeff)
+            if engine is not None and engine.mode_switch(coeff):
+                rec[TRAIN_MODE].fill_(to_train)
+                continue
             delta = torch._foreach_sub(rec[WEIGHT_BUFFER_LIST], rec[DISTRIBUTOR].local_blocked_params)
             torch._foreach_mul_(delta, (1 - mu_y) if to_train else (1 - torch.reciprocal(mu_y)))
             rec[DISTRIBUTOR].update_params(blocked_search_directions=tuple(delta), use_masked_tensors=False)
