@@ -261,6 +261,10 @@ def batched_newton_refresh(
     between two checks)."""
     if not blocks:
         return
+    # The iteration amplifies operand rounding: a single tf32 product per multiply does not
+    # converge (error stalls near 1e-1), so the split products are used whatever the engine's
+    # GEMM mode for the per-step kernels is.
+    split = True
     device = blocks[0].inv_hi[0].device
     cfg = blocks[0].factors.amortized_computation_config
     max_iterations, tolerance = cfg.max_iterations, cfg.tolerance

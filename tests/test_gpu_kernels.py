@@ -195,8 +195,11 @@ def test_native_engine_matches_torch_step(name):
         rec["native_engine"].check_status()
     for a, b in zip(l_ref, l_nat):
         assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (l_ref, l_nat)
+    # The eigenbasis of nearly degenerate factors reacts to 1e-5 perturbations of the factors, and
+    # the per-coordinate scaling in that basis amplifies it: a wider band for the SOAP variants.
+    atol = 4e-3 if name.startswith("soap") else 5e-4
     for p, q in zip(m_ref.parameters(), m_nat.parameters()):
-        assert torch.allclose(p, q, rtol=5e-3, atol=5e-4), (p - q).abs().max()
+        assert torch.allclose(p, q, rtol=5e-3, atol=atol), (p - q).abs().max()
     if name == "gpa":  # train -> eval -> train through the grouped mode-switch kernel
         for o in (o_ref, o_nat):
             o.eval()
@@ -219,6 +222,19 @@ def test_native_engine_matches_torch_step(name):
             assert (a - b).abs().max().item() / denom < 2e-2, path
 
     walk(s_ref, s_nat)
+
+
+@pytest.mark.parametrize("name", ["soap_adam_graft", "soap_qr_no_graft"])
+def test_native_soap_before_first_refresh_is_exact(name):
+    """Before the first refresh the eigenbases are identities, so project / second-moment update /
+    scale / unproject must reproduce the torch step to rounding: a tight check of the plumbing
+    that the chaotic multi-refresh comparison cannot give."""
+    kw = _configs()[name]
+    m_ref, _, _ = _train("torch", 2, **kw)
+    m_nat, o_nat, _ = _train("native", 2, **kw)
+    o_nat._per_group_state_lists[0]["native_engine"].check_status()
+    for p, q in zip(m_ref.parameters(), m_nat.parameters()):
+        assert torch.allclose(p, q, rtol=1e-4, atol=2e-6), (p - q).abs().max()
 
 
 def test_gpa_adamw_kernel_matches_torch_loop():
@@ -270,6 +286,6 @@ def test_native_newton_refresh_matches_eigen_roots(split):
             lam, Q = torch.linalg.eigh(A)
             want = (Q * lam.pow(-1.0 / root)) @ Q.T
             rel = (X.double() - want).abs().max() / want.abs().max()
-            assert rel < (2e-3 if split else 3e-2), (F.shape, root, rel)
+            assert rel < 2e-3, (F.shape, root, rel)
             checked += 1
     assert checked >= 6
