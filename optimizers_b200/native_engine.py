@@ -93,16 +93,16 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     if gc is not None and not isinstance(gc, (SGDPreconditionerConfig, AdaGradPreconditionerConfig)):
         return f"grafting config {type(gc).__name__} has no native step"
     dc = group[DISTRIBUTED_CONFIG]
-    if type(dc) not in (SingleDeviceDistributedConfig, DDPDistributedConfig):
-        return f"distributed config {type(dc).__name__} has no native step yet"
     if isinstance(dc, DDPDistributedConfig):
         if dc.communicate_params:
             return "communicate_params=True has no native step yet"
         if dc.communication_dtype not in (torch.float32, torch.bfloat16, torch.float16):
             return f"communication dtype {dc.communication_dtype} has no native step"
-    for p in group[PARAMS]:
-        if p.dtype != torch.float32 or not p.is_contiguous() or type(p.data) is not Tensor:
-            return "parameters must be plain contiguous fp32 tensors"
+    # What the distributor blocks: the parameters themselves, their local shards, or (lossless
+    # variants) this rank's gathered full copies.
+    for p in rec[DISTRIBUTOR]._get_params_or_grads():
+        if p.dtype != torch.float32 or not p.is_contiguous() or type(p.detach()) is not Tensor:
+            return "parameters (or their local shards) must be plain contiguous fp32 tensors"
     plist = rec[SHAMPOO_PRECONDITIONER_LIST]
     for block, sel in zip(
         rec[DISTRIBUTOR].local_blocked_params, plist._local_preconditioned_dims_selector_list, strict=True
@@ -168,7 +168,7 @@ class NativeGroupEngine:
 
         self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
         self._ddp = isinstance(group[DISTRIBUTED_CONFIG], DDPDistributedConfig)
-        self._p2p = self._ddp and cfg.comm_path == "p2p"
+        self._p2p = type(group[DISTRIBUTED_CONFIG]) is DDPDistributedConfig and cfg.comm_path == "p2p"
         self._pull = self._p2p and cfg.fuse_gradient_reduction
         self._comm_dtype_code = 0
         self._gather_table = None
@@ -182,7 +182,7 @@ class NativeGroupEngine:
         if self._p2p:
             self._setup_peer_memory()
         self._build_blocks()
-        n_ptrs = max(len(group[PARAMS]), 1)
+        n_ptrs = max(len(self._local_params), 1)
         # Two pinned staging buffers, used alternately, so that a pointer table still being
         # copied by the device is never overwritten by the host.
         self._grad_ptrs_host = [torch.zeros(n_ptrs, dtype=torch.int64).pin_memory() for _ in range(2)]
@@ -200,8 +200,12 @@ class NativeGroupEngine:
     def _build_blocks(self) -> None:
         rec, dist = self._rec, self._dist
         dev = self._device
-        params = self._group[PARAMS]
-        param_pos = {id(p): i for i, p in enumerate(params)}
+        # Local tensors the blocks are views of, aligned with dist._global_num_blocks_per_param.
+        self._local_params = [p.detach() for p in dist._get_params_or_grads()]
+        owner_of_block = [
+            i for i, count in enumerate(dist._global_num_blocks_per_param) for _ in range(count)
+        ]
+        local_owner = compress_list(owner_of_block, dist._distributor_selector)
         blocks: list[_Block] = []
         factors_list = self._plist._local_kronecker_factors_unwrapped
         m1s = rec.get(FILTERED_GRAD_LIST)
@@ -217,9 +221,8 @@ class NativeGroupEngine:
             b = _Block()
             b.index = i
             b.param_view = view
-            p = info.param
-            b.grad_slot = param_pos[id(p)]
-            b.grad_offset = (view.data_ptr() - p.data_ptr()) // 4
+            b.grad_slot = local_owner[i]
+            b.grad_offset = (view.data_ptr() - self._local_params[b.grad_slot].data_ptr()) // 4
             b.order = view.dim()
             if view.dim() == 1:
                 b.m, b.n = 1, view.shape[0]
@@ -449,6 +452,12 @@ class NativeGroupEngine:
         self._active = tuple(selector)
 
     def on_state_loaded(self) -> None:
+        if hasattr(self._dist, "refresh_assigned_full_params"):
+            # The lossless distributors re-gathered their full copies: block views moved.
+            self._build_blocks()
+            self._plans_for = None
+            self._gather_for = None
+            self._full_table = None
         self.refresh_inverse_mirrors()
 
     def mode_switch(self, coeff: float) -> bool:
@@ -486,8 +495,10 @@ class NativeGroupEngine:
         ptrs: list[int] = []
         selector: list[bool] = []
         any_grad = False
-        for p, count in zip(self._group[PARAMS], dist._global_num_blocks_per_param, strict=True):
-            g = p.grad
+        # Held until the next step: some distributors hand out freshly gathered gradients whose
+        # memory must outlive the kernels that read it through the pointer table.
+        self._grads_alive = list(dist._get_params_or_grads(get_grad=True))
+        for g, count in zip(self._grads_alive, dist._global_num_blocks_per_param, strict=True):
             usable = g is not None and g.numel() > 0
             if usable:
                 if g.dtype != torch.float32 or not g.is_contiguous():
@@ -656,6 +667,8 @@ class NativeGroupEngine:
         parameters.  DDP: all-gather (NCCL), or a cross-rank barrier after the epilogue's peer
         stores (p2p); then one grouped kernel adds every block's direction to the parameters."""
         if not self._ddp:
+            if hasattr(self._dist, "_write_back"):
+                self._dist._write_back()  # lossless variants: full copies -> local shards
             return
         dist_ = self._dist
         if self._p2p:
@@ -681,3 +694,5 @@ class NativeGroupEngine:
         if self._gather_table is not None:
             self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code)
             self.launches_per_step += 1
+        if hasattr(dist_, "_write_back"):
+            dist_._write_back()

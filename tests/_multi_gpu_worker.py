@@ -67,5 +67,89 @@ def main() -> None:
     dist.destroy_process_group()
 
 
+def sharded_main() -> None:
+    """``<backend>:<strategy>``: train the MLP under one of the sharded strategies with the torch
+    or the native step and write rank 0's view of the full final parameters."""
+    mode, out = sys.argv[1], sys.argv[2]
+    backend, strategy = mode.split(":")
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, fully_shard, ShardingStrategy
+    from torch.distributed.tensor import DTensor
+
+    from optimizers_b200 import (
+        AdaGradPreconditionerConfig,
+        compile_fsdp_parameter_metadata,
+        DistributedShampoo,
+        FSDPDistributedConfig,
+        FSDPParamAssignmentStrategy,
+        FullyShardDistributedConfig,
+        HSDPDistributedConfig,
+        HybridShardDistributedConfig,
+        NativeRuntimeConfig,
+    )
+
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(
+        torch.nn.Linear(96, 200, bias=False), torch.nn.ReLU(), torch.nn.Linear(200, 72, bias=False), torch.nn.ReLU(),
+        torch.nn.Linear(72, 10, bias=False),
+    ).to(dev)
+    mesh2d = init_device_mesh("cuda", (2, world // 2), mesh_dim_names=("replicate", "shard")) if "h" == strategy[0] else None
+    lossless = {
+        "fully_shard_rr": FSDPParamAssignmentStrategy.ROUND_ROBIN,
+        "fully_shard_rep": FSDPParamAssignmentStrategy.REPLICATE,
+        "hybrid_shard_rr": FSDPParamAssignmentStrategy.ROUND_ROBIN,
+    }
+    if strategy == "fsdp":
+        model = FSDP(model, use_orig_params=True)
+        dc = FSDPDistributedConfig(param_to_metadata=compile_fsdp_parameter_metadata(model))
+    elif strategy == "hsdp":
+        model = FSDP(model, device_mesh=mesh2d, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True)
+        dc = HSDPDistributedConfig(param_to_metadata=compile_fsdp_parameter_metadata(model), device_mesh=mesh2d)
+    elif strategy.startswith("fully_shard"):
+        model = fully_shard(model)
+        dc = FullyShardDistributedConfig(
+            param_assignment_strategy=lossless.get(strategy, FSDPParamAssignmentStrategy.DEFAULT)
+        )
+    else:
+        model = fully_shard(model, mesh=mesh2d)
+        dc = HybridShardDistributedConfig(
+            device_mesh=mesh2d, param_assignment_strategy=lossless.get(strategy, FSDPParamAssignmentStrategy.DEFAULT)
+        )
+    opt = DistributedShampoo(
+        model.parameters(), lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64,
+        precondition_frequency=3, start_preconditioning_step=3, weight_decay=1e-2,
+        grafting_config=AdaGradPreconditionerConfig(epsilon=1e-8), distributed_config=dc,
+        native_runtime_config=NativeRuntimeConfig(backend=backend),
+    )
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for _ in range(8):
+        x = torch.randn(64, 96, device=dev, generator=g)
+        y = torch.randint(0, 10, (64,), device=dev, generator=g)
+        shard = slice(rank * 64 // world, (rank + 1) * 64 // world)
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(x[shard]), y[shard]).backward()
+        opt.step()
+    engines = [rec.get("native_engine") for rec in opt._per_group_state_lists]
+    assert all((e is not None) == (backend == "native") for e in engines), engines
+    for e in engines:
+        if e is not None:
+            e.check_status()
+    torch.cuda.synchronize()
+    if strategy in ("fsdp", "hsdp"):
+        with FSDP.summon_full_params(model):
+            params = [p.detach().cpu().clone() for p in model.parameters()]
+    else:
+        params = [p.full_tensor().cpu() if isinstance(p, DTensor) else p.detach().cpu() for p in model.parameters()]
+    if rank == 0:
+        torch.save(params, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
-    main()
+    sharded_main() if ":" in sys.argv[1] else main()
