@@ -98,7 +98,9 @@ def sharded_main() -> None:
         torch.nn.Linear(96, 200, bias=False), torch.nn.ReLU(), torch.nn.Linear(200, 72, bias=False), torch.nn.ReLU(),
         torch.nn.Linear(72, 10, bias=False),
     ).to(dev)
-    mesh2d = init_device_mesh("cuda", (2, world // 2), mesh_dim_names=("replicate", "shard")) if "h" == strategy[0] else None
+    # FSDP1's hybrid strategy needs a shard dimension of at least 2 to flatten its parameters.
+    mesh_shape = (world // 2, 2) if strategy == "hsdp" else (2, world // 2)
+    mesh2d = init_device_mesh("cuda", mesh_shape, mesh_dim_names=("replicate", "shard")) if "h" == strategy[0] else None
     lossless = {
         "fully_shard_rr": FSDPParamAssignmentStrategy.ROUND_ROBIN,
         "fully_shard_rep": FSDPParamAssignmentStrategy.REPLICATE,
