@@ -52,6 +52,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--backend", choices=["auto", "native", "torch"], default="native")
     ap.add_argument("--gemm-mode", choices=["tf32x3", "tf32"], default="tf32x3")
     ap.add_argument("--comm", choices=["p2p", "nccl"], default="p2p", help="multi-GPU path of this framework")
+    ap.add_argument("--model", choices=["fused", "plain"], default="fused",
+                    help="this framework's arm: its GPT-2 with the fused norm / LM-head-loss kernels, or the plain "
+                    "PyTorch model that the reference arm always uses")
     ap.add_argument("--layers", type=int, default=12, help="debug only; the reported config needs 12")
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="debug only; the reported config needs 16")
     return ap.parse_args()
@@ -252,7 +255,15 @@ def main() -> None:
         sys.path.insert(0, REPO)
     torch.manual_seed(1234)
     torch.backends.cuda.matmul.allow_tf32 = False  # optimizer math of the reference stays fp32
-    model = make_gpt2(args.layers).to(dev)
+    fused_model = args.impl == "ours" and args.model == "fused"
+    if fused_model:
+        # Same architecture, initialisation and autocast numerics as make_gpt2; the normalisations
+        # and the LM head + cross-entropy run through this framework's CUDA kernels.
+        from optimizers_b200.models import GPT2, GPT2Config
+
+        model = GPT2(GPT2Config(n_layer=args.layers)).to(dev)
+    else:
+        model = make_gpt2(args.layers).to(dev)
     train_model = model
     # This framework's p2p path reduces the gradients inside the optimizer's prologue kernel
     # (owners pull their blocks from peer memory), so the model is not wrapped in DDP there.
@@ -301,10 +312,17 @@ def main() -> None:
         sampler.start()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    model_launches = 0
+    if fused_model:
+        from optimizers_b200.models import fused_ops
+
+        model_launches = -fused_ops.launch_count
     start.record()
     for i in range(args.steps):
         train_step(dev_tokens[i % n_batches])
     stop.record()
+    if fused_model:
+        model_launches += fused_ops.launch_count
     barrier()
     dev_ms = start.elapsed_time(stop)
 
@@ -335,7 +353,7 @@ def main() -> None:
     tokens_per_step = B * SEQ * world
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
-    launches = count_native_launches(opt) * args.steps if args.impl == "ours" else 0
+    launches = count_native_launches(opt) * args.steps + model_launches if args.impl == "ours" else 0
     if rank == 0:
         out = {
             "metric": "train tokens/sec (GPT-2 124M, Distributed Shampoo)",
@@ -353,6 +371,8 @@ def main() -> None:
             "impl": args.impl,
             "config": {
                 "model": f"gpt2-124m ({args.layers} layers, d_model 768, 12 heads, mlp 3072, vocab 50257)",
+                "model_impl": "framework GPT-2: fused LayerNorm and LM-head cross-entropy kernels" if fused_model
+                else "plain PyTorch modules",
                 "global_batch": B * world,
                 "seq_len": SEQ,
                 "parallelism": f"dp{world}" if world > 1 else "single",

@@ -1,0 +1,124 @@
+"""Optimizer-only benchmark through the public API: ``--blocks`` parameters of size d x d, fp32,
+gradients N(0, 1e-2), one ``optimizer.step()`` per iteration, timed with CUDA events.
+
+Two numbers per run:
+
+  step_ms      median time of a step that does not recompute the preconditioners (gradient
+               prologue, factor update, preconditioner application, epilogue)
+  refresh_ms   median extra time of a step that does (root inverse by eigendecomposition or by the
+               coupled Newton iteration, or the eigenbasis refresh of the eigenvalue-corrected
+               variant), measured as refresh step - plain step
+
+``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` with the same
+settings, for comparison on the same GPU.
+
+    python benchmarks/engine_microbench.py --d 2048 --blocks 16 --root eigen
+    python benchmarks/engine_microbench.py --d 1024 --blocks 64 --root newton --impl reference
+    python benchmarks/engine_microbench.py --optimizer gpa --d 4096 --blocks 16
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--optimizer", choices=["shampoo", "soap", "gpa"], default="shampoo")
+    ap.add_argument("--root", choices=["eigen", "newton"], default="eigen")
+    ap.add_argument("--d", type=int, default=2048)
+    ap.add_argument("--blocks", type=int, default=16)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--refreshes", type=int, default=2)
+    ap.add_argument("--backend", default="native")
+    ap.add_argument("--gemm-mode", default="tf32x3")
+    args = ap.parse_args()
+
+    import torch
+
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(REPO, "baseline", "_ref"))
+        import distributed_shampoo as lib
+    else:
+        sys.path.insert(0, REPO)
+        import optimizers_b200 as lib
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    d, nb = args.d, args.blocks
+    params = [torch.nn.Parameter(torch.randn(d, d, device=dev) * 0.02) for _ in range(nb)]
+    grads = [[torch.randn(d, d, device=dev) * 1e-2 for _ in range(nb)] for _ in range(2)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    period = 1000
+
+    if args.optimizer == "gpa":
+        if args.impl == "reference":
+            raise SystemExit("the reference wheel does not ship its gpa package")
+        from optimizers_b200.gpa_adamw import GPAAdamW
+
+        opt = GPAAdamW(params, lr=1e-3, weight_decay=1e-2)
+        opt.train()
+    else:
+        extra = {}
+        if args.impl == "ours":
+            extra["native_runtime_config"] = lib.NativeRuntimeConfig(backend=args.backend, gemm_mode=args.gemm_mode)
+        if args.optimizer == "soap":
+            pc = lib.EigenvalueCorrectedShampooPreconditionerConfig()
+        elif args.root == "newton":
+            pc = lib.RootInvShampooPreconditionerConfig(amortized_computation_config=lib.CoupledNewtonConfig())
+        else:
+            pc = lib.RootInvShampooPreconditionerConfig()
+        opt = lib.DistributedShampoo(
+            params, lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=max(d, 2048),
+            precondition_frequency=period, start_preconditioning_step=period,
+            grafting_config=lib.AdaGradPreconditionerConfig(epsilon=1e-10), preconditioner_config=pc, **extra,
+        )
+        # The shared step counter (a CPU tensor aliased under every parameter); preset so that the
+        # first warm-up step is the first preconditioned one.
+        step_counter = next(s["step"] for s in opt.state.values() if "step" in s)
+        step_counter.fill_(period - 1)
+
+    def one_step(i: int) -> float:
+        for p, g in zip(params, grads[i % 2]):
+            p.grad = g
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        opt.step()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e)
+
+    for i in range(3):
+        one_step(i)
+    plain = [one_step(i) for i in range(args.steps)]
+    refresh: list[float] = []
+    if args.optimizer != "gpa":
+        for i in range(args.refreshes + 1):
+            step_counter.fill_(period * (i + 2) - 1)  # the next step recomputes the preconditioners
+            t = one_step(i)
+            if i > 0:  # the first refresh also pays one-time set-up (workspaces, handles)
+                refresh.append(t)
+    step_ms = statistics.median(plain)
+    out = {
+        "impl": args.impl, "optimizer": args.optimizer, "root": args.root if args.optimizer == "shampoo" else None,
+        "d": d, "blocks": nb, "step_ms": round(step_ms, 4),
+        "refresh_ms": round(statistics.median(refresh) - step_ms, 3) if refresh else None,
+        "bytes_param_state": nb * d * d * 4,
+    }
+    if args.impl == "ours" and args.optimizer != "gpa":
+        eng = opt._per_group_state_lists[0].get("native_engine")
+        out["native_launches_per_step"] = eng.launches_per_step if eng is not None else 0
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

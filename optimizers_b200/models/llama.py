@@ -1,6 +1,9 @@
 """Llama-style decoder: RMSNorm, rotary position embedding, SwiGLU feed-forward, untied output
 head.  Defaults are the 1B configuration of the benchmarks: 16 layers, d_model 2048, 32 heads,
-FFN 8192, vocabulary 32000."""
+FFN 8192, vocabulary 32000.
+
+With ``fused=True`` (default) RMSNorm and the head + cross-entropy go through
+``optimizers_b200.models.fused_ops``."""
 
 from __future__ import annotations
 
@@ -9,6 +12,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+from optimizers_b200.models import fused_ops
 
 
 @dataclass
@@ -21,15 +26,19 @@ class LlamaConfig:
     max_seq: int = 2048
     rope_theta: float = 10000.0
     norm_eps: float = 1e-5
+    fused: bool = True
 
 
 class RMSNorm(nn.Module):
-    def __init__(self, dim: int, eps: float) -> None:
+    def __init__(self, dim: int, eps: float, fused: bool = True) -> None:
         super().__init__()
         self.eps = eps
+        self.fused = fused
         self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.fused:
+            return fused_ops.rms_norm(x, self.weight, self.eps)
         scale = torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + self.eps)
         return (x.float() * scale).to(x.dtype) * self.weight
 
@@ -50,12 +59,12 @@ class _Layer(nn.Module):
     def __init__(self, cfg: LlamaConfig) -> None:
         super().__init__()
         self.n_head = cfg.n_head
-        self.attn_norm = RMSNorm(cfg.d_model, cfg.norm_eps)
+        self.attn_norm = RMSNorm(cfg.d_model, cfg.norm_eps, cfg.fused)
         self.wq = nn.Linear(cfg.d_model, cfg.d_model, bias=False)
         self.wk = nn.Linear(cfg.d_model, cfg.d_model, bias=False)
         self.wv = nn.Linear(cfg.d_model, cfg.d_model, bias=False)
         self.wo = nn.Linear(cfg.d_model, cfg.d_model, bias=False)
-        self.ffn_norm = RMSNorm(cfg.d_model, cfg.norm_eps)
+        self.ffn_norm = RMSNorm(cfg.d_model, cfg.norm_eps, cfg.fused)
         self.w_gate = nn.Linear(cfg.d_model, cfg.d_ffn, bias=False)
         self.w_up = nn.Linear(cfg.d_model, cfg.d_ffn, bias=False)
         self.w_down = nn.Linear(cfg.d_ffn, cfg.d_model, bias=False)
@@ -79,7 +88,7 @@ class Llama(nn.Module):
         self.cfg = cfg = cfg or LlamaConfig()
         self.embed = nn.Embedding(cfg.vocab_size, cfg.d_model)
         self.layers = nn.ModuleList(_Layer(cfg) for _ in range(cfg.n_layer))
-        self.norm = RMSNorm(cfg.d_model, cfg.norm_eps)
+        self.norm = RMSNorm(cfg.d_model, cfg.norm_eps, cfg.fused)
         self.head = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
         for m in self.modules():
             if isinstance(m, (nn.Linear, nn.Embedding)):
@@ -91,6 +100,8 @@ class Llama(nn.Module):
         x = self.embed(idx)
         for layer in self.layers:
             x = layer(x, cos, sin)
+        if self.cfg.fused and targets is not None:
+            return fused_ops.lm_head_cross_entropy(self.norm(x), self.head.weight, targets)
         logits = self.head(self.norm(x))
         if targets is None:
             return logits

@@ -21,6 +21,10 @@
 namespace py = pybind11;
 using namespace ob200;
 
+namespace ob200 {
+void register_model_ops(pybind11::module_& m);  // model_kernels.cu
+}
+
 namespace {
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -458,4 +462,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_gpa_table", &build_gpa_table);
   m.def("gpa_adamw_step", &gpa_adamw_step);
   m.def("gpa_lerp", &gpa_lerp);
+  ob200::register_model_ops(m);
 }
