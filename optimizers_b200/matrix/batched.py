@@ -443,3 +443,127 @@ def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolera
         active = still
     for it in chunk:  # release iteration buffers
         it.M = it.Mp = it.pw = it.A = None
+
+
+# --------------------------------------------------------------------------------------------------
+# Batched quintic Newton-Schulz orthogonalisation on the grouped tensor-core GEMM
+# --------------------------------------------------------------------------------------------------
+class BatchedNewtonSchulz:
+    """Orthogonalises a fixed list of matrix shapes, all matrices advancing together: every
+    iteration is three grouped GEMM launches over the whole list instead of three library GEMMs
+    per matrix (reference: ``matrix_functions.py:956-1008``, called per block from
+    ``spectral_descent_preconditioner_list.py``).
+
+    With X tall (wide inputs are iterated transposed) and B = X^T X an iteration is
+        B      = Xt Xt^T                      (Xt = X^T as a K-major operand)
+        D      = b B + c B B                  (in place on the plain copy of B: beta = b, alpha = c)
+        X      = a X + X D,   Xt = a Xt + D Xt
+    where the last two products are one launch; the transposed iterate is advanced alongside because
+    the GEMM takes both operands K-major.  Operand (hi, lo) pairs of the iterate are double
+    buffered: a launch never writes operands that other tiles of the same launch still read."""
+
+    def __init__(self, ext: Any, shapes: list[tuple[int, int]], device: torch.device, split: bool = True) -> None:
+        self._ext = ext
+        self._split = split
+        self._device = device
+        self.shapes = list(shapes)
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        z = lambda r, c: torch.zeros(r, _pad4(c), device=device)  # noqa: E731
+        pair = lambda r, c: (z(r, c), z(r, c) if split else None)  # noqa: E731
+        self._items = []
+        for m, n in self.shapes:
+            wide = m < n
+            M, N = (n, m) if wide else (m, n)
+            it = {
+                "wide": wide, "M": M, "N": N,
+                "X": z(M, N), "Xt": z(N, M), "B": z(N, N),
+                "Xs": [pair(M, N), pair(M, N)], "Xts": [pair(N, M), pair(N, M)],
+                "Bs": pair(N, N), "Ds": pair(N, N),
+            }
+            self._items.append(it)
+        self._plans = [self._build(cur) for cur in (0, 1)]
+
+    def _build(self, cur: int):
+        ext, split = self._ext, self._split
+        nxt = cur ^ 1
+        SO = ext.FLAG_SPLIT_OUT
+
+        def v(p, k):
+            return p[0][:, :k], (p[1][:, :k] if p[1] is not None else None)
+
+        def spec(a, b, k, c, out):
+            a_hi, a_lo = v(a, k)
+            b_hi, b_lo = v(b, k)
+            if split:
+                return (a_hi, a_lo, b_hi, b_lo, c, out[0], out[1], None, c.stride(0), out[0].stride(0), SO, False)
+            # single-pass mode: operands are the plain arrays themselves
+            return (a_hi, None, b_hi, None, c, None, None, None, c.stride(0), 0, 0, False)
+
+        g1, g2, g3 = [], [], []
+        for it in self._items:
+            M, N = it["M"], it["N"]
+            if split:
+                xs, xts, bs, ds = it["Xs"][cur], it["Xts"][cur], it["Bs"], it["Ds"]
+                xs_n, xts_n = it["Xs"][nxt], it["Xts"][nxt]
+            else:
+                # plain arrays double as operands; ping-pong the iterate itself
+                xs, xts = (it["Xs"][cur][0], None), (it["Xts"][cur][0], None)
+                xs_n, xts_n = (it["Xs"][nxt][0], None), (it["Xts"][nxt][0], None)
+                bs, ds = (it["B"], None), (it["Ds"][0], None)
+            if split:
+                g1.append(spec(xts, xts, M, it["B"], bs))
+                g2.append(spec(bs, bs, N, it["B"], ds))
+                g3.append(spec(xs, ds, N, it["X"], xs_n))
+                g3.append(spec(ds, xs, N, it["Xt"], xts_n))
+            else:
+                g1.append(spec(xts, xts, M, it["B"], None))
+                g2.append(spec(bs, bs, N, ds[0], None))
+                g3.append(spec(xs, ds, N, xs_n[0], None))
+                g3.append(spec(ds, xs, N, xts_n[0], None))
+        return tuple(ext.build_gemm_plan(s) for s in (g1, g2, g3))
+
+    @torch.no_grad()
+    def __call__(self, mats: list[Tensor], num_iterations: int, coefficients: tuple[float, float, float]) -> list[Tensor]:
+        ext, split = self._ext, self._split
+        a, b, c = coefficients
+        norms = torch._foreach_norm(mats)
+        for it, A, nrm in zip(self._items, mats, norms, strict=True):
+            X = A / torch.clamp(nrm, min=1e-8)
+            if it["wide"]:
+                X = X.T
+            M, N = it["M"], it["N"]
+            it["X"][:, :N].copy_(X)
+            it["Xt"][:, :M].copy_(X.T)
+            if split:
+                ext.tf32_split(it["X"][:, :N], it["Xs"][0][0][:, :N], it["Xs"][0][1][:, :N])
+                ext.tf32_split(it["Xt"][:, :M], it["Xts"][0][0][:, :M], it["Xts"][0][1][:, :M])
+            else:
+                it["Xs"][0][0].copy_(it["X"])
+                it["Xts"][0][0].copy_(it["Xt"])
+        cur = 0
+        for _ in range(num_iterations):
+            p1, p2, p3 = self._plans[cur]
+            ext.run_gemm_plan(*p1, 1.0, 0.0, split, self._status)
+            if split:
+                ext.run_gemm_plan(*p2, c, b, split, self._status)
+                ext.run_gemm_plan(*p3, 1.0, a, split, self._status)
+            else:
+                # D = b B + c B B into its own array (B is an operand of this launch), X_next = a X + X D
+                for it in self._items:
+                    it["Ds"][0].copy_(it["B"])
+                ext.run_gemm_plan(*p2, c, b, split, self._status)
+                for it in self._items:
+                    it["Xs"][cur ^ 1][0].copy_(it["Xs"][cur][0])
+                    it["Xts"][cur ^ 1][0].copy_(it["Xts"][cur][0])
+                ext.run_gemm_plan(*p3, 1.0, a, split, self._status)
+            cur ^= 1
+        out = []
+        for it in self._items:
+            M, N = it["M"], it["N"]
+            X = it["X"][:, :N] if split else it["Xs"][cur][0][:, :N]
+            out.append((X.T if it["wide"] else X).clone())
+        return out
+
+    def check_status(self) -> None:
+        if int(self._status.item()) & 1:
+            raise RuntimeError("grouped GEMM pipeline wait timed out (device-side bounded wait expired)")

@@ -209,9 +209,25 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
     for (int ti = 0; ti < tm; ++ti)
       for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});
   }
+  // Wide tiles (32 rows x 128 columns) follow the narrow ones in the same array; the returned
+  // count packs both: narrow in the low 32 bits, wide in the high 32 bits.
+  const size_t narrow = tiles.size();
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const BlockDesc& b = blocks[i];
+    const int tm = (b.m + 31) / 32, tn = (b.n + 127) / 128;
+    for (int ti = 0; ti < tm; ++ti)
+      for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});
+  }
+  const size_t wide = tiles.size() - narrow;
   auto d_blocks = upload_bytes(blocks.data(), blocks.size() * sizeof(BlockDesc), device);
   auto d_tiles = upload_bytes(tiles.data(), tiles.size() * sizeof(TileRef), device);
-  return {d_blocks, d_tiles, static_cast<int64_t>(tiles.size())};
+  return {d_blocks, d_tiles, static_cast<int64_t>(narrow | (wide << 32))};
+}
+
+inline int narrow_tiles(int64_t packed) { return static_cast<int>(packed & 0xffffffff); }
+inline int wide_tiles(int64_t packed) { return static_cast<int>(packed >> 32); }
+inline const TileRef* wide_tile_ptr(const torch::Tensor& tiles, int64_t packed) {
+  return reinterpret_cast<const TileRef*>(tiles.data_ptr()) + narrow_tiles(packed);
 }
 
 void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles,
@@ -222,8 +238,8 @@ void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int6
   c10::cuda::CUDAGuard guard(blocks.device());
   PrologueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
-  a.tiles = reinterpret_cast<const TileRef*>(tiles.data_ptr());
-  a.num_tiles = static_cast<int>(num_tiles);
+  a.tiles = wide_tile_ptr(tiles, num_tiles);
+  a.num_tiles = wide_tiles(num_tiles);
   a.grad_ptrs = reinterpret_cast<const float* const*>(grad_ptrs.data_ptr<int64_t>());
   a.l2_weight_decay = static_cast<float>(l2_weight_decay);
   a.beta1 = static_cast<float>(beta1);
@@ -250,8 +266,8 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
   c10::cuda::CUDAGuard guard(blocks.device());
   EpilogueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
-  a.tiles = reinterpret_cast<const TileRef*>(tiles.data_ptr());
-  a.num_tiles = static_cast<int>(num_tiles);
+  a.tiles = wide_tile_ptr(tiles, num_tiles);
+  a.num_tiles = wide_tiles(num_tiles);
   a.lr = lr.data_ptr<float>();
   a.graft_only = graft_only ? 1 : 0;
   a.graft_kind = static_cast<int>(graft_kind);
@@ -276,8 +292,8 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
 
 void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype) {
   c10::cuda::CUDAGuard guard(blocks.device());
-  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()),
-                        reinterpret_cast<const TileRef*>(tiles.data_ptr()), static_cast<int>(num_tiles),
+  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
+                        wide_tiles(num_tiles),
                         static_cast<int>(dtype), at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
@@ -286,7 +302,7 @@ void eig_scale(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t 
                double eps, bool write_split) {
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_eig_scale(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), reinterpret_cast<const TileRef*>(tiles.data_ptr()),
-                   static_cast<int>(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
+                   narrow_tiles(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
                    static_cast<float>(eps), write_split ? 1 : 0, at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
@@ -294,7 +310,7 @@ void eig_scale(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t 
 void mode_switch(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double coeff, int64_t send_dtype) {
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_mode_switch(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), reinterpret_cast<const TileRef*>(tiles.data_ptr()),
-                     static_cast<int>(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
+                     narrow_tiles(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
                      at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }

@@ -133,7 +133,12 @@ class SignDescentPreconditionerList(PreconditionerList):
 class SpectralDescentPreconditionerList(PreconditionerList):
     """P = orthogonalise(G) for 2-D blocks only."""
 
-    def __init__(self, block_list: tuple[Tensor, ...], preconditioner_config: SpectralDescentPreconditionerConfig) -> None:
+    def __init__(
+        self,
+        block_list: tuple[Tensor, ...],
+        preconditioner_config: SpectralDescentPreconditionerConfig,
+        native_gemm_mode: str | None = None,
+    ) -> None:
         if any(b.dim() != 2 for b in block_list):
             raise ValueError(
                 "Spectral descent can only be used for 2D parameters, or parameters that have been reshaped to 2D. "
@@ -141,14 +146,45 @@ class SpectralDescentPreconditionerList(PreconditionerList):
             )
         super().__init__(block_list)
         self._preconditioner_config = preconditioner_config
+        # "tf32x3" / "tf32": run Newton-Schulz for all blocks together on the grouped tensor-core
+        # GEMM when the gradients are fp32 tensors on an sm_100 device; None: per-block torch path.
+        self._native_gemm_mode = native_gemm_mode
+        self._batched: dict[tuple[tuple[int, int], ...], object] = {}
 
     @profile_decorator
     def update_preconditioners(self, masked_grad_list, step, perform_amortized_computation=False) -> None:
         return
 
+    def _batched_newton_schulz(self, grads: tuple[Tensor, ...], cfg) -> tuple[Tensor, ...] | None:
+        from optimizers_b200.config import NewtonSchulzOrthogonalizationConfig
+
+        if (
+            self._native_gemm_mode is None or not grads or not isinstance(cfg, NewtonSchulzOrthogonalizationConfig)
+            or any(not g.is_cuda or g.dtype != torch.float32 for g in grads)
+            or torch.cuda.get_device_capability(grads[0].device)[0] != 10
+        ):
+            return None
+        from optimizers_b200.matrix.batched import BatchedNewtonSchulz
+        from optimizers_b200.ops import build
+
+        key = tuple((g.shape[0], g.shape[1]) for g in grads)
+        runner = self._batched.get(key)
+        if runner is None:
+            self._batched.clear()  # one live set of buffers: the selection changes rarely
+            runner = BatchedNewtonSchulz(build.load(), list(key), grads[0].device, split=self._native_gemm_mode == "tf32x3")
+            self._batched[key] = runner
+        out = runner(list(grads), cfg.num_iterations, cfg.coefficients)
+        scales = [cfg.scale_by_dims_fn(g.shape[1], g.shape[0]) for g in grads]
+        if any(sc != 1.0 for sc in scales):
+            torch._foreach_mul_(out, scales)
+        return tuple(out)
+
     @profile_decorator
     def precondition(self, masked_grad_list: tuple[Tensor, ...]) -> tuple[Tensor, ...]:
         cfg = self._preconditioner_config.orthogonalization_config
+        native = self._batched_newton_schulz(masked_grad_list, cfg)
+        if native is not None:
+            return native
         return tuple(matrix_orthogonalization(g, orthogonalization_config=cfg) for g in masked_grad_list)
 
     def compress_preconditioner_list(self, local_grad_selector: tuple[bool, ...]) -> None:

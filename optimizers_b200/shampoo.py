@@ -423,7 +423,11 @@ class DistributedShampoo(Optimizer):
             assert group[DISTRIBUTED_CONFIG].target_parameter_dimensionality == 2, (
                 f"group[DISTRIBUTED_CONFIG].target_parameter_dimensionality={group[DISTRIBUTED_CONFIG].target_parameter_dimensionality} must be 2 when using SpectralDescentPreconditionerConfig."
             )
-            return SpectralDescentPreconditionerList(block_list=blocks, preconditioner_config=cfg)
+            nrc = self._native_runtime_config
+            return SpectralDescentPreconditionerList(
+                block_list=blocks, preconditioner_config=cfg,
+                native_gemm_mode=None if nrc.backend == "torch" else nrc.gemm_mode,
+            )
         raise NotImplementedError(f"preconditioner_config={cfg} not supported!")
 
     @torch.no_grad()

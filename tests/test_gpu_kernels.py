@@ -289,3 +289,53 @@ def test_native_newton_refresh_matches_eigen_roots(split):
             assert rel < 2e-3, (F.shape, root, rel)
             checked += 1
     assert checked >= 6
+
+
+@pytest.mark.parametrize("split", [True, False])
+def test_batched_newton_schulz_matches_torch(split):
+    from optimizers_b200.matrix import functions as mf
+    from optimizers_b200.matrix.batched import BatchedNewtonSchulz
+    from optimizers_b200.ops import build
+
+    torch.manual_seed(0)
+    shapes = [(200, 96), (64, 300), (128, 128), (33, 7)]
+    mats = [torch.randn(m, n, device="cuda") for m, n in shapes]
+    coeffs = (3.4445, -4.7750, 2.0315)
+    runner = BatchedNewtonSchulz(build.load(), shapes, torch.device("cuda"), split=split)
+    for _ in range(2):  # buffers are reused across calls
+        got = runner(mats, 5, coeffs)
+    runner.check_status()
+    for A, X in zip(mats, got):
+        want = mf.newton_schulz(A, 5, coeffs)
+        tol = 2e-4 if split else 3e-2
+        assert X.shape == want.shape
+        assert (X - want).abs().max().item() < tol * max(1.0, want.abs().max().item()), (A.shape, (X - want).abs().max())
+
+
+def test_spectral_descent_native_matches_torch():
+    from optimizers_b200 import (
+        DistributedShampoo,
+        NativeRuntimeConfig,
+        SingleDeviceDistributedConfig,
+        SpectralDescentPreconditionerConfig,
+    )
+
+    results = []
+    for backend in ("torch", "auto"):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(96, 160, bias=False), torch.nn.Tanh(), torch.nn.Linear(160, 24, bias=False)).cuda()
+        opt = DistributedShampoo(
+            model.parameters(), lr=1e-2, betas=(0.9, 1.0), epsilon=1e-12, max_preconditioner_dim=4096,
+            preconditioner_config=SpectralDescentPreconditionerConfig(), grafting_config=None,
+            distributed_config=SingleDeviceDistributedConfig(target_parameter_dimensionality=2),
+            native_runtime_config=NativeRuntimeConfig(backend=backend),
+        )
+        g = torch.Generator(device="cuda").manual_seed(1)
+        for _ in range(5):
+            x = torch.randn(32, 96, device="cuda", generator=g)
+            opt.zero_grad()
+            model(x).square().mean().backward()
+            opt.step()
+        results.append([p.detach().clone() for p in model.parameters()])
+    for a, b in zip(*results):
+        assert torch.allclose(a, b, rtol=1e-3, atol=2e-4), (a - b).abs().max()
