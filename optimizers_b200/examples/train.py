@@ -58,7 +58,27 @@ def parse_args(argv=None) -> argparse.Namespace:
     ap.add_argument("--window-size", type=int, default=10)
     ap.add_argument("--checkpoint-dir", default=None)
     ap.add_argument("--metrics-dir", default=None)
-    return ap.parse_args(argv)
+    ap.add_argument("--config", default=None, metavar="YAML",
+                    help="YAML file of option defaults (keys are the option names with underscores, e.g. "
+                    "max_preconditioner_dim: 2048); a bare name is looked up under examples/configs/. "
+                    "Options given on the command line win.")
+    args = ap.parse_args(argv)
+    if args.config is not None:
+        import os
+
+        import yaml
+
+        path = args.config
+        if not os.path.exists(path):
+            path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "configs", f"{args.config}.yaml")
+        with open(path) as fh:
+            preset = yaml.safe_load(fh) or {}
+        unknown = set(preset) - set(vars(args))
+        if unknown:
+            raise SystemExit(f"unknown keys in {path}: {sorted(unknown)}")
+        ap.set_defaults(**preset)
+        args = ap.parse_args(argv)
+    return args
 
 
 def set_seed(seed: int) -> None:
