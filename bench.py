@@ -52,6 +52,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--backend", choices=["auto", "native", "torch"], default="native")
     ap.add_argument("--gemm-mode", choices=["tf32x3", "tf32"], default="tf32x3")
     ap.add_argument("--comm", choices=["p2p", "nccl"], default="p2p", help="multi-GPU path of this framework")
+    ap.add_argument("--parallelism", choices=["ddp", "hsdp"], default="ddp",
+                    help="N > 1: DDP distributor (default; the same strategy at every N) or the hybrid-sharded "
+                    "distributor over FSDP HYBRID_SHARD with a (N / min(N, 4)) x min(N, 4) replicate x shard mesh")
     ap.add_argument("--model", choices=["fused", "plain"], default="fused",
                     help="this framework's arm: its GPT-2 with the fused norm / LM-head-loss kernels, or the plain "
                     "PyTorch model that the reference arm always uses")
@@ -174,7 +177,7 @@ def make_gpt2(n_layer: int):
     return GPT2()
 
 
-def build_optimizer(impl: str, model, world: int, args):
+def build_optimizer(impl: str, model, world: int, args, mesh=None):
     import torch
 
     if impl == "reference":
@@ -186,14 +189,19 @@ def build_optimizer(impl: str, model, world: int, args):
     else:
         import optimizers_b200 as lib
 
-        fused = world > 1 and args.comm == "p2p" and args.backend != "torch"
+        fused = world > 1 and args.comm == "p2p" and args.backend != "torch" and mesh is None
         extra = {
             "native_runtime_config": lib.NativeRuntimeConfig(
                 backend=args.backend, gemm_mode=args.gemm_mode, comm_path="p2p" if fused else "nccl",
                 fuse_gradient_reduction=fused,
             )
         }
-    if world > 1:
+    if mesh is not None:
+        dist_cfg = lib.HSDPDistributedConfig(
+            param_to_metadata=lib.compile_fsdp_parameter_metadata(model), device_mesh=mesh,
+            communication_dtype=torch.bfloat16, num_trainers_per_group=-1,
+        )
+    elif world > 1:
         dist_cfg = lib.DDPDistributedConfig(communication_dtype=torch.bfloat16, num_trainers_per_group=world)
     else:
         dist_cfg = lib.DefaultSingleDeviceDistributedConfig
@@ -267,13 +275,25 @@ def main() -> None:
     train_model = model
     # This framework's p2p path reduces the gradients inside the optimizer's prologue kernel
     # (owners pull their blocks from peer memory), so the model is not wrapped in DDP there.
-    fused_comm = args.impl == "ours" and world > 1 and args.comm == "p2p" and args.backend != "torch"
-    if world > 1 and not fused_comm:
+    hsdp = world > 1 and args.parallelism == "hsdp"
+    mesh = None
+    fused_comm = args.impl == "ours" and world > 1 and args.comm == "p2p" and args.backend != "torch" and not hsdp
+    if hsdp:
+        from torch.distributed.device_mesh import init_device_mesh
+        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy
+
+        shard = min(world, 4)
+        mesh = init_device_mesh("cuda", (world // shard, shard), mesh_dim_names=("replicate", "shard"))
+        train_model = model = FSDP(
+            model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True,
+            device_id=local_rank,
+        )
+    elif world > 1 and not fused_comm:
         train_model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
     elif world > 1:
         for p in model.parameters():
             dist.broadcast(p.data, src=0)
-    opt = build_optimizer(args.impl, model, world, args)
+    opt = build_optimizer(args.impl, model, world, args, mesh)
     if hasattr(opt, "train"):
         opt.train()
 
@@ -375,7 +395,8 @@ def main() -> None:
                 else "plain PyTorch modules",
                 "global_batch": B * world,
                 "seq_len": SEQ,
-                "parallelism": f"dp{world}" if world > 1 else "single",
+                "parallelism": (f"hsdp{world} (replicate {world // min(world, 4)} x shard {min(world, 4)})" if hsdp
+                                else f"dp{world}") if world > 1 else "single",
                 "comm": ("p2p fused reduce-scatter + all-gather kernels" if fused_comm else "nccl") if world > 1 else "none",
                 "optimizer": "DistributedShampoo max_preconditioner_dim=2048 precondition_frequency=100 AdaGrad grafting, fp32 factors",
                 "gemm_mode": args.gemm_mode if args.impl == "ours" else "fp32 (cuBLAS)",

@@ -20,7 +20,8 @@ from the state after every refresh and after ``load_state_dict``.
 The eigenvalue-corrected variant (SOAP) replaces the two apply GEMMs by project -> scale ->
 unproject (``_soap_step``) and updates its second moment in the epilogue of the projection GEMM.
 
-Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 with every dim preconditioned,
+Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 (and contiguous order-3 blocks for
+root-inverse Shampoo) with every dim preconditioned,
 root-inverse or eigenvalue-corrected Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting,
 any weight decay type,
 classic momentum, GPA / Schedule-Free, single-device and DDP distributors (NCCL all-gather, or
@@ -107,15 +108,22 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     for block, sel in zip(
         rec[DISTRIBUTOR].local_blocked_params, plist._local_preconditioned_dims_selector_list, strict=True
     ):
-        if block.dim() > 2:
-            return f"block of order {block.dim()} has no native step yet"
+        if block.dim() > 3 or (block.dim() == 3 and not _order3_ok(block, pc)):
+            return f"block of order {block.dim()} and shape {tuple(block.shape)} has no native step yet"
         if not all(sel):
             return "blocks with unpreconditioned dims have no native step yet"
         if block.numel() == 0:
             return "empty blocks"
-    if any(b.dim() > 2 or b.numel() == 0 for b in rec[DISTRIBUTOR]._global_blocked_params):
+    if any(b.dim() > 3 or b.numel() == 0 or (b.dim() == 3 and not b.is_contiguous()) for b in rec[DISTRIBUTOR]._global_blocked_params):
         return "a block of another rank has no native step"
     return None
+
+
+def _order3_ok(block: Tensor, pc: Any) -> bool:
+    """Order-3 blocks (a, b, c) run natively for root-inverse Shampoo when they are contiguous and
+    a, b are multiples of 4, so that every mode unfolding is an exact, 16-byte aligned 2-D view."""
+    a, b, _ = block.shape
+    return type(pc) is RootInvShampooPreconditionerConfig and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
 
 
 def build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig):
@@ -137,6 +145,7 @@ class _Block:
         "index", "param_view", "grad_slot", "grad_offset", "m", "n", "n_pad", "m_pad", "order", "factors",
         "m1", "v", "mom", "z", "g_hi", "g_lo", "gt_hi", "gt_lo", "f_hi", "f_lo", "tt_hi", "tt_lo", "p",
         "inv_hi", "inv_lo", "ev", "qt_hi", "qt_lo", "t2_hi", "t2_lo",
+        "dims3", "view2d", "aux_g_hi", "aux_g_lo", "aux_gt_hi", "aux_gt_lo", "d1_hi", "d1_lo", "d2_hi", "d2_lo",
     )
 
 
@@ -224,8 +233,15 @@ class NativeGroupEngine:
             b.grad_slot = local_owner[i]
             b.grad_offset = (view.data_ptr() - self._local_params[b.grad_slot].data_ptr()) // 4
             b.order = view.dim()
+            b.dims3 = None
+            b.view2d = view
             if view.dim() == 1:
                 b.m, b.n = 1, view.shape[0]
+            elif view.dim() == 3:
+                # (a, b, c) is presented to the pointwise kernels as (a*b) x c.
+                b.dims3 = tuple(view.shape)
+                b.m, b.n = view.shape[0] * view.shape[1], view.shape[2]
+                b.view2d = view.view(b.m, b.n)
             else:
                 b.m, b.n = view.shape
             b.n_pad, b.m_pad = _pad4(b.n), _pad4(b.m)
@@ -236,6 +252,11 @@ class NativeGroupEngine:
             b.z = zs[i] if zs is not None else None
             two_d = b.order == 2
             need_g = two_d or self._soap
+            if b.dims3 is not None:
+                self._alloc_order3(b, zeros)
+                blocks.append(b)
+                continue
+            b.aux_g_hi = b.aux_g_lo = b.aux_gt_hi = b.aux_gt_lo = b.d1_hi = b.d1_lo = b.d2_hi = b.d2_lo = None
             b.g_hi = zeros(b.m, b.n_pad) if need_g else None
             b.g_lo = zeros(b.m, b.n_pad) if need_g and self._split else None
             b.gt_hi = zeros(b.n, b.m_pad)
@@ -258,6 +279,28 @@ class NativeGroupEngine:
                 b.t2_lo = zeros(b.n, b.m_pad) if two_d and self._split else None
             blocks.append(b)
         self._blocks = blocks
+
+    def _alloc_order3(self, b: _Block, zeros) -> None:
+        """Operand buffers of an order-3 block (a, b, c).  Mode unfoldings, all K-major:
+        X_a = [a, b*c] (``aux_g``), X_b = [b, c*a] (``aux_gt``, the transpose of X_a, re-viewed),
+        X_c = [c, a*b] (``gt``, the transpose of the (a*b) x c view).  The preconditioner chain
+        contracts the fastest index of the current layout and emits the new index slowest, so three
+        GEMMs walk (a,b,c) -> (c,a,b) -> (b,c,a) -> (a,b,c) without any transposition pass."""
+        a, bb, c = b.dims3
+        sp = self._split
+        pair = lambda r, cols: (zeros(r, cols), zeros(r, cols) if sp else None)  # noqa: E731
+        b.g_hi = b.g_lo = None
+        b.gt_hi, b.gt_lo = pair(c, a * bb)
+        b.f_hi, b.f_lo = pair(a * bb, _pad4(c))
+        b.aux_g_hi, b.aux_g_lo = pair(a, bb * c)
+        b.aux_gt_hi, b.aux_gt_lo = pair(bb * c, a)
+        b.d1_hi, b.d1_lo = pair(c, a * bb)
+        b.d2_hi, b.d2_lo = pair(bb, c * a)
+        b.tt_hi = b.tt_lo = None
+        b.p = zeros(a, bb * c)
+        b.inv_hi = [zeros(d, _pad4(d)) for d in b.dims3]
+        b.inv_lo = [zeros(d, _pad4(d)) if sp else None for d in b.dims3]
+        b.ev = b.qt_hi = b.qt_lo = b.t2_hi = b.t2_lo = None
 
     def _send_ptr(self, b: _Block) -> int:
         if not self._ddp or self._p2p:
@@ -324,10 +367,19 @@ class NativeGroupEngine:
         for b in blocks:
             specs.append(
                 (
-                    b.param_view, b.grad_offset, b.grad_slot, b.m, b.n, b.n_pad, b.m_pad, b.m1, b.v, b.mom, b.z,
+                    b.view2d, b.grad_offset, b.grad_slot, b.m, b.n, b.n_pad, b.m_pad, b.m1, b.v, b.mom, b.z,
                     b.g_hi, b.g_lo, b.gt_hi, b.gt_lo, b.f_hi, b.f_lo, b.p, self._norms[b.index], self._send_ptr(b),
-                    self._slot_offset(b), b.ev,
+                    self._slot_offset(b), b.ev, 0,
                 )
+            )
+        for b in blocks:
+            if b.dims3 is None:
+                continue
+            # Auxiliary a x (b*c) view: only the (hi, lo) operands of the mode-a and mode-b unfoldings.
+            a, bb, c = b.dims3
+            specs.append(
+                (b.param_view.view(a, bb * c), b.grad_offset, b.grad_slot, a, bb * c, bb * c, a)
+                + (None,) * 4 + (b.aux_g_hi, b.aux_g_lo, b.aux_gt_hi, b.aux_gt_lo) + (None,) * 4 + (0, 0, None, 1)
             )
         self._table = ext.build_block_table(specs)
         if self._soap:
@@ -337,10 +389,34 @@ class NativeGroupEngine:
         def op(t: Tensor, rows: int, k: int) -> Tensor:
             return t[:, :k] if t.shape[1] != k else t
 
-        syrk, gemm1, gemm2 = [], [], []
+        syrk, gemm0, gemm1, gemm2 = [], [], [], []
         pack_flag = F.FLAG_PACKED_C if self._packing else 0
+        sp = self._split
+
+        def chained(a_hi, a_lo, b_hi, b_lo, out_hi, out_lo):
+            """Product whose result is only the operand of the next product of the chain."""
+            if sp:
+                return (a_hi, a_lo, b_hi, b_lo, None, out_hi, out_lo, None, 0, out_hi.stride(0), F.FLAG_NO_C | F.FLAG_SPLIT_OUT, False)
+            return (a_hi, None, b_hi, None, out_hi, None, None, None, out_hi.stride(0), 0, 0, False)
+
         for b in blocks:
             fm = b.factors.factor_matrices
+            if b.dims3 is not None:
+                a, bb, c = b.dims3
+                lo = lambda t: t if sp else None  # noqa: E731
+                xa = (b.aux_g_hi, lo(b.aux_g_lo))
+                xb = (b.aux_gt_hi.view(bb, c * a), lo(b.aux_gt_lo.view(bb, c * a) if sp else None))
+                xc = (b.gt_hi, lo(b.gt_lo))
+                for (x_hi, x_lo), factor, d in ((xa, fm[0], a), (xb, fm[1], bb), (xc, fm[2], c)):
+                    syrk.append((x_hi, x_lo, x_hi, x_lo, factor, None, None, None, d, 0, pack_flag, self._packing))
+                inv = [(b.inv_hi[k][:, :d], lo(b.inv_lo[k][:, :d] if sp else None)) for k, d in enumerate(b.dims3)]
+                f = (b.f_hi[:, :c], lo(b.f_lo[:, :c] if sp else None))
+                gemm0.append(chained(*inv[2], *f, b.d1_hi, b.d1_lo))
+                d1 = (b.d1_hi.view(c * a, bb), lo(b.d1_lo.view(c * a, bb) if sp else None))
+                gemm1.append(chained(*inv[1], *d1, b.d2_hi, b.d2_lo))
+                d2 = (b.d2_hi.view(bb * c, a), lo(b.d2_lo.view(bb * c, a) if sp else None))
+                gemm2.append((*inv[0], *d2, b.p, None, None, self._norms[b.index, 1:2], bb * c, 0, F.FLAG_SUMSQ, False))
+                continue
             two_d = b.order == 2
             if two_d:
                 a_hi, a_lo = op(b.g_hi, b.m, b.n), (op(b.g_lo, b.m, b.n) if self._split else None)
@@ -365,6 +441,7 @@ class NativeGroupEngine:
                 r_hi, r_lo = op(b.inv_hi[0], b.n, b.n), (op(b.inv_lo[0], b.n, b.n) if self._split else None)
                 gemm2.append((f_hi, f_lo, r_hi, r_lo, b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
         self._syrk_plan = ext.build_gemm_plan(syrk)
+        self._gemm0_plan = ext.build_gemm_plan(gemm0) if gemm0 else None
         self._gemm1_plan = ext.build_gemm_plan(gemm1) if gemm1 else None
         self._gemm2_plan = ext.build_gemm_plan(gemm2)
 
@@ -468,7 +545,7 @@ class NativeGroupEngine:
             return False
         if getattr(self, "_full_table", None) is None:
             specs = [
-                (b.param_view, 0, 0, b.m, b.n, b.n_pad, b.m_pad, None, None, None, b.z) + (None,) * 8 + (0, 0, None)
+                (b.view2d, 0, 0, b.m, b.n, b.n_pad, b.m_pad, None, None, None, b.z) + (None,) * 8 + (0, 0, None, 0)
                 for b in self._blocks
             ]
             self._full_table = self._ext.build_block_table(specs) if specs else ()
@@ -592,6 +669,9 @@ class NativeGroupEngine:
         if self._soap:
             launches += self._soap_step(plist, graft_only)
         elif not graft_only:
+            if self._gemm0_plan is not None:
+                ext.run_gemm_plan(*self._gemm0_plan, 1.0, 0.0, self._split, self._status)
+                launches += 1
             if self._gemm1_plan is not None:
                 ext.run_gemm_plan(*self._gemm1_plan, 1.0, 0.0, self._split, self._status)
                 launches += 1
@@ -687,8 +767,10 @@ class NativeGroupEngine:
             for view, off, on in zip(dist_._global_blocked_params, dist_._global_block_byte_offsets, sel, strict=True):
                 if not on:
                     continue
+                if view.dim() == 3:
+                    view = view.view(view.shape[0] * view.shape[1], view.shape[2])
                 m, n = (1, view.shape[0]) if view.dim() == 1 else view.shape
-                specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 12 + (base + off, off, None))
+                specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 12 + (base + off, off, None, 0))
             self._gather_table = self._ext.build_block_table(specs) if specs else None
             self._gather_for = sel
         if self._gather_table is not None:

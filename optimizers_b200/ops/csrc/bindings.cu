@@ -169,7 +169,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
   torch::Device device(torch::kCPU);
   for (size_t i = 0; i < specs.size(); ++i) {
     const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 22, "block spec must have 22 fields");
+    TORCH_CHECK(s.size() == 23, "block spec must have 23 fields");
     BlockDesc& b = blocks[i];
     std::memset(&b, 0, sizeof(b));
     auto param = s[0].cast<torch::Tensor>();
@@ -205,6 +205,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
     b.send = reinterpret_cast<void*>(s[19].cast<int64_t>());
     b.slot_offset = s[20].cast<int64_t>();
     b.ev = opt(21);
+    b.aux = s[22].cast<int>();
     const int tm = (b.m + 31) / 32, tn = (b.n + 31) / 32;
     for (int ti = 0; ti < tm; ++ti)
       for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});

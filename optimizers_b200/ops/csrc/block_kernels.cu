@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(256, 3) grad_prologue_kernel(PrologueArgs a) {
     const int j = j0 + 4 * lane;
     const int cnt = b.n - j < 4 ? b.n - j : 4;  // valid columns of this lane's group (<= 0: none)
     const bool want_t = b.gt_hi != nullptr;
-    const bool has_m1 = b.m1 != nullptr, has_v = a.graft_kind == kGraftAdaGrad, l2 = a.l2_weight_decay != 0.f;
+    const bool has_m1 = b.m1 != nullptr, has_v = a.graft_kind == kGraftAdaGrad && b.v != nullptr;
+    const bool l2 = a.l2_weight_decay != 0.f, graft = a.graft_kind != kGraftNone && b.norms != nullptr;
     bool vec = ((b.n | b.param_pitch | b.grad_offset) & 3) == 0 && aligned16(b.param) && aligned16(b.m1) && aligned16(b.v);
     for (int r = 0; r < n_src; ++r) vec = vec && aligned16(srcs[r]);
 
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(256, 3) grad_prologue_kernel(PrologueArgs a) {
           fl[k] = 0.f;
         }
         vn[k] = 0.f;
-        if (a.graft_kind != kGraftNone) {
+        if (graft) {
           if (has_v) vn[k] = a.graft_beta2 * vo[r][k] + a.graft_weight * gk * gk;
           const float gd = graft_direction(f, vn[k], a.graft_kind, a.graft_bias_correction2, a.graft_epsilon);
           if (live) sq += gd * gd;
@@ -222,8 +223,10 @@ __global__ void __launch_bounds__(256, 3) grad_prologue_kernel(PrologueArgs a) {
           store4(b.g_hi + o, hi, true, 4);
           if (a.write_split) store4(b.g_lo + o, lo, true, 4);
         }
-        store4(b.f_hi + o, fh, true, 4);
-        if (a.write_split) store4(b.f_lo + o, fl, true, 4);
+        if (b.f_hi != nullptr) {
+          store4(b.f_hi + o, fh, true, 4);
+          if (a.write_split) store4(b.f_lo + o, fl, true, 4);
+        }
         if (has_m1) store4(b.m1 + e, mn, vec, cnt);
         if (has_v) store4(b.v + e, vn, vec, cnt);
       }
@@ -254,14 +257,14 @@ __global__ void __launch_bounds__(256, 3) grad_prologue_kernel(PrologueArgs a) {
         }
       }
     }
-    if (a.graft_kind != kGraftNone) {
+    if (graft) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
       if (lane == 0) red[warp] = sq;
     }
     if (bad) atomicOr(a.status, 2);
     __syncthreads();
-    if (a.graft_kind != kGraftNone && threadIdx.x == 0) {
+    if (graft && threadIdx.x == 0) {
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < 8; ++w) s += red[w];
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(256, kPlain ? 3 : 2) direction_epilogue_kernel
     const BlockDesc& b = a.blocks[ref.block];
     const int i0 = ref.ti * kTile, j = ref.tj * kWide + 4 * lane;
     const int cnt = b.n - j < 4 ? b.n - j : 4;
-    if (cnt <= 0) continue;
+    if (cnt <= 0 || b.aux) continue;
     float scale = 1.f;
     if (!a.graft_only && a.graft_kind != kGraftNone) scale = sqrtf(b.norms[0]) / (sqrtf(b.norms[1]) + 1e-16f);
     const bool has_v = a.graft_kind == kGraftAdaGrad;

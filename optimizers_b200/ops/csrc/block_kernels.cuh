@@ -22,7 +22,8 @@
 
 namespace ob200 {
 
-// One 2-D block (m x n).  1-D blocks are presented as 1 x n.
+// One 2-D block (m x n).  1-D blocks are presented as 1 x n; a contiguous order-3 block (a, b, c)
+// as (a*b) x c, plus an auxiliary descriptor a x (b*c) for the operand layouts of the other modes.
 struct BlockDesc {
   float* param;        // view into the parameter; element (i, j) at param[i * param_pitch + j]
   long long param_pitch;
@@ -45,6 +46,10 @@ struct BlockDesc {
   void* send;             // all-gather send slot in the communication dtype (null: update params)
   long long slot_offset;  // byte offset of the block's slot inside the gather buffer (peer push)
   float* ev;              // eigenvalue-corrected second moment [m, n] (null unless SOAP)
+  int aux;                // 1: a second 2-D view of an order-3 block that only needs the operand
+                          // splits of its gradient (g_*, gt_*); it carries no state (m1, v, f_* and
+                          // norms are null) and the epilogue kernels skip it
+  int pad_;
 };
 
 struct TileRef {
