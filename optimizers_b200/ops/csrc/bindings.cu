@@ -454,6 +454,33 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gpa_table(const std::vec
   return {d_descs, d_chunks, static_cast<int64_t>(chunks.size())};
 }
 
+// specs: (source address, destination address, bytes); addresses may belong to peer GPUs.
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_copy_table(const std::vector<std::tuple<int64_t, int64_t, int64_t>>& specs,
+                                                                   int64_t device_index) {
+  std::vector<CopyDesc> descs;
+  std::vector<int2> chunks;
+  for (const auto& [src, dst, bytes] : specs) {
+    TORCH_CHECK(bytes >= 0 && bytes % 4 == 0 && (src % 4) == 0 && (dst % 4) == 0, "peer_copy: 4-byte granularity");
+    if (bytes == 0) continue;
+    const int idx = static_cast<int>(descs.size());
+    descs.push_back({reinterpret_cast<const void*>(src), reinterpret_cast<void*>(dst), bytes});
+    const int64_t n_chunks = (bytes + kCopyChunkBytes - 1) / kCopyChunkBytes;
+    for (int64_t c = 0; c < n_chunks; ++c) chunks.push_back(make_int2(idx, static_cast<int>(c)));
+  }
+  torch::Device device(torch::kCUDA, static_cast<c10::DeviceIndex>(device_index));
+  auto d_descs = upload_bytes(descs.data(), descs.size() * sizeof(CopyDesc), device);
+  auto d_chunks = upload_bytes(chunks.data(), chunks.size() * sizeof(int2), device);
+  return {d_descs, d_chunks, static_cast<int64_t>(chunks.size())};
+}
+
+void peer_copy(const torch::Tensor& table, const torch::Tensor& chunks, int64_t num_chunks) {
+  if (num_chunks == 0) return;
+  c10::cuda::CUDAGuard guard(table.device());
+  launch_peer_copy(reinterpret_cast<const CopyDesc*>(table.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
+                   static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -479,5 +506,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_gpa_table", &build_gpa_table);
   m.def("gpa_adamw_step", &gpa_adamw_step);
   m.def("gpa_lerp", &gpa_lerp);
+  m.def("build_copy_table", &build_copy_table);
+  m.def("peer_copy", &peer_copy);
   ob200::register_model_ops(m);
 }

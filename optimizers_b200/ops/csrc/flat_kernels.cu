@@ -114,6 +114,36 @@ __global__ void __launch_bounds__(256) identity_error_kernel(const MatOp* __rest
   }
 }
 
+__global__ void __launch_bounds__(256) peer_copy_kernel(const CopyDesc* __restrict__ table,
+                                                        const int2* __restrict__ chunks, int num_chunks) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const CopyDesc d = table[ref.x];
+    const long long begin = static_cast<long long>(ref.y) * kCopyChunkBytes;
+    const long long left = d.bytes - begin;
+    const int n = static_cast<int>(left < kCopyChunkBytes ? left : kCopyChunkBytes);
+    const char* src = static_cast<const char*>(d.src) + begin;
+    char* dst = static_cast<char*>(d.dst) + begin;
+    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+      const int nv = n / 16;
+      const uint4* s4 = reinterpret_cast<const uint4*>(src);
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      // Four independent 16-byte loads per thread before the first store.
+      int i = threadIdx.x;
+      for (; i + 3 * 256 < nv; i += 4 * 256) {
+        const uint4 a = s4[i], b = s4[i + 256], e = s4[i + 512], f = s4[i + 768];
+        d4[i] = a; d4[i + 256] = b; d4[i + 512] = e; d4[i + 768] = f;
+      }
+      for (; i < nv; i += 256) d4[i] = s4[i];
+      for (int k = nv * 16 / 4 + threadIdx.x; k < n / 4; k += 256)
+        reinterpret_cast<uint32_t*>(dst)[k] = reinterpret_cast<const uint32_t*>(src)[k];
+    } else {
+      for (int k = threadIdx.x; k < n / 4; k += 256)
+        reinterpret_cast<uint32_t*>(dst)[k] = reinterpret_cast<const uint32_t*>(src)[k];
+    }
+  }
+}
+
 struct GpaScalars {
   float lr, beta1, beta2, eps, bc1, bc2, wd, avg_coeff, mu_y;
   int wd_on_y;
@@ -205,6 +235,12 @@ void launch_affine_identity_split(const MatOp* ops, const int2* chunks, int num_
 void launch_identity_error(const MatOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream) {
   if (num_chunks <= 0) return;
   identity_error_kernel<<<grid_for(num_chunks), 256, 0, stream>>>(ops, chunks, num_chunks);
+}
+
+void launch_peer_copy(const CopyDesc* table, const int2* chunks, int num_chunks, cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  const int cap = 148 * 8;
+  peer_copy_kernel<<<num_chunks < cap ? num_chunks : cap, 256, 0, stream>>>(table, chunks, num_chunks);
 }
 
 void launch_tf32_split(const float* src, long long src_pitch, float* hi, float* lo, long long dst_pitch, int rows,

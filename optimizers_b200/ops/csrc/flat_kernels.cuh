@@ -25,6 +25,23 @@ struct GpaTensorDesc {
   int pad_;
 };
 
+// One contiguous copy of a grouped scatter / gather over local and peer memory.
+struct CopyDesc {
+  const void* src;
+  void* dst;
+  long long bytes;  // multiple of 4
+};
+
+constexpr int kCopyChunkBytes = 64 * 1024;  // bytes handled by one CTA iteration
+
+// peer_copy: every (src, dst, bytes) entry of the table in one launch; either side may be another
+// GPU's memory (plain loads / stores over NVLink).  This is the data movement of the lossless
+// fully-shard exchange: gradient shards pushed straight from the local shard tensors into the
+// owners' receive buffers, updated parameter chunks pushed from the owners' full copies into the
+// shard holders' receive buffers; packing into a send buffer and the collective call are gone
+// (reference: distributed_shampoo/distributor/_shampoo_fully_shard_utils.py:519-588, :806-835).
+void launch_peer_copy(const CopyDesc* table, const int2* chunks, int num_chunks, cudaStream_t stream);
+
 // One square matrix of a grouped pointwise pass over many matrices of different sizes.
 struct MatOp {
   const float* src;  // d x d, row pitch ld_src

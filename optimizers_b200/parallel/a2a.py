@@ -22,6 +22,7 @@ Reference counterparts: ``distributed_shampoo/utils/shampoo_fully_shard_utils.py
 from __future__ import annotations
 
 import abc
+import contextlib
 import logging
 import math
 from collections.abc import Callable
@@ -63,6 +64,21 @@ def _compute_param_chunk_sizes(params: tuple[DTensor, ...], group_size: int) -> 
     return out
 
 
+_default_comm_path = "nccl"
+
+
+@contextlib.contextmanager
+def exchange_comm_path(comm_path: str):
+    """Contexts created inside use ``comm_path`` ("nccl": all_to_all collective; "p2p": stores
+    into peer memory from inside one kernel) unless they are given one explicitly."""
+    global _default_comm_path
+    previous, _default_comm_path = _default_comm_path, comm_path
+    try:
+        yield
+    finally:
+        _default_comm_path = previous
+
+
 def _views(buffer: Tensor, sizes: list[int]) -> list[Tensor]:
     ends = list(accumulate(sizes))
     return [buffer[e - s : e] for s, e in zip(sizes, ends, strict=True)]
@@ -78,6 +94,7 @@ class AllToAllContext(abc.ABC):
         assigned_params_mask: tuple[bool, ...],
         dist_group: dist.ProcessGroup,
         owner_ranks: list[int] | None = None,
+        comm_path: str | None = None,
     ) -> None:
         if not params:
             raise ValueError("params cannot be empty")
@@ -106,6 +123,9 @@ class AllToAllContext(abc.ABC):
         self._total_send_size, self._total_recv_size = sum(self._send_sizes), sum(self._recv_sizes)
         self._send_buffer = torch.empty(self._total_send_size, dtype=self._dtype, device=self._device)
         self._recv_buffer = torch.empty(self._total_recv_size, dtype=self._dtype, device=self._device)
+        self._p2p = (comm_path or _default_comm_path) == "p2p" and self._device.type == "cuda" and n > 1
+        if self._p2p:
+            self._setup_peer_exchange()
         self._send_list = _views(self._send_buffer, self._send_sizes)
         self._recv_list = _views(self._recv_buffer, self._recv_sizes)
         self._precompute_subclass_metadata()
@@ -115,6 +135,79 @@ class AllToAllContext(abc.ABC):
 
     @abc.abstractmethod
     def _precompute_subclass_metadata(self) -> None: ...
+
+    # ------------------------------------------------------------------------------------------
+    # Peer-memory exchange (comm_path="p2p"): the receive buffer lives in memory every rank of the
+    # group can address; senders store their sections straight into it from the source tensors.
+    # ------------------------------------------------------------------------------------------
+    def _section_sizes(self, sender: int, receiver: int) -> int:
+        """Elements ``sender`` delivers to ``receiver`` (known to every rank from the shared metadata)."""
+        raise NotImplementedError
+
+    def _setup_peer_exchange(self) -> None:
+        from optimizers_b200.ops import build
+        from optimizers_b200.parallel.symm_arena import SymmetricArena
+
+        n, es = self._group_size, torch.empty(0, dtype=self._dtype).element_size()
+        if es != 4:
+            raise NotImplementedError("comm_path='p2p' of the lossless exchange supports 4-byte parameter dtypes")
+        if n > 8:
+            raise RuntimeError("comm_path='p2p' needs all ranks of the shard group on one NVLink domain (at most 8)")
+        self._ext = build.load()
+        sizes = [[self._section_sizes(q, r) for r in range(n)] for q in range(n)]
+        assert [sizes[q][self._rank] for q in range(n)] == self._recv_sizes
+        assert sizes[self._rank] == self._send_sizes
+        recv_total = max(sum(sizes[q][r] for q in range(n)) for r in range(n))
+        self._arena = SymmetricArena({"recv": recv_total * es, "flags": 2 * 32 * 4}, self._device, self._dist_group)
+        self._recv_buffer = self._arena.region("recv", self._total_recv_size * es).view(self._dtype)
+        # byte address of this rank's section inside every receiver's buffer
+        bases = self._arena.peer_addresses("recv")
+        self._dest_base = [bases[r] + sum(sizes[q][r] for q in range(self._rank)) * es for r in range(n)]
+        self._flags = self._arena.region("flags").view(torch.int32)
+        self._flag_bases = [
+            torch.tensor([a + k * 128 for a in self._arena.peer_addresses("flags")], dtype=torch.int64, device=self._device)
+            for k in range(2)
+        ]
+        self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
+        self._barrier_seq = 0
+        self._zeros = torch.zeros(0, dtype=self._dtype, device=self._device)
+
+    def _peer_barrier(self, which: int) -> None:
+        self._ext.peer_barrier(
+            self._flags[which * 32 : which * 32 + 32], self._flag_bases[which], self._rank, self._group_size,
+            self._barrier_seq, self._status,
+        )
+
+    def _execute_peer_push(self, sections: list[list[Tensor | int]]) -> None:
+        """``sections[r]``: the tensors (or, for an absent source, the element count to zero-fill)
+        that make up this rank's section for receiver ``r``, in section order."""
+        es = 4
+        self._barrier_seq += 1
+        self._peer_barrier(0)  # every receiver has consumed the previous exchange
+        specs = []
+        need_zero = max((x for sec in sections for x in sec if isinstance(x, int)), default=0)
+        if need_zero > self._zeros.numel():
+            self._zeros = torch.zeros(need_zero, dtype=self._dtype, device=self._device)
+        keep = []
+        for r, sec in enumerate(sections):
+            at = self._dest_base[r]
+            for x in sec:
+                if isinstance(x, int):
+                    src, count = self._zeros, x
+                else:
+                    src = x if x.is_contiguous() else x.contiguous()
+                    count = src.numel()
+                    keep.append(src)
+                specs.append((src.data_ptr(), at, count * es))
+                at += count * es
+        table = self._ext.build_copy_table(specs, self._device.index)
+        self._ext.peer_copy(*table)
+        self._peer_barrier(1)  # every sender's stores have landed
+        self._keep_alive = (keep, table)
+
+    def check_status(self) -> None:
+        if self._p2p and int(self._status.item()) & 4:
+            raise RuntimeError("a peer rank did not reach the exchange barrier in time (bounded device-side wait expired)")
 
     def _execute_all_to_all(self) -> None:
         # The sections are contiguous in the flat buffers, so the single-tensor form applies; it
@@ -204,9 +297,22 @@ class GatherGradientsContext(AllToAllContext):
                 out[i] = full.squeeze() if not shape else full.view(shape)
         return out
 
+    def _section_sizes(self, sender: int, receiver: int) -> int:
+        return sum(self._param_chunk_sizes[i][sender] for i in self._params_owned_by[receiver])
+
     def _exchange(self, source: Callable[[int], Tensor | None], present: list[bool]) -> list[Tensor | None]:
-        self._pack_send_buffer(source)
-        self._execute_all_to_all()
+        if self._p2p:
+            sections: list[list[Tensor | int]] = [[] for _ in range(self._group_size)]
+            for r in range(self._group_size):
+                for i in self._params_owned_by[r]:
+                    size = self._param_chunk_sizes[i][self._rank]
+                    if size > 0:
+                        data = source(i)
+                        sections[r].append(size if data is None else data[:size])
+            self._execute_peer_push(sections)
+        else:
+            self._pack_send_buffer(source)
+            self._execute_all_to_all()
         # Clones: the persistent buffers are overwritten by the next exchange.
         return [t.clone() if t is not None else None for t in self._unpack_recv_buffer(present)]
 
@@ -232,6 +338,9 @@ class RedistributeParamsContext(AllToAllContext):
     def _compute_send_recv_sizes(self) -> tuple[list[int], list[int]]:
         n = self._group_size
         return [self._chunks_of_mine_on(r) for r in range(n)], [self._shards_for_owner(r) for r in range(n)]
+
+    def _section_sizes(self, sender: int, receiver: int) -> int:
+        return sum(self._param_chunk_sizes[i][receiver] for i in self._params_owned_by[sender])
 
     def _precompute_subclass_metadata(self) -> None:
         n = self._group_size
@@ -280,10 +389,16 @@ class RedistributeParamsContext(AllToAllContext):
             parts += [full.new_empty(0)] * (n - len(parts))
             chunks.append(parts)
         src = [chunks[self._local_position[i]][r] for i, r, _ in self._send_plan]
-        dst = [view for _, _, view in self._send_plan]
-        if dst:
-            torch._foreach_copy_(dst, src)
-        self._execute_all_to_all()
+        if self._p2p:
+            sections: list[list[Tensor | int]] = [[] for _ in range(n)]
+            for (_, r, _), piece in zip(self._send_plan, src, strict=True):
+                sections[r].append(piece)
+            self._execute_peer_push(sections)
+        else:
+            dst = [view for _, _, view in self._send_plan]
+            if dst:
+                torch._foreach_copy_(dst, src)
+            self._execute_all_to_all()
         if self._recv_dst:
             torch._foreach_copy_(self._recv_dst, self._recv_src)
 

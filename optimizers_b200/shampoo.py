@@ -360,7 +360,14 @@ class DistributedShampoo(Optimizer):
             if not group[PARAMS]:
                 raise ValueError(f"Shampoo got an empty parameter group={group}")
             cls = self._select_distributor_class(group[DISTRIBUTED_CONFIG])
-            rec[DISTRIBUTOR] = cls(group, self._runtime_config)
+            nrc = self._native_runtime_config
+            on_gpu = group[PARAMS][0].device.type == "cuda"
+            # The lossless distributors' exchange follows the native comm path (peer-memory pushes
+            # instead of all_to_all) unless the torch back-end was asked for.
+            from optimizers_b200.parallel.a2a import exchange_comm_path
+
+            with exchange_comm_path(nrc.comm_path if (nrc.backend != "torch" and on_gpu) else "nccl"):
+                rec[DISTRIBUTOR] = cls(group, self._runtime_config)
             if not rec[DISTRIBUTOR].local_blocked_params:
                 logger.warning(
                     "There is no params assigned to the current rank. "

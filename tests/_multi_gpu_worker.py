@@ -71,7 +71,8 @@ def sharded_main() -> None:
     """``<backend>:<strategy>``: train the MLP under one of the sharded strategies with the torch
     or the native step and write rank 0's view of the full final parameters."""
     mode, out = sys.argv[1], sys.argv[2]
-    backend, strategy = mode.split(":")
+    backend, strategy, *rest = mode.split(":")
+    comm_path = rest[0] if rest else "nccl"
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, fully_shard, ShardingStrategy
     from torch.distributed.tensor import DTensor
@@ -126,7 +127,7 @@ def sharded_main() -> None:
         model.parameters(), lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64,
         precondition_frequency=3, start_preconditioning_step=3, weight_decay=1e-2,
         grafting_config=AdaGradPreconditionerConfig(epsilon=1e-8), distributed_config=dc,
-        native_runtime_config=NativeRuntimeConfig(backend=backend),
+        native_runtime_config=NativeRuntimeConfig(backend=backend, comm_path=comm_path),
     )
     g = torch.Generator(device="cuda").manual_seed(1)
     for _ in range(8):
@@ -136,6 +137,13 @@ def sharded_main() -> None:
         opt.zero_grad()
         torch.nn.functional.cross_entropy(model(x[shard]), y[shard]).backward()
         opt.step()
+    if comm_path == "p2p":
+        for rec in opt._per_group_state_lists:
+            d = rec["distributor"]
+            if d._gather_grads_ctx._group_size > 1:  # a shard group of one rank has nothing to exchange
+                assert d._gather_grads_ctx._p2p and d._redistribute_ctx._p2p
+            d._gather_grads_ctx.check_status()
+            d._redistribute_ctx.check_status()
     engines = [rec.get("native_engine") for rec in opt._per_group_state_lists]
     assert all((e is not None) == (backend == "native") for e in engines), engines
     for e in engines:

@@ -48,3 +48,17 @@ def test_native_sharded_matches_torch(tmp_path, strategy):
     _run(f"native:{strategy}", n, got, 29544)
     for a, b in zip(torch.load(ref), torch.load(got)):
         assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("strategy", ["fully_shard_rr", "hybrid_shard_rr"])
+def test_lossless_peer_memory_exchange_matches_all_to_all(tmp_path, strategy):
+    """ROUND_ROBIN lossless distributors with the exchange done by one kernel that stores into
+    the receivers' memory over NVLink (comm_path="p2p") against the all_to_all collective."""
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    ref, got = str(tmp_path / "ref.pt"), str(tmp_path / "got.pt")
+    _run(f"native:{strategy}", n, ref, 29545)
+    _run(f"native:{strategy}:p2p", n, got, 29546)
+    # The exchange moves bits; the engine's norm reductions use atomics, so two runs agree to an ulp.
+    for a, b in zip(torch.load(ref), torch.load(got)):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (a - b).abs().max()
