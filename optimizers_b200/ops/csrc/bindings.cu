@@ -206,29 +206,22 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
     b.slot_offset = s[20].cast<int64_t>();
     b.ev = opt(21);
     b.aux = s[22].cast<int>();
-    const int tm = (b.m + 31) / 32, tn = (b.n + 31) / 32;
-    for (int ti = 0; ti < tm; ++ti)
-      for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});
   }
-  // Wide tiles (32 rows x 128 columns) follow the narrow ones in the same array; the returned
-  // count packs both: narrow in the low 32 bits, wide in the high 32 bits.
-  const size_t narrow = tiles.size();
+  // Tiles of 32 rows x 128 columns.
   for (size_t i = 0; i < specs.size(); ++i) {
     const BlockDesc& b = blocks[i];
     const int tm = (b.m + 31) / 32, tn = (b.n + 127) / 128;
     for (int ti = 0; ti < tm; ++ti)
       for (int tj = 0; tj < tn; ++tj) tiles.push_back({static_cast<int>(i), ti, tj, 0});
   }
-  const size_t wide = tiles.size() - narrow;
   auto d_blocks = upload_bytes(blocks.data(), blocks.size() * sizeof(BlockDesc), device);
   auto d_tiles = upload_bytes(tiles.data(), tiles.size() * sizeof(TileRef), device);
-  return {d_blocks, d_tiles, static_cast<int64_t>(narrow | (wide << 32))};
+  return {d_blocks, d_tiles, static_cast<int64_t>(tiles.size())};
 }
 
-inline int narrow_tiles(int64_t packed) { return static_cast<int>(packed & 0xffffffff); }
-inline int wide_tiles(int64_t packed) { return static_cast<int>(packed >> 32); }
-inline const TileRef* wide_tile_ptr(const torch::Tensor& tiles, int64_t packed) {
-  return reinterpret_cast<const TileRef*>(tiles.data_ptr()) + narrow_tiles(packed);
+inline int wide_tiles(int64_t count) { return static_cast<int>(count); }
+inline const TileRef* wide_tile_ptr(const torch::Tensor& tiles, int64_t) {
+  return reinterpret_cast<const TileRef*>(tiles.data_ptr());
 }
 
 void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles,
@@ -302,16 +295,16 @@ void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int
 void eig_scale(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double bc2, double inv_root,
                double eps, bool write_split) {
   c10::cuda::CUDAGuard guard(blocks.device());
-  launch_eig_scale(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), reinterpret_cast<const TileRef*>(tiles.data_ptr()),
-                   narrow_tiles(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
+  launch_eig_scale(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
+                   wide_tiles(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
                    static_cast<float>(eps), write_split ? 1 : 0, at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 void mode_switch(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double coeff, int64_t send_dtype) {
   c10::cuda::CUDAGuard guard(blocks.device());
-  launch_mode_switch(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), reinterpret_cast<const TileRef*>(tiles.data_ptr()),
-                     narrow_tiles(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
+  launch_mode_switch(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
+                     wide_tiles(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
                      at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }

@@ -10,7 +10,6 @@ namespace ob200 {
 namespace {
 
 constexpr int kTile = 32;
-constexpr int kRowsPerThread = 4;  // 32 x 8 threads cover a 32 x 32 (narrow) tile
 
 // torch.lerp semantics: the formula switches at weight 0.5.
 __device__ __forceinline__ float lerpf(float a, float b, float w) {
@@ -415,44 +414,40 @@ __global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __
   }
 }
 
-template <typename T>
-__device__ __forceinline__ void store_send(void* base, long long idx, float x);
-template <>
-__device__ __forceinline__ void store_send<float>(void* base, long long idx, float x) {
-  static_cast<float*>(base)[idx] = x;
-}
-template <>
-__device__ __forceinline__ void store_send<__nv_bfloat16>(void* base, long long idx, float x) {
-  static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(x);
-}
-template <>
-__device__ __forceinline__ void store_send<__half>(void* base, long long idx, float x) {
-  static_cast<__half*>(base)[idx] = __float2half_rn(x);
-}
-
 __global__ void __launch_bounds__(256) eig_scale_kernel(const BlockDesc* __restrict__ blocks,
                                                         const TileRef* __restrict__ tiles, int num_tiles, float bc2,
                                                         float inv_root, float eps, int write_split) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     const TileRef ref = tiles[t];
     const BlockDesc& b = blocks[ref.block];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int j = ref.tj * kTile + tx;
+    const int i0 = ref.ti * kTile, j = ref.tj * kWide + 4 * lane;
+    const int cnt = b.n - j < 4 ? b.n - j : 4;
+    if (cnt <= 0) continue;
+    const bool vec = (b.n & 3) == 0 && aligned16(b.ev) && aligned16(b.p);
+    float ev[4][4], p[4][4];
 #pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r) {
-      const int i = ref.ti * kTile + ty + r * 8;
-      if (i >= b.m || j >= b.n) continue;
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + warp + 8 * r;
+      if (i >= b.m) continue;
       const long long e = static_cast<long long>(i) * b.n + j;
-      const float denom = powf(b.ev[e] / bc2, inv_root) + eps;
-      const float s = b.p[e] / denom;
-      const long long o = static_cast<long long>(i) * b.n_pad + j;
-      if (write_split) {
-        const float h = tf32_round(s);
-        b.f_hi[o] = h;
-        b.f_lo[o] = s - h;
-      } else {
-        b.f_hi[o] = s;
+      load4<false>(ev[r], b.ev + e, vec, cnt);
+      load4<false>(p[r], b.p + e, vec, cnt);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + warp + 8 * r;
+      if (i >= b.m) continue;
+      float hi[4], lo[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float s = k < cnt ? p[r][k] / (powf(ev[r][k] / bc2, inv_root) + eps) : 0.f;
+        hi[k] = write_split ? tf32_round(s) : s;
+        lo[k] = s - hi[k];
       }
+      const long long o = static_cast<long long>(i) * b.n_pad + j;  // n_pad % 4 == 0
+      store4(b.f_hi + o, hi, true, 4);
+      if (write_split) store4(b.f_lo + o, lo, true, 4);
     }
   }
 }
@@ -460,29 +455,35 @@ __global__ void __launch_bounds__(256) eig_scale_kernel(const BlockDesc* __restr
 __global__ void __launch_bounds__(256) mode_switch_kernel(const BlockDesc* __restrict__ blocks,
                                                           const TileRef* __restrict__ tiles, int num_tiles, float coeff,
                                                           int send_dtype) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     const TileRef ref = tiles[t];
     const BlockDesc& b = blocks[ref.block];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int j = ref.tj * kTile + tx;
+    const int i0 = ref.ti * kTile, j = ref.tj * kWide + 4 * lane;
+    const int cnt = b.n - j < 4 ? b.n - j : 4;
+    if (cnt <= 0) continue;
+    const bool vec = ((b.n | b.param_pitch) & 3) == 0 && aligned16(b.param) && aligned16(b.z) && aligned16(b.send);
+    float w[4][4], z[4][4];
 #pragma unroll
-    for (int r = 0; r < kRowsPerThread; ++r) {
-      const int i = ref.ti * kTile + ty + r * 8;
-      if (i >= b.m || j >= b.n) continue;
-      const long long e = static_cast<long long>(i) * b.n + j;
-      const long long pe = static_cast<long long>(i) * b.param_pitch + j;
-      const float w = b.param[pe];
-      const float delta = (b.z[e] - w) * coeff;
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + warp + 8 * r;
+      if (i >= b.m) continue;
+      load4<false>(w[r], b.param + static_cast<long long>(i) * b.param_pitch + j, vec, cnt);
+      load4<false>(z[r], b.z + static_cast<long long>(i) * b.n + j, vec, cnt);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + warp + 8 * r;
+      if (i >= b.m) continue;
+      float delta[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) delta[k] = (z[r][k] - w[r][k]) * coeff;
       if (b.send != nullptr) {
-        if (send_dtype == 1) {
-          store_send<__nv_bfloat16>(b.send, e, delta);
-        } else if (send_dtype == 2) {
-          store_send<__half>(b.send, e, delta);
-        } else {
-          store_send<float>(b.send, e, delta);
-        }
+        store_send4(b.send, static_cast<long long>(i) * b.n + j, delta, send_dtype, vec, cnt);
       } else {
-        b.param[pe] = w + delta;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) delta[k] += w[r][k];
+        store4(b.param + static_cast<long long>(i) * b.param_pitch + j, delta, vec, cnt);
       }
     }
   }

@@ -55,7 +55,7 @@ struct BlockDesc {
 struct TileRef {
   int block;
   int ti;  // 32-row tile index
-  int tj;  // column tile index: 32 columns (narrow list) or 128 columns (wide list)
+  int tj;  // 128-column tile index
   int pad_;
 };
 
