@@ -12,6 +12,11 @@ around library GEMMs.
     its slowest unaligned kernels); one kernel then reads each row once, emits the loss and
     overwrites the row with ``softmax - onehot`` for the backward GEMMs.
 
+``linear``
+    ``F.linear`` whose backward computes the bias gradient with a column-sum kernel that reads the
+    incoming gradient once with 8-byte accesses (the generic reduction runs at a fraction of the
+    memory bandwidth for this shape).
+
 ``layer_norm`` / ``rms_norm``
     fp32 statistics, output directly in the autocast dtype (what the following linear layer
     consumes), backward with a two-stage dgamma / dbeta reduction.
@@ -168,3 +173,43 @@ def rms_norm(x: Tensor, weight: Tensor, eps: float = 1e-6) -> Tensor:
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     return (y * weight.float()).to(x.dtype)
+
+
+# --------------------------------------------------------------------------------------------------
+# Linear with a fast bias gradient
+# --------------------------------------------------------------------------------------------------
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Tensor, dtype: torch.dtype):  # type: ignore[override]
+        xb, wb = x.to(dtype), weight.to(dtype)
+        ctx.save_for_backward(xb, wb)
+        ctx.dtypes = (x.dtype, weight.dtype, bias.dtype)
+        return F.linear(xb, wb, bias.to(dtype))
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):  # type: ignore[override]
+        xb, wb = ctx.saved_tensors
+        xd, wd, bd = ctx.dtypes
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.mm(dy2, wb).view(xb.shape).to(xd)
+        if ctx.needs_input_grad[1]:
+            dw = torch.mm(dy2.t(), xb.reshape(-1, xb.shape[-1])).to(wd)
+        if ctx.needs_input_grad[2]:
+            db = _ext().colsum_partial(dy2).sum(0).to(bd)
+            _count()
+        return dx, dw, db, None
+
+
+def linear(x: Tensor, weight: Tensor, bias: Tensor | None) -> Tensor:
+    """``F.linear`` in the autocast dtype; on the GPU the bias gradient comes from a dedicated kernel."""
+    cd = _compute_dtype(x)
+    if (
+        bias is not None and _native(x) and cd in (torch.float32, torch.bfloat16) and weight.shape[0] % 4 == 0
+        and torch.is_grad_enabled()
+    ):
+        return _Linear.apply(x, weight, bias, cd)
+    return F.linear(x, weight, bias)

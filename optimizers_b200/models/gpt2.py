@@ -44,14 +44,18 @@ class _Block(nn.Module):
     def _norm(self, ln: nn.LayerNorm, x: torch.Tensor) -> torch.Tensor:
         return fused_ops.layer_norm(x, ln.weight, ln.bias, ln.eps) if self.fused else ln(x)
 
+    def _lin(self, layer: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+        return fused_ops.linear(x, layer.weight, layer.bias) if self.fused else layer(x)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, T, C = x.shape
-        q, k, v = self.attn_qkv(self._norm(self.ln_1, x)).split(C, dim=2)
+        q, k, v = self._lin(self.attn_qkv, self._norm(self.ln_1, x)).split(C, dim=2)
         shape = (B, T, self.n_head, C // self.n_head)
         q, k, v = (t.view(shape).transpose(1, 2) for t in (q, k, v))
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        x = x + self.attn_proj(a.transpose(1, 2).reshape(B, T, C))
-        return x + self.mlp_proj(F.gelu(self.mlp_fc(self._norm(self.ln_2, x)), approximate="tanh"))
+        x = x + self._lin(self.attn_proj, a.transpose(1, 2).reshape(B, T, C))
+        h = F.gelu(self._lin(self.mlp_fc, self._norm(self.ln_2, x)), approximate="tanh")
+        return x + self._lin(self.mlp_proj, h)
 
 
 class GPT2(nn.Module):

@@ -195,7 +195,7 @@ norm_fwd_kernel(const InT* __restrict__ x, const float* __restrict__ gamma, cons
 // kSmemAcc: wide rows keep no per-lane dgamma / dbeta accumulators (they would spill); every row adds
 // its contributions to the shared-memory sums directly.
 template <int kVecs, bool kRms, bool kSmemAcc, typename InT, typename GradT>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, 2)
 norm_bwd_kernel(const GradT* __restrict__ dy, const InT* __restrict__ x, const float* __restrict__ gamma,
                 const float* __restrict__ mean, const float* __restrict__ rstd, InT* __restrict__ dx,
                 float* __restrict__ partial, long long rows) {
@@ -265,6 +265,48 @@ norm_bwd_kernel(const GradT* __restrict__ dy, const InT* __restrict__ x, const f
   __syncthreads();
   float* out = partial + static_cast<long long>(blockIdx.x) * 2 * C;
   for (int i = threadIdx.x; i < 2 * C; i += kNormThreads) out[i] = (&acc[0][0])[i];
+}
+
+// ------------------------------------------------------------------------------------------------
+// Column sums of a [rows, N] matrix (bias gradient of a linear layer): partial[s][n] = sum over the
+// s-th row slice.  A lane owns four consecutive columns (8- or 16-byte loads), the eight warps of a
+// CTA interleave rows, shared memory combines them.
+// ------------------------------------------------------------------------------------------------
+constexpr int kColsumThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kColsumThreads)
+colsum_kernel(const T* __restrict__ x, float* __restrict__ partial, long long rows, int N, int rows_per_slice) {
+  __shared__ float acc[kColsumThreads / 32][128];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 128 + lane * 4;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_slice;
+  const long long r1 = r0 + rows_per_slice < rows ? r0 + rows_per_slice : rows;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (col < N) {
+    long long r = r0 + warp;
+    // two independent loads in flight per iteration
+    for (; r + 8 < r1; r += 16) {
+      const float4 a = load4(x + r * N + col), b = load4(x + (r + 8) * N + col);
+      sum.x += a.x + b.x; sum.y += a.y + b.y; sum.z += a.z + b.z; sum.w += a.w + b.w;
+    }
+    for (; r < r1; r += 8) {
+      const float4 a = load4(x + r * N + col);
+      sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+    }
+  }
+  acc[warp][lane * 4] = sum.x; acc[warp][lane * 4 + 1] = sum.y;
+  acc[warp][lane * 4 + 2] = sum.z; acc[warp][lane * 4 + 3] = sum.w;
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c < N) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < kColsumThreads / 32; ++w) t += acc[w][threadIdx.x];
+      partial[static_cast<long long>(blockIdx.y) * N + c] = t;
+    }
+  }
 }
 
 int norm_grid(long long rows) {
@@ -403,7 +445,36 @@ std::tuple<torch::Tensor, torch::Tensor> norm_bwd(const torch::Tensor& dy, const
   return {dx, partial};
 }
 
+// x [rows, N] fp32 / bf16 (N % 4 == 0) -> partial [slices, N] fp32 whose sum over dim 0 is the column sum
+torch::Tensor colsum_partial(const torch::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && check_float_like(x), "colsum: x must be [rows, N] fp32/bf16");
+  const int64_t rows = x.size(0), N = x.size(1);
+  TORCH_CHECK(N % 4 == 0 && N < (1LL << 31), "colsum: N must be a multiple of 4");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "colsum: x must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int col_blocks = static_cast<int>((N + 127) / 128);
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  int slices = std::max<int>(1, std::min<int64_t>((4 * sms + col_blocks - 1) / col_blocks, (rows + 63) / 64));
+  const int rows_per_slice = static_cast<int>((rows + slices - 1) / slices);
+  slices = static_cast<int>((rows + rows_per_slice - 1) / std::max(rows_per_slice, 1));
+  auto partial = torch::empty({std::max(slices, 1), N}, x.options().dtype(torch::kFloat32));
+  if (rows == 0) return partial.zero_();
+  dim3 grid(col_blocks, slices);
+  auto st = at::cuda::getCurrentCUDAStream();
+  if (x.scalar_type() == torch::kFloat32) {
+    colsum_kernel<float><<<grid, kColsumThreads, 0, st>>>(x.data_ptr<float>(), partial.data_ptr<float>(), rows,
+                                                          static_cast<int>(N), rows_per_slice);
+  } else {
+    colsum_kernel<__nv_bfloat16><<<grid, kColsumThreads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()),
+                                                                  partial.data_ptr<float>(), rows, static_cast<int>(N),
+                                                                  rows_per_slice);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return partial;
+}
+
 void register_model_ops(pybind11::module_& m) {
+  m.def("colsum_partial", &colsum_partial);
   m.def("xent_fwd_bwd", &xent_fwd_bwd);
   m.def("norm_fwd", &norm_fwd);
   m.def("norm_bwd", &norm_bwd);

@@ -102,3 +102,34 @@ def test_fused_llama_matches_plain_under_autocast():
     for (n, a), (_, b) in zip(fused.named_parameters(), plain.named_parameters()):
         scale = b.grad.abs().max().item() + 1e-8
         assert (a.grad - b.grad).abs().max().item() <= 0.08 * scale + 1e-5, n
+
+
+@pytest.mark.parametrize("shape", [(16384, 768), (1000, 2304), (37, 12), (5, 3072)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_colsum_kernel_matches_torch(ext, shape, dtype):
+    torch.manual_seed(0)
+    x = torch.randn(*shape, device="cuda").to(dtype)
+    got = ext.colsum_partial(x).sum(0)
+    want = x.double().sum(0)
+    assert torch.allclose(got.double(), want, rtol=1e-4, atol=1e-3 * shape[0] ** 0.5)
+
+
+def test_fused_linear_matches_torch_under_autocast():
+    from optimizers_b200.models import fused_ops
+
+    torch.manual_seed(0)
+    x = torch.randn(8, 64, 256, device="cuda", requires_grad=True)
+    lin = torch.nn.Linear(256, 512).cuda()
+    x2 = x.detach().clone().requires_grad_()
+    lin2 = torch.nn.Linear(256, 512).cuda()
+    lin2.load_state_dict(lin.state_dict())
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = fused_ops.linear(x, lin.weight, lin.bias)
+        y2 = lin2(x2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    y2.backward(g)
+    assert torch.equal(y, y2)
+    assert torch.allclose(x.grad, x2.grad, rtol=1e-2, atol=1e-3)
+    assert torch.allclose(lin.weight.grad, lin2.weight.grad, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(lin.bias.grad, lin2.bias.grad, rtol=2e-2, atol=2e-2)
