@@ -15,6 +15,8 @@ settings, for comparison on the same GPU.
     python benchmarks/engine_microbench.py --d 2048 --blocks 16 --root eigen
     python benchmarks/engine_microbench.py --d 1024 --blocks 64 --root newton --impl reference
     python benchmarks/engine_microbench.py --optimizer gpa --d 4096 --blocks 16
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        benchmarks/engine_microbench.py --d 2048 --blocks 64 --comm p2p      # block work split over 8 ranks
 """
 
 from __future__ import annotations
@@ -33,15 +35,24 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--optimizer", choices=["shampoo", "soap", "gpa"], default="shampoo")
     ap.add_argument("--root", choices=["eigen", "newton"], default="eigen")
+    ap.add_argument("--eigenbasis", choices=["eigh", "qr"], default="eigh", help="refresh method of --optimizer soap")
     ap.add_argument("--d", type=int, default=2048)
     ap.add_argument("--blocks", type=int, default=16)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--refreshes", type=int, default=2)
     ap.add_argument("--backend", default="native")
     ap.add_argument("--gemm-mode", default="tf32x3")
+    ap.add_argument("--comm", choices=["nccl", "p2p"], default="nccl",
+                    help="under torchrun (N > 1, DDP distributor, bf16 search directions): NCCL all-gather or the "
+                    "epilogue's stores into every peer's gather buffer")
     args = ap.parse_args()
 
     import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(REPO, "baseline", "_ref"))
@@ -50,8 +61,11 @@ def main() -> None:
         sys.path.insert(0, REPO)
         import optimizers_b200 as lib
 
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(0)
     d, nb = args.d, args.blocks
     params = [torch.nn.Parameter(torch.randn(d, d, device=dev) * 0.02) for _ in range(nb)]
@@ -69,9 +83,18 @@ def main() -> None:
     else:
         extra = {}
         if args.impl == "ours":
-            extra["native_runtime_config"] = lib.NativeRuntimeConfig(backend=args.backend, gemm_mode=args.gemm_mode)
+            extra["native_runtime_config"] = lib.NativeRuntimeConfig(
+                backend=args.backend, gemm_mode=args.gemm_mode, comm_path=args.comm if world > 1 else "nccl"
+            )
+        if world > 1:
+            extra["distributed_config"] = lib.DDPDistributedConfig(
+                communication_dtype=torch.bfloat16, num_trainers_per_group=world
+            )
         if args.optimizer == "soap":
-            pc = lib.EigenvalueCorrectedShampooPreconditionerConfig()
+            pc = lib.EigenvalueCorrectedShampooPreconditionerConfig(
+                amortized_computation_config=lib.QREigendecompositionConfig()
+                if args.eigenbasis == "qr" else lib.EighEigendecompositionConfig()
+            )
         elif args.root == "newton":
             pc = lib.RootInvShampooPreconditionerConfig(amortized_computation_config=lib.CoupledNewtonConfig())
         else:
@@ -90,12 +113,19 @@ def main() -> None:
         for p, g in zip(params, grads[i % 2]):
             p.grad = g
         flush.zero_()
+        if world > 1:
+            dist.barrier()  # ranks enter the step together
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         opt.step()
         e.record()
         torch.cuda.synchronize()
-        return s.elapsed_time(e)
+        ms = s.elapsed_time(e)
+        if world > 1:  # the slowest rank counts
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
     for i in range(3):
         one_step(i)
@@ -109,7 +139,9 @@ def main() -> None:
                 refresh.append(t)
     step_ms = statistics.median(plain)
     out = {
-        "impl": args.impl, "optimizer": args.optimizer, "root": args.root if args.optimizer == "shampoo" else None,
+        "impl": args.impl, "optimizer": args.optimizer,
+        "root": args.root if args.optimizer == "shampoo" else (args.eigenbasis if args.optimizer == "soap" else None),
+        "n_gpus": world, "comm": args.comm if world > 1 else None,
         "d": d, "blocks": nb, "step_ms": round(step_ms, 4),
         "refresh_ms": round(statistics.median(refresh) - step_ms, 3) if refresh else None,
         "bytes_param_state": nb * d * d * 4,
@@ -117,7 +149,10 @@ def main() -> None:
     if args.impl == "ours" and args.optimizer != "gpa":
         eng = opt._per_group_state_lists[0].get("native_engine")
         out["native_launches_per_step"] = eng.launches_per_step if eng is not None else 0
-    print(json.dumps(out))
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -567,3 +567,98 @@ class BatchedNewtonSchulz:
     def check_status(self) -> None:
         if int(self._status.item()) & 1:
             raise RuntimeError("grouped GEMM pipeline wait timed out (device-side bounded wait expired)")
+
+
+# --------------------------------------------------------------------------------------------------
+# Eigenbasis refresh of the eigenvalue-corrected variant: all factors of a group concurrently
+# --------------------------------------------------------------------------------------------------
+def eigenbasis_refresh_supported(cfg: Any) -> bool:
+    from optimizers_b200.config import QREigendecompositionConfig
+
+    if isinstance(cfg, QREigendecompositionConfig):
+        return True
+    return isinstance(cfg, EighEigendecompositionConfig) and cfg.eigendecomposition_offload_device == ""
+
+
+def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | float) -> None:
+    """Recompute ``factor_matrices_eigenvectors`` of every block (eigh, or the warm-started QR
+    iteration of ``matrix_functions.py:799-852``) with the factors spread over a pool of streams,
+    each driven by its own host thread, so that the library factorisations and the convergence
+    reads of different factors overlap; the main thread reads the device twice in total
+    (finiteness of the inputs, finiteness of the results) instead of three times per factor.
+    The mathematics per factor is that of ``matrix_eigendecomposition``."""
+    if not blocks:
+        return
+    device = blocks[0].factors.factor_matrices[0].device
+    main = torch.cuda.current_stream(device)
+    items: list[_Item] = []
+    for b in blocks:
+        kf = b.factors
+        for k, factor in enumerate(kf.factor_matrices):
+            A = kf.unpack(factor / bias_correction2)
+            if kf.use_trace_scaling:
+                A = A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent)
+            items.append(_Item(b, k, A, 0.0))
+    finite = torch.stack([torch.isfinite(it.A).all() for it in items]).cpu()
+    for it, ok in zip(items, finite.tolist()):
+        if not ok:
+            index = it.block.factors.factor_matrix_indices[it.k]
+            raise PreconditionerValueError(
+                f"Encountered nan/inf values in factor matrix {index}! "
+                "To mitigate, check if nan inputs are being passed into the network or nan gradients are being passed to the optimizer. "
+                "Otherwise, in some cases, this may be due to divergence of the algorithm. To mitigate, try decreasing the learning rate or increasing grafting epsilon."
+            )
+    ready = torch.cuda.Event()
+    ready.record(main)
+    executor, streams = _pool(device)
+
+    def work(it: _Item, slot: int) -> None:
+        kf = it.block.factors
+        stream = streams[slot]
+        with torch.cuda.device(device), torch.cuda.stream(stream):
+            stream.wait_event(ready)
+            old_q = kf.factor_matrices_eigenvectors[it.k]
+            try:
+                _, Q = mf.matrix_eigendecomposition(
+                    A=it.A,
+                    eigendecomposition_config=kf.amortized_computation_config,
+                    eigenvectors_estimate=old_q.to(dtype=it.A.dtype),
+                    epsilon=kf.epsilon,
+                )
+                it.q_hi = Q.to(dtype=old_q.dtype)
+            except Exception as exception:  # keep the previous eigenbasis of this factor
+                it.error = exception
+            it.done = torch.cuda.Event()
+            it.done.record(stream)
+
+    order = sorted(range(len(items)), key=lambda i: -items[i].A.shape[0])
+    futures = [executor.submit(work, items[i], n % _POOL_SIZE) for n, i in enumerate(order)]
+    for f in futures:
+        f.result()
+    for it in items:
+        assert it.done is not None
+        main.wait_event(it.done)
+    good = [it for it in items if it.error is None]
+    if good:
+        ok_list = torch.stack([torch.isfinite(it.q_hi).all() for it in good]).cpu().tolist()
+        for it, ok in zip(good, ok_list):
+            if not ok:
+                index = it.block.factors.factor_matrix_indices[it.k]
+                raise PreconditionerValueError(
+                    f"Encountered nan or inf values in eigenvectors of factor matrix {index}! "
+                    "To mitigate, check factor matrix before the matrix computation."
+                )
+            it.block.factors.factor_matrices_eigenvectors[it.k].copy_(it.q_hi)
+    main.synchronize()  # scratch allocated on the pool streams may now be reused
+    last_error: dict[int, Exception | None] = {}
+    for it in items:
+        if it.error is not None:
+            index = it.block.factors.factor_matrix_indices[it.k]
+            logger.warning(
+                f"Matrix computation failed for factor matrix {index} with exception={it.error!r}. Using previous preconditioner and continuing..."
+            )
+            last_error[id(it.block)] = it.error
+        else:
+            last_error.setdefault(id(it.block), None)
+    for b in blocks:
+        b.factors.note_refresh_outcome(last_error.get(id(b)))

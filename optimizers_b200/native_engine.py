@@ -730,8 +730,11 @@ class NativeGroupEngine:
         plist = self._plist
         cfg = self._group[PRECONDITIONER_CONFIG].amortized_computation_config
         if self._soap:
-            for b in blocks:
-                b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
+            if batched.eigenbasis_refresh_supported(cfg):
+                batched.batched_eigenbasis_refresh(blocks, plist._bias_correction2)
+            else:
+                for b in blocks:
+                    b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
         elif batched.eigen_refresh_supported(cfg):
             batched.batched_eigen_refresh(self._ext, blocks, plist._bias_correction2, self._split, self._status)
         elif batched.newton_refresh_supported(cfg):

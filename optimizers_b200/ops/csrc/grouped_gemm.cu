@@ -133,9 +133,10 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
             // the 128-byte swizzle row.
             const uint64_t koff = static_cast<uint64_t>(k * 2);
             if (kSplit) {
+              // Consecutive products share one operand descriptor (b_hi, then a_hi).
               umma_tf32(d_tmem, a_lo + koff, b_hi + koff, kIdesc, (kb | k) != 0);
-              umma_tf32(d_tmem, a_hi + koff, b_lo + koff, kIdesc, 1);
               umma_tf32(d_tmem, a_hi + koff, b_hi + koff, kIdesc, 1);
+              umma_tf32(d_tmem, a_hi + koff, b_lo + koff, kIdesc, 1);
             } else {
               umma_tf32(d_tmem, a_hi + koff, b_hi + koff, kIdesc, (kb | k) != 0);
             }

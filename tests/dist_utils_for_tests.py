@@ -48,7 +48,7 @@ def _run_once(fn, world: int, args):
                 rank, status, payload = queue.get(timeout=5)
             except Exception:
                 waited += 5
-                if waited >= 240 or all(not p.is_alive() for p in procs):
+                if waited >= 120 or all(not p.is_alive() for p in procs):
                     raise _TransientRendezvousError("a rank exited or stalled without reporting")
                 continue
             if status == "error":
@@ -71,9 +71,9 @@ def run_distributed(fn, world: int, *args):
     Loopback rendezvous of several gloo ranks occasionally fails to connect under load; such a
     set-up failure (never a failure inside ``fn``) is retried."""
     last = None
-    for _ in range(3):
+    for _ in range(5):
         try:
             return _run_once(fn, world, args)
         except _TransientRendezvousError as e:
             last = e
-    raise AssertionError(f"gloo rendezvous failed three times: {last}")
+    raise AssertionError(f"gloo rendezvous failed five times: {last}")
