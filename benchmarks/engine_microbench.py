@@ -16,7 +16,7 @@ settings, for comparison on the same GPU.
     python benchmarks/engine_microbench.py --d 1024 --blocks 64 --root newton --impl reference
     python benchmarks/engine_microbench.py --optimizer gpa --d 4096 --blocks 16
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
-        benchmarks/engine_microbench.py --d 2048 --blocks 64 --comm p2p      # block work split over 8 ranks
+        benchmarks/engine_microbench.py --dim 2048 --blocks 64 --comm p2p      # block work split over 8 ranks
 """
 
 from __future__ import annotations
@@ -36,7 +36,7 @@ def main() -> None:
     ap.add_argument("--optimizer", choices=["shampoo", "soap", "gpa"], default="shampoo")
     ap.add_argument("--root", choices=["eigen", "newton"], default="eigen")
     ap.add_argument("--eigenbasis", choices=["eigh", "qr"], default="eigh", help="refresh method of --optimizer soap")
-    ap.add_argument("--d", type=int, default=2048)
+    ap.add_argument("--dim", "--d", dest="d", type=int, default=2048, help="block size (use --dim under torchrun, which claims --d)")
     ap.add_argument("--blocks", type=int, default=16)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--refreshes", type=int, default=2)
