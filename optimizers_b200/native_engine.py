@@ -179,6 +179,8 @@ class NativeGroupEngine:
         self._ddp = isinstance(group[DISTRIBUTED_CONFIG], DDPDistributedConfig)
         self._p2p = type(group[DISTRIBUTED_CONFIG]) is DDPDistributedConfig and cfg.comm_path == "p2p"
         self._pull = self._p2p and cfg.fuse_gradient_reduction
+        self._gemm_push = self._p2p and cfg.fuse_direction_push and not self._soap
+        self.gemm_push_steps = 0  # steps whose all-gather ran from the GEMM epilogue
         self._comm_dtype_code = 0
         self._gather_table = None
         self._gather_for: tuple[bool, ...] | None = None
@@ -320,7 +322,8 @@ class NativeGroupEngine:
         world = dist_._group_size
         if world > 8:
             raise RuntimeError("comm_path='p2p' needs all ranks of a group on one NVLink domain (at most 8)")
-        regions = {"gather": dist_._global_dist_buffer.numel(), "flags": 2 * 32 * 4}
+        regions = {"gather": dist_._global_dist_buffer.numel(), "flags": 2 * 32 * 4,
+                   "scales": 4 * max(len(dist_._global_blocked_params), 1)}
         params = self._group[PARAMS]
         if self._pull:
             if dist_._group_size != dist_._global_size:
@@ -334,6 +337,10 @@ class NativeGroupEngine:
         ]
         self._gather_local = self._arena.region("gather", dist_._global_dist_buffer.numel())
         self._gather_bases = self._arena.peer_addresses("gather")
+        # Per-block grafting scales of the GEMM-epilogue push path, indexed by global block.
+        self._scales_local = self._arena.region("scales").view(torch.float32)
+        self._scale_bases = self._arena.peer_addresses("scales")
+        self._scale_copy_for: tuple[bool, ...] | None = None
         if self._pull:
             flat = self._arena.region("grads", regions["grads"]).view(torch.float32)
             bases = self._arena.peer_addresses("grads")
@@ -444,6 +451,14 @@ class NativeGroupEngine:
         self._gemm0_plan = ext.build_gemm_plan(gemm0) if gemm0 else None
         self._gemm1_plan = ext.build_gemm_plan(gemm1) if gemm1 else None
         self._gemm2_plan = ext.build_gemm_plan(gemm2)
+        if self._gemm_push:
+            # Same products; the result goes to the block's slot of every gather buffer instead of b.p.
+            flags = F.FLAG_SUMSQ | F.FLAG_NO_C | F.FLAG_PEER_PUSH
+            push = [
+                (s[0], s[1], s[2], s[3], None, None, None, s[7], s[8], 0, flags, False, self._slot_offset(b))
+                for s, b in zip(gemm2, blocks, strict=True)
+            ]
+            self._gemm2_push_plan = ext.build_gemm_plan(push)
 
     def _build_soap_plans(self, blocks: list[_Block]) -> None:
         """GEMM plans of the eigenvalue-corrected step.  With Qt the transposed eigenvector
@@ -628,10 +643,21 @@ class NativeGroupEngine:
         if self._plans_for != active:
             self._build_plans(active)
             self._plans_for = active
+        alpha = 0.0
+        if weight_decay != 0.0 and weight_decay_type != WeightDecayType.L2:
+            if weight_decay_type == WeightDecayType.DECOUPLED:
+                alpha = weight_decay
+            elif weight_decay_type == WeightDecayType.CORRECTED:
+                alpha = weight_decay * rec[LR_CPU_PINNED].item() / peak_lr
+            else:
+                alpha = weight_decay / peak_lr
+        # All ranks take the same decision: it depends on the step and the configuration only.
+        use_push = self._gemm_push and not graft_only and not classic and not primal
+        scaled = (lr, alpha) if use_push else None
         if not rec[MASKED_BLOCKED_GRADS] or self._table is None:
             # Nothing to compute here; other ranks may still need this rank in their collective.
             self.launches_per_step = 0
-            self._finish_update()
+            self._finish_update(scaled)
             return
         if self._p2p:
             # Every rank has finished its backward pass (its gradients are complete) and has applied
@@ -675,17 +701,21 @@ class NativeGroupEngine:
             if self._gemm1_plan is not None:
                 ext.run_gemm_plan(*self._gemm1_plan, 1.0, 0.0, self._split, self._status)
                 launches += 1
-            ext.run_gemm_plan(*self._gemm2_plan, 1.0, 0.0, self._split, self._status)
+            if use_push:
+                # The last preconditioner GEMM stores its tiles into every rank's gather buffer.
+                ext.run_gemm_plan_push(
+                    *self._gemm2_push_plan, 1.0, 0.0, self._split, self._status, self._gather_bases, self._comm_dtype_code
+                )
+            else:
+                ext.run_gemm_plan(*self._gemm2_plan, 1.0, 0.0, self._split, self._status)
             launches += 1
 
-        alpha = 0.0
-        if weight_decay != 0.0 and weight_decay_type != WeightDecayType.L2:
-            if weight_decay_type == WeightDecayType.DECOUPLED:
-                alpha = weight_decay
-            elif weight_decay_type == WeightDecayType.CORRECTED:
-                alpha = weight_decay * rec[LR_CPU_PINNED].item() / peak_lr
-            else:
-                alpha = weight_decay / peak_lr
+        if use_push:
+            launches += self._push_scales(has_grafting)
+            self.gemm_push_steps += 1
+            self.launches_per_step = launches
+            self._finish_update(scaled)
+            return
         if primal and not rec[TRAIN_MODE]:
             raise RuntimeError(
                 "Called _apply_in_place_primal_averaging when not in train mode. Call optimizer.train() before calling optimizer.step()!"
@@ -745,7 +775,30 @@ class NativeGroupEngine:
         self.refresh_inverse_mirrors(blocks)
         self.check_status()
 
-    def _finish_update(self) -> None:
+    def _push_scales(self, has_grafting: bool) -> int:
+        """Send each local block's grafting scale ||graft direction|| / ||P|| to slot [global block]
+        of every rank's scale table (one grouped peer copy of 4-byte entries)."""
+        ext, dist_ = self._ext, self._dist
+        if getattr(self, "_scales_src", None) is None:
+            self._scales_src = torch.ones(max(len(self._blocks), 1), dtype=torch.float32, device=self._device)
+            self._global_index = [i for i, mine in enumerate(dist_._distributor_selector) if mine]
+        if has_grafting and self._graft_kind != _GRAFT_NONE:
+            torch.div(self._norms[:, 0].sqrt(), self._norms[:, 1].sqrt().add_(1e-16), out=self._scales_src)
+        else:
+            self._scales_src.fill_(1.0)
+        if self._scale_copy_for != self._plans_for:
+            base = self._scales_src.data_ptr()
+            specs = [
+                (base + 4 * b.index, peer + 4 * self._global_index[b.index], 4)
+                for b in self._active_blocks
+                for peer in self._scale_bases
+            ]
+            self._scale_copy = ext.build_copy_table(specs, self._device.index)
+            self._scale_copy_for = self._plans_for
+        ext.peer_copy(*self._scale_copy)
+        return 4
+
+    def _finish_update(self, scaled: tuple[Tensor, float] | None = None) -> None:
         """Deliver the search directions.  Single device: the epilogue already updated the
         parameters.  DDP: all-gather (NCCL), or a cross-rank barrier after the epilogue's peer
         stores (p2p); then one grouped kernel adds every block's direction to the parameters."""
@@ -767,17 +820,23 @@ class NativeGroupEngine:
         if self._gather_for != sel:
             specs = []
             base = recv.data_ptr()
-            for view, off, on in zip(dist_._global_blocked_params, dist_._global_block_byte_offsets, sel, strict=True):
+            for index, (view, off, on) in enumerate(
+                zip(dist_._global_blocked_params, dist_._global_block_byte_offsets, sel, strict=True)
+            ):
                 if not on:
                     continue
                 if view.dim() == 3:
                     view = view.view(view.shape[0] * view.shape[1], view.shape[2])
                 m, n = (1, view.shape[0]) if view.dim() == 1 else view.shape
-                specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 12 + (base + off, off, None, 0))
+                scale = self._scales_local[index : index + 1] if self._p2p else None
+                specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 11 + (scale, base + off, off, None, 0))
             self._gather_table = self._ext.build_block_table(specs) if specs else None
             self._gather_for = sel
         if self._gather_table is not None:
-            self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code)
+            if scaled is not None:
+                self._ext.gathered_apply_scaled(*self._gather_table, self._comm_dtype_code, scaled[0], scaled[1])
+            else:
+                self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code)
             self.launches_per_step += 1
         if hasattr(dist_, "_write_back"):
             dist_._write_back()

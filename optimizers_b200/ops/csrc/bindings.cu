@@ -94,7 +94,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vec
   torch::Device device(torch::kCPU);
   for (size_t i = 0; i < specs.size(); ++i) {
     const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 12, "GEMM spec must have 12 fields");
+    TORCH_CHECK(s.size() == 12 || s.size() == 13, "GEMM spec must have 12 fields (13 with a push offset)");
     GemmSpec g;
     g.a_hi = s[0].cast<torch::Tensor>();
     g.a_lo = s[1].cast<std::optional<torch::Tensor>>();
@@ -127,6 +127,8 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vec
     p.ldc = static_cast<int>(g.ldc);
     p.ldd = static_cast<int>(g.ldd);
     p.flags = static_cast<int>(g.flags);
+    p.push_offset = s.size() == 13 ? s[12].cast<int64_t>() : 0;
+    if (p.flags & kFlagPeerPush) TORCH_CHECK(s.size() == 13, "a pushing problem needs its slot offset");
     if (p.flags & kFlagPackedC) TORCH_CHECK(p.M == p.N && g.upper_tiles_only, "packed output needs a square upper-tile problem");
     if (!(p.flags & kFlagNoC)) TORCH_CHECK(p.c != nullptr, "C is required unless kFlagNoC is set");
     if (p.flags & kFlagSplitOut) TORCH_CHECK(p.d_hi != nullptr && p.d_lo != nullptr, "split output needs d_hi and d_lo");
@@ -158,6 +160,24 @@ void run_gemm_plan(const torch::Tensor& problems, const torch::Tensor& tiles, in
                       reinterpret_cast<const GemmTile*>(tiles.data_ptr()), static_cast<int>(num_tiles),
                       static_cast<float>(alpha), static_cast<float>(beta), split, status.data_ptr<int>(), sms,
                       at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// run_gemm_plan with the kFlagPeerPush problems storing into the gather buffers at `peer_bases`.
+void run_gemm_plan_push(const torch::Tensor& problems, const torch::Tensor& tiles, int64_t num_tiles, double alpha,
+                        double beta, bool split, torch::Tensor status, const std::vector<int64_t>& peer_bases,
+                        int64_t send_dtype) {
+  c10::cuda::CUDAGuard guard(problems.device());
+  TORCH_CHECK(peer_bases.size() <= 8, "at most 8 peers");
+  PeerPush push{};
+  push.num_peers = static_cast<int>(peer_bases.size());
+  push.dtype = static_cast<int>(send_dtype);
+  for (size_t r = 0; r < peer_bases.size(); ++r) push.base[r] = static_cast<unsigned long long>(peer_bases[r]);
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  launch_grouped_gemm(reinterpret_cast<const GemmProblem*>(problems.data_ptr()),
+                      reinterpret_cast<const GemmTile*>(tiles.data_ptr()), static_cast<int>(num_tiles),
+                      static_cast<float>(alpha), static_cast<float>(beta), split, status.data_ptr<int>(), sms,
+                      at::cuda::getCurrentCUDAStream(), &push);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -288,7 +308,18 @@ void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
                         wide_tiles(num_tiles),
-                        static_cast<int>(dtype), at::cuda::getCurrentCUDAStream());
+                        static_cast<int>(dtype), nullptr, 0.f, at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// The slots hold unscaled Shampoo directions P (pushed from the GEMM epilogue); BlockDesc::norms
+// points at the block's grafting scale: W <- W - lr (scale P + wd_alpha W).
+void gathered_apply_scaled(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype,
+                           const torch::Tensor& lr, double wd_alpha) {
+  c10::cuda::CUDAGuard guard(blocks.device());
+  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
+                        wide_tiles(num_tiles), static_cast<int>(dtype), lr.data_ptr<float>(),
+                        static_cast<float>(wd_alpha), at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -483,6 +514,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("FLAG_NO_C") = kFlagNoC;
   m.def("build_gemm_plan", &build_gemm_plan);
   m.def("run_gemm_plan", &run_gemm_plan);
+  m.def("run_gemm_plan_push", &run_gemm_plan_push);
+  m.attr("FLAG_PEER_PUSH") = kFlagPeerPush;
+  m.def("gathered_apply_scaled", &gathered_apply_scaled);
   m.def("build_block_table", &build_block_table);
   m.def("grad_prologue", &grad_prologue);
   m.def("direction_epilogue", &direction_epilogue);

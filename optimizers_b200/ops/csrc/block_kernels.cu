@@ -386,8 +386,11 @@ __global__ void __launch_bounds__(256, kPlain ? 3 : 2) direction_epilogue_kernel
 // Every rank applies every block's gathered search direction: param += cast(slot).
 __global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __restrict__ blocks,
                                                              const TileRef* __restrict__ tiles, int num_tiles,
-                                                             int dtype) {
+                                                             int dtype, const float* __restrict__ lr_ptr,
+                                                             float wd_alpha) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool scaled = lr_ptr != nullptr;
+  const float lr = scaled ? *lr_ptr : 0.f;
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     const TileRef ref = tiles[t];
     const BlockDesc& b = blocks[ref.block];
@@ -407,8 +410,14 @@ __global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __
     for (int r = 0; r < 4; ++r) {
       const int i = i0 + warp + 8 * r;
       if (i >= b.m) continue;
+      if (scaled) {
+        const float sc = b.norms != nullptr ? b.norms[0] : 1.f;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) w[r][k] += d[r][k];
+        for (int k = 0; k < 4; ++k) w[r][k] -= lr * (sc * d[r][k] + wd_alpha * w[r][k]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w[r][k] += d[r][k];
+      }
       store4(b.param + static_cast<long long>(i) * b.param_pitch + j, w[r], vec, cnt);
     }
   }
@@ -553,10 +562,10 @@ void launch_peer_barrier(int* local_flags, const unsigned long long* peer_flag_b
   peer_barrier_kernel<<<1, 32, 0, stream>>>(local_flags, peer_flag_bases, my_rank, world, seq, status);
 }
 
-void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype,
-                           cudaStream_t stream) {
+void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype, const float* lr,
+                           float wd_alpha, cudaStream_t stream) {
   if (num_tiles <= 0) return;
-  gathered_apply_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, dtype);
+  gathered_apply_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, dtype, lr, wd_alpha);
 }
 
 }  // namespace ob200

@@ -127,7 +127,10 @@ void launch_direction_epilogue(const EpilogueArgs& args, cudaStream_t stream);
 // slot of the receive buffer in the communication dtype (BlockDesc::send points at the slot),
 // to the parameter block.  One grouped launch replaces the reference's _foreach_add_ over views
 // of the gather buffer (distributed_shampoo/distributor/shampoo_ddp_distributor.py:330-360).
-void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype,
-                           cudaStream_t stream);
+// With `lr` non-null the slots hold unscaled directions P and BlockDesc::norms points at the
+// block's grafting scale s: W <- W - lr (s P + wd_alpha W); this finishes, on every rank, the
+// update whose directions the preconditioner GEMM pushed from its epilogue.
+void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype, const float* lr,
+                           float wd_alpha, cudaStream_t stream);
 
 }  // namespace ob200

@@ -177,7 +177,70 @@ __device__ __forceinline__ void gpa_chunk(const GpaTensorDesc& d, long long begi
   }
 }
 
-__global__ void __launch_bounds__(256) gpa_adamw_kernel(const GpaTensorDesc* __restrict__ table,
+__device__ __forceinline__ void gpa_element(float g, float& y, float& z, float& m, float& v, const GpaScalars& s,
+                                            float y_step, float shrink) {
+  m = lerpf(m, g, 1.f - s.beta1);
+  v = s.beta2 * v + (1.f - s.beta2) * g * g;
+  const float gn = (m / s.bc1) / (sqrtf(v / s.bc2) + s.eps);
+  if (s.wd != 0.f) {
+    if (s.wd_on_y) {
+      y *= shrink;
+    } else {
+      z *= shrink;
+    }
+  }
+  y = lerpf(y, z, s.avg_coeff);
+  y += y_step * gn;
+  z -= s.lr * gn;
+}
+
+// fp32 parameters with 16-byte aligned arrays: two 16-byte groups per thread and array are loaded
+// before anything is stored, twice per 4096-element chunk.
+__device__ __forceinline__ void gpa_chunk_vec4(const GpaTensorDesc& d, long long begin, long long end,
+                                               const GpaScalars& s) {
+  const float y_step = s.lr * (s.mu_y * (1.f - s.avg_coeff) - 1.f);
+  const float shrink = 1.f - s.lr * s.wd;
+  const float4* g4 = reinterpret_cast<const float4*>(static_cast<const float*>(d.grad) + begin);
+  float4* y4 = reinterpret_cast<float4*>(static_cast<float*>(d.param) + begin);
+  float4* z4 = reinterpret_cast<float4*>(d.z + begin);
+  float4* m4 = reinterpret_cast<float4*>(d.m + begin);
+  float4* v4 = reinterpret_cast<float4*>(d.v + begin);
+  const int nvec = static_cast<int>((end - begin) / 4);
+  for (int base = 0; base < nvec; base += 512) {
+    float4 g[2], y[2], z[2], m[2], v[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = base + u * 256 + threadIdx.x;
+      if (i < nvec) {
+        g[u] = g4[i]; y[u] = y4[i]; z[u] = z4[i]; m[u] = m4[i]; v[u] = v4[i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = base + u * 256 + threadIdx.x;
+      if (i < nvec) {
+        gpa_element(g[u].x, y[u].x, z[u].x, m[u].x, v[u].x, s, y_step, shrink);
+        gpa_element(g[u].y, y[u].y, z[u].y, m[u].y, v[u].y, s, y_step, shrink);
+        gpa_element(g[u].z, y[u].z, z[u].z, m[u].z, v[u].z, s, y_step, shrink);
+        gpa_element(g[u].w, y[u].w, z[u].w, m[u].w, v[u].w, s, y_step, shrink);
+        y4[i] = y[u]; z4[i] = z[u]; m4[i] = m[u]; v4[i] = v[u];
+      }
+    }
+  }
+  // ragged tail of the last chunk
+  for (long long i = begin + 4LL * nvec + threadIdx.x; i < end; i += blockDim.x) {
+    float y = static_cast<float*>(d.param)[i], z = d.z[i], m = d.m[i], v = d.v[i];
+    gpa_element(static_cast<const float*>(d.grad)[i], y, z, m, v, s, y_step, shrink);
+    static_cast<float*>(d.param)[i] = y; d.z[i] = z; d.m[i] = m; d.v[i] = v;
+  }
+}
+
+__device__ __forceinline__ bool gpa_aligned16(const GpaTensorDesc& d) {
+  return ((reinterpret_cast<uintptr_t>(d.param) | reinterpret_cast<uintptr_t>(d.grad) | reinterpret_cast<uintptr_t>(d.z) |
+           reinterpret_cast<uintptr_t>(d.m) | reinterpret_cast<uintptr_t>(d.v)) & 15) == 0;
+}
+
+__global__ void __launch_bounds__(256, 3) gpa_adamw_kernel(const GpaTensorDesc* __restrict__ table,
                                                         const int2* __restrict__ chunks, int num_chunks, GpaScalars s) {
   for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
     const int2 ref = chunks[c];
@@ -186,7 +249,11 @@ __global__ void __launch_bounds__(256) gpa_adamw_kernel(const GpaTensorDesc* __r
     const long long begin = static_cast<long long>(ref.y) * kGpaChunk;
     const long long end = begin + kGpaChunk < d.numel ? begin + kGpaChunk : d.numel;
     if (d.dtype == 0) {
-      gpa_chunk<float>(d, begin, end, s);
+      if (gpa_aligned16(d)) {
+        gpa_chunk_vec4(d, begin, end, s);
+      } else {
+        gpa_chunk<float>(d, begin, end, s);
+      }
     } else if (d.dtype == 1) {
       gpa_chunk<__nv_bfloat16>(d, begin, end, s);
     } else {

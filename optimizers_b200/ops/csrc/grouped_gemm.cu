@@ -6,6 +6,9 @@
 #include "grouped_gemm.cuh"
 #include "ptx.cuh"
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 namespace ob200 {
 
 namespace {
@@ -31,7 +34,7 @@ struct Cfg {
 template <int kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __restrict__ tiles, int num_tiles,
-                    float alpha, float beta, int* __restrict__ status) {
+                    float alpha, float beta, int* __restrict__ status, const PeerPush push) {
   using C = Cfg<kSplit>;
   constexpr int kStages = C::kStages;
 
@@ -163,6 +166,8 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
       float* __restrict__ Dhi = p->d_hi;
       float* __restrict__ Dlo = p->d_lo;
       const int ldc = p->ldc, ldd = p->ldd;
+      const bool do_push = (flags & kFlagPeerPush) && push.num_peers > 0;
+      const long long push_offset = p->push_offset;
       const int buf = it & 1;
       if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag)) break;
       tc_fence_after_sync();
@@ -220,6 +225,20 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
                   Dhi[od] = hi;
                   Dlo[od] = val - hi;
                 }
+                if (do_push) {
+                  // A warp stores 32 consecutive elements of one row into each rank's slot.
+                  const long long e = static_cast<long long>(row) * N + col;
+                  for (int r = 0; r < push.num_peers; ++r) {
+                    void* dst = reinterpret_cast<void*>(push.base[r] + push_offset);
+                    if (push.dtype == 1) {
+                      static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(val);
+                    } else if (push.dtype == 2) {
+                      static_cast<__half*>(dst)[e] = __float2half_rn(val);
+                    } else {
+                      static_cast<float*>(dst)[e] = val;
+                    }
+                  }
+                }
                 sq += val * val;
               }
               o += packed ? (N - row - 1) : ldc;
@@ -257,7 +276,7 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
 
 template <int kSplit>
 void launch_impl(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
-                 int* status, int max_ctas, cudaStream_t stream) {
+                 int* status, int max_ctas, cudaStream_t stream, const PeerPush& push) {
   using C = Cfg<kSplit>;
   static bool configured = false;
   if (!configured) {
@@ -266,18 +285,20 @@ void launch_impl(const GemmProblem* problems, const GemmTile* tiles, int num_til
   }
   const int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
   grouped_gemm_kernel<kSplit><<<grid, kThreads, C::kSmemBytes, stream>>>(problems, tiles, num_tiles, alpha, beta,
-                                                                        status);
+                                                                        status, push);
 }
 
 }  // namespace
 
 void launch_grouped_gemm(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
-                         bool split, int* status, int max_ctas, cudaStream_t stream) {
+                         bool split, int* status, int max_ctas, cudaStream_t stream, const PeerPush* push) {
   if (num_tiles <= 0) return;
+  PeerPush none{};
+  const PeerPush& pp = push != nullptr ? *push : none;
   if (split) {
-    launch_impl<1>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream);
+    launch_impl<1>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
   } else {
-    launch_impl<0>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream);
+    launch_impl<0>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
   }
 }
 

@@ -21,6 +21,8 @@
 //                   (row pitch ldd) so it can feed the next GEMM of a chain
 //   kFlagSumSq      add the sum of squares of the results to *sumsq (Frobenius norm partials)
 //   kFlagNoC        do not write C (only the split / sumsq outputs)
+//   kFlagPeerPush   the result is also stored, in the communication dtype, into every rank's gather
+//                   buffer over NVLink (fused all-gather of the search directions)
 //   kFlagSquareAcc  the accumulator is squared before alpha/beta are applied: with C the running
 //                   second moment V this is V <- beta2 V + w (Q_L^T G Q_R)^2 fused into the projection
 #pragma once
@@ -35,6 +37,10 @@ constexpr int kFlagSplitOut = 2;
 constexpr int kFlagSumSq = 4;
 constexpr int kFlagNoC = 8;
 constexpr int kFlagSquareAcc = 16;  // C = beta * C + alpha * acc^2 (second moment in the eigenbasis)
+constexpr int kFlagPeerPush = 32;   // also store the result, cast to the communication dtype, into the
+                                    // problem's slot of every rank's gather buffer (PeerPush): the
+                                    // all-gather of the search directions happens tile by tile from
+                                    // the epilogue of the GEMM that produces them
 
 constexpr int kErrPipelineTimeout = 1;  // a bounded mbarrier wait expired
 
@@ -49,6 +55,15 @@ struct alignas(128) GemmProblem {
   int ldd;  // row pitch of d_hi / d_lo
   int flags;
   int pad_[2];
+  long long push_offset;  // byte offset of the problem's slot inside the gather buffers (kFlagPeerPush)
+};
+
+// Destination of kFlagPeerPush stores: the gather buffer of every rank of the group (this rank
+// included), all laid out identically.  Plain stores over NVLink; no TMA touches peer memory.
+struct PeerPush {
+  unsigned long long base[8];
+  int num_peers;  // 0: no problem of the launch pushes
+  int dtype;      // 0 fp32, 1 bf16, 2 fp16
 };
 
 struct GemmTile {
@@ -64,6 +79,6 @@ constexpr int kBK = 32;  // fp32 elements = 128 bytes = one swizzle row
 
 // Host-side launch.  `status` is a device int the kernel writes a non-zero error code to.
 void launch_grouped_gemm(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
-                         bool split, int* status, int max_ctas, cudaStream_t stream);
+                         bool split, int* status, int max_ctas, cudaStream_t stream, const PeerPush* push = nullptr);
 
 }  // namespace ob200

@@ -106,8 +106,12 @@ class DDPDistributor(DistributorInterface):
         self._group_size: int = cfg.num_trainers_per_group if cfg.num_trainers_per_group != -1 else self._global_size
         # Collective: every rank creates every sub-group and keeps its own.
         self._dist_group: dist.ProcessGroup = dist.new_subgroups(group_size=self._group_size, group=dist_group)[0]
-        ranks = dist.get_process_group_ranks(group=self._dist_group)
-        self._owner_mesh_rows: tuple[tuple[int, ...], ...] = tuple(batched(ranks, self._group_size))
+        # The mesh must be the same object request on every rank (its creation is collective): all
+        # ranks of the parent group, one row per sub-group.  Column j then is the set of ranks that
+        # hold identical copies of the state owned by the j-th member of each sub-group.
+        parent = dist_group if dist_group is not None else dist.group.WORLD
+        all_ranks = dist.get_process_group_ranks(group=parent)
+        self._owner_mesh_rows: tuple[tuple[int, ...], ...] = tuple(batched(all_ranks, self._group_size))
 
     # -- parameters may be DTensors (composable replicate()) ------------------------------------
     @torch.no_grad()

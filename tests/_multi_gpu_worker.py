@@ -34,6 +34,7 @@ def main() -> None:
         backend="torch" if mode == "torch" else "native",
         comm_path="p2p" if mode.startswith("p2p") else "nccl",
         fuse_gradient_reduction=fused,
+        fuse_direction_push=mode == "p2p_gemm",
     )
     opt = DistributedShampoo(
         model.parameters(), lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64,
@@ -53,6 +54,9 @@ def main() -> None:
     for rec in opt._per_group_state_lists:
         if rec.get("native_engine") is not None:
             rec["native_engine"].check_status()
+            pushed = rec["native_engine"].gemm_push_steps
+            # 8 steps, preconditioning from step 3: six steps gather from the GEMM epilogue
+            assert pushed == (6 if mode == "p2p_gemm" else 0), pushed
         else:
             assert mode == "torch"
     torch.cuda.synchronize()

@@ -13,6 +13,10 @@ import torch.multiprocessing as mp
 def _entry(rank, world, store_path, fn, args, queue):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), GLOO_SOCKET_IFNAME="lo")
     torch.set_num_threads(1)
+    if os.environ.get("OB200_TEST_STALL_DUMP"):
+        import faulthandler
+
+        faulthandler.dump_traceback_later(60, file=open(f"{os.environ['OB200_TEST_STALL_DUMP']}.{rank}", "w"))
     try:
         # File-store rendezvous: no TCP port to collide on.
         dist.init_process_group("gloo", init_method=f"file://{store_path}", rank=rank, world_size=world)

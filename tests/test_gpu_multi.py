@@ -1,5 +1,6 @@
-"""Multi-GPU tests of the native DDP engine: NCCL all-gather path and the peer-to-peer path
-(fused reduce-scatter in the prologue, fused all-gather in the epilogue) against the torch step."""
+"""Multi-GPU tests of the native DDP engine: NCCL all-gather path and the peer-to-peer paths
+(reduce-scatter fused into the prologue, all-gather fused into the epilogue of the last
+preconditioner GEMM or into the pointwise epilogue) against the torch step."""
 
 import os
 import subprocess
@@ -24,7 +25,7 @@ def _run(mode: str, nproc: int, out: str, port: int) -> None:
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("mode", ["native_nccl", "p2p_push", "p2p_pull"])
+@pytest.mark.parametrize("mode", ["native_nccl", "p2p_push", "p2p_pull", "p2p_gemm"])
 def test_native_ddp_matches_torch_ddp(tmp_path, mode):
     n = min(torch.cuda.device_count(), 4)
     ref, got = str(tmp_path / "ref.pt"), str(tmp_path / "got.pt")
