@@ -54,7 +54,7 @@ def _pad4(n: int) -> int:
 
 
 class _Item:
-    __slots__ = ("block", "k", "A", "root", "qs_hi", "qs_lo", "q_hi", "q_lo", "error", "done")
+    __slots__ = ("block", "k", "A", "root", "qs_hi", "qs_lo", "q_hi", "q_lo", "error", "done", "lam", "Q")
 
     def __init__(self, block: Any, k: int, A: Tensor, root: float) -> None:
         self.block, self.k, self.A, self.root = block, k, A, root
@@ -66,8 +66,17 @@ def eigen_refresh_supported(cfg: Any) -> bool:
     return isinstance(cfg, EigenConfig) and cfg.eigendecomposition_offload_device == ""
 
 
+def eigdec_refresh_supported(cfg: Any) -> bool:
+    """Eigendecomposed Shampoo: plain eigh (no adaptive skipping, no offload) runs batched."""
+    return (
+        isinstance(cfg, EighEigendecompositionConfig) and cfg.eigendecomposition_offload_device == "" and cfg.tolerance == 0.0
+    )
+
+
 def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor | float, split: bool, status: Tensor) -> None:
     """Refresh ``inv_factor_matrices`` (state) and the ``inv_hi/inv_lo`` mirrors of ``blocks``.
+    For eigendecomposed Shampoo (``factors.kind == "eigendecomposed"``) the state refreshed is the
+    pair (eigenvalues, eigenvectors) and the mirrors receive the reconstruction, split in place.
 
     ``blocks`` are the native engine's block records (``.factors`` is the ``BlockFactors`` of the
     block, ``.inv_hi/.inv_lo`` the mirrors).  Raises ``PreconditionerValueError`` on non-finite
@@ -103,7 +112,7 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
 
     def work(it: _Item, slot: int) -> None:
         kf = it.block.factors
-        cfg: EigenConfig = kf.amortized_computation_config
+        cfg = kf.amortized_computation_config  # EigenConfig, or EighEigendecompositionConfig (eigendecomposed)
         stream = streams[slot]
         with torch.cuda.device(device), torch.cuda.stream(stream):
             stream.wait_event(ready)
@@ -117,10 +126,12 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
                         tolerance=0.0,
                     ),
                 )
+                it.lam = lam
                 scale = mf.stabilized_inverse_power(
                     lam, Fraction(it.root), kf.epsilon, cfg.rank_deficient_stability_config
                 )
                 Q = Q.contiguous()
+                it.Q = Q
                 Qs = (Q * scale.unsqueeze(0)).contiguous()
                 d = Q.shape[0]
                 ld = _pad4(d)
@@ -168,6 +179,14 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
     for it in good:
         d = it.A.shape[0]
         kf = it.block.factors
+        if kf.kind == "eigendecomposed":
+            kf.factor_matrices_eigenvalues[it.k].copy_(it.lam)
+            kf.factor_matrices_eigenvectors[it.k].copy_(it.Q)
+            mirror = it.block.inv_hi[it.k][:, :d]
+            flags.append(torch.isfinite(mirror).all() & torch.isfinite(it.lam).all())
+            if split:  # the reconstruction becomes the (hi, lo) operand pair in place
+                ext.tf32_split(mirror, mirror, it.block.inv_lo[it.k][:, :d])
+            continue
         state = kf.inv_factor_matrices[it.k]
         state.copy_(kf.pack(it.block.inv_hi[it.k][:, :d]).to(dtype=state.dtype))
         flags.append(torch.isfinite(state).all())

@@ -22,7 +22,7 @@ unproject (``_soap_step``) and updates its second moment in the epilogue of the 
 
 Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 (and contiguous order-3 blocks for
 root-inverse Shampoo) with every dim preconditioned,
-root-inverse or eigenvalue-corrected Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting,
+root-inverse, eigendecomposed or eigenvalue-corrected Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting,
 any weight decay type,
 classic momentum, GPA / Schedule-Free, single-device and DDP distributors (NCCL all-gather, or
 peer-to-peer stores and loads over NVLink with ``comm_path="p2p"``).  Anything else makes
@@ -45,6 +45,7 @@ from optimizers_b200.config import (
     DDPDistributedConfig,
     DISTRIBUTED_CONFIG,
     DISTRIBUTOR,
+    EigendecomposedShampooPreconditionerConfig,
     EigenvalueCorrectedShampooPreconditionerConfig,
     FILTERED_GRAD_LIST,
     GRAFTING_CONFIG,
@@ -81,6 +82,10 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     if type(pc) is RootInvShampooPreconditionerConfig:
         if pc.factor_matrix_dtype != torch.float32 or pc.inv_factor_matrix_dtype != torch.float32:
             return "factor matrices must be fp32"
+    elif type(pc) is EigendecomposedShampooPreconditionerConfig:
+        dtypes = (pc.factor_matrix_dtype, pc.factor_matrix_eigenvectors_dtype, pc.factor_matrix_eigenvalues_dtype)
+        if any(d != torch.float32 for d in dtypes):
+            return "factor matrices, eigenvectors and eigenvalues must be fp32"
     elif type(pc) is EigenvalueCorrectedShampooPreconditionerConfig:
         dtypes = (pc.factor_matrix_dtype, pc.factor_matrix_eigenvectors_dtype, pc.corrected_eigenvalues_dtype)
         if any(d != torch.float32 for d in dtypes):
@@ -123,7 +128,8 @@ def _order3_ok(block: Tensor, pc: Any) -> bool:
     """Order-3 blocks (a, b, c) run natively for root-inverse Shampoo when they are contiguous and
     a, b are multiples of 4, so that every mode unfolding is an exact, 16-byte aligned 2-D view."""
     a, b, _ = block.shape
-    return type(pc) is RootInvShampooPreconditionerConfig and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
+    root_like = type(pc) in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig)
+    return root_like and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
 
 
 def build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig):
@@ -165,6 +171,10 @@ class NativeGroupEngine:
         self._glist = rec[GRAFTING_PRECONDITIONER_LIST]
         self._packing = group[PRECONDITIONER_CONFIG].use_symmetric_packing
         self._soap = type(group[PRECONDITIONER_CONFIG]) is EigenvalueCorrectedShampooPreconditionerConfig
+        # Eigendecomposed Shampoo checkpoints (eigenvalues, eigenvectors); its inverse roots
+        # Q f(lambda) Q^T only change at a refresh, so the step is the root-inverse step on mirrors
+        # rebuilt then (the torch formulation rebuilds them from the eigendecomposition every step).
+        self._eigdec = type(group[PRECONDITIONER_CONFIG]) is EigendecomposedShampooPreconditionerConfig
         self.launches_per_step = 0
 
         gc = group[GRAFTING_CONFIG]
@@ -265,9 +275,12 @@ class NativeGroupEngine:
             b.gt_lo = zeros(b.n, b.m_pad) if self._split else None
             b.f_hi = zeros(b.m, b.n_pad)
             b.f_lo = zeros(b.m, b.n_pad) if self._split else None
-            b.tt_hi = zeros(b.n, b.m_pad) if two_d else None
-            b.tt_lo = zeros(b.n, b.m_pad) if two_d and self._split else None
-            b.p = zeros(b.m, b.n)
+            # The chain intermediate T^T [n, m_pad] takes over the memory of G^T, whose last reader
+            # (the factor SYRK) has run before the first chain GEMM writes.
+            b.tt_hi = b.gt_hi if two_d else None
+            b.tt_lo = b.gt_lo if two_d and self._split else None
+            # Likewise the search direction P [m, n] reuses G (hi part) when the pitches agree.
+            b.p = b.g_hi if (b.g_hi is not None and b.n_pad == b.n) else zeros(b.m, b.n)
             dims = (b.m, b.n) if two_d else (b.n,)
             b.inv_hi = [zeros(d, _pad4(d)) for d in dims]
             b.inv_lo = [zeros(d, _pad4(d)) if self._split else None for d in dims]
@@ -296,10 +309,13 @@ class NativeGroupEngine:
         b.f_hi, b.f_lo = pair(a * bb, _pad4(c))
         b.aux_g_hi, b.aux_g_lo = pair(a, bb * c)
         b.aux_gt_hi, b.aux_gt_lo = pair(bb * c, a)
-        b.d1_hi, b.d1_lo = pair(c, a * bb)
-        b.d2_hi, b.d2_lo = pair(bb, c * a)
+        # Chain intermediates and the result reuse operand arrays whose last reader (the factor
+        # SYRK) precedes the chain: (c, ab) <- X_c, (b, ca) <- X_b, P (a, bc) <- X_a (hi part).
+        b.d1_hi, b.d1_lo = b.gt_hi, b.gt_lo
+        b.d2_hi = b.aux_gt_hi.view(bb, c * a)
+        b.d2_lo = b.aux_gt_lo.view(bb, c * a) if sp else None
         b.tt_hi = b.tt_lo = None
-        b.p = zeros(a, bb * c)
+        b.p = b.aux_g_hi
         b.inv_hi = [zeros(d, _pad4(d)) for d in b.dims3]
         b.inv_lo = [zeros(d, _pad4(d)) if sp else None for d in b.dims3]
         b.ev = b.qt_hi = b.qt_lo = b.t2_hi = b.t2_lo = None
@@ -530,7 +546,22 @@ class NativeGroupEngine:
                             hi[:, :d].copy_(src)
             return
         for b in self._blocks if blocks is None else blocks:
-            for k, inv in enumerate(b.factors.get_unpacked_inv_factor_matrices()):
+            if self._eigdec:
+                from fractions import Fraction
+
+                from optimizers_b200.matrix import functions as mf
+
+                kf = b.factors
+                stability = kf.amortized_computation_config.rank_deficient_stability_config
+                invs = [
+                    mf.matrix_inverse_root_from_eigendecomposition(
+                        L=lam, Q=Q, root=Fraction(root), epsilon=kf.epsilon, rank_deficient_stability_config=stability
+                    )
+                    for Q, lam, root in zip(kf.factor_matrices_eigenvectors, kf.factor_matrices_eigenvalues, kf.roots, strict=True)
+                ]
+            else:
+                invs = b.factors.get_unpacked_inv_factor_matrices()
+            for k, inv in enumerate(invs):
                 d = inv.shape[0]
                 if self._split:
                     self._ext.tf32_split(inv, b.inv_hi[k][:, :d], b.inv_lo[k][:, :d])
@@ -765,6 +796,13 @@ class NativeGroupEngine:
             else:
                 for b in blocks:
                     b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
+        elif self._eigdec:
+            if batched.eigdec_refresh_supported(cfg):
+                batched.batched_eigen_refresh(self._ext, blocks, plist._bias_correction2, self._split, self._status)
+                self.check_status()
+                return  # the mirrors were written by the refresh itself
+            for b in blocks:
+                b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
         elif batched.eigen_refresh_supported(cfg):
             batched.batched_eigen_refresh(self._ext, blocks, plist._bias_correction2, self._split, self._status)
         elif batched.newton_refresh_supported(cfg):
