@@ -140,9 +140,18 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vec
   for (const Order& o : order) {
     const GemmProblem& p = problems[o.problem];
     const bool upper = specs[o.problem][11].cast<bool>();
-    for (int m0 = 0; m0 < p.M; m0 += kBM) {
-      for (int n0 = upper ? m0 : 0; n0 < p.N; n0 += kBN) {
-        tiles.push_back({o.problem, m0, n0, 0});
+    // Tiles are issued in bands of kBandRows tile rows, column by column inside a band, so that
+    // the ~148 tiles in flight together touch about 2 * sqrt(148) operand panels instead of a
+    // whole row of them: for K = 4096 a (hi, lo) panel is 4 MB and a full tile row of B panels
+    // alone would exceed the L2.
+    constexpr int kBandRows = 12;
+    for (int band = 0; band < p.M; band += kBandRows * kBM) {
+      const int band_end = std::min(p.M, band + kBandRows * kBM);
+      for (int n0 = upper ? band : 0; n0 < p.N; n0 += kBN) {
+        for (int m0 = band; m0 < band_end; m0 += kBM) {
+          if (upper && n0 < m0) continue;
+          tiles.push_back({o.problem, m0, n0, 0});
+        }
       }
     }
   }

@@ -393,3 +393,46 @@ def test_native_engine_order3_blocks_match_torch_step(graft):
             assert (a - b).abs().max().item() / denom < 5e-2, path  # 8 steps of a ReLU conv net amplify 1e-5 differences
 
     walk(results[0][1], results[1][1])
+
+
+@pytest.mark.parametrize("name", ["adam_graft", "soap_adam_graft", "eigendecomposed_adam_graft", "gpa"])
+def test_native_engine_resumes_from_checkpoint(name):
+    """Train 5 steps, checkpoint (model + optimizer), train 4 more; a fresh model / optimizer loaded
+    from the checkpoint must retrace those 4 steps: the engine's operand mirrors are rebuilt from
+    the loaded state (``on_state_loaded``)."""
+    import copy
+
+    from optimizers_b200 import DistributedShampoo, NativeRuntimeConfig
+
+    kw = _configs()[name]
+    dev = torch.device("cuda")
+
+    def make():
+        torch.manual_seed(0)
+        model = _mlp(dev)
+        opt = DistributedShampoo(model.parameters(), native_runtime_config=NativeRuntimeConfig(backend="native"), **kw)
+        opt.train()
+        return model, opt
+
+    def run(model, opt, first, count):
+        g = torch.Generator(device="cuda").manual_seed(100 + first)
+        for _ in range(count):
+            x = torch.randn(64, 96, device=dev, generator=g)
+            y = torch.randint(0, 10, (64,), device=dev, generator=g)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+
+    model, opt = make()
+    run(model, opt, 0, 5)
+    ckpt = copy.deepcopy({"model": model.state_dict(), "opt": opt.state_dict()})
+    run(model, opt, 5, 4)
+
+    model2, opt2 = make()
+    model2.load_state_dict(ckpt["model"])
+    opt2.load_state_dict(ckpt["opt"])
+    run(model2, opt2, 5, 4)
+    for rec in opt2._per_group_state_lists:
+        rec["native_engine"].check_status()
+    for p, q in zip(model.parameters(), model2.parameters()):
+        assert torch.allclose(p, q, rtol=1e-4, atol=1e-6), (p - q).abs().max()
