@@ -37,6 +37,9 @@ from optimizers_b200.matrix import functions as mf
 logger: logging.Logger = logging.getLogger(__name__)
 
 _POOL_SIZE = 8
+_JACOBI_MAX_SWEEPS = 24
+_JACOBI_TOLERANCE = 2e-6  # relative size of a column pair's inner product below which it is left alone
+
 _pools: dict[int, tuple[ThreadPoolExecutor, list[torch.cuda.Stream]]] = {}
 _tls = threading.local()
 
@@ -110,6 +113,29 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
     ready.record(main)
     executor, streams = _pool(device)
 
+    def finish(it: _Item, lam: Tensor, Q: Tensor) -> None:
+        """Eigenpairs -> the two GEMM operands of the reconstruction, (Q s) and Q, as (hi, lo) pairs."""
+        kf = it.block.factors
+        cfg = kf.amortized_computation_config
+        it.lam = lam
+        scale = mf.stabilized_inverse_power(lam, Fraction(it.root), kf.epsilon, cfg.rank_deficient_stability_config)
+        Q = Q.contiguous()
+        it.Q = Q
+        Qs = (Q * scale.unsqueeze(0)).contiguous()
+        d = Q.shape[0]
+        ld = _pad4(d)
+        if split:
+            it.qs_hi, it.qs_lo = torch.zeros(d, ld, device=device), torch.zeros(d, ld, device=device)
+            it.q_hi, it.q_lo = torch.zeros(d, ld, device=device), torch.zeros(d, ld, device=device)
+            ext.tf32_split(Qs, it.qs_hi[:, :d], it.qs_lo[:, :d])
+            ext.tf32_split(Q, it.q_hi[:, :d], it.q_lo[:, :d])
+        else:
+            it.qs_hi = torch.zeros(d, ld, device=device)
+            it.q_hi = torch.zeros(d, ld, device=device)
+            it.qs_hi[:, :d].copy_(Qs)
+            it.q_hi[:, :d].copy_(Q)
+            it.qs_lo = it.q_lo = None
+
     def work(it: _Item, slot: int) -> None:
         kf = it.block.factors
         cfg = kf.amortized_computation_config  # EigenConfig, or EighEigendecompositionConfig (eigendecomposed)
@@ -126,32 +152,39 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
                         tolerance=0.0,
                     ),
                 )
-                it.lam = lam
-                scale = mf.stabilized_inverse_power(
-                    lam, Fraction(it.root), kf.epsilon, cfg.rank_deficient_stability_config
-                )
-                Q = Q.contiguous()
-                it.Q = Q
-                Qs = (Q * scale.unsqueeze(0)).contiguous()
-                d = Q.shape[0]
-                ld = _pad4(d)
-                if split:
-                    it.qs_hi, it.qs_lo = torch.zeros(d, ld, device=device), torch.zeros(d, ld, device=device)
-                    it.q_hi, it.q_lo = torch.zeros(d, ld, device=device), torch.zeros(d, ld, device=device)
-                    ext.tf32_split(Qs, it.qs_hi[:, :d], it.qs_lo[:, :d])
-                    ext.tf32_split(Q, it.q_hi[:, :d], it.q_lo[:, :d])
-                else:
-                    it.qs_hi = torch.zeros(d, ld, device=device)
-                    it.q_hi = torch.zeros(d, ld, device=device)
-                    it.qs_hi[:, :d].copy_(Qs)
-                    it.q_hi[:, :d].copy_(Q)
-                    it.qs_lo = it.q_lo = None
+                finish(it, lam, Q)
             except Exception as exception:  # keep the previous inverse root of this factor
                 it.error = exception
             it.done = torch.cuda.Event()
             it.done.record(stream)
 
-    order = sorted(range(len(items)), key=lambda i: -items[i].A.shape[0])
+    # Small factors: one launch of the shared-memory Jacobi eigensolver for all of them; the
+    # library eigensolver (stream pool) takes the rest and any matrix Jacobi did not converge on.
+    pooled = list(range(len(items)))
+    small = [i for i in pooled if items[i].A.shape[0] <= ext.JACOBI_MAX_N]
+    if small:
+        ridged = []
+        for i in small:
+            kf = items[i].block.factors
+            stability = kf.amortized_computation_config.rank_deficient_stability_config
+            ridged.append(mf._ridge(items[i].A, kf.epsilon * getattr(stability, "perturb_before_computation", 0)).contiguous())
+        lams, qs, sweeps = ext.jacobi_eigh(ridged, _JACOBI_MAX_SWEEPS, _JACOBI_TOLERANCE)
+        used = sweeps.cpu().tolist()
+        done_here = set()
+        for i, lam, Q, n_sweeps in zip(small, lams, qs, used, strict=True):
+            if n_sweeps > _JACOBI_MAX_SWEEPS:
+                continue  # not converged: let the library solver handle it
+            try:
+                finish(items[i], lam, Q)
+            except Exception as exception:
+                items[i].error = exception
+            items[i].done = torch.cuda.Event()
+            items[i].done.record(main)
+            done_here.add(i)
+        pooled = [i for i in pooled if i not in done_here]
+        ready.record(main)
+
+    order = sorted(pooled, key=lambda i: -items[i].A.shape[0])
     futures = [executor.submit(work, items[i], n % _POOL_SIZE) for n, i in enumerate(order)]
     for f in futures:
         f.result()
@@ -599,7 +632,7 @@ def eigenbasis_refresh_supported(cfg: Any) -> bool:
     return isinstance(cfg, EighEigendecompositionConfig) and cfg.eigendecomposition_offload_device == ""
 
 
-def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | float) -> None:
+def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | float, ext: Any = None) -> None:
     """Recompute ``factor_matrices_eigenvectors`` of every block (eigh, or the warm-started QR
     iteration of ``matrix_functions.py:799-852``) with the factors spread over a pool of streams,
     each driven by its own host thread, so that the library factorisations and the convergence
@@ -650,7 +683,30 @@ def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | flo
             it.done = torch.cuda.Event()
             it.done.record(stream)
 
-    order = sorted(range(len(items)), key=lambda i: -items[i].A.shape[0])
+    pooled = list(range(len(items)))
+    cfg0 = blocks[0].factors.amortized_computation_config
+    if ext is not None and isinstance(cfg0, EighEigendecompositionConfig) and cfg0.tolerance == 0.0:
+        # Small factors: one launch of the shared-memory Jacobi eigensolver for all of them.
+        small = [i for i in pooled if items[i].A.shape[0] <= ext.JACOBI_MAX_N]
+        if small:
+            stability = cfg0.rank_deficient_stability_config
+            ridged = [
+                mf._ridge(items[i].A, items[i].block.factors.epsilon * getattr(stability, "perturb_before_computation", 0)).contiguous()
+                for i in small
+            ]
+            _, qs, sweeps = ext.jacobi_eigh(ridged, _JACOBI_MAX_SWEEPS, _JACOBI_TOLERANCE)
+            done_here = set()
+            for i, Q, n_sweeps in zip(small, qs, sweeps.cpu().tolist(), strict=True):
+                if n_sweeps > _JACOBI_MAX_SWEEPS:
+                    continue
+                it = items[i]
+                it.q_hi = Q.to(dtype=it.block.factors.factor_matrices_eigenvectors[it.k].dtype)
+                it.done = torch.cuda.Event()
+                it.done.record(main)
+                done_here.add(i)
+            pooled = [i for i in pooled if i not in done_here]
+            ready.record(main)
+    order = sorted(pooled, key=lambda i: -items[i].A.shape[0])
     futures = [executor.submit(work, items[i], n % _POOL_SIZE) for n, i in enumerate(order)]
     for f in futures:
         f.result()

@@ -792,7 +792,7 @@ class NativeGroupEngine:
         cfg = self._group[PRECONDITIONER_CONFIG].amortized_computation_config
         if self._soap:
             if batched.eigenbasis_refresh_supported(cfg):
-                batched.batched_eigenbasis_refresh(blocks, plist._bias_correction2)
+                batched.batched_eigenbasis_refresh(blocks, plist._bias_correction2, self._ext)
             else:
                 for b in blocks:
                     b.factors.amortized_computation(bias_correction2=plist._bias_correction2)

@@ -506,6 +506,35 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_copy_table(const std::ve
   return {d_descs, d_chunks, static_cast<int64_t>(chunks.size())};
 }
 
+// Eigendecomposition of a list of small symmetric fp32 matrices (n <= 128) in one launch.
+// Returns (eigenvalue tensors, eigenvector tensors, sweeps used per matrix as a device int tensor).
+std::tuple<std::vector<torch::Tensor>, std::vector<torch::Tensor>, torch::Tensor> jacobi_eigh(
+    const std::vector<torch::Tensor>& mats, int64_t max_sweeps, double tol) {
+  TORCH_CHECK(!mats.empty(), "jacobi_eigh: empty batch");
+  const auto device = mats[0].device();
+  c10::cuda::CUDAGuard guard(device);
+  std::vector<JacobiDesc> descs(mats.size());
+  std::vector<torch::Tensor> lams, qs;
+  for (size_t i = 0; i < mats.size(); ++i) {
+    const auto& a = mats[i];
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == torch::kFloat32 && a.dim() == 2 && a.size(0) == a.size(1) &&
+                    a.stride(1) == 1 && a.size(0) <= kJacobiMaxN && a.size(0) >= 1,
+                "jacobi_eigh: square fp32 CUDA matrices of size <= ", kJacobiMaxN);
+    const int64_t n = a.size(0);
+    lams.push_back(torch::empty({n}, a.options()));
+    qs.push_back(torch::empty({n, n}, a.options()));
+    descs[i] = {a.data_ptr<float>(), qs.back().data_ptr<float>(), lams.back().data_ptr<float>(), static_cast<int>(n),
+                static_cast<int>(a.stride(0)), static_cast<int>(n), 0};
+  }
+  auto d_descs = upload_bytes(descs.data(), descs.size() * sizeof(JacobiDesc), device);
+  auto sweeps = torch::zeros({static_cast<int64_t>(mats.size())}, torch::dtype(torch::kInt32).device(device));
+  launch_jacobi_eigh(reinterpret_cast<const JacobiDesc*>(d_descs.data_ptr()), static_cast<int>(mats.size()),
+                     static_cast<int>(max_sweeps), static_cast<float>(tol), sweeps.data_ptr<int>(),
+                     at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {lams, qs, sweeps};
+}
+
 void peer_copy(const torch::Tensor& table, const torch::Tensor& chunks, int64_t num_chunks) {
   if (num_chunks == 0) return;
   c10::cuda::CUDAGuard guard(table.device());
@@ -542,6 +571,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_gpa_table", &build_gpa_table);
   m.def("gpa_adamw_step", &gpa_adamw_step);
   m.def("gpa_lerp", &gpa_lerp);
+  m.def("jacobi_eigh", &jacobi_eigh);
+  m.attr("JACOBI_MAX_N") = kJacobiMaxN;
   m.def("build_copy_table", &build_copy_table);
   m.def("peer_copy", &peer_copy);
   ob200::register_model_ops(m);

@@ -144,6 +144,146 @@ __global__ void __launch_bounds__(256) peer_copy_kernel(const CopyDesc* __restri
   }
 }
 
+constexpr int kJacobiThreads = 256;
+constexpr int kJacobiPitch = kJacobiMaxN + 1;  // odd: column reads and row (transposed) reads are both conflict-free
+
+__global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const JacobiDesc* __restrict__ descs,
+                                                                     int max_sweeps, float tol,
+                                                                     int* __restrict__ sweeps_out) {
+  extern __shared__ float jsm[];
+  float* a = jsm;                                // column j of A V at a + j * pitch
+  float* v = jsm + kJacobiMaxN * kJacobiPitch;   // column j of V
+  __shared__ int rotated;
+  __shared__ float lam_s[kJacobiMaxN];
+  const JacobiDesc d = descs[blockIdx.x];
+  const int n = d.n;
+  const int np = n + (n & 1);  // even number of players; the extra one is a zero column
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int kWarps = kJacobiThreads / 32;
+
+  // A is symmetric: row j read contiguously is column j.
+  for (int j = warp; j < np; j += kWarps) {
+    for (int i = lane; i < np; i += 32) {
+      a[j * kJacobiPitch + i] = (i < n && j < n) ? d.a[static_cast<long long>(j) * d.lda + i] : 0.f;
+      v[j * kJacobiPitch + i] = (i == j) ? 1.f : 0.f;
+    }
+  }
+  __syncthreads();
+
+  int sweep = 0;
+  bool converged = false;
+  for (; sweep < max_sweeps && !converged; ++sweep) {
+    if (threadIdx.x == 0) rotated = 0;
+    __syncthreads();
+    for (int r = 0; r < np - 1; ++r) {
+      // Round r of the round-robin tournament: player np-1 stays, the others rotate.
+      for (int k = warp; k < np / 2; k += kWarps) {
+        int p, q;
+        if (k == 0) {
+          p = np - 1;
+          q = r;
+        } else {
+          p = (r + k) % (np - 1);
+          q = (r - k + (np - 1)) % (np - 1);
+        }
+        float* ap = a + p * kJacobiPitch;
+        float* aq = a + q * kJacobiPitch;
+        float alpha = 0.f, beta = 0.f, gamma = 0.f;
+        for (int i = lane; i < n; i += 32) {
+          const float x = ap[i], y = aq[i];
+          alpha += x * x;
+          beta += y * y;
+          gamma += x * y;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          alpha += __shfl_xor_sync(0xffffffffu, alpha, o);
+          beta += __shfl_xor_sync(0xffffffffu, beta, o);
+          gamma += __shfl_xor_sync(0xffffffffu, gamma, o);
+        }
+        if (fabsf(gamma) > tol * sqrtf(alpha * beta) && fabsf(gamma) > 1e-37f) {
+          const float zeta = (beta - alpha) / (2.f * gamma);
+          const float t = copysignf(1.f, zeta) / (fabsf(zeta) + sqrtf(1.f + zeta * zeta));
+          const float c = rsqrtf(1.f + t * t), s = c * t;
+          float* vp = v + p * kJacobiPitch;
+          float* vq = v + q * kJacobiPitch;
+          for (int i = lane; i < n; i += 32) {
+            const float x = ap[i], y = aq[i];
+            ap[i] = c * x - s * y;
+            aq[i] = s * x + c * y;
+            const float vx = vp[i], vy = vq[i];
+            vp[i] = c * vx - s * vy;
+            vq[i] = s * vx + c * vy;
+          }
+          if (lane == 0) rotated = 1;
+        }
+      }
+      __syncthreads();
+    }
+    converged = rotated == 0;
+    __syncthreads();
+  }
+
+  // lambda_j = v_j . (A v_j); ascending order by rank (ties broken by index).
+  for (int j = warp; j < n; j += kWarps) {
+    float dot = 0.f;
+    for (int i = lane; i < n; i += 32) dot += v[j * kJacobiPitch + i] * a[j * kJacobiPitch + i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) lam_s[j] = dot;
+  }
+  __syncthreads();
+  // Thousands of fp32 rotations leave V orthogonal only to ~3e-5; one Newton-Schulz step
+  // V <- V (3 I - V^T V) / 2 squares that error.  M = 1.5 I - 0.5 V^T V goes where A V was.
+  for (int j = warp; j < n; j += kWarps) {
+    for (int k = 0; k <= j; ++k) {
+      float dot = 0.f;
+      for (int i = lane; i < n; i += 32) dot += v[j * kJacobiPitch + i] * v[k * kJacobiPitch + i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (lane == 0) {
+        const float m = (j == k ? 1.5f : 0.f) - 0.5f * dot;
+        a[j * kJacobiPitch + k] = m;
+        a[k * kJacobiPitch + j] = m;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = warp; i < n; i += kWarps) {  // row i of V (component i of every eigenvector) is owned by one warp
+    float acc[kJacobiMaxN / 32];
+#pragma unroll
+    for (int u = 0; u < kJacobiMaxN / 32; ++u) acc[u] = 0.f;
+    for (int k = 0; k < n; ++k) {
+      const float x = v[k * kJacobiPitch + i];
+#pragma unroll
+      for (int u = 0; u < kJacobiMaxN / 32; ++u) {
+        const int j = lane + 32 * u;
+        if (j < n) acc[u] += x * a[k * kJacobiPitch + j];
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < kJacobiMaxN / 32; ++u) {
+      const int j = lane + 32 * u;
+      if (j < n) v[j * kJacobiPitch + i] = acc[u];
+    }
+  }
+  __syncthreads();
+  int* rank_of = reinterpret_cast<int*>(a);  // M is no longer needed
+  for (int j = threadIdx.x; j < n; j += kJacobiThreads) {
+    const float x = lam_s[j];
+    int rank = 0;
+    for (int k = 0; k < n; ++k) rank += (lam_s[k] < x) || (lam_s[k] == x && k < j);
+    rank_of[j] = rank;
+    d.lam[rank] = x;
+  }
+  __syncthreads();
+  // Q[i][rank(j)] = v_j[i]; lanes run over j so that the scattered destination stays within a row.
+  for (int i = warp; i < n; i += kWarps)
+    for (int j = lane; j < n; j += 32) d.q[static_cast<long long>(i) * d.ldq + rank_of[j]] = v[j * kJacobiPitch + i];
+  if (threadIdx.x == 0) sweeps_out[blockIdx.x] = converged ? sweep : max_sweeps + 1;
+}
+
 struct GpaScalars {
   float lr, beta1, beta2, eps, bc1, bc2, wd, avg_coeff, mu_y;
   int wd_on_y;
@@ -302,6 +442,18 @@ void launch_affine_identity_split(const MatOp* ops, const int2* chunks, int num_
 void launch_identity_error(const MatOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream) {
   if (num_chunks <= 0) return;
   identity_error_kernel<<<grid_for(num_chunks), 256, 0, stream>>>(ops, chunks, num_chunks);
+}
+
+void launch_jacobi_eigh(const JacobiDesc* descs, int count, int max_sweeps, float tol, int* sweeps,
+                        cudaStream_t stream) {
+  if (count <= 0) return;
+  constexpr int smem = 2 * kJacobiMaxN * kJacobiPitch * static_cast<int>(sizeof(float));
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(jacobi_eigh_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    configured = true;
+  }
+  jacobi_eigh_kernel<<<count, kJacobiThreads, smem, stream>>>(descs, max_sweeps, tol, sweeps);
 }
 
 void launch_peer_copy(const CopyDesc* table, const int2* chunks, int num_chunks, cudaStream_t stream) {

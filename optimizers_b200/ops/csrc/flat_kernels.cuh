@@ -42,6 +42,27 @@ constexpr int kCopyChunkBytes = 64 * 1024;  // bytes handled by one CTA iteratio
 // (reference: distributed_shampoo/distributor/_shampoo_fully_shard_utils.py:519-588, :806-835).
 void launch_peer_copy(const CopyDesc* table, const int2* chunks, int num_chunks, cudaStream_t stream);
 
+// One symmetric matrix of a batched eigendecomposition.
+struct JacobiDesc {
+  const float* a;  // n x n, row pitch lda (symmetric)
+  float* q;        // n x n, row pitch ldq: eigenvectors as columns, ascending eigenvalue order
+  float* lam;      // n eigenvalues, ascending
+  int n, lda, ldq, pad_;
+};
+
+constexpr int kJacobiMaxN = 128;
+
+// jacobi_eigh: eigendecomposition of many small symmetric matrices (n <= 128), one CTA per
+// matrix, entirely in shared memory: one-sided (Hestenes) Jacobi on the columns of A with a
+// round-robin pair schedule (n/2 disjoint pairs per round, one warp per pair), V accumulated
+// alongside; at convergence the columns of A V are lambda_j v_j.  Sweeps stop when no pair of a
+// sweep exceeded the relative threshold, or after `max_sweeps`.  It replaces the per-matrix library
+// eigensolver calls (torch.linalg.eigh -> syevd, reference matrix_functions.py:754) for the small
+// factors, where launch and workspace overhead dominates; `sweeps` (one int per matrix) reports the
+// number of sweeps used, max_sweeps + 1 meaning not converged.
+void launch_jacobi_eigh(const JacobiDesc* descs, int count, int max_sweeps, float tol, int* sweeps,
+                        cudaStream_t stream);
+
 // One square matrix of a grouped pointwise pass over many matrices of different sizes.
 struct MatOp {
   const float* src;  // d x d, row pitch ld_src
