@@ -22,7 +22,7 @@ unproject (``_soap_step``) and updates its second moment in the epilogue of the 
 
 Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 (and contiguous order-3 blocks for
 root-inverse Shampoo) with every dim preconditioned,
-root-inverse, eigendecomposed or eigenvalue-corrected Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting,
+root-inverse, eigendecomposed, KL or eigenvalue-corrected Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting,
 any weight decay type,
 classic momentum, GPA / Schedule-Free, single-device and DDP distributors (NCCL all-gather, or
 peer-to-peer stores and loads over NVLink with ``comm_path="p2p"``).  Anything else makes
@@ -45,6 +45,7 @@ from optimizers_b200.config import (
     DDPDistributedConfig,
     DISTRIBUTED_CONFIG,
     DISTRIBUTOR,
+    EigendecomposedKLShampooPreconditionerConfig,
     EigendecomposedShampooPreconditionerConfig,
     EigenvalueCorrectedShampooPreconditionerConfig,
     FILTERED_GRAD_LIST,
@@ -58,6 +59,7 @@ from optimizers_b200.config import (
     PARAMS,
     PRECONDITIONER_CONFIG,
     PreconditionerValueError,
+    RootInvKLShampooPreconditionerConfig,
     RootInvShampooPreconditionerConfig,
     SGDPreconditionerConfig,
     SHAMPOO_PRECONDITIONER_LIST,
@@ -79,10 +81,10 @@ def _pad4(n: int) -> int:
 
 def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     pc = group[PRECONDITIONER_CONFIG]
-    if type(pc) is RootInvShampooPreconditionerConfig:
+    if type(pc) in (RootInvShampooPreconditionerConfig, RootInvKLShampooPreconditionerConfig):
         if pc.factor_matrix_dtype != torch.float32 or pc.inv_factor_matrix_dtype != torch.float32:
             return "factor matrices must be fp32"
-    elif type(pc) is EigendecomposedShampooPreconditionerConfig:
+    elif type(pc) in (EigendecomposedShampooPreconditionerConfig, EigendecomposedKLShampooPreconditionerConfig):
         dtypes = (pc.factor_matrix_dtype, pc.factor_matrix_eigenvectors_dtype, pc.factor_matrix_eigenvalues_dtype)
         if any(d != torch.float32 for d in dtypes):
             return "factor matrices, eigenvectors and eigenvalues must be fp32"
@@ -128,7 +130,7 @@ def _order3_ok(block: Tensor, pc: Any) -> bool:
     """Order-3 blocks (a, b, c) run natively for root-inverse Shampoo when they are contiguous and
     a, b are multiples of 4, so that every mode unfolding is an exact, 16-byte aligned 2-D view."""
     a, b, _ = block.shape
-    root_like = type(pc) in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig)
+    root_like = type(pc) in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig)  # not KL
     return root_like and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
 
 
@@ -151,7 +153,7 @@ class _Block:
         "index", "param_view", "grad_slot", "grad_offset", "m", "n", "n_pad", "m_pad", "order", "factors",
         "m1", "v", "mom", "z", "g_hi", "g_lo", "gt_hi", "gt_lo", "f_hi", "f_lo", "tt_hi", "tt_lo", "p",
         "inv_hi", "inv_lo", "ev", "qt_hi", "qt_lo", "t2_hi", "t2_lo",
-        "dims3", "view2d", "aux_g_hi", "aux_g_lo", "aux_gt_hi", "aux_gt_lo", "d1_hi", "d1_lo", "d2_hi", "d2_lo",
+        "dims3", "view2d", "y_hi", "y_lo", "zt_hi", "zt_lo", "aux_g_hi", "aux_g_lo", "aux_gt_hi", "aux_gt_lo", "d1_hi", "d1_lo", "d2_hi", "d2_lo",
     )
 
 
@@ -174,7 +176,14 @@ class NativeGroupEngine:
         # Eigendecomposed Shampoo checkpoints (eigenvalues, eigenvectors); its inverse roots
         # Q f(lambda) Q^T only change at a refresh, so the step is the root-inverse step on mirrors
         # rebuilt then (the torch formulation rebuilds them from the eigendecomposition every step).
-        self._eigdec = type(group[PRECONDITIONER_CONFIG]) is EigendecomposedShampooPreconditionerConfig
+        self._eigdec = type(group[PRECONDITIONER_CONFIG]) in (
+            EigendecomposedShampooPreconditionerConfig, EigendecomposedKLShampooPreconditionerConfig
+        )
+        # KL-Shampoo: the Gram of a dim is taken of the gradient preconditioned along the other dim,
+        # two extra GEMMs per 2-D block in front of the factor SYRK.
+        self._kl = type(group[PRECONDITIONER_CONFIG]) in (
+            RootInvKLShampooPreconditionerConfig, EigendecomposedKLShampooPreconditionerConfig
+        )
         self.launches_per_step = 0
 
         gc = group[GRAFTING_CONFIG]
@@ -277,6 +286,12 @@ class NativeGroupEngine:
             b.f_lo = zeros(b.m, b.n_pad) if self._split else None
             # The chain intermediate T^T [n, m_pad] takes over the memory of G^T, whose last reader
             # (the factor SYRK) has run before the first chain GEMM writes.
+            b.y_hi = b.y_lo = b.zt_hi = b.zt_lo = None
+            if self._kl and two_d:
+                # Y = G R^(-1/p) [m, n] and Z^T = G^T L^(-1/p) [n, m]: operands of the KL factor Grams.
+                b.y_hi, b.zt_hi = zeros(b.m, b.n_pad), zeros(b.n, b.m_pad)
+                if self._split:
+                    b.y_lo, b.zt_lo = zeros(b.m, b.n_pad), zeros(b.n, b.m_pad)
             b.tt_hi = b.gt_hi if two_d else None
             b.tt_lo = b.gt_lo if two_d and self._split else None
             # Likewise the search direction P [m, n] reuses G (hi part) when the pitches agree.
@@ -303,6 +318,7 @@ class NativeGroupEngine:
         GEMMs walk (a,b,c) -> (c,a,b) -> (b,c,a) -> (a,b,c) without any transposition pass."""
         a, bb, c = b.dims3
         sp = self._split
+        b.y_hi = b.y_lo = b.zt_hi = b.zt_lo = None
         pair = lambda r, cols: (zeros(r, cols), zeros(r, cols) if sp else None)  # noqa: E731
         b.g_hi = b.g_lo = None
         b.gt_hi, b.gt_lo = pair(c, a * bb)
@@ -412,7 +428,7 @@ class NativeGroupEngine:
         def op(t: Tensor, rows: int, k: int) -> Tensor:
             return t[:, :k] if t.shape[1] != k else t
 
-        syrk, gemm0, gemm1, gemm2 = [], [], [], []
+        syrk, gemm0, gemm1, gemm2, kl = [], [], [], [], []
         pack_flag = F.FLAG_PACKED_C if self._packing else 0
         sp = self._split
 
@@ -441,11 +457,24 @@ class NativeGroupEngine:
                 gemm2.append((*inv[0], *d2, b.p, None, None, self._norms[b.index, 1:2], bb * c, 0, F.FLAG_SUMSQ, False))
                 continue
             two_d = b.order == 2
-            if two_d:
-                a_hi, a_lo = op(b.g_hi, b.m, b.n), (op(b.g_lo, b.m, b.n) if self._split else None)
-                syrk.append((a_hi, a_lo, a_hi, a_lo, fm[0], None, None, None, b.m, 0, pack_flag, self._packing))
             t_hi, t_lo = op(b.gt_hi, b.n, b.m), (op(b.gt_lo, b.n, b.m) if self._split else None)
-            syrk.append((t_hi, t_lo, t_hi, t_lo, fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
+            if two_d and self._kl:
+                # KL-Shampoo statistics: L <- Gram of G R^(-1/p), R <- Gram of L^(-1/p) G, with the
+                # current inverse roots (reference: shampoo_preconditioner_list.py:1945-2046).
+                a_hi, a_lo = op(b.g_hi, b.m, b.n), (op(b.g_lo, b.m, b.n) if sp else None)
+                ri = (op(b.inv_hi[1], b.n, b.n), op(b.inv_lo[1], b.n, b.n) if sp else None)
+                li = (op(b.inv_hi[0], b.m, b.m), op(b.inv_lo[0], b.m, b.m) if sp else None)
+                kl.append(chained(a_hi, a_lo, *ri, b.y_hi, b.y_lo))
+                kl.append(chained(t_hi, t_lo, *li, b.zt_hi, b.zt_lo))
+                y = (op(b.y_hi, b.m, b.n), op(b.y_lo, b.m, b.n) if sp else None)
+                zt = (op(b.zt_hi, b.n, b.m), op(b.zt_lo, b.n, b.m) if sp else None)
+                syrk.append((*y, *y, fm[0], None, None, None, b.m, 0, pack_flag, self._packing))
+                syrk.append((*zt, *zt, fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
+            else:
+                if two_d:
+                    a_hi, a_lo = op(b.g_hi, b.m, b.n), (op(b.g_lo, b.m, b.n) if self._split else None)
+                    syrk.append((a_hi, a_lo, a_hi, a_lo, fm[0], None, None, None, b.m, 0, pack_flag, self._packing))
+                syrk.append((t_hi, t_lo, t_hi, t_lo, fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
 
             f_hi, f_lo = op(b.f_hi, b.m, b.n), (op(b.f_lo, b.m, b.n) if self._split else None)
             sumsq = self._norms[b.index, 1:2]
@@ -464,6 +493,7 @@ class NativeGroupEngine:
                 r_hi, r_lo = op(b.inv_hi[0], b.n, b.n), (op(b.inv_lo[0], b.n, b.n) if self._split else None)
                 gemm2.append((f_hi, f_lo, r_hi, r_lo, b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
         self._syrk_plan = ext.build_gemm_plan(syrk)
+        self._kl_plan = ext.build_gemm_plan(kl) if kl else None
         self._gemm0_plan = ext.build_gemm_plan(gemm0) if gemm0 else None
         self._gemm1_plan = ext.build_gemm_plan(gemm1) if gemm1 else None
         self._gemm2_plan = ext.build_gemm_plan(gemm2)
@@ -717,6 +747,9 @@ class NativeGroupEngine:
             self._arena.world if self._pull else 0, 1.0 / self._arena.world if self._pull else 1.0,
         )
         launches += 2
+        if not self._soap and self._kl_plan is not None:
+            ext.run_gemm_plan(*self._kl_plan, 1.0, 0.0, self._split, self._status)
+            launches += 1
         ext.run_gemm_plan(*self._syrk_plan, plist._weighting_factor, plist._beta2, self._split, self._status)
         launches += 1
 
