@@ -14,6 +14,8 @@ def _entry(rank, world, store_path, fn, args, queue):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), GLOO_SOCKET_IFNAME="lo")
     torch.set_num_threads(1)
     if os.environ.get("OB200_TEST_STALL_DUMP"):
+        # Debug aid: OB200_TEST_STALL_DUMP=/some/prefix makes every rank write its Python stack to
+        # <prefix>.<rank> if it is still running after 60 s (shows which collective a rank sits in).
         import faulthandler
 
         faulthandler.dump_traceback_later(60, file=open(f"{os.environ['OB200_TEST_STALL_DUMP']}.{rank}", "w"))
