@@ -47,6 +47,11 @@ _tls = threading.local()
 def _pool(device: torch.device) -> tuple[ThreadPoolExecutor, list[torch.cuda.Stream]]:
     key = device.index if device.index is not None else torch.cuda.current_device()
     if key not in _pools:
+        # torch initialises its linear-algebra back-end lazily and not thread-safely: the first
+        # eigh / qr must happen on one thread before the pool's threads call them concurrently.
+        warm = torch.eye(2, device=device)
+        torch.linalg.eigh(warm)
+        torch.linalg.qr(warm)
         streams = [torch.cuda.Stream(device=device) for _ in range(_POOL_SIZE)]
         _pools[key] = (ThreadPoolExecutor(max_workers=_POOL_SIZE, thread_name_prefix="ob200-eigh"), streams)
     return _pools[key]

@@ -102,8 +102,6 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
         return f"grafting config {type(gc).__name__} has no native step"
     dc = group[DISTRIBUTED_CONFIG]
     if isinstance(dc, DDPDistributedConfig):
-        if dc.communicate_params:
-            return "communicate_params=True has no native step yet"
         if dc.communication_dtype not in (torch.float32, torch.bfloat16, torch.float16):
             return f"communication dtype {dc.communication_dtype} has no native step"
     # What the distributor blocks: the parameters themselves, their local shards, or (lossless
@@ -198,7 +196,8 @@ class NativeGroupEngine:
         self._ddp = isinstance(group[DISTRIBUTED_CONFIG], DDPDistributedConfig)
         self._p2p = type(group[DISTRIBUTED_CONFIG]) is DDPDistributedConfig and cfg.comm_path == "p2p"
         self._pull = self._p2p and cfg.fuse_gradient_reduction
-        self._gemm_push = self._p2p and cfg.fuse_direction_push and not self._soap
+        self._comm_params = bool(getattr(group[DISTRIBUTED_CONFIG], "communicate_params", False)) and self._ddp
+        self._gemm_push = self._p2p and cfg.fuse_direction_push and not self._soap and not self._comm_params
         self.gemm_push_steps = 0  # steps whose all-gather ran from the GEMM epilogue
         self._comm_dtype_code = 0
         self._gather_table = None
@@ -787,7 +786,7 @@ class NativeGroupEngine:
         ext.direction_epilogue(
             blocks_t, tiles_t, n_tiles, lr, graft_only, self._graft_kind if has_grafting else _GRAFT_NONE, g_bc2,
             g_eps, alpha, primal, mu_y, mu_x, classic, momentum, dampening, nesterov, self._comm_dtype_code, self._split,
-            self._gather_bases if self._p2p else [],
+            self._gather_bases if self._p2p else [], self._comm_params,
         )
         launches += 1
         self.launches_per_step = launches
@@ -907,7 +906,7 @@ class NativeGroupEngine:
             if scaled is not None:
                 self._ext.gathered_apply_scaled(*self._gather_table, self._comm_dtype_code, scaled[0], scaled[1])
             else:
-                self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code)
+                self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code, self._comm_params)
             self.launches_per_step += 1
         if hasattr(dist_, "_write_back"):
             dist_._write_back()

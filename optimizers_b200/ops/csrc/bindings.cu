@@ -285,13 +285,15 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
                         const torch::Tensor& lr, bool graft_only, int64_t graft_kind, double graft_bc2,
                         double graft_eps, double wd_alpha, bool primal_averaging, const torch::Tensor& mu_y,
                         const torch::Tensor& mu_x, bool classic_momentum, double momentum, double dampening,
-                        bool nesterov, int64_t send_dtype, bool split_input, const std::vector<int64_t>& peer_bases) {
+                        bool nesterov, int64_t send_dtype, bool split_input, const std::vector<int64_t>& peer_bases,
+                        bool send_params) {
   c10::cuda::CUDAGuard guard(blocks.device());
   EpilogueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
   a.tiles = wide_tile_ptr(tiles, num_tiles);
   a.num_tiles = wide_tiles(num_tiles);
   a.lr = lr.data_ptr<float>();
+  a.send_params = send_params ? 1 : 0;
   a.graft_only = graft_only ? 1 : 0;
   a.graft_kind = static_cast<int>(graft_kind);
   a.graft_bias_correction2 = static_cast<float>(graft_bc2);
@@ -313,11 +315,12 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
-void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype) {
+void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype,
+                    bool copy_params) {
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
                         wide_tiles(num_tiles),
-                        static_cast<int>(dtype), nullptr, 0.f, at::cuda::getCurrentCUDAStream());
+                        static_cast<int>(dtype), nullptr, 0.f, copy_params, at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -328,7 +331,7 @@ void gathered_apply_scaled(const torch::Tensor& blocks, const torch::Tensor& til
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
                         wide_tiles(num_tiles), static_cast<int>(dtype), lr.data_ptr<float>(),
-                        static_cast<float>(wd_alpha), at::cuda::getCurrentCUDAStream());
+                        static_cast<float>(wd_alpha), false, at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

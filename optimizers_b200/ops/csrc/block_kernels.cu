@@ -369,6 +369,10 @@ __global__ void __launch_bounds__(256, kPlain ? 3 : 2) direction_epilogue_kernel
       }
       if (!kPlain && a.classic_momentum) store4(b.mom + e, mnew, vec, cnt);
       if (!kPlain && a.primal_averaging) store4(b.z + e, znew, vec, cnt);
+      if (a.send_params && (a.num_push_peers > 0 || b.send != nullptr)) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out[k] += w[r][k];
+      }
       if (a.num_push_peers > 0) {
         for (int s = 0; s < a.num_push_peers; ++s)
           store_send4(reinterpret_cast<void*>(a.peer_base[s] + b.slot_offset), e, out, a.send_dtype, vec, cnt);
@@ -387,7 +391,7 @@ __global__ void __launch_bounds__(256, kPlain ? 3 : 2) direction_epilogue_kernel
 __global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __restrict__ blocks,
                                                              const TileRef* __restrict__ tiles, int num_tiles,
                                                              int dtype, const float* __restrict__ lr_ptr,
-                                                             float wd_alpha) {
+                                                             float wd_alpha, int copy_params) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool scaled = lr_ptr != nullptr;
   const float lr = scaled ? *lr_ptr : 0.f;
@@ -410,7 +414,10 @@ __global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __
     for (int r = 0; r < 4; ++r) {
       const int i = i0 + warp + 8 * r;
       if (i >= b.m) continue;
-      if (scaled) {
+      if (copy_params) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w[r][k] = d[r][k];
+      } else if (scaled) {
         const float sc = b.norms != nullptr ? b.norms[0] : 1.f;
 #pragma unroll
         for (int k = 0; k < 4; ++k) w[r][k] -= lr * (sc * d[r][k] + wd_alpha * w[r][k]);
@@ -563,9 +570,10 @@ void launch_peer_barrier(int* local_flags, const unsigned long long* peer_flag_b
 }
 
 void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype, const float* lr,
-                           float wd_alpha, cudaStream_t stream) {
+                           float wd_alpha, bool copy_params, cudaStream_t stream) {
   if (num_tiles <= 0) return;
-  gathered_apply_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, dtype, lr, wd_alpha);
+  gathered_apply_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, dtype, lr, wd_alpha,
+                                                                 copy_params ? 1 : 0);
 }
 
 }  // namespace ob200

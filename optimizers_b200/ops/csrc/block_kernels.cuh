@@ -99,6 +99,7 @@ struct EpilogueArgs {
   int num_push_peers;             // G > 0: store the direction into the gather buffer of all G ranks
                                   // (all-gather fused into the epilogue); 0: BlockDesc::send or params
   unsigned long long peer_base[8];  // gather-buffer base address on each rank (this rank included)
+  int send_params;                // 1: what is sent is the updated parameter W + update (communicate_params)
 };
 
 // eig_scale: S = P / ((ev / bc2)^(1/root) + eps) on the projected filtered gradient held in
@@ -130,7 +131,8 @@ void launch_direction_epilogue(const EpilogueArgs& args, cudaStream_t stream);
 // With `lr` non-null the slots hold unscaled directions P and BlockDesc::norms points at the
 // block's grafting scale s: W <- W - lr (s P + wd_alpha W); this finishes, on every rank, the
 // update whose directions the preconditioner GEMM pushed from its epilogue.
+// `copy_params`: the slots hold updated parameters (communicate_params): W <- slot.
 void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype, const float* lr,
-                           float wd_alpha, cudaStream_t stream);
+                           float wd_alpha, bool copy_params, cudaStream_t stream);
 
 }  // namespace ob200

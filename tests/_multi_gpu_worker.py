@@ -12,6 +12,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main() -> None:
     mode, out = sys.argv[1], sys.argv[2]
+    comm_params = mode.endswith("+params")  # updated parameters travel instead of search directions
+    mode = mode.removesuffix("+params")
     from optimizers_b200 import (
         AdamPreconditionerConfig,
         DDPDistributedConfig,
@@ -40,7 +42,9 @@ def main() -> None:
         model.parameters(), lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64,
         precondition_frequency=3, start_preconditioning_step=3, weight_decay=1e-2,
         grafting_config=AdamPreconditionerConfig(),
-        distributed_config=DDPDistributedConfig(communication_dtype=torch.float32, num_trainers_per_group=world),
+        distributed_config=DDPDistributedConfig(
+            communication_dtype=torch.float32, num_trainers_per_group=world, communicate_params=comm_params
+        ),
         native_runtime_config=native,
     )
     g = torch.Generator(device="cuda").manual_seed(1)

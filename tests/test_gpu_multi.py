@@ -35,6 +35,19 @@ def test_native_ddp_matches_torch_ddp(tmp_path, mode):
         assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode", ["native_nccl", "p2p_push"])
+def test_native_ddp_communicate_params_matches_torch(tmp_path, mode):
+    """communicate_params=True: owners apply their blocks' updates and the updated parameters
+    are gathered (NCCL, or stored into the peers' buffers by the epilogue)."""
+    n = min(torch.cuda.device_count(), 4)
+    ref, got = str(tmp_path / "ref.pt"), str(tmp_path / "got.pt")
+    _run("torch+params", n, ref, 29547)
+    _run(f"{mode}+params", n, got, 29548)
+    for a, b in zip(torch.load(ref), torch.load(got)):
+        assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
+
+
 SHARDED = ["fsdp", "hsdp", "fully_shard", "fully_shard_rr", "fully_shard_rep", "hybrid_shard", "hybrid_shard_rr"]
 
 
