@@ -44,6 +44,8 @@ def main() -> None:
     ap.add_argument("--every", type=int, default=25)
     ap.add_argument("--impls", default="native,torch,reference")
     ap.add_argument("--precondition-frequency", type=int, default=20)
+    ap.add_argument("--epsilon", type=float, default=1e-10)
+    ap.add_argument("--gemm-mode", default="tf32x3")
     args = ap.parse_args()
 
     import torch
@@ -63,11 +65,11 @@ def main() -> None:
         else:
             import optimizers_b200 as lib
 
-            extra = {"native_runtime_config": lib.NativeRuntimeConfig(backend=impl)}
+            extra = {"native_runtime_config": lib.NativeRuntimeConfig(backend=impl, gemm_mode=args.gemm_mode)}
         torch.manual_seed(0)
         model = GPT2(GPT2Config(vocab_size=vocab, n_ctx=seq, n_layer=4, n_head=4, d_model=256, d_mlp=1024, fused=False)).to(dev)
         opt = lib.DistributedShampoo(
-            model.parameters(), lr=3e-3, betas=(0.9, 0.999), epsilon=1e-10, weight_decay=1e-4,
+            model.parameters(), lr=3e-3, betas=(0.9, 0.999), epsilon=args.epsilon, weight_decay=1e-4,
             max_preconditioner_dim=512, precondition_frequency=args.precondition_frequency,
             start_preconditioning_step=args.precondition_frequency,
             grafting_config=lib.AdamPreconditionerConfig(beta2=0.999, epsilon=1e-8), **extra,
@@ -81,7 +83,7 @@ def main() -> None:
             opt.zero_grad(set_to_none=True)
             if step % args.every == 0 or step == args.steps - 1:
                 losses.append(round(float(loss.item()), 4))
-        print(json.dumps({"impl": impl, "ln_vocab": round(math.log(vocab), 4), "every": args.every, "losses": losses}))
+        print(json.dumps({"impl": impl, "epsilon": args.epsilon, "gemm_mode": args.gemm_mode if impl == "native" else None, "ln_vocab": round(math.log(vocab), 4), "every": args.every, "losses": losses}))
 
 
 if __name__ == "__main__":
