@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <optional>
 #include <vector>
@@ -144,7 +145,11 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vec
     // the ~148 tiles in flight together touch about 2 * sqrt(148) operand panels instead of a
     // whole row of them: for K = 4096 a (hi, lo) panel is 4 MB and a full tile row of B panels
     // alone would exceed the L2.
-    constexpr int kBandRows = 12;
+    static const int kBandRows = [] {
+      const char* env = std::getenv("OB200_GEMM_BAND_ROWS");  // tuning knob; 1 = plain row-major order
+      const int v = env != nullptr ? std::atoi(env) : 12;
+      return v > 0 ? v : 12;
+    }();
     for (int band = 0; band < p.M; band += kBandRows * kBM) {
       const int band_end = std::min(p.M, band + kBandRows * kBM);
       for (int n0 = upper ? band : 0; n0 < p.N; n0 += kBN) {

@@ -31,7 +31,9 @@ struct Cfg {
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
 };
 
-template <int kSplit>
+// kPush: instantiation whose epilogue also stores into the peers' gather buffers; kept apart so
+// that the store loop of the common instantiation is not burdened with it.
+template <int kSplit, bool kPush>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __restrict__ tiles, int num_tiles,
                     float alpha, float beta, int* __restrict__ status, const PeerPush push) {
@@ -166,7 +168,7 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
       float* __restrict__ Dhi = p->d_hi;
       float* __restrict__ Dlo = p->d_lo;
       const int ldc = p->ldc, ldd = p->ldd;
-      const bool do_push = (flags & kFlagPeerPush) && push.num_peers > 0;
+      const bool do_push = kPush && (flags & kFlagPeerPush) && push.num_peers > 0;
       const long long push_offset = p->push_offset;
       const int buf = it & 1;
       if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag)) break;
@@ -225,7 +227,7 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
                   Dhi[od] = hi;
                   Dlo[od] = val - hi;
                 }
-                if (do_push) {
+                if (kPush && do_push) {
                   // A warp stores 32 consecutive elements of one row into each rank's slot.
                   const long long e = static_cast<long long>(row) * N + col;
                   for (int r = 0; r < push.num_peers; ++r) {
@@ -274,18 +276,18 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
   }
 }
 
-template <int kSplit>
+template <int kSplit, bool kPush>
 void launch_impl(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
                  int* status, int max_ctas, cudaStream_t stream, const PeerPush& push) {
   using C = Cfg<kSplit>;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(grouped_gemm_kernel<kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaFuncSetAttribute(grouped_gemm_kernel<kSplit, kPush>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     configured = true;
   }
   const int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
-  grouped_gemm_kernel<kSplit><<<grid, kThreads, C::kSmemBytes, stream>>>(problems, tiles, num_tiles, alpha, beta,
-                                                                        status, push);
+  grouped_gemm_kernel<kSplit, kPush><<<grid, kThreads, C::kSmemBytes, stream>>>(problems, tiles, num_tiles, alpha,
+                                                                               beta, status, push);
 }
 
 }  // namespace
@@ -295,10 +297,13 @@ void launch_grouped_gemm(const GemmProblem* problems, const GemmTile* tiles, int
   if (num_tiles <= 0) return;
   PeerPush none{};
   const PeerPush& pp = push != nullptr ? *push : none;
+  const bool pushing = pp.num_peers > 0;
   if (split) {
-    launch_impl<1>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
+    if (pushing) launch_impl<1, true>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
+    else launch_impl<1, false>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
   } else {
-    launch_impl<0>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
+    if (pushing) launch_impl<0, true>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
+    else launch_impl<0, false>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
   }
 }
 
