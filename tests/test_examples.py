@@ -49,3 +49,47 @@ def test_resolvers_and_strategies():
     wrapped = SingleGPUStrategy().wrap_model(model, 0, "gloo")
     assert wrapped.model is model and wrapped.distributed_config is None
     assert STRATEGIES["hsdp"]().requires_device_mesh and STRATEGIES["ddp"]().requires_distributed
+
+
+def test_yaml_presets_parse_and_command_line_wins(tmp_path):
+    import glob
+    import os
+
+    folder = os.path.join(os.path.dirname(train.__file__), "configs")
+    presets = sorted(glob.glob(os.path.join(folder, "*.yaml")))
+    assert len(presets) >= 4
+    for path in presets:
+        args = train.parse_args(["--config", path])
+        assert args.steps > 0
+    args = train.parse_args(["--config", "resnet18_ddp", "--steps", "3"])
+    assert (args.model, args.parallelism, args.steps, args.max_preconditioner_dim) == ("resnet18", "ddp", 3, 1024)
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("no_such_option: 1\n")
+    with pytest.raises(SystemExit):
+        train.parse_args(["--config", str(bad)])
+
+
+def test_exchange_comm_path_is_scoped():
+    from optimizers_b200.parallel import a2a
+
+    assert a2a._default_comm_path == "nccl"
+    with a2a.exchange_comm_path("p2p"):
+        assert a2a._default_comm_path == "p2p"
+    assert a2a._default_comm_path == "nccl"
+
+
+def test_fused_ops_fall_back_to_the_same_formulas_on_cpu():
+    from optimizers_b200.models import fused_ops
+
+    torch.manual_seed(0)
+    x = torch.randn(5, 12, requires_grad=True)
+    w = torch.randn(7, 12, requires_grad=True)
+    b = torch.randn(7)
+    t = torch.randint(0, 7, (5,))
+    assert torch.equal(fused_ops.linear(x, w, b), torch.nn.functional.linear(x, w, b))
+    want = torch.nn.functional.cross_entropy(torch.nn.functional.linear(x, w), t)
+    assert torch.allclose(fused_ops.lm_head_cross_entropy(x, w, t), want)
+    g = torch.ones(12)
+    assert torch.allclose(fused_ops.layer_norm(x, g, torch.zeros(12)), torch.nn.functional.layer_norm(x, (12,), g, torch.zeros(12)))
+    rms = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+    assert torch.allclose(fused_ops.rms_norm(x, g), rms, atol=1e-6)
