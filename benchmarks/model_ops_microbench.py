@@ -3,6 +3,7 @@
   lm_head_xent   x[T, C] @ W[V, C]^T -> mean cross-entropy, forward + backward (dx, dW)
   layer_norm     fp32 [T, C] -> bf16, forward + backward
   rms_norm       same without mean / bias
+  colsum         column sums of a [T, C] bf16 matrix (bias gradient)
 
 Timed with CUDA events, L2 flushed between iterations.  Bandwidth figures count the algorithmic
 bytes of the fused kernels only (cross-entropy: one read and one write of the bf16 logits).
@@ -96,6 +97,11 @@ def main() -> None:
         return run
 
     dy = torch.randn(T, C, device=dev).to(torch.bfloat16)
+    ms = timed(lambda: ext.colsum(dy), args.iters, flush)
+    out["colsum_kernel_ms"] = ms
+    out["colsum_kernel_gbs"] = T * C * 2 / ms / 1e6
+    if not args.skip_torch:
+        out["colsum_torch_ms"] = timed(lambda: dy.sum(0, dtype=torch.float32), args.iters, flush)
     if ext.norm_supported(C):
         for rms in (False, True):
             name = "rms_norm" if rms else "layer_norm"

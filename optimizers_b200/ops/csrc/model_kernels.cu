@@ -268,16 +268,20 @@ norm_bwd_kernel(const GradT* __restrict__ dy, const InT* __restrict__ x, const f
 }
 
 // ------------------------------------------------------------------------------------------------
-// Column sums of a [rows, N] matrix (bias gradient of a linear layer): partial[s][n] = sum over the
-// s-th row slice.  A lane owns four consecutive columns (8- or 16-byte loads), the eight warps of a
-// CTA interleave rows, shared memory combines them.
+// Column sums of a [rows, N] matrix (bias gradient of a linear layer).  A lane owns four
+// consecutive columns (8- or 16-byte loads), the eight warps of a CTA interleave the rows of one
+// row slice with four loads in flight each, shared memory combines them into partial[slice][n];
+// the CTA that finishes last for a column block then adds the slices in index order (a fixed order:
+// the result does not depend on scheduling) and writes out[n], so no second launch is needed.
 // ------------------------------------------------------------------------------------------------
 constexpr int kColsumThreads = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(kColsumThreads)
-colsum_kernel(const T* __restrict__ x, float* __restrict__ partial, long long rows, int N, int rows_per_slice) {
+colsum_kernel(const T* __restrict__ x, float* __restrict__ partial, float* __restrict__ out, int* __restrict__ counters,
+              long long rows, int N, int rows_per_slice) {
   __shared__ float acc[kColsumThreads / 32][128];
+  __shared__ int is_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = blockIdx.x * 128 + lane * 4;
   const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_slice;
@@ -285,10 +289,11 @@ colsum_kernel(const T* __restrict__ x, float* __restrict__ partial, long long ro
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
   if (col < N) {
     long long r = r0 + warp;
-    // two independent loads in flight per iteration
-    for (; r + 8 < r1; r += 16) {
+    for (; r + 24 < r1; r += 32) {
       const float4 a = load4(x + r * N + col), b = load4(x + (r + 8) * N + col);
-      sum.x += a.x + b.x; sum.y += a.y + b.y; sum.z += a.z + b.z; sum.w += a.w + b.w;
+      const float4 c = load4(x + (r + 16) * N + col), d = load4(x + (r + 24) * N + col);
+      sum.x += (a.x + b.x) + (c.x + d.x); sum.y += (a.y + b.y) + (c.y + d.y);
+      sum.z += (a.z + b.z) + (c.z + d.z); sum.w += (a.w + b.w) + (c.w + d.w);
     }
     for (; r < r1; r += 8) {
       const float4 a = load4(x + r * N + col);
@@ -298,15 +303,27 @@ colsum_kernel(const T* __restrict__ x, float* __restrict__ partial, long long ro
   acc[warp][lane * 4] = sum.x; acc[warp][lane * 4 + 1] = sum.y;
   acc[warp][lane * 4 + 2] = sum.z; acc[warp][lane * 4 + 3] = sum.w;
   __syncthreads();
-  if (threadIdx.x < 128) {
-    const int c = blockIdx.x * 128 + threadIdx.x;
-    if (c < N) {
-      float t = 0.f;
+  const int c = blockIdx.x * 128 + (threadIdx.x & 127);
+  if (threadIdx.x < 128 && c < N) {
+    float t = 0.f;
 #pragma unroll
-      for (int w = 0; w < kColsumThreads / 32; ++w) t += acc[w][threadIdx.x];
-      partial[static_cast<long long>(blockIdx.y) * N + c] = t;
-    }
+    for (int w = 0; w < kColsumThreads / 32; ++w) t += acc[w][threadIdx.x];
+    partial[static_cast<long long>(blockIdx.y) * N + c] = t;
   }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&counters[blockIdx.x], 1) == static_cast<int>(gridDim.y) - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // Two halves of the slices by the two halves of the CTA, each in ascending slice order.
+  const int half = threadIdx.x >> 7;
+  float t = 0.f;
+  if (c < N)
+    for (int sl = half; sl < static_cast<int>(gridDim.y); sl += 2) t += __ldcg(partial + static_cast<long long>(sl) * N + c);
+  if (half == 1) acc[0][threadIdx.x & 127] = t;
+  __syncthreads();
+  if (half == 0 && c < N) out[c] = t + acc[0][threadIdx.x];
 }
 
 int norm_grid(long long rows) {
@@ -445,36 +462,40 @@ std::tuple<torch::Tensor, torch::Tensor> norm_bwd(const torch::Tensor& dy, const
   return {dx, partial};
 }
 
-// x [rows, N] fp32 / bf16 (N % 4 == 0) -> partial [slices, N] fp32 whose sum over dim 0 is the column sum
-torch::Tensor colsum_partial(const torch::Tensor& x) {
+// x [rows, N] fp32 / bf16 (N % 4 == 0) -> column sums [N] fp32
+torch::Tensor colsum(const torch::Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && check_float_like(x), "colsum: x must be [rows, N] fp32/bf16");
   const int64_t rows = x.size(0), N = x.size(1);
   TORCH_CHECK(N % 4 == 0 && N < (1LL << 31), "colsum: N must be a multiple of 4");
   TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "colsum: x must be 16-byte aligned");
   c10::cuda::CUDAGuard guard(x.device());
+  auto f32 = x.options().dtype(torch::kFloat32);
+  if (rows == 0) return torch::zeros({N}, f32);
   const int col_blocks = static_cast<int>((N + 127) / 128);
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   int slices = std::max<int>(1, std::min<int64_t>((4 * sms + col_blocks - 1) / col_blocks, (rows + 63) / 64));
   const int rows_per_slice = static_cast<int>((rows + slices - 1) / slices);
-  slices = static_cast<int>((rows + rows_per_slice - 1) / std::max(rows_per_slice, 1));
-  auto partial = torch::empty({std::max(slices, 1), N}, x.options().dtype(torch::kFloat32));
-  if (rows == 0) return partial.zero_();
+  slices = static_cast<int>((rows + rows_per_slice - 1) / rows_per_slice);
+  auto partial = torch::empty({slices, N}, f32);
+  auto out = torch::empty({N}, f32);
+  auto counters = torch::zeros({col_blocks}, x.options().dtype(torch::kInt32));
   dim3 grid(col_blocks, slices);
   auto st = at::cuda::getCurrentCUDAStream();
   if (x.scalar_type() == torch::kFloat32) {
-    colsum_kernel<float><<<grid, kColsumThreads, 0, st>>>(x.data_ptr<float>(), partial.data_ptr<float>(), rows,
+    colsum_kernel<float><<<grid, kColsumThreads, 0, st>>>(x.data_ptr<float>(), partial.data_ptr<float>(),
+                                                          out.data_ptr<float>(), counters.data_ptr<int>(), rows,
                                                           static_cast<int>(N), rows_per_slice);
   } else {
-    colsum_kernel<__nv_bfloat16><<<grid, kColsumThreads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()),
-                                                                  partial.data_ptr<float>(), rows, static_cast<int>(N),
-                                                                  rows_per_slice);
+    colsum_kernel<__nv_bfloat16><<<grid, kColsumThreads, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), partial.data_ptr<float>(), out.data_ptr<float>(),
+        counters.data_ptr<int>(), rows, static_cast<int>(N), rows_per_slice);
   }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  return partial;
+  return out;
 }
 
 void register_model_ops(pybind11::module_& m) {
-  m.def("colsum_partial", &colsum_partial);
+  m.def("colsum", &colsum);
   m.def("xent_fwd_bwd", &xent_fwd_bwd);
   m.def("norm_fwd", &norm_fwd);
   m.def("norm_bwd", &norm_bwd);
