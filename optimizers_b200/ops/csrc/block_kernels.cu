@@ -457,7 +457,11 @@ __global__ void __launch_bounds__(256) eig_scale_kernel(const BlockDesc* __restr
       float hi[4], lo[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float s = k < cnt ? p[r][k] / (powf(ev[r][k] / bc2, inv_root) + eps) : 0.f;
+        // Roots 2 and 4 (the defaults) avoid the general power function, which made the kernel
+        // instruction bound.
+        const float base = ev[r][k] / bc2;
+        const float pw = inv_root == 0.5f ? sqrtf(base) : inv_root == 0.25f ? sqrtf(sqrtf(base)) : powf(base, inv_root);
+        const float s = k < cnt ? p[r][k] / (pw + eps) : 0.f;
         hi[k] = write_split ? tf32_round(s) : s;
         lo[k] = s - hi[k];
       }

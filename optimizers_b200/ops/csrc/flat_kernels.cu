@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(256) peer_copy_kernel(const CopyDesc* __restri
   }
 }
 
-constexpr int kJacobiThreads = 256;
+constexpr int kJacobiThreads = 1024;  // 32 warps: two column pairs per warp and round at n = 128
 constexpr int kJacobiPitch = kJacobiMaxN + 1;  // odd: column reads and row (transposed) reads are both conflict-free
 
 __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const JacobiDesc* __restrict__ descs,
