@@ -31,7 +31,7 @@ from typing import Any
 import torch
 from torch import Tensor
 
-from optimizers_b200.config import EigenConfig, EighEigendecompositionConfig, PreconditionerValueError
+from optimizers_b200.config import EigenConfig, EighEigendecompositionConfig, PerturbationConfig, PreconditionerValueError
 from optimizers_b200.matrix import functions as mf
 
 logger: logging.Logger = logging.getLogger(__name__)
@@ -59,6 +59,14 @@ def _pool(device: torch.device) -> tuple[ThreadPoolExecutor, list[torch.cuda.Str
 
 def _pad4(n: int) -> int:
     return (n + 3) // 4 * 4
+
+
+def _all_finite(tensors: list[Tensor]) -> list[bool]:
+    """Per-tensor finiteness with one multi-tensor launch and one host read: a norm is finite
+    exactly when every element is (the max norm cannot overflow)."""
+    if not tensors:
+        return []
+    return torch.isfinite(torch.stack(torch._foreach_norm(tensors, float("inf")))).cpu().tolist()
 
 
 class _Item:
@@ -103,8 +111,8 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
             if kf.use_trace_scaling:
                 A = A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent)
             items.append(_Item(b, k, A, kf.roots[k]))
-    finite = torch.stack([torch.isfinite(it.A).all() for it in items]).cpu()
-    for it, ok in zip(items, finite.tolist()):
+    finite = _all_finite([it.A for it in items])
+    for it, ok in zip(items, finite):
         if not ok:
             index = it.block.factors.factor_matrix_indices[it.k]
             raise PreconditionerValueError(
@@ -176,16 +184,56 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
         lams, qs, sweeps = ext.jacobi_eigh(ridged, _JACOBI_MAX_SWEEPS, _JACOBI_TOLERANCE)
         used = sweeps.cpu().tolist()
         done_here = set()
+        # Converged matrices of one size and root share their follow-up work: a handful of
+        # launches per group instead of a dozen per matrix.
+        groups: dict[tuple[int, float], list[tuple[int, Tensor, Tensor]]] = {}
         for i, lam, Q, n_sweeps in zip(small, lams, qs, used, strict=True):
             if n_sweeps > _JACOBI_MAX_SWEEPS:
                 continue  # not converged: let the library solver handle it
+            kf = items[i].block.factors
+            if not isinstance(kf.amortized_computation_config.rank_deficient_stability_config, PerturbationConfig):
+                # the pseudo-inverse cut-off is per matrix: no shared follow-up
+                try:
+                    finish(items[i], lam, Q)
+                except Exception as exception:
+                    items[i].error = exception
+                items[i].done = torch.cuda.Event()
+                items[i].done.record(main)
+                done_here.add(i)
+                continue
+            groups.setdefault((lam.shape[0], float(items[i].root)), []).append((i, lam, Q))
+        for (d, root), members in groups.items():
+            kf0 = items[members[0][0]].block.factors
+            stability = kf0.amortized_computation_config.rank_deficient_stability_config
             try:
-                finish(items[i], lam, Q)
+                lam_b = torch.stack([m[1] for m in members])  # [B, d]
+                q_b = torch.stack([m[2] for m in members])  # [B, d, d]
+                scale_b = mf.stabilized_inverse_power(
+                    lam_b, Fraction(root), kf0.epsilon, stability, lambda_min=lam_b.min(dim=-1, keepdim=True).values
+                )
+                qs_b = q_b * scale_b.unsqueeze(-2)
+                n_b, ld = len(members), _pad4(d)
+                bufs = [torch.zeros(n_b, d, ld, device=device) for _ in range(4 if split else 2)]
+                if split:
+                    ext.tf32_split(qs_b.view(n_b * d, d), bufs[0].view(n_b * d, ld)[:, :d], bufs[1].view(n_b * d, ld)[:, :d])
+                    ext.tf32_split(q_b.view(n_b * d, d), bufs[2].view(n_b * d, ld)[:, :d], bufs[3].view(n_b * d, ld)[:, :d])
+                else:
+                    bufs[0][:, :, :d].copy_(qs_b)
+                    bufs[1][:, :, :d].copy_(q_b)
+                for n, (i, lam, Q) in enumerate(members):
+                    it = items[i]
+                    it.lam, it.Q = lam, Q
+                    if split:
+                        it.qs_hi, it.qs_lo, it.q_hi, it.q_lo = bufs[0][n], bufs[1][n], bufs[2][n], bufs[3][n]
+                    else:
+                        it.qs_hi, it.q_hi, it.qs_lo, it.q_lo = bufs[0][n], bufs[1][n], None, None
             except Exception as exception:
-                items[i].error = exception
-            items[i].done = torch.cuda.Event()
-            items[i].done.record(main)
-            done_here.add(i)
+                for i, _, _ in members:
+                    items[i].error = exception
+            for i, _, _ in members:
+                items[i].done = torch.cuda.Event()
+                items[i].done.record(main)
+                done_here.add(i)
         pooled = [i for i in pooled if i not in done_here]
         ready.record(main)
 
@@ -213,7 +261,7 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
 
     # 4. checkpoint state (packed upper triangle) from the result + one finiteness read; the
     #    operand mirrors are then rebuilt from the state so that both always agree exactly
-    flags = []
+    checked: list[Tensor] = []
     for it in good:
         d = it.A.shape[0]
         kf = it.block.factors
@@ -221,22 +269,20 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
             kf.factor_matrices_eigenvalues[it.k].copy_(it.lam)
             kf.factor_matrices_eigenvectors[it.k].copy_(it.Q)
             mirror = it.block.inv_hi[it.k][:, :d]
-            flags.append(torch.isfinite(mirror).all() & torch.isfinite(it.lam).all())
+            checked.append(mirror)  # finite only if the eigenvalues it was built from are
             if split:  # the reconstruction becomes the (hi, lo) operand pair in place
                 ext.tf32_split(mirror, mirror, it.block.inv_lo[it.k][:, :d])
             continue
         state = kf.inv_factor_matrices[it.k]
         state.copy_(kf.pack(it.block.inv_hi[it.k][:, :d]).to(dtype=state.dtype))
-        flags.append(torch.isfinite(state).all())
-    if flags:
-        ok_list = torch.stack(flags).cpu().tolist()
-        for it, ok in zip(good, ok_list):
-            if not ok:
-                index = it.block.factors.factor_matrix_indices[it.k]
-                raise PreconditionerValueError(
-                    f"Encountered nan or inf values in matrices of factor matrix {index}! "
-                    "To mitigate, check factor matrix before the matrix computation."
-                )
+        checked.append(state)
+    for it, ok in zip(good, _all_finite(checked)):
+        if not ok:
+            index = it.block.factors.factor_matrix_indices[it.k]
+            raise PreconditionerValueError(
+                f"Encountered nan or inf values in matrices of factor matrix {index}! "
+                "To mitigate, check factor matrix before the matrix computation."
+            )
     main.synchronize()  # scratch allocated on the pool streams may now be reused
 
     # failure bookkeeping per block
@@ -340,7 +386,7 @@ def batched_newton_refresh(
             it.block, it.k, it.d, it.root, it.A = b, k, A.shape[0], root.numerator, A
             it.converged, it.last_err, it.iters = False, float("inf"), 0
             items.append(it)
-    finite = torch.stack([torch.isfinite(it.A).all() for it in items]).cpu().tolist()
+    finite = _all_finite([it.A for it in items])
     for it, ok in zip(items, finite):
         if not ok:
             index = it.block.factors.factor_matrix_indices[it.k]
@@ -656,8 +702,8 @@ def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | flo
             if kf.use_trace_scaling:
                 A = A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent)
             items.append(_Item(b, k, A, 0.0))
-    finite = torch.stack([torch.isfinite(it.A).all() for it in items]).cpu()
-    for it, ok in zip(items, finite.tolist()):
+    finite = _all_finite([it.A for it in items])
+    for it, ok in zip(items, finite):
         if not ok:
             index = it.block.factors.factor_matrix_indices[it.k]
             raise PreconditionerValueError(
@@ -720,7 +766,7 @@ def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | flo
         main.wait_event(it.done)
     good = [it for it in items if it.error is None]
     if good:
-        ok_list = torch.stack([torch.isfinite(it.q_hi).all() for it in good]).cpu().tolist()
+        ok_list = _all_finite([it.q_hi for it in good])
         for it, ok in zip(good, ok_list):
             if not ok:
                 index = it.block.factors.factor_matrix_indices[it.k]
