@@ -66,6 +66,33 @@ __global__ void __launch_bounds__(256) affine_identity_split_kernel(const MatOp*
     const MatOp op = ops[ref.x];
     const int row0 = ref.y * kMatRowsPerChunk;
     const int rows = min(kMatRowsPerChunk, op.d - row0);
+    const bool vec = ((op.d | op.ld_src | op.ld_dst) & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(op.src) | reinterpret_cast<uintptr_t>(op.dst_hi) |
+                       reinterpret_cast<uintptr_t>(op.dst_lo)) & 15) == 0;
+    if (vec) {
+      // 16-byte accesses: a thread owns four consecutive columns of a row.
+      const int d4 = op.d >> 2;
+      for (int e = threadIdx.x; e < rows * d4; e += blockDim.x) {
+        const int i = row0 + e / d4, j = (e % d4) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(op.src + static_cast<long long>(i) * op.ld_src + j);
+        float x[4] = {a * v.x, a * v.y, a * v.z, a * v.w};
+        if (i >= j && i < j + 4) x[i - j] += b;
+        const long long o = static_cast<long long>(i) * op.ld_dst + j;
+        if (op.dst_lo != nullptr) {
+          float h[4], l[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            h[k] = tf32_round(x[k]);
+            l[k] = x[k] - h[k];
+          }
+          *reinterpret_cast<float4*>(op.dst_hi + o) = make_float4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<float4*>(op.dst_lo + o) = make_float4(l[0], l[1], l[2], l[3]);
+        } else {
+          *reinterpret_cast<float4*>(op.dst_hi + o) = make_float4(x[0], x[1], x[2], x[3]);
+        }
+      }
+      continue;
+    }
     for (int e = threadIdx.x; e < rows * op.d; e += blockDim.x) {
       const int i = row0 + e / op.d, j = e % op.d;
       float x = a * op.src[static_cast<long long>(i) * op.ld_src + j];
