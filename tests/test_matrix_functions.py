@@ -117,7 +117,7 @@ def test_orthogonalization():
         torch.testing.assert_close(gram, torch.eye(k), atol=1e-4, rtol=1e-4)
         N = mf.matrix_orthogonalization(A, NewtonSchulzOrthogonalizationConfig(num_iterations=12))
         s = torch.linalg.svdvals(N)
-        assert s.max() < 1.3 and s.min() > 0.5  # quintic Newton-Schulz keeps singular values in a band around 1
+        assert s.max() < 1.3 and s.min() > 0.5  # quintic Newton-Schulz keeps singular values in a band near 1
     scaled = mf.matrix_orthogonalization(
         torch.eye(3), SVDOrthogonalizationConfig(scale_by_dims_fn=lambda d_in, d_out: 2.0, scale_by_nuclear_norm=True)
     )
