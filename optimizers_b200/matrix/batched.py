@@ -36,7 +36,11 @@ from optimizers_b200.matrix import functions as mf
 
 logger: logging.Logger = logging.getLogger(__name__)
 
-_POOL_SIZE = 8
+import os as _os
+
+# Streams / host threads of the refresh pool (OB200_REFRESH_POOL overrides; the library eigensolver
+# gains little beyond a handful of concurrent problems).
+_POOL_SIZE = max(1, int(_os.environ.get("OB200_REFRESH_POOL", "8")))
 _JACOBI_MAX_SWEEPS = 24
 _JACOBI_TOLERANCE = 2e-6  # relative size of a column pair's inner product below which it is left alone
 
