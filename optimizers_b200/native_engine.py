@@ -132,6 +132,18 @@ def _order3_ok(block: Tensor, pc: Any) -> bool:
     return root_like and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
 
 
+def maybe_build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig):
+    """Return a native engine for the group, or ``None`` to use the torch step.
+
+    ``backend="torch"`` and non-CUDA groups always get ``None``.  ``backend="native"`` raises when
+    the group cannot be covered; ``"auto"`` falls back silently."""
+    if cfg.backend == "torch" or group[PARAMS][0].device.type != "cuda":
+        if cfg.backend == "native":
+            raise RuntimeError("native backend requested for a parameter group that is not on a CUDA device")
+        return None
+    return build_native_engine(optimizer, rec, group, cfg)
+
+
 def build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig):
     reason = _why_not_covered(rec, group)
     if reason is None and torch.cuda.get_device_capability(group[PARAMS][0].device)[0] != 10:
@@ -193,6 +205,11 @@ class NativeGroupEngine:
             self._graft_kind = _GRAFT_ADAGRAD
 
         self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
+        # Host mirror of the status word: every step ends with an asynchronous copy into pinned
+        # memory and begins by looking at the copy of the step before (no synchronisation), so a
+        # device-side timeout or a non-finite gradient surfaces one step late at the latest.
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_event: torch.cuda.Event | None = None
         self._ddp = isinstance(group[DISTRIBUTED_CONFIG], DDPDistributedConfig)
         self._p2p = type(group[DISTRIBUTED_CONFIG]) is DDPDistributedConfig and cfg.comm_path == "p2p"
         self._pull = self._p2p and cfg.fuse_gradient_reduction
@@ -212,9 +229,12 @@ class NativeGroupEngine:
             self._setup_peer_memory()
         self._build_blocks()
         n_ptrs = max(len(self._local_params), 1)
-        # Two pinned staging buffers, used alternately, so that a pointer table still being
-        # copied by the device is never overwritten by the host.
+        # Pinned staging buffers for the gradient pointer table, used in turn; each carries the
+        # event of its last upload, and the host waits for that event before rewriting the buffer,
+        # so a copy still queued on the device never sees another step's pointers however far the
+        # host runs ahead.
         self._grad_ptrs_host = [torch.zeros(n_ptrs, dtype=torch.int64).pin_memory() for _ in range(2)]
+        self._grad_ptrs_uploaded: list[torch.cuda.Event | None] = [None, None]
         self._grad_ptrs_flip = 0
         if not self._pull:
             self._grad_ptrs_dev = torch.zeros(n_ptrs, dtype=torch.int64, device=self._device)
@@ -626,6 +646,11 @@ class NativeGroupEngine:
             self._full_table = self._ext.build_block_table(specs) if specs else ()
         if self._full_table:
             self._ext.mode_switch(*self._full_table, coeff, 0)
+        if hasattr(self._dist, "_write_back"):
+            # Lossless sharded distributors block this rank's gathered full copies; the model reads
+            # its dim-0 shards, so the switched values travel back through the distributor's
+            # (collective) write-back on every rank.
+            self._dist._write_back()
         return True
 
     def collect_gradients(self) -> tuple[int, ...]:
@@ -669,8 +694,15 @@ class NativeGroupEngine:
         if ptrs != self._last_ptrs:
             self._grad_ptrs_flip ^= 1
             staging = self._grad_ptrs_host[self._grad_ptrs_flip]
+            uploaded = self._grad_ptrs_uploaded[self._grad_ptrs_flip]
+            if uploaded is not None:
+                uploaded.synchronize()
             staging[: len(ptrs)] = torch.tensor(ptrs, dtype=torch.int64)
             self._grad_ptrs_dev.copy_(staging, non_blocking=True)
+            if self._device.type == "cuda":
+                event = torch.cuda.Event()
+                event.record()
+                self._grad_ptrs_uploaded[self._grad_ptrs_flip] = event
             self._last_ptrs = ptrs
         local_any = any_grad and any(dist.local_grad_selector)
         return tuple(ptrs) if local_any else ()
@@ -683,22 +715,43 @@ class NativeGroupEngine:
     # ------------------------------------------------------------------------------------------
     # The step
     # ------------------------------------------------------------------------------------------
-    def check_status(self) -> None:
-        """Read the device status word (one synchronisation) and raise on kernel-reported errors."""
-        code = int(self._status.item())
+    def _raise_for(self, code: int) -> None:
         if code & 1:
             raise RuntimeError("grouped GEMM pipeline wait timed out (device-side bounded wait expired)")
         if code & 4:
             raise RuntimeError("a peer rank did not reach the cross-rank barrier in time (bounded device-side wait expired)")
         if code & 2:
             self._status.zero_()
+            self._status_host.zero_()
             raise PreconditionerValueError("Encountered NaN/Inf in a gradient passed to the optimizer.")
+
+    def check_status(self) -> None:
+        """Read the device status word (one synchronisation) and raise on kernel-reported errors."""
+        self._raise_for(int(self._status.item()))
+
+    def _poll_status(self) -> None:
+        """Non-blocking twin of ``check_status``: inspects the pinned copy made at the end of the
+        previous step once that copy has completed (it has, unless the host runs more than a step
+        ahead of the device, in which case the look is deferred to the next step)."""
+        event = self._status_event
+        if event is not None and event.query():
+            self._status_event = None
+            code = int(self._status_host[0])
+            if code:
+                self._raise_for(code)
+
+    def _post_status(self) -> None:
+        if self._status_event is None:  # the previous copy has been consumed: the buffer is free
+            self._status_host.copy_(self._status, non_blocking=True)
+            self._status_event = torch.cuda.Event()
+            self._status_event.record()
 
     def step(
         self, group, step, lr, beta1, beta3, weight_decay, peak_lr, weight_decay_type, has_grafting, refresh,
         use_bias_correction, graft_only, primal, classic, mu_y, mu_x, momentum, dampening, nesterov,
     ) -> None:
         rec, ext = self._rec, self._ext
+        self._poll_status()
         active = self._active if self._active is not None else (True,) * len(self._blocks)
         if self._plans_for != active:
             self._build_plans(active)
@@ -869,6 +922,10 @@ class NativeGroupEngine:
         return 4
 
     def _finish_update(self, scaled: tuple[Tensor, float] | None = None) -> None:
+        self._deliver(scaled)
+        self._post_status()
+
+    def _deliver(self, scaled: tuple[Tensor, float] | None = None) -> None:
         """Deliver the search directions.  Single device: the epilogue already updated the
         parameters.  DDP: all-gather (NCCL), or a cross-rank barrier after the epilogue's peer
         stores (p2p); then one grouped kernel adds every block's direction to the parameters."""
@@ -902,11 +959,14 @@ class NativeGroupEngine:
                 specs.append((view, 0, 0, m, n, _pad4(n), _pad4(m)) + (None,) * 11 + (scale, base + off, off, None, 0))
             self._gather_table = self._ext.build_block_table(specs) if specs else None
             self._gather_for = sel
+        # p2p: the slots were filled by this rank's and the peers' kernels; after a device-side
+        # timeout they may be partial, so the apply kernel checks the status word itself.
+        guard = self._status if self._p2p else None
         if self._gather_table is not None:
             if scaled is not None:
-                self._ext.gathered_apply_scaled(*self._gather_table, self._comm_dtype_code, scaled[0], scaled[1])
+                self._ext.gathered_apply_scaled(*self._gather_table, self._comm_dtype_code, scaled[0], scaled[1], guard)
             else:
-                self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code, self._comm_params)
+                self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code, self._comm_params, guard)
             self.launches_per_step += 1
         if hasattr(dist_, "_write_back"):
             dist_._write_back()

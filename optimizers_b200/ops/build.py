@@ -76,7 +76,7 @@ def load() -> ModuleType:
         if shutil.which("nvcc") is None:
             raise RuntimeError(
                 f"The sm_100a extension {_SO} has not been built and no nvcc is available; "
-                "run `python -c 'import __graft_entry__ as g; g.build()'` where the CUDA toolkit is installed."
+                "run `make build` where the CUDA toolkit is installed."
             )
         build()
     import torch  # noqa: F401  (the extension links against libtorch)

@@ -253,10 +253,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_block_table(const std::v
   return {d_blocks, d_tiles, static_cast<int64_t>(tiles.size())};
 }
 
-inline int wide_tiles(int64_t count) { return static_cast<int>(count); }
-inline const TileRef* wide_tile_ptr(const torch::Tensor& tiles, int64_t) {
-  return reinterpret_cast<const TileRef*>(tiles.data_ptr());
-}
+inline const TileRef* tile_ptr(const torch::Tensor& tiles) { return reinterpret_cast<const TileRef*>(tiles.data_ptr()); }
 
 void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles,
                    const torch::Tensor& grad_ptrs, double l2_weight_decay, double beta1, double beta3,
@@ -266,8 +263,8 @@ void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int6
   c10::cuda::CUDAGuard guard(blocks.device());
   PrologueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
-  a.tiles = wide_tile_ptr(tiles, num_tiles);
-  a.num_tiles = wide_tiles(num_tiles);
+  a.tiles = tile_ptr(tiles);
+  a.num_tiles = static_cast<int>(num_tiles);
   a.grad_ptrs = reinterpret_cast<const float* const*>(grad_ptrs.data_ptr<int64_t>());
   a.l2_weight_decay = static_cast<float>(l2_weight_decay);
   a.beta1 = static_cast<float>(beta1);
@@ -295,8 +292,8 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
   c10::cuda::CUDAGuard guard(blocks.device());
   EpilogueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
-  a.tiles = wide_tile_ptr(tiles, num_tiles);
-  a.num_tiles = wide_tiles(num_tiles);
+  a.tiles = tile_ptr(tiles);
+  a.num_tiles = static_cast<int>(num_tiles);
   a.lr = lr.data_ptr<float>();
   a.send_params = send_params ? 1 : 0;
   a.graft_only = graft_only ? 1 : 0;
@@ -321,38 +318,39 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
 }
 
 void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype,
-                    bool copy_params) {
+                    bool copy_params, const std::optional<torch::Tensor>& status) {
   c10::cuda::CUDAGuard guard(blocks.device());
-  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
-                        wide_tiles(num_tiles),
-                        static_cast<int>(dtype), nullptr, 0.f, copy_params, at::cuda::getCurrentCUDAStream());
+  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
+                        static_cast<int>(num_tiles), static_cast<int>(dtype), nullptr, 0.f, copy_params,
+                        status.has_value() ? status->data_ptr<int>() : nullptr, at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 // The slots hold unscaled Shampoo directions P (pushed from the GEMM epilogue); BlockDesc::norms
 // points at the block's grafting scale: W <- W - lr (scale P + wd_alpha W).
 void gathered_apply_scaled(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype,
-                           const torch::Tensor& lr, double wd_alpha) {
+                           const torch::Tensor& lr, double wd_alpha, const std::optional<torch::Tensor>& status) {
   c10::cuda::CUDAGuard guard(blocks.device());
-  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
-                        wide_tiles(num_tiles), static_cast<int>(dtype), lr.data_ptr<float>(),
-                        static_cast<float>(wd_alpha), false, at::cuda::getCurrentCUDAStream());
+  launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
+                        static_cast<int>(num_tiles), static_cast<int>(dtype), lr.data_ptr<float>(),
+                        static_cast<float>(wd_alpha), false, status.has_value() ? status->data_ptr<int>() : nullptr,
+                        at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 void eig_scale(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double bc2, double inv_root,
                double eps, bool write_split) {
   c10::cuda::CUDAGuard guard(blocks.device());
-  launch_eig_scale(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
-                   wide_tiles(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
+  launch_eig_scale(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
+                   static_cast<int>(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
                    static_cast<float>(eps), write_split ? 1 : 0, at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 void mode_switch(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double coeff, int64_t send_dtype) {
   c10::cuda::CUDAGuard guard(blocks.device());
-  launch_mode_switch(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), wide_tile_ptr(tiles, num_tiles),
-                     wide_tiles(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
+  launch_mode_switch(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
+                     static_cast<int>(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
                      at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }

@@ -391,7 +391,12 @@ __global__ void __launch_bounds__(256, kPlain ? 3 : 2) direction_epilogue_kernel
 __global__ void __launch_bounds__(256) gathered_apply_kernel(const BlockDesc* __restrict__ blocks,
                                                              const TileRef* __restrict__ tiles, int num_tiles,
                                                              int dtype, const float* __restrict__ lr_ptr,
-                                                             float wd_alpha, int copy_params) {
+                                                             float wd_alpha, int copy_params,
+                                                             const int* __restrict__ status) {
+  // A producer of the gather buffer gave up on a bounded wait (GEMM pipeline, peer barrier): the
+  // slots may hold partial or stale directions, so the parameters are left as they are and the
+  // host raises when it reads the status word.
+  if (status != nullptr && (*status & (kErrGemmTimeout | kErrPeerTimeout)) != 0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool scaled = lr_ptr != nullptr;
   const float lr = scaled ? *lr_ptr : 0.f;
@@ -535,7 +540,7 @@ __global__ void peer_barrier_kernel(int* local_flags, const unsigned long long* 
 
 int grid_for(int num_tiles) {
   // A few waves of CTAs per SM; the kernels loop over the tile list.
-  const int cap = 148 * 8;
+  const int cap = sm_count() * 8;
   return num_tiles < cap ? num_tiles : cap;
 }
 
@@ -574,10 +579,10 @@ void launch_peer_barrier(int* local_flags, const unsigned long long* peer_flag_b
 }
 
 void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype, const float* lr,
-                           float wd_alpha, bool copy_params, cudaStream_t stream) {
+                           float wd_alpha, bool copy_params, const int* status, cudaStream_t stream) {
   if (num_tiles <= 0) return;
   gathered_apply_kernel<<<grid_for(num_tiles), 256, 0, stream>>>(blocks, tiles, num_tiles, dtype, lr, wd_alpha,
-                                                                 copy_params ? 1 : 0);
+                                                                 copy_params ? 1 : 0, status);
 }
 
 }  // namespace ob200

@@ -114,6 +114,7 @@ void launch_eig_scale(const BlockDesc* blocks, const TileRef* tiles, int num_til
 void launch_mode_switch(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, float coeff, int send_dtype,
                         cudaStream_t stream);
 
+constexpr int kErrGemmTimeout = 1;  // grouped GEMM: a bounded pipeline wait expired (kErrPipelineTimeout)
 constexpr int kErrPeerTimeout = 4;  // a bounded wait on a peer's flag expired
 
 // Cross-rank barrier over peer memory: writes `seq` into slot `my_rank` of every peer's flag
@@ -132,7 +133,9 @@ void launch_direction_epilogue(const EpilogueArgs& args, cudaStream_t stream);
 // block's grafting scale s: W <- W - lr (s P + wd_alpha W); this finishes, on every rank, the
 // update whose directions the preconditioner GEMM pushed from its epilogue.
 // `copy_params`: the slots hold updated parameters (communicate_params): W <- slot.
+// `status` (may be null): the group's device status word; when a timeout bit is set in it the
+// kernel leaves the parameters untouched.
 void launch_gathered_apply(const BlockDesc* blocks, const TileRef* tiles, int num_tiles, int dtype, const float* lr,
-                           float wd_alpha, bool copy_params, cudaStream_t stream);
+                           float wd_alpha, bool copy_params, const int* status, cudaStream_t stream);
 
 }  // namespace ob200

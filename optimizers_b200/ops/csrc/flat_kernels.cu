@@ -454,7 +454,7 @@ __global__ void __launch_bounds__(256) gpa_lerp_kernel(const GpaTensorDesc* __re
 }
 
 int grid_for(long long work_items) {
-  const long long cap = 148 * 8;
+  const long long cap = sm_count() * 8;
   return static_cast<int>(work_items < cap ? (work_items > 0 ? work_items : 1) : cap);
 }
 
@@ -485,7 +485,7 @@ void launch_jacobi_eigh(const JacobiDesc* descs, int count, int max_sweeps, floa
 
 void launch_peer_copy(const CopyDesc* table, const int2* chunks, int num_chunks, cudaStream_t stream) {
   if (num_chunks <= 0) return;
-  const int cap = 148 * 8;
+  const int cap = sm_count() * 8;
   peer_copy_kernel<<<num_chunks < cap ? num_chunks : cap, 256, 0, stream>>>(table, chunks, num_chunks);
 }
 

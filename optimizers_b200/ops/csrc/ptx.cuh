@@ -12,6 +12,21 @@
 
 namespace ob200 {
 
+// Number of SMs of the current device (cached per device); grids of the persistent-style kernels
+// are sized from it.
+inline int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 constexpr unsigned long long kWaitBudgetNs = 2000ull * 1000ull * 1000ull;  // 2 s per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

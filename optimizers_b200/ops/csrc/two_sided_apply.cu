@@ -1,6 +1,7 @@
 // See two_sided_apply.h.
 #include "two_sided_apply.h"
 
+#include <atomic>
 #include <cstdio>
 
 namespace ob200 {
@@ -38,7 +39,9 @@ void sgemm_nn(const float* A, const float* B, float* C, int M, int N, int K, cud
 static __device__ __align__(256) float g_noalloc_scratch[OB200_NOALLOC_MAX_ELEMS];
 
 constexpr int kMaxDevices = 64;
-float* g_scratch_addr[kMaxDevices] = {};
+// Device address of the scratch array, per device.  Threads that race on the first call of a
+// device all resolve the same address; the atomic only makes the publication well defined.
+std::atomic<float*> g_scratch_addr[kMaxDevices];
 
 }  // namespace
 
@@ -65,18 +68,30 @@ extern "C" int ob200_two_sided_apply_noalloc(const float* L, const float* G, con
   }
   int device = -1;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return OB200_NOALLOC_ERR_CUDA;
-  if (g_scratch_addr[device] == nullptr) {
+  float* scratch = g_scratch_addr[device].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // Once per device, with that device current: the symbol's address on *this* device.
-    float* addr = nullptr;
-    const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_noalloc_scratch);
-    if (err != cudaSuccess || addr == nullptr) {
+    const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_noalloc_scratch);
+    if (err != cudaSuccess || scratch == nullptr) {
       std::fprintf(stderr, "ob200_two_sided_apply_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(err));
       return OB200_NOALLOC_ERR_CUDA;
     }
-    g_scratch_addr[device] = addr;
+    g_scratch_addr[device].store(scratch, std::memory_order_release);
   }
-  launch_two_sided_apply(L, G, R, P, g_scratch_addr[device], m, n, stream);
-  return cudaPeekAtLastError() == cudaSuccess ? OB200_NOALLOC_OK : OB200_NOALLOC_ERR_CUDA;
+  // The return code speaks for this call's two launches only: an error that some earlier,
+  // unrelated call left pending is taken off first, and each launch is checked right after it.
+  (void)cudaGetLastError();
+  sgemm_nn(G, R, scratch, m, n, n, stream);  // T = G R
+  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) {
+    sgemm_nn(L, scratch, P, m, n, m, stream);  // P = L T
+    err = cudaGetLastError();
+  }
+  if (err != cudaSuccess) {
+    std::fprintf(stderr, "ob200_two_sided_apply_noalloc: kernel launch failed: %s\n", cudaGetErrorString(err));
+    return OB200_NOALLOC_ERR_CUDA;
+  }
+  return OB200_NOALLOC_OK;
 }
 
 extern "C" const char* ob200_noalloc_strerror(int code) {

@@ -29,6 +29,11 @@
  *     later reads.  Two calls that overlap on the GPU (different streams without an ordering
  *     between them) race on the array; serialise them on one stream or with events.
  *   - The work is enqueued on `stream` and the function returns without synchronising.
+ *   - The function may be called from several host threads.  Threads that make the first call on
+ *     a device at the same time each resolve the scratch address (the same value) themselves.
+ *   - The return code reports this call's own launches: a launch error left pending by an earlier,
+ *     unrelated CUDA call of the process is cleared, not reported; errors that only show when the
+ *     kernels execute surface at the caller's next synchronisation, as with any launch.
  *
  * Returns 0 on success or one of the negative codes below; ob200_noalloc_strerror gives a text.
  */

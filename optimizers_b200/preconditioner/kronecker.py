@@ -21,7 +21,7 @@ Factors (and inverse roots) are stored as the packed row-major upper triangle wh
 
 The classes here hold the state and implement every operation with torch operators.  On a B200
 the optimizer drives the same state through the grouped sm_100a kernels
-(``optimizers_b200.engine``); the methods below then serve as oracle and fallback.
+(``optimizers_b200.native_engine``); the methods below then serve as oracle and fallback.
 
 Reference counterpart: ``distributed_shampoo/preconditioner/shampoo_preconditioner_list.py``
 (state :106-161, :446-1007; refresh driver :314-443; list :1215-1695; variants :1709-2046).

@@ -534,7 +534,7 @@ class DistributedShampoo(Optimizer):
             logger.info(f"DistributedShampoo optimizer initialization is using shampoo_pt2_compile_config={shampoo_pt2_compile_config}")
 
         # Native engines: one per group whose configuration the sm_100a kernels cover.
-        from optimizers_b200.engine import maybe_build_native_engine
+        from optimizers_b200.native_engine import maybe_build_native_engine
 
         for rec, group in self._groups():
             rec[NATIVE_ENGINE] = maybe_build_native_engine(self, rec, group, self._native_runtime_config)

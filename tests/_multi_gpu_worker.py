@@ -12,6 +12,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main() -> None:
     mode, out = sys.argv[1], sys.argv[2]
+    bf16_comm = mode.endswith("+bf16")  # search directions travel in bf16, as in the benchmarks
+    mode = mode.removesuffix("+bf16")
     comm_params = mode.endswith("+params")  # updated parameters travel instead of search directions
     mode = mode.removesuffix("+params")
     from optimizers_b200 import (
@@ -43,7 +45,8 @@ def main() -> None:
         precondition_frequency=3, start_preconditioning_step=3, weight_decay=1e-2,
         grafting_config=AdamPreconditionerConfig(),
         distributed_config=DDPDistributedConfig(
-            communication_dtype=torch.float32, num_trainers_per_group=world, communicate_params=comm_params
+            communication_dtype=torch.bfloat16 if bf16_comm else torch.float32, num_trainers_per_group=world,
+            communicate_params=comm_params,
         ),
         native_runtime_config=native,
     )
@@ -80,7 +83,8 @@ def sharded_main() -> None:
     or the native step and write rank 0's view of the full final parameters."""
     mode, out = sys.argv[1], sys.argv[2]
     backend, strategy, *rest = mode.split(":")
-    comm_path = rest[0] if rest else "nccl"
+    comm_path = "p2p" if "p2p" in rest else "nccl"
+    gpa = "gpa" in rest  # primal averaging: the saved parameters are those of eval mode
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, fully_shard, ShardingStrategy
     from torch.distributed.tensor import DTensor
@@ -94,6 +98,7 @@ def sharded_main() -> None:
         FullyShardDistributedConfig,
         HSDPDistributedConfig,
         HybridShardDistributedConfig,
+        GeneralizedPrimalAveragingConfig,
         NativeRuntimeConfig,
     )
 
@@ -136,7 +141,10 @@ def sharded_main() -> None:
         precondition_frequency=3, start_preconditioning_step=3, weight_decay=1e-2,
         grafting_config=AdaGradPreconditionerConfig(epsilon=1e-8), distributed_config=dc,
         native_runtime_config=NativeRuntimeConfig(backend=backend, comm_path=comm_path),
+        **({"iterate_averaging_config": GeneralizedPrimalAveragingConfig(eval_interp_coeff=0.9, train_interp_coeff=0.7)} if gpa else {}),
     )
+    if gpa:
+        opt.train()
     g = torch.Generator(device="cuda").manual_seed(1)
     for _ in range(8):
         x = torch.randn(64, 96, device=dev, generator=g)
@@ -145,6 +153,8 @@ def sharded_main() -> None:
         opt.zero_grad()
         torch.nn.functional.cross_entropy(model(x[shard]), y[shard]).backward()
         opt.step()
+    if gpa:
+        opt.eval()  # what an evaluation or a checkpoint would see: the averaged x sequence
     if comm_path == "p2p":
         for rec in opt._per_group_state_lists:
             d = rec["distributor"]

@@ -48,6 +48,33 @@ def test_native_ddp_communicate_params_matches_torch(tmp_path, mode):
         assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode", ["native_nccl", "p2p_push", "p2p_pull", "p2p_gemm"])
+def test_native_ddp_bf16_communication_matches_torch(tmp_path, mode):
+    """The communication dtype of the benchmarks: directions are cast to bf16 by the kernel that
+    stores them into the gather buffers, as the torch step casts them before its all-gather."""
+    n = min(torch.cuda.device_count(), 4)
+    ref, got = str(tmp_path / "ref.pt"), str(tmp_path / "got.pt")
+    _run("torch+bf16", n, ref, 29551)
+    _run(f"{mode}+bf16", n, got, 29552)
+    for a, b in zip(torch.load(ref), torch.load(got)):
+        assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("strategy", ["fully_shard_rr", "fully_shard_rep"])
+def test_lossless_primal_averaging_eval_parameters_match_torch(tmp_path, strategy):
+    """Lossless distributors block gathered full copies; optimizer.eval() under the native engine
+    has to reach the model's own shards (the grouped switch kernel plus the distributor's
+    write-back), so the eval-mode parameters equal those of the torch step."""
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    ref, got = str(tmp_path / "ref.pt"), str(tmp_path / "got.pt")
+    _run(f"torch:{strategy}:gpa", n, ref, 29553)
+    _run(f"native:{strategy}:gpa", n, got, 29554)
+    for a, b in zip(torch.load(ref), torch.load(got)):
+        assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
+
+
 SHARDED = ["fsdp", "hsdp", "fully_shard", "fully_shard_rr", "fully_shard_rep", "hybrid_shard", "hybrid_shard_rr"]
 
 
