@@ -1,0 +1,576 @@
+"""Batched symmetric eigensolver built from matrix products: spectral divide and conquer.
+
+``torch.linalg.eigh`` (the reference's eigensolver, ``distributed_shampoo/preconditioner/
+matrix_functions.py:725-770``) reduces to tridiagonal form with memory-bound Householder
+updates, one matrix at a time.  On a tensor-core machine nearly all of the work of an
+eigendecomposition can instead be matrix products over *all* factors of a refresh at once:
+
+1. shift and scale:  ``X0 = (A - sigma I) / ||A - sigma I||_F`` with ``sigma = trace(A) / n``;
+2. matrix sign function by a fixed schedule of odd quintic polynomials
+   ``X <- X (a I + b X^2 + c X^4)`` (three symmetric products per iteration, no inverses);
+   ``P = (I + sign(X0)) / 2`` is the orthogonal projector onto the eigenvalues above ``sigma``
+   and ``k = ||P||_F^2`` its rank;
+3. an orthonormal basis ``[V1 V2]`` adapted to the split: Householder QR of ``P Omega`` (``Omega``
+   a fixed random ``n x k`` matrix), ``V1`` spans ``range(P)``, ``V2`` its complement;
+4. the two half-size problems ``V1^T A V1`` and ``V2^T A V2`` go back on the work list; problems of
+   size <= ``leaf`` are finished by the shared-memory Jacobi kernel.  The basis of every
+   subproblem in the coordinates of its root matrix is carried along (``B <- B V``), so a leaf's
+   eigenvectors are one more product.
+
+A subproblem whose spread ``||A - sigma I||_F`` is at the rounding level of its root matrix is a
+numerically multiple eigenvalue: any orthonormal basis serves and it is closed at once.  A sign
+iteration that did not converge (an eigenvalue within ~1e-7 of the split point) is repeated with
+a nudged split point.  Matrices the scheme gives up on are reported to the caller, which falls
+back to the library eigensolver for them.
+
+The driver below is written against a small backend interface.  ``TorchBackend`` implements it
+with plain tensor operations on any device (the CPU tests run the whole algorithm through it);
+``NativeBackend`` runs every product on the grouped tcgen05 GEMM, the QR panels on the
+``householder_panel`` kernel and the leaves on ``jacobi_eigh``.
+"""
+
+from __future__ import annotations
+
+import logging
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+from torch import Tensor
+
+logger: logging.Logger = logging.getLogger(__name__)
+
+# Schedule of odd quintics p(x) = a x + b x^3 + c x^5 for the sign function of a matrix whose
+# eigenvalues lie in [-1, 1]; every |x| >= 1e-7 ends within 1e-9 of 1.
+#
+# The first polynomial, applied 14 times, has the largest slope at 0 (3.19) among the quintics that
+# are increasing on [0, 0.5], stay in [0.5, 1] on [0.5, 1] and have |p'| <= 2 there (a linear
+# programme).  It is chosen for numerical stability, not for speed: a rounding error of the products
+# that does not commute with the matrix is multiplied, per iteration, by the divided differences of
+# p between pairs of eigenvalues.  Minimax ("equi-oscillating") polynomials reach 1 in 14 instead of
+# 17 iterations but oscillate over the whole of [0, 1] with slopes up to 13 among eigenvalues that
+# have already grown to O(1), which amplifies such errors by three orders of magnitude (measured:
+# commutator ||[P, A]|| / ||A|| of 2e-4 instead of 3e-6 at the accuracy of the tf32x3 products).
+# Here eigenvalues grow monotonically until they enter the band [0.5, 1], where slopes are bounded.
+# The last three polynomials are minimax on [0.5, 1] and [0.95, 1] (small oscillation, slopes < 1)
+# and the Newton-Schulz quintic.
+_BAND = (3.19298245614035, -5.543859649122806, 3.087719298245614)
+SIGN_SCHEDULE: tuple[tuple[float, float, float], ...] = (_BAND,) * 14 + (
+    (2.6073662581361705, -3.2052873333580942, 1.5974301564951396),
+    (1.9203115684161138, -1.3422577427092492, 0.42194449535688716),
+    (1.875, -1.25, 0.375),
+)
+
+LEAF = 128  # largest problem the Jacobi kernel takes
+_MAX_ATTEMPTS = 3  # sign computations per subproblem before its root is given up
+_MAX_ROUNDS = 40  # rounds of the work list before the remaining roots are given up
+_IDEMPOTENCY_TOL = 0.05  # bound on |trace(P) - ||P||_F^2| = |sum p (1 - p)| over the eigenvalues p of P
+_NUDGE = 3e-5  # relative shift of the split point for a repeated sign computation
+
+
+@dataclass
+class Sub:
+    """One symmetric subproblem: ``A`` (n x n) is the restriction of root matrix ``root`` to the
+    subspace spanned by the columns of ``B`` (d_root x n); its eigenvalues belong at positions
+    ``offset .. offset + n`` of the root's (unsorted) spectrum."""
+
+    root: int
+    n: int
+    offset: int
+    A: Any = None  # backend handle of the matrix
+    B: Any = None  # backend handle of the basis; None for a root (identity)
+    attempt: int = 0
+    sigma: float = 0.0
+    spread: float = 0.0
+    rank: int = 0
+    idem_err: float = 0.0
+    extra: dict = field(default_factory=dict)  # backend scratch
+
+
+class TorchBackend:
+    """Reference implementation of the backend interface with plain tensor operations."""
+
+    def __init__(self, device: torch.device, dtype: torch.dtype = torch.float32, seed: int = 1234) -> None:
+        self.device, self.dtype = device, dtype
+        self._omega: Tensor | None = None
+        self._seed = seed
+        self.passes = 2
+
+    # -- set-up -----------------------------------------------------------------------------
+    def begin(self, mats: list[Tensor]) -> list[Sub]:
+        dmax = max(m.shape[0] for m in mats)
+        gen = torch.Generator(device="cpu").manual_seed(self._seed)
+        self._omega = torch.randn(dmax, dmax, generator=gen).to(device=self.device, dtype=self.dtype)
+        self.lams = [torch.zeros(m.shape[0], device=self.device, dtype=self.dtype) for m in mats]
+        self.vecs = [torch.zeros(m.shape[0], m.shape[0], device=self.device, dtype=self.dtype) for m in mats]
+        self.root_norms = [float(torch.linalg.norm(m)) for m in mats]
+        return [Sub(root=i, n=m.shape[0], offset=0, A=m.to(self.dtype).clone()) for i, m in enumerate(mats)]
+
+    # -- one round ----------------------------------------------------------------------------
+    def measure(self, subs: list[Sub]) -> None:
+        """sigma = trace / n (nudged on a repeated attempt) and spread = ||A - sigma I||_F."""
+        for s in subs:
+            sigma = float(torch.trace(s.A)) / s.n
+            shifted = s.A - sigma * torch.eye(s.n, device=self.device, dtype=self.dtype)
+            spread = float(torch.linalg.norm(shifted))
+            if s.attempt:
+                sigma += _NUDGE * s.attempt * spread * (1 if s.attempt % 2 else -1)
+                spread = float(torch.linalg.norm(s.A - sigma * torch.eye(s.n, device=self.device, dtype=self.dtype)))
+            s.sigma, s.spread = sigma, spread
+
+    def sign_projector(self, subs: list[Sub]) -> None:
+        """P = (I + sign(A - sigma I)) / 2, rank = ||P||_F^2, idem_err = trace(P) - ||P||_F^2."""
+        for s in subs:
+            eye = torch.eye(s.n, device=self.device, dtype=self.dtype)
+            X = (s.A - s.sigma * eye) / s.spread
+            last = len(SIGN_SCHEDULE) - 1
+            for i, (a, b, c) in enumerate(SIGN_SCHEDULE):
+                Y = X @ X
+                Y = 0.5 * (Y + Y.T)
+                W = c * (Y @ Y) + b * Y + a * eye
+                W = 0.5 * (W + W.T)
+                X = X @ W
+                X = 0.5 * (X + X.T)
+                if i == last:
+                    X = 0.5 * X + 0.5 * eye
+            s.extra["P"] = X
+            fro2 = float((X * X).sum())
+            s.rank = int(round(fro2))
+            s.idem_err = float(torch.trace(X)) - fro2
+
+    def split_basis(self, subs: list[Sub]) -> None:
+        """Qt (n x n, rows orthonormal): the first ``rank`` rows span range(P)."""
+        for s in subs:
+            k, n = s.rank, s.n
+            P = s.extra.pop("P")
+            Y = P @ self._omega[:n, :k]  # n x k
+            Q, _ = torch.linalg.qr(Y, mode="complete")
+            for _ in range(self.passes - 1):
+                Q, _ = torch.linalg.qr(P @ Q[:, :k], mode="complete")
+            s.extra["Qt"] = Q.T.contiguous()
+
+    def project(self, subs: list[Sub]) -> list[Sub]:
+        """Children (V1^T A V1, above sigma) and (V2^T A V2, below) with their bases B V."""
+        children = []
+        for s in subs:
+            Qt = s.extra.pop("Qt")
+            k = s.rank
+            for rows, off in ((slice(0, k), s.offset), (slice(k, s.n), s.offset + k)):
+                Vt = Qt[rows]
+                A_child = Vt @ s.A @ Vt.T
+                A_child = 0.5 * (A_child + A_child.T)
+                B_child = Vt.T.contiguous() if s.B is None else s.B @ Vt.T
+                children.append(Sub(root=s.root, n=Vt.shape[0], offset=off, A=A_child, B=B_child))
+            s.A = s.B = None
+        return children
+
+    def close_scalar(self, subs: list[Sub]) -> None:
+        """Numerically multiple eigenvalue: eigenvalues = diag(A), eigenvectors = columns of B."""
+        for s in subs:
+            self.lams[s.root][s.offset : s.offset + s.n] = torch.diagonal(s.A)
+            self.vecs[s.root][:, s.offset : s.offset + s.n] = (
+                torch.eye(s.n, device=self.device, dtype=self.dtype) if s.B is None else s.B
+            )
+
+    def close_leaves(self, subs: list[Sub]) -> list[int]:
+        """Eigendecomposition of the small problems; returns the roots of those that failed."""
+        for s in subs:
+            lam, Q = torch.linalg.eigh(s.A)
+            self.lams[s.root][s.offset : s.offset + s.n] = lam
+            self.vecs[s.root][:, s.offset : s.offset + s.n] = Q if s.B is None else s.B @ Q
+        return []
+
+    def finish(self, roots_ok: list[bool]) -> tuple[list[Tensor | None], list[Tensor | None]]:
+        lams: list[Tensor | None] = []
+        vecs: list[Tensor | None] = []
+        for ok, lam, Q in zip(roots_ok, self.lams, self.vecs, strict=True):
+            if not ok:
+                lams.append(None)
+                vecs.append(None)
+                continue
+            order = torch.argsort(lam, stable=True)
+            lams.append(lam[order])
+            vecs.append(Q[:, order].contiguous())
+        return lams, vecs
+
+
+class _Timed:
+    """Wraps a backend whose ``profile`` attribute is a dict: every phase is bracketed by a device
+    synchronisation and its wall time is added to ``profile[phase]`` (diagnostics only; the
+    synchronisations serialise host and device)."""
+
+    def __init__(self, backend: Any) -> None:
+        self._backend = backend
+
+    def __getattr__(self, name: str) -> Any:
+        attr = getattr(self._backend, name)
+        if not callable(attr) or name.startswith("_"):
+            return attr
+        import time
+
+        def timed(*args: Any, **kwargs: Any) -> Any:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            out = attr(*args, **kwargs)
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            prof = self._backend.profile
+            prof[name] = prof.get(name, 0.0) + (time.perf_counter() - t0) * 1e3
+            return out
+
+        return timed
+
+
+def eigh_divide_and_conquer(
+    backend: Any, mats: list[Tensor], leaf: int = LEAF, scalar_tol: float = 4.0
+) -> tuple[list[Tensor | None], list[Tensor | None], dict[str, Any]]:
+    """Eigendecompositions (ascending eigenvalues, eigenvectors as columns) of the symmetric
+    matrices ``mats``, all advanced together.  Returns ``(eigenvalues, eigenvectors, info)``; the
+    entries of matrices the scheme gave up on are ``None`` and their indices are in
+    ``info["failed"]``.
+
+    ``scalar_tol``: a subproblem is closed as a multiple eigenvalue when its spread is below
+    ``scalar_tol * eps * ||root matrix||_F``."""
+    eps = torch.finfo(torch.float32).eps
+    backend = _Timed(backend) if getattr(backend, "profile", None) is not None else backend
+    work = backend.begin(mats)
+    failed: set[int] = set()
+    rounds = 0
+    signs = 0
+    cubes = 0.0  # sum of n^3 over all sign computations: the unit the cost of a refresh scales with
+    while work:
+        rounds += 1
+        work = [s for s in work if s.root not in failed]
+        leaves = [s for s in work if s.n <= leaf]
+        big = [s for s in work if s.n > leaf]
+        if leaves:
+            failed.update(backend.close_leaves(leaves))
+        if not big:
+            break
+        if rounds > _MAX_ROUNDS:
+            failed.update(s.root for s in big)
+            break
+        backend.measure(big)
+        scalar = [s for s in big if s.spread <= scalar_tol * eps * backend.root_norms[s.root] or s.spread == 0.0]
+        if scalar:
+            backend.close_scalar(scalar)
+        active = [s for s in big if not (s.spread <= scalar_tol * eps * backend.root_norms[s.root] or s.spread == 0.0)]
+        if not active:
+            work = []
+            continue
+        backend.sign_projector(active)
+        signs += len(active)
+        cubes += sum(float(s.n) ** 3 for s in active)
+        good, retry = [], []
+        for s in active:
+            bad = not (abs(s.idem_err) <= _IDEMPOTENCY_TOL) or s.rank <= 0 or s.rank >= s.n  # also catches NaN
+            if not bad:
+                good.append(s)
+                continue
+            s.attempt += 1
+            s.extra.clear()
+            if s.attempt >= _MAX_ATTEMPTS:
+                failed.add(s.root)
+            else:
+                retry.append(s)
+        children: list[Sub] = []
+        if good:
+            backend.split_basis(good)
+            children = backend.project(good)
+        work = retry + children
+    ok = [i not in failed for i in range(len(mats))]
+    lams, vecs = backend.finish(ok)
+    return lams, vecs, {"failed": sorted(failed), "rounds": rounds, "sign_computations": signs, "sign_cubes": cubes}
+
+
+# ----------------------------------------------------------------------------------------------
+# The sm_100a backend
+# ----------------------------------------------------------------------------------------------
+def _pad4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+class _Mat:
+    """A matrix in padded storage, as the plain array and/or as the tf32 (hi, lo) operand pair.
+    ``rows x cols`` with row pitch ``pad4(cols)``; the attributes are the exact-size views."""
+
+    __slots__ = ("rows", "cols", "plain", "hi", "lo")
+
+    def __init__(self, rows: int, cols: int, device: torch.device, plain: bool = True, pair: bool = True) -> None:
+        self.rows, self.cols = rows, cols
+        ld = _pad4(cols)
+        mk = lambda: torch.empty(rows, ld, device=device, dtype=torch.float32)[:, :cols]  # noqa: E731
+        self.plain = mk() if plain else None
+        self.hi = mk() if pair else None
+        self.lo = mk() if pair else None
+
+
+_OMEGA_CACHE: dict[tuple, _Mat] = {}
+
+
+class NativeBackend:
+    """Backend of ``eigh_divide_and_conquer`` on the sm_100a kernels.  Every product is a problem of
+    a grouped tcgen05 launch over all subproblems of a round (symmetric results compute only the
+    tiles on or above the diagonal); the host reads the device twice per round (split points and
+    spreads; ranks and idempotency defects) and once at the end (leaf convergence)."""
+
+    def __init__(self, ext: Any, device: torch.device, status: Tensor | None = None, range_passes: int = 2, seed: int = 1234) -> None:
+        self.ext, self.device = ext, device
+        self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=device)
+        self.range_passes = range_passes
+        self._seed = seed
+        self._leaf_sweeps: list[tuple[list[Sub], Tensor]] = []
+        self.profile: dict[str, float] | None = None  # set to {} to collect per-phase times
+        self.jacobi_max_sweeps = 24
+        self.jacobi_tolerance = 2e-6
+
+    # -- helpers ----------------------------------------------------------------------------
+    def _gemm(self, specs: list[tuple], alpha: float = 1.0, beta: float = 0.0, gamma: float = 0.0) -> None:
+        if specs:
+            plan = self.ext.build_gemm_plan(specs)
+            self.ext.run_gemm_plan(*plan, alpha, beta, True, self.status, gamma)
+
+    def _spec(self, a: _Mat, b: _Mat, out: _Mat | None, c: Tensor | None = None, flags: int = 0, sumsq: Tensor | None = None,
+              sym: bool = False, c_ld: int = 0) -> tuple:
+        """C = alpha A B^T (+ beta C) with the (hi, lo) pair of the result written to ``out``."""
+        F = self.ext
+        if sym:
+            flags |= F.FLAG_MIRROR
+        d_hi = d_lo = None
+        ldd = 0
+        if out is not None and out.hi is not None:
+            flags |= F.FLAG_SPLIT_OUT
+            d_hi, d_lo, ldd = out.hi, out.lo, out.hi.stride(0)
+        if c is None:
+            flags |= F.FLAG_NO_C
+        else:
+            c_ld = c.stride(0)
+        return (a.hi, a.lo, b.hi, b.lo, c, d_hi, d_lo, sumsq, c_ld, ldd, flags, sym)
+
+    # -- set-up -----------------------------------------------------------------------------
+    def begin(self, mats: list[Tensor]) -> list[Sub]:
+        ext, dev = self.ext, self.device
+        dmax = max(m.shape[0] for m in mats)
+        key = (dev.index, dmax, self._seed)
+        if key not in _OMEGA_CACHE:
+            _OMEGA_CACHE.clear()  # one test matrix per process is enough; sizes rarely change
+            gen = torch.Generator(device="cpu").manual_seed(self._seed)
+            omega_t = torch.randn(dmax, dmax, generator=gen).to(dev)  # rows are the columns of Omega
+            om = _Mat(dmax, dmax, dev, plain=False)
+            ext.tf32_split(omega_t, om.hi, om.lo)
+            _OMEGA_CACHE[key] = om
+        self._omega_t = _OMEGA_CACHE[key]
+        self.lams = [torch.zeros(m.shape[0], device=dev) for m in mats]
+        self.vecs = [torch.zeros(m.shape[0], m.shape[0], device=dev) for m in mats]
+        self.root_norms = torch.stack(torch._foreach_norm(list(mats))).cpu().tolist()
+        subs = []
+        for i, m in enumerate(mats):
+            n = m.shape[0]
+            A = _Mat(n, n, dev)
+            A.plain.copy_(m)
+            ext.tf32_split(A.plain, A.hi, A.lo)
+            subs.append(Sub(root=i, n=n, offset=0, A=A))
+        self._leaf_sweeps = []
+        return subs
+
+    # -- one round ----------------------------------------------------------------------------
+    def measure(self, subs: list[Sub]) -> None:
+        ext = self.ext
+        stats = torch.zeros(len(subs), 2, device=self.device)
+        table = ext.build_sym_table([(s.A.plain, None, None, stats[i], 0.0, 0.0) for i, s in enumerate(subs)])
+        ext.sym_measure(table[0], len(subs))
+        for s, (sigma, spread) in zip(subs, stats.cpu().tolist(), strict=True):
+            if s.attempt:
+                shift = _NUDGE * s.attempt * spread * (1 if s.attempt % 2 else -1)
+                # trace(A - sigma I) = 0, so the shifted spread follows without another pass
+                spread = math.sqrt(spread * spread + s.n * shift * shift)
+                sigma += shift
+            s.sigma, s.spread = sigma, spread
+
+    def sign_projector(self, subs: list[Sub]) -> None:
+        ext, dev, F = self.ext, self.device, self.ext
+        X = [[_Mat(s.n, s.n, dev, plain=False) for s in subs] for _ in range(2)]
+        Y = [_Mat(s.n, s.n, dev) for s in subs]
+        W = [_Mat(s.n, s.n, dev, plain=False) for s in subs]
+        stats = torch.zeros(len(subs), 2, device=dev)
+        table = ext.build_sym_table(
+            [(s.A.plain, X[0][i].hi, X[0][i].lo, None, 1.0 / s.spread, -s.sigma / s.spread) for i, s in enumerate(subs)]
+        )
+        ext.shift_scale_split(*table)
+        idx = range(len(subs))
+        plans = []
+        for cur in (0, 1):
+            nxt = cur ^ 1
+            g1 = [self._spec(X[cur][i], X[cur][i], Y[i], c=Y[i].plain, sym=True) for i in idx]
+            # W = c Y Y + b Y + a I: beta applies to the plain copy of Y that C holds
+            g2 = [self._spec(Y[i], Y[i], W[i], c=Y[i].plain, flags=F.FLAG_ADD_DIAG, sym=True) for i in idx]
+            g3 = [self._spec(X[cur][i], W[i], X[nxt][i], sym=True) for i in idx]
+            plans.append([ext.build_gemm_plan(g) for g in (g1, g2, g3)])
+        cur = 0
+        last = len(SIGN_SCHEDULE) - 1
+        for it, (a, b, c) in enumerate(SIGN_SCHEDULE):
+            p1, p2, p3 = plans[cur]
+            ext.run_gemm_plan(*p1, 1.0, 0.0, True, self.status)
+            ext.run_gemm_plan(*p2, c, b, True, self.status, a)
+            if it == last:
+                # P = X W / 2 + I / 2 with ||P||_F^2 and trace(P) from the epilogue
+                final = [
+                    self._spec(X[cur][i], W[i], X[cur ^ 1][i], flags=F.FLAG_ADD_DIAG | F.FLAG_SUMSQ | F.FLAG_TRACE,
+                               sumsq=stats[i], sym=True)
+                    for i in idx
+                ]
+                self._gemm(final, 0.5, 0.0, 0.5)
+            else:
+                ext.run_gemm_plan(*p3, 1.0, 0.0, True, self.status)
+            cur ^= 1
+        for i, (s, (fro2, trace)) in enumerate(zip(subs, stats.cpu().tolist(), strict=True)):
+            s.extra["P"] = X[cur][i]
+            finite = fro2 == fro2 and abs(fro2) != float("inf")
+            s.rank = int(round(fro2)) if finite else -1
+            s.idem_err = trace - fro2 if finite else float("nan")
+
+    def split_basis(self, subs: list[Sub]) -> None:
+        ext, dev = self.ext, self.device
+        om = self._omega_t
+        qr_specs, g = [], []
+        for s in subs:
+            k, n = s.rank, s.n
+            P = s.extra.pop("P")
+            Yt = _Mat(k, n, dev)  # rows: the columns of P Omega
+            Zt = _Mat(n, n, dev)
+            s.extra["Qt"] = Zt
+            g.append((om.hi, om.lo, P.hi, P.lo, Yt.plain, Yt.hi, Yt.lo, None, Yt.plain.stride(0), Yt.hi.stride(0),
+                      ext.FLAG_SPLIT_OUT, False, None, (0, 0, 0, 0, k, n, n)))
+            qr_specs.append((Yt.plain, Yt.hi, Yt.lo, n, k, Zt.plain, Zt.hi, Zt.lo))
+            s.extra["P_keep"] = P
+        # the Omega view ends before its array along K unless n == dmax: K = n must then be a multiple of 32;
+        # otherwise fall back to a sliced operand (its own tensor map)
+        fixed = []
+        for spec, s in zip(g, subs, strict=True):
+            n, k = s.n, s.rank
+            if n == om.cols or n % 32 == 0:
+                fixed.append(spec)
+            else:
+                fixed.append((om.hi[:k, :n], om.lo[:k, :n]) + spec[2:13] + (None,))
+        self._gemm(fixed)
+        ext.householder_qr(qr_specs, self.status)
+        for _ in range(self.range_passes - 1):
+            # One more pass from the orthonormal basis just found: Y <- P V1, whose conditioning is 1.
+            g, qr_specs = [], []
+            for s in subs:
+                k, n = s.rank, s.n
+                P, Zt_old = s.extra["P_keep"], s.extra["Qt"]
+                Yt, Zt = _Mat(k, n, dev), _Mat(n, n, dev)
+                v1 = _Mat.__new__(_Mat)
+                v1.rows, v1.cols, v1.plain, v1.hi, v1.lo = k, n, None, Zt_old.hi[:k], Zt_old.lo[:k]
+                g.append(self._spec(v1, P, Yt, c=Yt.plain))
+                qr_specs.append((Yt.plain, Yt.hi, Yt.lo, n, k, Zt.plain, Zt.hi, Zt.lo))
+                s.extra["Qt"] = Zt
+            self._gemm(g)
+            ext.householder_qr(qr_specs, self.status)
+        for s in subs:
+            s.extra.pop("P_keep")
+
+    def project(self, subs: list[Sub]) -> list[Sub]:
+        ext, dev = self.ext, self.device
+        children: list[Sub] = []
+        g1, g2, g3 = [], [], []
+        for s in subs:
+            Qt = s.extra.pop("Qt")
+            k, n = s.rank, s.n
+            for r0, r1, off in ((0, k, s.offset), (k, n, s.offset + k)):
+                m = r1 - r0
+                vt = _Mat.__new__(_Mat)
+                vt.rows, vt.cols, vt.plain, vt.hi, vt.lo = m, n, None, Qt.hi[r0:r1], Qt.lo[r0:r1]
+                T = _Mat(m, n, dev, plain=False)  # V^T A
+                Ac = _Mat(m, m, dev)
+                g1.append(self._spec(vt, s.A, T))
+                g2.append(self._spec(T, vt, Ac, c=Ac.plain, sym=True))
+                d = self.lams[s.root].shape[0]
+                Bc = _Mat(d, m, dev, plain=True)
+                if s.B is None:
+                    # B = I V: a transposed copy of V^T
+                    s.extra.setdefault("transposes", []).append((vt, Bc))
+                else:
+                    g3.append(self._spec(s.B, vt, Bc, c=Bc.plain))
+                children.append(Sub(root=s.root, n=m, offset=off, A=Ac, B=Bc))
+        self._gemm(g1)
+        self._gemm(g2)
+        self._gemm(g3)
+        tr = [(vt.hi, vt.lo, Bc) for s in subs for vt, Bc in s.extra.pop("transposes", [])]
+        if tr:
+            # (hi + lo) is the exact fp32 value: transpose hi and lo separately is not a valid split of
+            # the transposed value only if rounding differed, and tf32 rounding is elementwise
+            table = ext.build_transpose_table([(hi, Bc.hi, None, None) for hi, lo, Bc in tr] + [(lo, Bc.lo, None, None) for hi, lo, Bc in tr])
+            ext.transpose_split(*table)
+            for hi, lo, Bc in tr:
+                torch.add(Bc.hi, Bc.lo, out=Bc.plain)
+        for s in subs:
+            s.A = s.B = None
+        return children
+
+    def close_scalar(self, subs: list[Sub]) -> None:
+        for s in subs:
+            self.lams[s.root][s.offset : s.offset + s.n] = torch.diagonal(s.A.plain)
+            cols = self.vecs[s.root][:, s.offset : s.offset + s.n]
+            if s.B is None:
+                cols.copy_(torch.eye(s.n, device=self.device))
+            else:
+                cols.copy_(s.B.plain)
+
+    def close_leaves(self, subs: list[Sub]) -> list[int]:
+        ext, dev = self.ext, self.device
+        mats, qs, lams = [], [], []
+        holders = []
+        for s in subs:
+            mats.append(s.A.plain)
+            lams.append(self.lams[s.root][s.offset : s.offset + s.n])
+            if s.B is None:
+                qs.append(self.vecs[s.root])  # a root that is itself a leaf: eigenvectors as columns
+                holders.append(None)
+            else:
+                Qt = _Mat(s.n, s.n, dev)
+                qs.append(Qt.plain)
+                holders.append(Qt)
+        with_basis = [i for i, h in enumerate(holders) if h is not None]
+        direct = [i for i, h in enumerate(holders) if h is None]
+        sweeps = []
+        if direct:
+            sweeps.append(([subs[i] for i in direct], ext.jacobi_eigh_into(
+                [mats[i] for i in direct], [qs[i] for i in direct], [lams[i] for i in direct], False,
+                self.jacobi_max_sweeps, self.jacobi_tolerance)))
+        if with_basis:
+            sweeps.append(([subs[i] for i in with_basis], ext.jacobi_eigh_into(
+                [mats[i] for i in with_basis], [qs[i] for i in with_basis], [lams[i] for i in with_basis], True,
+                self.jacobi_max_sweeps, self.jacobi_tolerance)))
+            g = []
+            for i in with_basis:
+                s, Qt = subs[i], holders[i]
+                ext.tf32_split(Qt.plain, Qt.hi, Qt.lo)
+                cols = self.vecs[s.root][:, s.offset : s.offset + s.n]
+                g.append(self._spec(s.B, Qt, None, c=cols))
+            self._gemm(g)
+        self._leaf_sweeps.extend(sweeps)
+        return []  # convergence of the leaves is read once, in finish()
+
+    def finish(self, roots_ok: list[bool]) -> tuple[list[Tensor | None], list[Tensor | None]]:
+        roots_ok = list(roots_ok)
+        for subs, sweeps in self._leaf_sweeps:
+            for s, used in zip(subs, sweeps.cpu().tolist(), strict=True):
+                if used > self.jacobi_max_sweeps:
+                    roots_ok[s.root] = False
+        self._leaf_sweeps = []
+        self.failed_in_finish = [i for i, ok in enumerate(roots_ok) if not ok]
+        lams: list[Tensor | None] = []
+        vecs: list[Tensor | None] = []
+        for ok, lam, Q in zip(roots_ok, self.lams, self.vecs, strict=True):
+            if not ok:
+                lams.append(None)
+                vecs.append(None)
+                continue
+            sorted_lam, order = torch.sort(lam, stable=True)
+            lams.append(sorted_lam)
+            vecs.append(Q.index_select(1, order))
+        return lams, vecs

@@ -21,7 +21,7 @@ _NAME = "optimizers_b200_C"
 _SO = _HERE / f"{_NAME}.so"
 _module: ModuleType | None = None
 
-SOURCES = ["bindings.cu", "grouped_gemm.cu", "block_kernels.cu", "flat_kernels.cu", "two_sided_apply.cu", "model_kernels.cu"]
+SOURCES = ["bindings.cu", "grouped_gemm.cu", "block_kernels.cu", "flat_kernels.cu", "eig_kernels.cu", "two_sided_apply.cu", "model_kernels.cu"]
 NVCC_FLAGS = [
     "-gencode",
     "arch=compute_100a,code=sm_100a",

@@ -9,12 +9,16 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <array>
+#include <map>
+#include <memory>
 #include <cstdlib>
 #include <cstring>
 #include <optional>
 #include <vector>
 
 #include "block_kernels.cuh"
+#include "eig_kernels.cuh"
 #include "flat_kernels.cuh"
 #include "grouped_gemm.cuh"
 #include "two_sided_apply.h"
@@ -74,75 +78,85 @@ torch::Tensor upload_bytes(const void* src, size_t bytes, const torch::Device& d
   return host.to(device);
 }
 
-// One GEMM problem as given from Python.
-struct GemmSpec {
-  torch::Tensor a_hi, b_hi;
-  std::optional<torch::Tensor> a_lo, b_lo, c, d_hi, d_lo, sumsq;
-  int64_t ldc = 0, ldd = 0, flags = 0;
-  bool upper_tiles_only = false;  // symmetric result: schedule only tiles on or above the diagonal
-};
-
-// Returns (problem table bytes, tile list bytes, number of tiles), the first two on the device.
-std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vector<py::tuple>& specs) {
-  TORCH_CHECK(!specs.empty(), "empty GEMM plan");
-  std::vector<GemmProblem> problems(specs.size());
-  std::vector<GemmTile> tiles;
-  struct Order {
-    int problem;
-    int K;
+// Host-side assembly of grouped-GEMM launch tables.  Problems of any number of launches go into
+// one device buffer laid out as [problem table][tensor maps]; a tensor map is encoded once per
+// distinct array (pointer, extents, pitch) however many problems view it.  Each launch owns a
+// contiguous range of the common tile list.
+class PlanBuilder {
+ public:
+  struct Operand {
+    const torch::Tensor* hi = nullptr;
+    const torch::Tensor* lo = nullptr;  // may be null (single-product mode)
+    int row0 = 0, k0 = 0;
   };
-  std::vector<Order> order;
-  torch::Device device(torch::kCPU);
-  for (size_t i = 0; i < specs.size(); ++i) {
-    const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 12 || s.size() == 13, "GEMM spec must have 12 fields (13 with a push offset)");
-    GemmSpec g;
-    g.a_hi = s[0].cast<torch::Tensor>();
-    g.a_lo = s[1].cast<std::optional<torch::Tensor>>();
-    g.b_hi = s[2].cast<torch::Tensor>();
-    g.b_lo = s[3].cast<std::optional<torch::Tensor>>();
-    g.c = s[4].cast<std::optional<torch::Tensor>>();
-    g.d_hi = s[5].cast<std::optional<torch::Tensor>>();
-    g.d_lo = s[6].cast<std::optional<torch::Tensor>>();
-    g.sumsq = s[7].cast<std::optional<torch::Tensor>>();
-    g.ldc = s[8].cast<int64_t>();
-    g.ldd = s[9].cast<int64_t>();
-    g.flags = s[10].cast<int64_t>();
-    g.upper_tiles_only = s[11].cast<bool>();
-    device = g.a_hi.device();
+  struct Problem {
+    Operand a, b;
+    float* c = nullptr;
+    float* d_hi = nullptr;
+    float* d_lo = nullptr;
+    float* sumsq = nullptr;
+    int M = 0, N = 0, K = 0, ldc = 0, ldd = 0, flags = 0;
+    long long push_offset = 0;
+    bool upper_tiles_only = false;
+  };
 
-    GemmProblem& p = problems[i];
+  void begin_launch() { launch_begin_ = static_cast<int>(problems_.size()); }
+
+  void add(const Problem& q) {
+    GemmProblem p;
     std::memset(&p, 0, sizeof(p));
-    p.M = static_cast<int>(g.a_hi.size(0));
-    p.N = static_cast<int>(g.b_hi.size(0));
-    p.K = static_cast<int>(g.a_hi.size(1));
-    TORCH_CHECK(g.b_hi.size(1) == p.K, "A and B must agree on K");
-    p.a_hi = encode_operand(g.a_hi, kBM);
-    p.b_hi = encode_operand(g.b_hi, kBN);
-    p.a_lo = g.a_lo.has_value() ? encode_operand(*g.a_lo, kBM) : p.a_hi;
-    p.b_lo = g.b_lo.has_value() ? encode_operand(*g.b_lo, kBN) : p.b_hi;
-    p.c = fptr(g.c);
-    p.d_hi = fptr(g.d_hi);
-    p.d_lo = fptr(g.d_lo);
-    p.sumsq = fptr(g.sumsq);
-    p.ldc = static_cast<int>(g.ldc);
-    p.ldd = static_cast<int>(g.ldd);
-    p.flags = static_cast<int>(g.flags);
-    p.push_offset = s.size() == 13 ? s[12].cast<int64_t>() : 0;
-    if (p.flags & kFlagPeerPush) TORCH_CHECK(s.size() == 13, "a pushing problem needs its slot offset");
-    if (p.flags & kFlagPackedC) TORCH_CHECK(p.M == p.N && g.upper_tiles_only, "packed output needs a square upper-tile problem");
+    TORCH_CHECK(q.M > 0 && q.N > 0 && q.K > 0, "empty GEMM problem");
+    for (const Operand* op : {&q.a, &q.b}) {
+      const int64_t array_k = op->hi->size(1);
+      TORCH_CHECK(op->k0 % 4 == 0 && op->k0 >= 0 && op->k0 + q.K <= array_k, "operand view exceeds its array along K");
+      TORCH_CHECK(op->k0 + q.K == array_k || q.K % kBK == 0,
+                  "an operand view that ends before its array along K needs K to be a multiple of ", kBK);
+      TORCH_CHECK(op->row0 >= 0, "negative row origin");
+    }
+    TORCH_CHECK(q.a.row0 + q.M <= q.a.hi->size(0) && q.b.row0 + q.N <= q.b.hi->size(0), "operand view exceeds its array");
+    device_ = q.a.hi->device();
+    index_.push_back({map_of(*q.a.hi, kBM), q.a.lo != nullptr ? map_of(*q.a.lo, kBM) : -1, map_of(*q.b.hi, kBN),
+                      q.b.lo != nullptr ? map_of(*q.b.lo, kBN) : -1});
+    p.a_row0 = q.a.row0;
+    p.a_k0 = q.a.k0;
+    p.b_row0 = q.b.row0;
+    p.b_k0 = q.b.k0;
+    p.c = q.c;
+    p.d_hi = q.d_hi;
+    p.d_lo = q.d_lo;
+    p.sumsq = q.sumsq;
+    p.M = q.M;
+    p.N = q.N;
+    p.K = q.K;
+    p.ldc = q.ldc;
+    p.ldd = q.ldd;
+    p.flags = q.flags;
+    p.push_offset = q.push_offset;
+    if (p.flags & kFlagPackedC) TORCH_CHECK(p.M == p.N && q.upper_tiles_only, "packed output needs a square upper-tile problem");
+    if (p.flags & kFlagMirror) {
+      TORCH_CHECK(p.M == p.N && q.upper_tiles_only && !(p.flags & kFlagPackedC),
+                  "mirrored output needs a square, unpacked upper-tile problem");
+    }
     if (!(p.flags & kFlagNoC)) TORCH_CHECK(p.c != nullptr, "C is required unless kFlagNoC is set");
     if (p.flags & kFlagSplitOut) TORCH_CHECK(p.d_hi != nullptr && p.d_lo != nullptr, "split output needs d_hi and d_lo");
-    if (p.flags & kFlagSumSq) TORCH_CHECK(p.sumsq != nullptr, "sumsq output missing");
-    order.push_back({static_cast<int>(i), p.K});
+    if (p.flags & (kFlagSumSq | kFlagTrace)) TORCH_CHECK(p.sumsq != nullptr, "sumsq output missing");
+    problems_.push_back(p);
+    upper_.push_back(q.upper_tiles_only);
   }
-  // Longest K loops first so the persistent CTAs finish together.
-  std::stable_sort(order.begin(), order.end(), [](const Order& x, const Order& y) { return x.K > y.K; });
-  for (const Order& o : order) {
-    const GemmProblem& p = problems[o.problem];
-    const bool upper = specs[o.problem][11].cast<bool>();
+
+  // Closes the current launch: its tiles are appended to the tile list, longest K loops first so
+  // that the persistent CTAs finish together.  Returns (first tile, number of tiles).
+  std::pair<int64_t, int64_t> end_launch() {
+    struct Order {
+      int problem;
+      int K;
+    };
+    std::vector<Order> order;
+    for (int i = launch_begin_; i < static_cast<int>(problems_.size()); ++i) order.push_back({i, problems_[i].K});
+    std::stable_sort(order.begin(), order.end(), [](const Order& x, const Order& y) { return x.K > y.K; });
+    const int64_t first = static_cast<int64_t>(tiles_.size());
     // Tiles are issued in bands of kBandRows tile rows, column by column inside a band, so that
-    // the ~148 tiles in flight together touch about 2 * sqrt(148) operand panels instead of a
+    // the tiles in flight together touch about 2 * sqrt(#SMs) operand panels instead of a
     // whole row of them: for K = 4096 a (hi, lo) panel is 4 MB and a full tile row of B panels
     // alone would exceed the L2.
     static const int kBandRows = [] {
@@ -150,30 +164,175 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vec
       const int v = env != nullptr ? std::atoi(env) : 12;
       return v > 0 ? v : 12;
     }();
-    for (int band = 0; band < p.M; band += kBandRows * kBM) {
-      const int band_end = std::min(p.M, band + kBandRows * kBM);
-      for (int n0 = upper ? band : 0; n0 < p.N; n0 += kBN) {
-        for (int m0 = band; m0 < band_end; m0 += kBM) {
-          if (upper && n0 < m0) continue;
-          tiles.push_back({o.problem, m0, n0, 0});
+    for (const Order& o : order) {
+      const GemmProblem& p = problems_[o.problem];
+      const bool upper = upper_[o.problem];
+      for (int band = 0; band < p.M; band += kBandRows * kBM) {
+        const int band_end = std::min(p.M, band + kBandRows * kBM);
+        for (int n0 = upper ? band : 0; n0 < p.N; n0 += kBN) {
+          for (int m0 = band; m0 < band_end; m0 += kBM) {
+            if (upper && n0 < m0) continue;
+            tiles_.push_back({o.problem, m0, n0, 0});
+          }
         }
       }
     }
+    launch_begin_ = static_cast<int>(problems_.size());
+    return {first, static_cast<int64_t>(tiles_.size()) - first};
   }
-  auto d_problems = upload_bytes(problems.data(), problems.size() * sizeof(GemmProblem), device);
-  auto d_tiles = upload_bytes(tiles.data(), tiles.size() * sizeof(GemmTile), device);
-  TORCH_CHECK(reinterpret_cast<uintptr_t>(d_problems.data_ptr()) % 128 == 0, "problem table must be 128-byte aligned");
-  return {d_problems, d_tiles, static_cast<int64_t>(tiles.size())};
+
+  bool empty() const { return problems_.empty(); }
+
+  // Uploads everything; returns (problem table + tensor maps, tile list).
+  std::pair<torch::Tensor, torch::Tensor> finalize() {
+    TORCH_CHECK(!problems_.empty(), "empty GEMM plan");
+    const size_t table_bytes = problems_.size() * sizeof(GemmProblem);
+    const size_t map_bytes = maps_.size() * sizeof(CUtensorMap);
+    auto buffer = torch::empty({static_cast<int64_t>(table_bytes + map_bytes)}, torch::dtype(torch::kUInt8).device(device_));
+    const auto base = reinterpret_cast<uintptr_t>(buffer.data_ptr());
+    TORCH_CHECK(base % 128 == 0, "problem table must be 128-byte aligned");
+    const auto* dev_maps = reinterpret_cast<const CUtensorMap*>(base + table_bytes);
+    for (size_t i = 0; i < problems_.size(); ++i) {
+      const auto& ix = index_[i];
+      GemmProblem& p = problems_[i];
+      p.a_hi = dev_maps + ix[0];
+      p.a_lo = dev_maps + (ix[1] >= 0 ? ix[1] : ix[0]);
+      p.b_hi = dev_maps + ix[2];
+      p.b_lo = dev_maps + (ix[3] >= 0 ? ix[3] : ix[2]);
+    }
+    auto host = torch::empty({static_cast<int64_t>(table_bytes + map_bytes)}, torch::dtype(torch::kUInt8));
+    std::memcpy(host.data_ptr(), problems_.data(), table_bytes);
+    std::memcpy(static_cast<uint8_t*>(host.data_ptr()) + table_bytes, maps_.data(), map_bytes);
+    buffer.copy_(host);
+    auto d_tiles = upload_bytes(tiles_.data(), tiles_.size() * sizeof(GemmTile), device_);
+    return {buffer, d_tiles};
+  }
+
+ private:
+  int map_of(const torch::Tensor& t, int box_rows) {
+    const std::array<int64_t, 5> key = {reinterpret_cast<int64_t>(t.data_ptr()), t.size(0), t.size(1), t.stride(0), box_rows};
+    auto it = cache_.find(key);
+    if (it != cache_.end()) return it->second;
+    maps_.push_back(encode_operand(t, box_rows));
+    const int idx = static_cast<int>(maps_.size()) - 1;
+    cache_.emplace(key, idx);
+    return idx;
+  }
+
+  std::vector<GemmProblem> problems_;
+  std::vector<std::array<int, 4>> index_;
+  std::vector<bool> upper_;
+  std::vector<GemmTile> tiles_;
+  std::vector<CUtensorMap> maps_;
+  std::map<std::array<int64_t, 5>, int> cache_;
+  torch::Device device_{torch::kCPU};
+  int launch_begin_ = 0;
+};
+
+// Holds the tensors of one Python GEMM spec alive while the builder refers to them.
+struct SpecTensors {
+  torch::Tensor a_hi, b_hi;
+  std::optional<torch::Tensor> a_lo, b_lo, c, d_hi, d_lo, sumsq;
+};
+
+// Spec fields: (a_hi, a_lo | None, b_hi, b_lo | None, c | None, d_hi | None, d_lo | None, sumsq | None,
+//               ldc, ldd, flags, upper_tiles_only [, push_offset [, (a_row0, a_k0, b_row0, b_k0, M, N, K)]])
+// With the last field the operands are views, of the given origin and extent, of the arrays passed.
+void add_spec(PlanBuilder& builder, const py::tuple& s, std::vector<std::unique_ptr<SpecTensors>>& keep) {
+  TORCH_CHECK(s.size() >= 12 && s.size() <= 14, "GEMM spec must have 12 to 14 fields");
+  keep.push_back(std::make_unique<SpecTensors>());
+  SpecTensors& g = *keep.back();
+  g.a_hi = s[0].cast<torch::Tensor>();
+  g.a_lo = s[1].cast<std::optional<torch::Tensor>>();
+  g.b_hi = s[2].cast<torch::Tensor>();
+  g.b_lo = s[3].cast<std::optional<torch::Tensor>>();
+  g.c = s[4].cast<std::optional<torch::Tensor>>();
+  g.d_hi = s[5].cast<std::optional<torch::Tensor>>();
+  g.d_lo = s[6].cast<std::optional<torch::Tensor>>();
+  g.sumsq = s[7].cast<std::optional<torch::Tensor>>();
+  PlanBuilder::Problem q;
+  q.a.hi = &g.a_hi;
+  q.a.lo = g.a_lo.has_value() ? &*g.a_lo : nullptr;
+  q.b.hi = &g.b_hi;
+  q.b.lo = g.b_lo.has_value() ? &*g.b_lo : nullptr;
+  q.c = fptr(g.c);
+  q.d_hi = fptr(g.d_hi);
+  q.d_lo = fptr(g.d_lo);
+  q.sumsq = fptr(g.sumsq);
+  q.ldc = static_cast<int>(s[8].cast<int64_t>());
+  q.ldd = static_cast<int>(s[9].cast<int64_t>());
+  q.flags = static_cast<int>(s[10].cast<int64_t>());
+  q.upper_tiles_only = s[11].cast<bool>();
+  q.push_offset = s.size() >= 13 && !s[12].is_none() ? s[12].cast<int64_t>() : 0;
+  if (q.flags & kFlagPeerPush) TORCH_CHECK(s.size() >= 13 && !s[12].is_none(), "a pushing problem needs its slot offset");
+  if (q.flags & kFlagTrace) TORCH_CHECK(g.sumsq.has_value() && g.sumsq->numel() >= 2, "trace output needs a two-element sumsq");
+  if (s.size() == 14 && !s[13].is_none()) {
+    const auto view = s[13].cast<std::vector<int64_t>>();
+    TORCH_CHECK(view.size() == 7, "operand view must be (a_row0, a_k0, b_row0, b_k0, M, N, K)");
+    q.a.row0 = static_cast<int>(view[0]);
+    q.a.k0 = static_cast<int>(view[1]);
+    q.b.row0 = static_cast<int>(view[2]);
+    q.b.k0 = static_cast<int>(view[3]);
+    q.M = static_cast<int>(view[4]);
+    q.N = static_cast<int>(view[5]);
+    q.K = static_cast<int>(view[6]);
+  } else {
+    q.M = static_cast<int>(g.a_hi.size(0));
+    q.N = static_cast<int>(g.b_hi.size(0));
+    q.K = static_cast<int>(g.a_hi.size(1));
+    TORCH_CHECK(g.b_hi.size(1) == q.K, "A and B must agree on K");
+  }
+  builder.add(q);
+}
+
+// Returns (problem table bytes, tile list bytes, number of tiles), the first two on the device.
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_gemm_plan(const std::vector<py::tuple>& specs) {
+  TORCH_CHECK(!specs.empty(), "empty GEMM plan");
+  PlanBuilder builder;
+  std::vector<std::unique_ptr<SpecTensors>> keep;
+  builder.begin_launch();
+  for (const py::tuple& s : specs) add_spec(builder, s, keep);
+  const auto range = builder.end_launch();
+  auto [table, tiles] = builder.finalize();
+  return {table, tiles, range.second};
+}
+
+// Several launches in one table and one upload.  Returns (table, tiles, [(first tile, tiles), ...]);
+// launch i runs with run_gemm_plan_range(table, tiles, first_i, count_i, ...).
+std::tuple<torch::Tensor, torch::Tensor, std::vector<std::pair<int64_t, int64_t>>> build_gemm_plans(
+    const std::vector<std::vector<py::tuple>>& launches) {
+  PlanBuilder builder;
+  std::vector<std::unique_ptr<SpecTensors>> keep;
+  std::vector<std::pair<int64_t, int64_t>> ranges;
+  for (const auto& specs : launches) {
+    builder.begin_launch();
+    for (const py::tuple& s : specs) add_spec(builder, s, keep);
+    ranges.push_back(builder.end_launch());
+  }
+  auto [table, tiles] = builder.finalize();
+  return {table, tiles, ranges};
+}
+
+void run_gemm_range(const torch::Tensor& problems, const torch::Tensor& tiles, int64_t first_tile, int64_t num_tiles,
+                    double alpha, double beta, bool split, torch::Tensor status, double gamma) {
+  if (num_tiles <= 0) return;
+  c10::cuda::CUDAGuard guard(problems.device());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  launch_grouped_gemm(reinterpret_cast<const GemmProblem*>(problems.data_ptr()),
+                      reinterpret_cast<const GemmTile*>(tiles.data_ptr()) + first_tile, static_cast<int>(num_tiles),
+                      static_cast<float>(alpha), static_cast<float>(beta), split, status.data_ptr<int>(), sms,
+                      at::cuda::getCurrentCUDAStream(), nullptr, static_cast<float>(gamma));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 void run_gemm_plan(const torch::Tensor& problems, const torch::Tensor& tiles, int64_t num_tiles, double alpha,
-                   double beta, bool split, torch::Tensor status) {
+                   double beta, bool split, torch::Tensor status, double gamma) {
   c10::cuda::CUDAGuard guard(problems.device());
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   launch_grouped_gemm(reinterpret_cast<const GemmProblem*>(problems.data_ptr()),
                       reinterpret_cast<const GemmTile*>(tiles.data_ptr()), static_cast<int>(num_tiles),
                       static_cast<float>(alpha), static_cast<float>(beta), split, status.data_ptr<int>(), sms,
-                      at::cuda::getCurrentCUDAStream());
+                      at::cuda::getCurrentCUDAStream(), nullptr, static_cast<float>(gamma));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -541,6 +700,401 @@ std::tuple<std::vector<torch::Tensor>, std::vector<torch::Tensor>, torch::Tensor
   return {lams, qs, sweeps};
 }
 
+// jacobi_eigh writing into caller-provided storage: qs[i] is an n x n view (any row pitch) that
+// receives the eigenvectors as columns (or as rows with `transposed`), lams[i] an n-vector.
+torch::Tensor jacobi_eigh_into(const std::vector<torch::Tensor>& mats, const std::vector<torch::Tensor>& qs,
+                               const std::vector<torch::Tensor>& lams, bool transposed, int64_t max_sweeps, double tol) {
+  TORCH_CHECK(!mats.empty() && mats.size() == qs.size() && mats.size() == lams.size(), "jacobi_eigh_into: list sizes");
+  const auto device = mats[0].device();
+  c10::cuda::CUDAGuard guard(device);
+  std::vector<JacobiDesc> descs(mats.size());
+  for (size_t i = 0; i < mats.size(); ++i) {
+    const auto& a = mats[i];
+    const auto& q = qs[i];
+    const auto& l = lams[i];
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == torch::kFloat32 && a.dim() == 2 && a.size(0) == a.size(1) &&
+                    a.stride(1) == 1 && a.size(0) <= kJacobiMaxN && a.size(0) >= 1,
+                "jacobi_eigh_into: square fp32 CUDA matrices of size <= ", kJacobiMaxN);
+    const int64_t n = a.size(0);
+    TORCH_CHECK(q.scalar_type() == torch::kFloat32 && q.dim() == 2 && q.size(0) == n && q.size(1) == n && q.stride(1) == 1);
+    TORCH_CHECK(l.scalar_type() == torch::kFloat32 && l.dim() == 1 && l.size(0) == n && l.stride(0) == 1);
+    descs[i] = {a.data_ptr<float>(), q.data_ptr<float>(), l.data_ptr<float>(), static_cast<int>(n),
+                static_cast<int>(a.stride(0)), static_cast<int>(q.stride(0)), transposed ? 1 : 0};
+  }
+  auto d_descs = upload_bytes(descs.data(), descs.size() * sizeof(JacobiDesc), device);
+  auto sweeps = torch::zeros({static_cast<int64_t>(mats.size())}, torch::dtype(torch::kInt32).device(device));
+  launch_jacobi_eigh(reinterpret_cast<const JacobiDesc*>(d_descs.data_ptr()), static_cast<int>(mats.size()),
+                     static_cast<int>(max_sweeps), static_cast<float>(tol), sweeps.data_ptr<int>(),
+                     at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return sweeps;
+}
+
+// Panels of the blocked Householder QR.  Each spec: (ct, n, c0, c1, v_hi, v_lo, ttv_hi, ttv_lo, tv_hi, tv_lo)
+// with ct the transposed storage (rows are columns of the factored matrix; ct.stride(0) is the pitch),
+// v_* of shape [n - c0, QR_PANEL] contiguous and ttv_* / tv_* of shape [c1 - c0, n - c0] with a common pitch.
+torch::Tensor build_qr_panel_table(const std::vector<py::tuple>& specs) {
+  std::vector<QrPanelDesc> descs(specs.size());
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 10, "QR panel spec must have 10 fields");
+    auto ct = s[0].cast<torch::Tensor>();
+    TORCH_CHECK(ct.is_cuda() && ct.scalar_type() == torch::kFloat32 && ct.dim() == 2 && ct.stride(1) == 1);
+    device = ct.device();
+    QrPanelDesc& d = descs[i];
+    std::memset(&d, 0, sizeof(d));
+    d.ct = ct.data_ptr<float>();
+    d.ld = static_cast<int>(ct.stride(0));
+    d.n = s[1].cast<int>();
+    d.c0 = s[2].cast<int>();
+    d.c1 = s[3].cast<int>();
+    TORCH_CHECK(d.c0 >= 0 && d.c1 > d.c0 && d.c1 - d.c0 <= kQrPanel && d.c1 <= d.n && d.c1 <= ct.size(0) && d.n <= ct.size(1),
+                "QR panel bounds");
+    const int L = d.n - d.c0, nb = d.c1 - d.c0;
+    auto get = [&](int k, int64_t rows, int64_t cols) {
+      auto t = s[k].cast<torch::Tensor>();
+      TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.dim() == 2 && t.stride(1) == 1 &&
+                      t.size(0) >= rows && t.size(1) >= cols,
+                  "QR panel operand ", k, " too small");
+      return t;
+    };
+    auto v_hi = get(4, L, kQrPanel), v_lo = get(5, L, kQrPanel);
+    TORCH_CHECK(v_hi.stride(0) == kQrPanel && v_lo.stride(0) == kQrPanel, "V must have pitch QR_PANEL");
+    auto ttv_hi = get(6, nb, L), ttv_lo = get(7, nb, L), tv_hi = get(8, nb, L), tv_lo = get(9, nb, L);
+    d.ldw = static_cast<int>(ttv_hi.stride(0));
+    TORCH_CHECK(ttv_lo.stride(0) == d.ldw && tv_hi.stride(0) == d.ldw && tv_lo.stride(0) == d.ldw, "common pitch");
+    d.v_hi = v_hi.data_ptr<float>();
+    d.v_lo = v_lo.data_ptr<float>();
+    d.ttv_hi = ttv_hi.data_ptr<float>();
+    d.ttv_lo = ttv_lo.data_ptr<float>();
+    d.tv_hi = tv_hi.data_ptr<float>();
+    d.tv_lo = tv_lo.data_ptr<float>();
+  }
+  return upload_bytes(descs.data(), descs.size() * sizeof(QrPanelDesc), device);
+}
+
+void householder_panel(const torch::Tensor& table, int64_t count) {
+  c10::cuda::CUDAGuard guard(table.device());
+  launch_householder_panel(reinterpret_cast<const QrPanelDesc*>(table.data_ptr()), static_cast<int>(count),
+                           at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// Blocked Householder QR of a batch of matrices, entirely on the device and without host
+// synchronisation: for every panel of kQrPanel columns one launch of the panel kernel over all
+// matrices that still have such a panel, then two grouped tensor-core GEMM launches that apply the
+// block reflector to the remaining columns (C <- C - (C V T) V^T in the transposed storage); a
+// second sweep over the panels in reverse accumulates Q^T the same way, touching only the trailing
+// block each reflector acts on.  All launch tables are assembled here and uploaded once.
+//
+// Each spec: (ct, ct_hi, ct_lo, n, k, zt, zt_hi, zt_lo)
+//   ct, ct_hi, ct_lo  [>= k, n] views (row pitch a multiple of 4): row c is column c of the n x k matrix
+//                     to factor, plain and as a tf32 (hi, lo) pair; overwritten (R and reflectors)
+//   zt, zt_hi, zt_lo  [n, n] views: receive Q^T of the full n x n orthogonal factor, plain and split;
+//                     its first k rows span the columns of the matrix, the others their complement
+// Replaces torch.linalg.qr (cuSOLVER geqrf + orgqr) of the reference's QR iteration
+// (distributed_shampoo/preconditioner/matrix_functions.py:843).
+void householder_qr(const std::vector<py::tuple>& specs, torch::Tensor status) {
+  TORCH_CHECK(!specs.empty(), "householder_qr: empty batch");
+  struct Item {
+    torch::Tensor ct, ct_hi, ct_lo, zt, zt_hi, zt_lo;
+    torch::Tensor v_hi, v_lo, ttv_hi, ttv_lo, tv_hi, tv_lo, u_hi, u_lo;
+    torch::Tensor ttv_hi_v, ttv_lo_v, tv_hi_v, tv_lo_v;  // [k16, n] views of the padded arrays
+    int n = 0, k = 0, npan = 0;
+    std::vector<int64_t> voff;  // first row of panel j inside v_hi / v_lo
+  };
+  std::vector<Item> items(specs.size());
+  int max_pan = 0;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 8, "householder_qr spec must have 8 fields");
+    Item& it = items[i];
+    it.ct = s[0].cast<torch::Tensor>();
+    it.ct_hi = s[1].cast<torch::Tensor>();
+    it.ct_lo = s[2].cast<torch::Tensor>();
+    it.n = s[3].cast<int>();
+    it.k = s[4].cast<int>();
+    it.zt = s[5].cast<torch::Tensor>();
+    it.zt_hi = s[6].cast<torch::Tensor>();
+    it.zt_lo = s[7].cast<torch::Tensor>();
+    TORCH_CHECK(it.k >= 1 && it.k <= it.n, "householder_qr: need 1 <= k <= n");
+    for (const torch::Tensor* t : {&it.ct, &it.ct_hi, &it.ct_lo}) {
+      TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->dim() == 2 && t->stride(1) == 1 &&
+                      t->size(0) >= it.k && t->size(1) == it.n && t->stride(0) == it.ct.stride(0),
+                  "householder_qr: ct arrays must be [>= k, n] fp32 views with one pitch");
+    }
+    for (const torch::Tensor* t : {&it.zt, &it.zt_hi, &it.zt_lo}) {
+      TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->dim() == 2 && t->stride(1) == 1 &&
+                      t->size(0) == it.n && t->size(1) == it.n && t->stride(0) == it.zt.stride(0),
+                  "householder_qr: zt arrays must be [n, n] fp32 views with one pitch");
+    }
+    device = it.ct.device();
+    it.npan = (it.k + kQrPanel - 1) / kQrPanel;
+    max_pan = std::max(max_pan, it.npan);
+    int64_t rows = 0;
+    for (int j = 0; j < it.npan; ++j) {
+      it.voff.push_back(rows);
+      rows += it.n - j * kQrPanel;
+    }
+    const auto opts = it.ct.options();
+    const int64_t k16 = static_cast<int64_t>(it.npan) * kQrPanel, ldw = (it.n + 3) / 4 * 4;
+    it.v_hi = torch::empty({rows, kQrPanel}, opts);
+    it.v_lo = torch::empty({rows, kQrPanel}, opts);
+    it.ttv_hi = torch::empty({k16, ldw}, opts);
+    it.ttv_lo = torch::empty({k16, ldw}, opts);
+    it.tv_hi = torch::empty({k16, ldw}, opts);
+    it.tv_lo = torch::empty({k16, ldw}, opts);
+    it.ttv_hi_v = it.ttv_hi.narrow(1, 0, it.n);
+    it.ttv_lo_v = it.ttv_lo.narrow(1, 0, it.n);
+    it.tv_hi_v = it.tv_hi.narrow(1, 0, it.n);
+    it.tv_lo_v = it.tv_lo.narrow(1, 0, it.n);
+    it.u_hi = torch::zeros({it.n, kQrPanel}, opts);
+    it.u_lo = torch::zeros({it.n, kQrPanel}, opts);
+  }
+  c10::cuda::CUDAGuard guard(device);
+  auto stream = at::cuda::getCurrentCUDAStream();
+
+  // Panel descriptors, panel-major.
+  std::vector<QrPanelDesc> panels;
+  std::vector<std::pair<int, int>> panel_range(max_pan);
+  for (int j = 0; j < max_pan; ++j) {
+    const int first = static_cast<int>(panels.size());
+    for (const Item& it : items) {
+      if (j >= it.npan) continue;
+      QrPanelDesc d;
+      std::memset(&d, 0, sizeof(d));
+      d.ct = it.ct.data_ptr<float>();
+      d.ld = static_cast<int>(it.ct.stride(0));
+      d.n = it.n;
+      d.c0 = j * kQrPanel;
+      d.c1 = std::min(it.k, d.c0 + kQrPanel);
+      d.v_hi = it.v_hi.data_ptr<float>() + it.voff[j] * kQrPanel;
+      d.v_lo = it.v_lo.data_ptr<float>() + it.voff[j] * kQrPanel;
+      d.ldw = static_cast<int>(it.ttv_hi.stride(0));
+      const int64_t row = static_cast<int64_t>(d.c0) * d.ldw;  // the kernel indexes columns from c0 itself
+      d.ttv_hi = it.ttv_hi.data_ptr<float>() + row + d.c0;
+      d.ttv_lo = it.ttv_lo.data_ptr<float>() + row + d.c0;
+      d.tv_hi = it.tv_hi.data_ptr<float>() + row + d.c0;
+      d.tv_lo = it.tv_lo.data_ptr<float>() + row + d.c0;
+      panels.push_back(d);
+    }
+    panel_range[j] = {first, static_cast<int>(panels.size()) - first};
+  }
+  auto d_panels = upload_bytes(panels.data(), panels.size() * sizeof(QrPanelDesc), device);
+  const auto* panel_table = reinterpret_cast<const QrPanelDesc*>(d_panels.data_ptr());
+
+  PlanBuilder builder;
+  using Range = std::pair<int64_t, int64_t>;
+  std::vector<Range> fwd1(max_pan), fwd2(max_pan), bwd1(max_pan), bwd2(max_pan);
+  auto stage = [&](bool forward, bool second, int j) {
+    builder.begin_launch();
+    for (Item& it : items) {
+      if (j >= it.npan) continue;
+      const int c0 = j * kQrPanel, c1 = std::min(it.k, c0 + kQrPanel), nb = c1 - c0;
+      const int L = it.n - c0;
+      const int rows = forward ? it.k - c1 : L;  // rows of the updated block
+      if (rows <= 0) continue;
+      const int row0 = forward ? c1 : c0;
+      torch::Tensor& x = forward ? it.ct : it.zt;
+      torch::Tensor& x_hi = forward ? it.ct_hi : it.zt_hi;
+      torch::Tensor& x_lo = forward ? it.ct_lo : it.zt_lo;
+      PlanBuilder::Problem q;
+      if (!second) {  // U = X[row0:, c0:] (W^T)[c0:c1, c0:]^T with W^T = T^T V^T (forward) or T V^T (backward)
+        q.a = {&x_hi, &x_lo, row0, c0};
+        q.b = {forward ? &it.ttv_hi_v : &it.tv_hi_v, forward ? &it.ttv_lo_v : &it.tv_lo_v, c0, c0};
+        q.M = rows;
+        q.N = nb;
+        q.K = L;
+        q.d_hi = it.u_hi.data_ptr<float>();
+        q.d_lo = it.u_lo.data_ptr<float>();
+        q.ldd = kQrPanel;
+        q.flags = kFlagNoC | kFlagSplitOut;
+      } else {  // X[row0:, c0:] -= U V^T
+        q.a = {&it.u_hi, &it.u_lo, 0, 0};
+        q.b = {&it.v_hi, &it.v_lo, static_cast<int>(it.voff[j]), 0};
+        q.M = rows;
+        q.N = L;
+        q.K = kQrPanel;
+        const int64_t off = static_cast<int64_t>(row0) * x.stride(0) + c0;
+        q.c = x.data_ptr<float>() + off;
+        q.ldc = static_cast<int>(x.stride(0));
+        q.d_hi = x_hi.data_ptr<float>() + off;
+        q.d_lo = x_lo.data_ptr<float>() + off;
+        q.ldd = static_cast<int>(x.stride(0));
+        q.flags = kFlagSplitOut;
+      }
+      builder.add(q);
+    }
+    return builder.end_launch();
+  };
+  for (int j = 0; j < max_pan; ++j) {
+    fwd1[j] = stage(true, false, j);
+    fwd2[j] = stage(true, true, j);
+  }
+  for (int j = 0; j < max_pan; ++j) {
+    bwd1[j] = stage(false, false, j);
+    bwd2[j] = stage(false, true, j);
+  }
+  auto [table, tiles] = builder.finalize();
+  const auto* problems = reinterpret_cast<const GemmProblem*>(table.data_ptr());
+  const auto* tile_list = reinterpret_cast<const GemmTile*>(tiles.data_ptr());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  auto gemm = [&](const Range& r, float alpha, float beta) {
+    if (r.second <= 0) return;
+    launch_grouped_gemm(problems, tile_list + r.first, static_cast<int>(r.second), alpha, beta, /*split=*/true,
+                        status.data_ptr<int>(), sms, stream);
+  };
+
+  // Z = I (plain and split) in one launch.
+  std::vector<SymOp> eye_ops;
+  std::vector<int2> eye_chunks;
+  for (const Item& it : items) {
+    for (int which = 0; which < 2; ++which) {
+      SymOp op;
+      std::memset(&op, 0, sizeof(op));
+      op.src = it.zt.data_ptr<float>();
+      op.n = it.n;
+      op.ld_src = op.ld_dst = static_cast<int>(it.zt.stride(0));
+      op.dst_hi = which == 0 ? it.zt.data_ptr<float>() : it.zt_hi.data_ptr<float>();
+      op.dst_lo = which == 0 ? nullptr : it.zt_lo.data_ptr<float>();
+      op.a = 0.f;  // the source is not read
+      op.b = 1.f;
+      const int idx = static_cast<int>(eye_ops.size());
+      eye_ops.push_back(op);
+      for (int r = 0; r < (op.n + kSymRowsPerChunk - 1) / kSymRowsPerChunk; ++r) eye_chunks.push_back(make_int2(idx, r));
+    }
+  }
+  auto d_eye_ops = upload_bytes(eye_ops.data(), eye_ops.size() * sizeof(SymOp), device);
+  auto d_eye_chunks = upload_bytes(eye_chunks.data(), eye_chunks.size() * sizeof(int2), device);
+  launch_shift_scale_split(reinterpret_cast<const SymOp*>(d_eye_ops.data_ptr()),
+                           reinterpret_cast<const int2*>(d_eye_chunks.data_ptr()), static_cast<int>(eye_chunks.size()), stream);
+
+  for (int j = 0; j < max_pan; ++j) {
+    launch_householder_panel(panel_table + panel_range[j].first, panel_range[j].second, stream);
+    gemm(fwd1[j], 1.f, 0.f);
+    gemm(fwd2[j], -1.f, 1.f);
+  }
+  for (int j = max_pan - 1; j >= 0; --j) {
+    gemm(bwd1[j], 1.f, 0.f);
+    gemm(bwd2[j], -1.f, 1.f);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  // The launch tables and the workspace are referenced by kernels still in flight: torch's caching
+  // allocator only reuses their memory for work queued later on this same stream.
+}
+
+// Table for the per-matrix passes of the eigensolver.  Each spec: (src, dst_hi | None, dst_lo | None,
+// stats | None, a, b).
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_sym_table(const std::vector<py::tuple>& specs) {
+  std::vector<SymOp> ops(specs.size());
+  std::vector<int2> chunks;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 6, "sym spec must have 6 fields");
+    auto src = s[0].cast<torch::Tensor>();
+    TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1 && src.size(0) == src.size(1));
+    device = src.device();
+    SymOp& op = ops[i];
+    std::memset(&op, 0, sizeof(op));
+    op.src = src.data_ptr<float>();
+    op.n = static_cast<int>(src.size(0));
+    op.ld_src = static_cast<int>(src.stride(0));
+    auto hi = s[1].cast<std::optional<torch::Tensor>>();
+    auto lo = s[2].cast<std::optional<torch::Tensor>>();
+    if (hi.has_value()) {
+      TORCH_CHECK(hi->dim() == 2 && hi->stride(1) == 1 && hi->size(0) >= op.n && hi->size(1) >= op.n);
+      op.dst_hi = hi->data_ptr<float>();
+      op.ld_dst = static_cast<int>(hi->stride(0));
+    }
+    if (lo.has_value()) {
+      TORCH_CHECK(hi.has_value() && lo->stride(0) == hi->stride(0));
+      op.dst_lo = lo->data_ptr<float>();
+    }
+    auto stats = s[3].cast<std::optional<torch::Tensor>>();
+    if (stats.has_value()) {
+      TORCH_CHECK(stats->numel() >= 2 && stats->is_contiguous());
+      op.stats = fptr(stats);
+    }
+    op.a = s[4].cast<float>();
+    op.b = s[5].cast<float>();
+    for (int r = 0; r < (op.n + kSymRowsPerChunk - 1) / kSymRowsPerChunk; ++r) chunks.push_back(make_int2(static_cast<int>(i), r));
+  }
+  auto d_ops = upload_bytes(ops.data(), ops.size() * sizeof(SymOp), device);
+  auto d_chunks = upload_bytes(chunks.data(), chunks.size() * sizeof(int2), device);
+  return {d_ops, d_chunks, static_cast<int64_t>(chunks.size())};
+}
+
+void sym_measure(const torch::Tensor& ops, int64_t count) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_sym_measure(reinterpret_cast<const SymOp*>(ops.data_ptr()), static_cast<int>(count), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void sq_offdiag(const torch::Tensor& ops, int64_t count) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_sq_offdiag(reinterpret_cast<const SymOp*>(ops.data_ptr()), static_cast<int>(count), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void shift_scale_split(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_shift_scale_split(reinterpret_cast<const SymOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
+                           static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// Each spec: (src [rows, cols], dst | None, dst_hi | None, dst_lo | None); destinations are [cols, rows].
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_transpose_table(const std::vector<py::tuple>& specs) {
+  std::vector<TransposeOp> ops(specs.size());
+  std::vector<int4> tiles;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 4, "transpose spec must have 4 fields");
+    auto src = s[0].cast<torch::Tensor>();
+    TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1);
+    device = src.device();
+    TransposeOp& op = ops[i];
+    std::memset(&op, 0, sizeof(op));
+    op.src = src.data_ptr<float>();
+    op.rows = static_cast<int>(src.size(0));
+    op.cols = static_cast<int>(src.size(1));
+    op.ld_src = static_cast<int>(src.stride(0));
+    int64_t ld = -1;
+    auto take = [&](int k) -> float* {
+      auto t = s[k].cast<std::optional<torch::Tensor>>();
+      if (!t.has_value()) return nullptr;
+      TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->dim() == 2 && t->stride(1) == 1 &&
+                      t->size(0) >= op.cols && t->size(1) >= op.rows,
+                  "transpose destination too small");
+      TORCH_CHECK(ld < 0 || ld == t->stride(0), "transpose destinations must share one pitch");
+      ld = t->stride(0);
+      return t->data_ptr<float>();
+    };
+    op.dst = take(1);
+    op.dst_hi = take(2);
+    op.dst_lo = take(3);
+    TORCH_CHECK((op.dst_hi == nullptr) == (op.dst_lo == nullptr), "dst_hi and dst_lo come together");
+    TORCH_CHECK(ld > 0, "no destination");
+    op.ld_dst = static_cast<int>(ld);
+    for (int r = 0; r < (op.rows + 31) / 32; ++r)
+      for (int c = 0; c < (op.cols + 31) / 32; ++c) tiles.push_back(make_int4(static_cast<int>(i), r, c, 0));
+  }
+  auto d_ops = upload_bytes(ops.data(), ops.size() * sizeof(TransposeOp), device);
+  auto d_tiles = upload_bytes(tiles.data(), tiles.size() * sizeof(int4), device);
+  return {d_ops, d_tiles, static_cast<int64_t>(tiles.size())};
+}
+
+void transpose_split(const torch::Tensor& ops, const torch::Tensor& tiles, int64_t num_tiles) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_transpose_split(reinterpret_cast<const TransposeOp*>(ops.data_ptr()), reinterpret_cast<const int4*>(tiles.data_ptr()),
+                         static_cast<int>(num_tiles), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 void peer_copy(const torch::Tensor& table, const torch::Tensor& chunks, int64_t num_chunks) {
   if (num_chunks == 0) return;
   c10::cuda::CUDAGuard guard(table.device());
@@ -557,7 +1111,25 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("FLAG_SUMSQ") = kFlagSumSq;
   m.attr("FLAG_NO_C") = kFlagNoC;
   m.def("build_gemm_plan", &build_gemm_plan);
-  m.def("run_gemm_plan", &run_gemm_plan);
+  m.def("run_gemm_plan", &run_gemm_plan, py::arg("problems"), py::arg("tiles"), py::arg("num_tiles"), py::arg("alpha"),
+        py::arg("beta"), py::arg("split"), py::arg("status"), py::arg("gamma") = 0.0);
+  m.def("build_gemm_plans", &build_gemm_plans);
+  m.def("run_gemm_plan_range", &run_gemm_range, py::arg("problems"), py::arg("tiles"), py::arg("first_tile"),
+        py::arg("num_tiles"), py::arg("alpha"), py::arg("beta"), py::arg("split"), py::arg("status"), py::arg("gamma") = 0.0);
+  m.attr("FLAG_MIRROR") = kFlagMirror;
+  m.attr("FLAG_ADD_DIAG") = kFlagAddDiag;
+  m.attr("FLAG_TRACE") = kFlagTrace;
+  m.def("build_qr_panel_table", &build_qr_panel_table);
+  m.def("householder_panel", &householder_panel);
+  m.def("householder_qr", &householder_qr);
+  m.attr("QR_PANEL") = kQrPanel;
+  m.def("build_sym_table", &build_sym_table);
+  m.def("sym_measure", &sym_measure);
+  m.def("sq_offdiag", &sq_offdiag);
+  m.def("shift_scale_split", &shift_scale_split);
+  m.def("build_transpose_table", &build_transpose_table);
+  m.def("transpose_split", &transpose_split);
+  m.def("jacobi_eigh_into", &jacobi_eigh_into);
   m.def("run_gemm_plan_push", &run_gemm_plan_push);
   m.attr("FLAG_PEER_PUSH") = kFlagPeerPush;
   m.def("gathered_apply_scaled", &gathered_apply_scaled);

@@ -1,0 +1,308 @@
+// See eig_kernels.cuh.
+#include "eig_kernels.cuh"
+#include "ptx.cuh"
+
+namespace ob200 {
+
+namespace {
+
+constexpr int kQrWarps = kQrThreads / 32;
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+__device__ __forceinline__ void store_split(float* hi, float* lo, long long o, float x) {
+  const float h = tf32_round(x);
+  hi[o] = h;
+  lo[o] = x - h;
+}
+
+// Householder QR of one panel.  P[j * pitch + i] is entry i (counted from row c0) of panel column
+// j; it lives in shared memory when the panel fits there and is worked on in place in global
+// memory otherwise (the same code runs on a generic pointer).
+//
+// Column step j needs, for every other panel column j', the inner product of the part of column j
+// below the pivot with the same part of column j' (one block-wide reduction of up to 16 values):
+//   j' = j   sum of squares -> the reflector's beta, tau and scaling
+//   j' > j   w_j' = P[j'][j] + scale * dot: the coefficient of the update of a column still to factor
+//   j' < j   z_j' = the same expression on a stored reflector: (V^T v_j)[j'], the input of T's column j
+__global__ void __launch_bounds__(kQrThreads, 1) householder_panel_kernel(const QrPanelDesc* __restrict__ descs) {
+  extern __shared__ float qsm[];
+  __shared__ float red[kQrWarps][kQrPanel];
+  __shared__ float wsh[kQrPanel];
+  __shared__ float scal[4];
+  __shared__ float taus[kQrPanel];
+  __shared__ float zmat[kQrPanel][kQrPanel];  // zmat[j][m] = (V^T v_j)[m], m < j
+  __shared__ float tmat[kQrPanel][kQrPanel];  // T, upper triangular
+
+  const QrPanelDesc d = descs[blockIdx.x];
+  const int nb = d.c1 - d.c0;
+  const int L = d.n - d.c0;
+  if (nb <= 0 || L <= 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool in_smem = static_cast<long long>(L) * kQrPanel <= kQrSmemFloats;
+  float* gpanel = d.ct + static_cast<long long>(d.c0) * d.ld + d.c0;
+  float* P = in_smem ? qsm : gpanel;
+  const long long pitch = in_smem ? L : d.ld;
+
+  if (in_smem) {
+    for (int j = 0; j < nb; ++j)
+      for (int i = tid; i < L; i += kQrThreads) P[j * pitch + i] = gpanel[static_cast<long long>(j) * d.ld + i];
+  }
+  for (int e = tid; e < kQrPanel * kQrPanel; e += kQrThreads) {
+    zmat[e / kQrPanel][e % kQrPanel] = 0.f;
+    tmat[e / kQrPanel][e % kQrPanel] = 0.f;
+  }
+  __syncthreads();
+
+  for (int j = 0; j < nb; ++j) {
+    float acc[kQrPanel];
+#pragma unroll
+    for (int jj = 0; jj < kQrPanel; ++jj) acc[jj] = 0.f;
+    for (int i = tid; i < L; i += kQrThreads) {
+      if (i > j) {
+        const float x = P[j * pitch + i];
+#pragma unroll
+        for (int jj = 0; jj < kQrPanel; ++jj)
+          if (jj < nb) acc[jj] = fmaf(x, P[jj * pitch + i], acc[jj]);
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < kQrPanel; ++jj) {
+      const float s = warp_sum(acc[jj]);
+      if (lane == 0) red[warp][jj] = s;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      float t = 0.f;
+      if (lane < kQrPanel)
+        for (int w = 0; w < kQrWarps; ++w) t += red[w][lane];
+      const float ssq = __shfl_sync(0xffffffffu, t, j);
+      const float alpha = P[j * pitch + j];
+      float beta = alpha, tau = 0.f, scale = 0.f;
+      if (ssq > 0.f) {
+        beta = -copysignf(sqrtf(alpha * alpha + ssq), alpha);
+        tau = (beta - alpha) / beta;
+        scale = 1.f / (alpha - beta);
+      }
+      float wv = 0.f;
+      if (lane < nb && lane != j) wv = P[lane * pitch + j] + scale * t;
+      if (lane < kQrPanel) wsh[lane] = wv;
+      if (lane < j) zmat[j][lane] = wv;
+      if (lane == 0) {
+        scal[0] = tau;
+        scal[1] = scale;
+        scal[2] = beta;
+        taus[j] = tau;
+      }
+    }
+    __syncthreads();
+    const float tau = scal[0], scale = scal[1], beta = scal[2];
+    for (int i = tid; i < L; i += kQrThreads) {
+      if (i > j) {
+        const float vi = P[j * pitch + i] * scale;
+        for (int jj = j + 1; jj < nb; ++jj) P[jj * pitch + i] -= tau * wsh[jj] * vi;
+        P[j * pitch + i] = vi;
+      } else if (i == j) {
+        for (int jj = j + 1; jj < nb; ++jj) P[jj * pitch + j] -= tau * wsh[jj];
+        P[j * pitch + j] = beta;
+      }
+    }
+    // The next step's reads of other threads' entries (pivot entries, by warp 0) come after its
+    // first barrier, which every writer of this step has then passed.
+  }
+  __syncthreads();
+
+  // T: T[j][j] = tau_j, T[0:j, j] = -tau_j T[0:j, 0:j] z_j (one warp, lane = row).
+  if (warp == 0) {
+    for (int j = 0; j < nb; ++j) {
+      if (lane < j) {
+        float s = 0.f;
+        for (int m = lane; m < j; ++m) s = fmaf(tmat[lane][m], zmat[j][m], s);
+        tmat[lane][j] = -taus[j] * s;
+      } else if (lane == j) {
+        tmat[j][j] = taus[j];
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+
+  for (int i = tid; i < L; i += kQrThreads) {
+    float v[kQrPanel];
+#pragma unroll
+    for (int jj = 0; jj < kQrPanel; ++jj) {
+      float x = 0.f;
+      if (jj < nb) x = (i == jj) ? 1.f : (i > jj ? P[jj * pitch + i] : 0.f);
+      v[jj] = x;
+    }
+#pragma unroll
+    for (int jj = 0; jj < kQrPanel; ++jj) store_split(d.v_hi, d.v_lo, static_cast<long long>(i) * kQrPanel + jj, v[jj]);
+#pragma unroll
+    for (int jj = 0; jj < kQrPanel; ++jj) {
+      if (jj < nb) {
+        float ttv = 0.f, tv = 0.f;
+#pragma unroll
+        for (int m = 0; m < kQrPanel; ++m) {
+          if (m <= jj) ttv = fmaf(tmat[m][jj], v[m], ttv);
+          if (m >= jj) tv = fmaf(tmat[jj][m], v[m], tv);
+        }
+        const long long o = static_cast<long long>(jj) * d.ldw + i;  // ttv_* / tv_* point at (row c0, column c0)
+        store_split(d.ttv_hi, d.ttv_lo, o, ttv);
+        store_split(d.tv_hi, d.tv_lo, o, tv);
+      }
+    }
+  }
+  if (in_smem) {
+    for (int j = 0; j < nb; ++j)
+      for (int i = tid; i < L; i += kQrThreads) gpanel[static_cast<long long>(j) * d.ld + i] = P[j * pitch + i];
+  }
+}
+
+constexpr int kSymThreads = 512;
+
+__device__ __forceinline__ float block_sum(float x, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  x = warp_sum(x);
+  __syncthreads();  // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = x;
+  __syncthreads();
+  float t = 0.f;
+  const int warps = blockDim.x >> 5;
+  for (int w = 0; w < warps; ++w) t += scratch[w];
+  return t;
+}
+
+__global__ void __launch_bounds__(kSymThreads) sym_measure_kernel(const SymOp* __restrict__ ops) {
+  __shared__ float scratch[kSymThreads / 32];
+  const SymOp op = ops[blockIdx.x];
+  const int n = op.n;
+  float tr = 0.f;
+  for (int i = threadIdx.x; i < n; i += kSymThreads) tr += op.src[static_cast<long long>(i) * op.ld_src + i];
+  const float sigma = block_sum(tr, scratch) / static_cast<float>(n);
+  float ss = 0.f;
+  for (int i = threadIdx.x / 32; i < n; i += kSymThreads / 32) {
+    const float* row = op.src + static_cast<long long>(i) * op.ld_src;
+    float part = 0.f;
+    for (int j = threadIdx.x & 31; j < n; j += 32) {
+      const float x = row[j] - (i == j ? sigma : 0.f);
+      part = fmaf(x, x, part);
+    }
+    ss += part;
+  }
+  const float total = block_sum(ss, scratch);
+  if (threadIdx.x == 0) {
+    op.stats[0] = sigma;
+    op.stats[1] = sqrtf(total);
+  }
+}
+
+__global__ void __launch_bounds__(kSymThreads) sq_offdiag_kernel(const SymOp* __restrict__ ops) {
+  __shared__ float scratch[kSymThreads / 32];
+  const SymOp op = ops[blockIdx.x];
+  const int n = op.n;
+  float all = 0.f, diag = 0.f;
+  for (int i = threadIdx.x / 32; i < n; i += kSymThreads / 32) {
+    const float* row = op.src + static_cast<long long>(i) * op.ld_src;
+    float part = 0.f;
+    for (int j = threadIdx.x & 31; j < n; j += 32) {
+      const float x = row[j];
+      part = fmaf(x, x, part);
+      if (i == j) diag = fmaf(x, x, diag);
+    }
+    all += part;
+  }
+  const float a = block_sum(all, scratch);
+  const float dg = block_sum(diag, scratch);
+  if (threadIdx.x == 0) {
+    op.stats[0] = a;
+    op.stats[1] = dg;
+  }
+}
+
+__global__ void __launch_bounds__(256) shift_scale_split_kernel(const SymOp* __restrict__ ops,
+                                                                const int2* __restrict__ chunks, int num_chunks) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const SymOp op = ops[ref.x];
+    const int row0 = ref.y * kSymRowsPerChunk;
+    const int rows = min(kSymRowsPerChunk, op.n - row0);
+    for (int e = threadIdx.x; e < rows * op.n; e += blockDim.x) {
+      const int i = row0 + e / op.n, j = e % op.n;
+      float x = op.a != 0.f ? op.a * op.src[static_cast<long long>(i) * op.ld_src + j] : 0.f;  // a == 0: src is not read
+      if (i == j) x += op.b;
+      const long long o = static_cast<long long>(i) * op.ld_dst + j;
+      if (op.dst_lo != nullptr) {
+        store_split(op.dst_hi, op.dst_lo, o, x);
+      } else {
+        op.dst_hi[o] = x;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) transpose_split_kernel(const TransposeOp* __restrict__ ops,
+                                                              const int4* __restrict__ tiles, int num_tiles) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const int4 ref = tiles[t];
+    const TransposeOp op = ops[ref.x];
+    const int r0 = ref.y * 32, c0 = ref.z * 32;
+    for (int k = ty; k < 32; k += 8) {
+      const int r = r0 + k, c = c0 + tx;
+      tile[k][tx] = (r < op.rows && c < op.cols) ? op.src[static_cast<long long>(r) * op.ld_src + c] : 0.f;
+    }
+    __syncthreads();
+    for (int k = ty; k < 32; k += 8) {
+      const int c = c0 + k, r = r0 + tx;  // destination row c, destination column r
+      if (c < op.cols && r < op.rows) {
+        const float x = tile[tx][k];
+        const long long o = static_cast<long long>(c) * op.ld_dst + r;
+        if (op.dst != nullptr) op.dst[o] = x;
+        if (op.dst_hi != nullptr) store_split(op.dst_hi, op.dst_lo, o, x);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+void launch_householder_panel(const QrPanelDesc* descs, int count, cudaStream_t stream) {
+  if (count <= 0) return;
+  static bool configured = false;
+  constexpr int kBytes = kQrSmemFloats * 4;
+  if (!configured) {
+    cudaFuncSetAttribute(householder_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+    configured = true;
+  }
+  householder_panel_kernel<<<count, kQrThreads, kBytes, stream>>>(descs);
+}
+
+void launch_sym_measure(const SymOp* ops, int count, cudaStream_t stream) {
+  if (count <= 0) return;
+  sym_measure_kernel<<<count, kSymThreads, 0, stream>>>(ops);
+}
+
+void launch_sq_offdiag(const SymOp* ops, int count, cudaStream_t stream) {
+  if (count <= 0) return;
+  sq_offdiag_kernel<<<count, kSymThreads, 0, stream>>>(ops);
+}
+
+void launch_shift_scale_split(const SymOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  const int cap = sm_count() * 8;
+  shift_scale_split_kernel<<<num_chunks < cap ? num_chunks : cap, 256, 0, stream>>>(ops, chunks, num_chunks);
+}
+
+void launch_transpose_split(const TransposeOp* ops, const int4* tiles, int num_tiles, cudaStream_t stream) {
+  if (num_tiles <= 0) return;
+  const int cap = sm_count() * 16;
+  transpose_split_kernel<<<num_tiles < cap ? num_tiles : cap, 256, 0, stream>>>(ops, tiles, num_tiles);
+}
+
+}  // namespace ob200

@@ -306,8 +306,14 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
   }
   __syncthreads();
   // Q[i][rank(j)] = v_j[i]; lanes run over j so that the scattered destination stays within a row.
-  for (int i = warp; i < n; i += kWarps)
-    for (int j = lane; j < n; j += 32) d.q[static_cast<long long>(i) * d.ldq + rank_of[j]] = v[j * kJacobiPitch + i];
+  if (d.transposed) {
+    // Row rank(j) of q is eigenvector j: lanes run over its components.
+    for (int j = warp; j < n; j += kWarps)
+      for (int i = lane; i < n; i += 32) d.q[static_cast<long long>(rank_of[j]) * d.ldq + i] = v[j * kJacobiPitch + i];
+  } else {
+    for (int i = warp; i < n; i += kWarps)
+      for (int j = lane; j < n; j += 32) d.q[static_cast<long long>(i) * d.ldq + rank_of[j]] = v[j * kJacobiPitch + i];
+  }
   if (threadIdx.x == 0) sweeps_out[blockIdx.x] = converged ? sweep : max_sweeps + 1;
 }
 

@@ -47,7 +47,8 @@ struct JacobiDesc {
   const float* a;  // n x n, row pitch lda (symmetric)
   float* q;        // n x n, row pitch ldq: eigenvectors as columns, ascending eigenvalue order
   float* lam;      // n eigenvalues, ascending
-  int n, lda, ldq, pad_;
+  int n, lda, ldq;
+  int transposed;  // 1: eigenvectors are written as the rows of q instead
 };
 
 constexpr int kJacobiMaxN = 128;

@@ -36,7 +36,7 @@ struct Cfg {
 template <int kSplit, bool kPush>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __restrict__ tiles, int num_tiles,
-                    float alpha, float beta, int* __restrict__ status, const PeerPush push) {
+                    float alpha, float beta, float gamma, int* __restrict__ status, const PeerPush push) {
   using C = Cfg<kSplit>;
   constexpr int kStages = C::kStages;
 
@@ -94,11 +94,13 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
           }
           uint8_t* s = stage_base + stage * C::kStageBytes;
           mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d(s, &p->a_hi, &full_bar[stage], kb * kBK, tile.m0);
-          tma_load_2d(s + kTileBytesA, &p->b_hi, &full_bar[stage], kb * kBK, tile.n0);
+          const int ak = p->a_k0 + kb * kBK, bk = p->b_k0 + kb * kBK;
+          const int ar = p->a_row0 + tile.m0, br = p->b_row0 + tile.n0;
+          tma_load_2d(s, p->a_hi, &full_bar[stage], ak, ar);
+          tma_load_2d(s + kTileBytesA, p->b_hi, &full_bar[stage], bk, br);
           if (kSplit) {
-            tma_load_2d(s + kTileBytesA + kTileBytesB, &p->a_lo, &full_bar[stage], kb * kBK, tile.m0);
-            tma_load_2d(s + 2 * kTileBytesA + kTileBytesB, &p->b_lo, &full_bar[stage], kb * kBK, tile.n0);
+            tma_load_2d(s + kTileBytesA + kTileBytesB, p->a_lo, &full_bar[stage], ak, ar);
+            tma_load_2d(s + 2 * kTileBytesA + kTileBytesB, p->b_lo, &full_bar[stage], bk, br);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -174,19 +176,30 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
       if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag)) break;
       tc_fence_after_sync();
       const int row0 = tile.m0 + q * 32;
-      float sq = 0.f;
+      float sq = 0.f, tr = 0.f;
+      // Symmetric result (kFlagMirror): only entries on or above the diagonal are taken from the
+      // accumulator; every 32 x 32 chunk strictly above the diagonal is also stored transposed and
+      // the chunks on the diagonal are symmetrised, so the stored matrix is symmetric bit for bit
+      // (an antisymmetric rounding residue would be amplified by the polynomial iterations that
+      // consume these products).
+      const bool sym = (flags & kFlagMirror) != 0;
+      const bool diag_tile = sym && tile.n0 == tile.m0;
       if (row0 < M) {
 #pragma unroll 1
         for (int c = 0; c < kBN / 32; ++c) {
           const int col0 = tile.n0 + c * 32;
           if (col0 >= N) break;
           if ((flags & kFlagPackedC) && col0 + 31 < row0) continue;  // chunk strictly below the diagonal
+          if (diag_tile && c < q) continue;  // written as the transpose of chunk (c, q)
+          const bool mirror = sym && (!diag_tile || c > q);
+          const bool diag_chunk = diag_tile && c == q;
           float v[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kBN + c * 32, v);
 #pragma unroll
           for (int j = 0; j < 32; ++j) st[lane * kStagePitch + j] = v[j];
           __syncwarp();
           const int col = col0 + lane;
+          float sq_chunk = 0.f;
           if (col < N) {
             const int rows = min(32, M - row0);
             const bool packed = (flags & kFlagPackedC) != 0;
@@ -219,34 +232,82 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
               if (live) {
                 float acc = st[rr * kStagePitch + lane];
                 if (flags & kFlagSquareAcc) acc *= acc;
-                const float val = alpha * acc + beta * old[rr];
-                if (write_c) Cp[o] = val;
+                float val = alpha * acc + beta * old[rr];
+                if ((flags & kFlagAddDiag) && row == col) val += gamma;
+                if (sym) st[rr * kStagePitch + lane] = val;  // read back transposed below
+                if (!diag_chunk) {
+                  if ((flags & kFlagTrace) && row == col) tr += val;
+                  if (write_c) Cp[o] = val;
+                  if (flags & kFlagSplitOut) {
+                    const long long od = static_cast<long long>(row) * ldd + col;
+                    const float hi = tf32_round(val);
+                    Dhi[od] = hi;
+                    Dlo[od] = val - hi;
+                  }
+                  if (kPush && do_push) {
+                    // A warp stores 32 consecutive elements of one row into each rank's slot.
+                    const long long e = static_cast<long long>(row) * N + col;
+                    for (int r = 0; r < push.num_peers; ++r) {
+                      void* dst = reinterpret_cast<void*>(push.base[r] + push_offset);
+                      if (push.dtype == 1) {
+                        static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(val);
+                      } else if (push.dtype == 2) {
+                        static_cast<__half*>(dst)[e] = __float2half_rn(val);
+                      } else {
+                        static_cast<float*>(dst)[e] = val;
+                      }
+                    }
+                  }
+                  sq_chunk += val * val;
+                }
+              }
+              o += packed ? (N - row - 1) : ldc;
+            }
+          }
+          __syncwarp();
+          if (diag_chunk) {
+            // Entry (row0 + rr, col0 + lane) takes the value computed for whichever of it and its
+            // transpose lies on or above the diagonal.
+            if (col < N) {
+              const int rows = min(32, M - row0);
+              const bool write_c = !(flags & kFlagNoC);
+              for (int rr = 0; rr < rows; ++rr) {
+                const float val = lane >= rr ? st[rr * kStagePitch + lane] : st[lane * kStagePitch + rr];
+                const int row = row0 + rr;
+                if ((flags & kFlagTrace) && rr == lane) tr += val;
+                if (write_c) Cp[static_cast<long long>(row) * ldc + col] = val;
                 if (flags & kFlagSplitOut) {
                   const long long od = static_cast<long long>(row) * ldd + col;
                   const float hi = tf32_round(val);
                   Dhi[od] = hi;
                   Dlo[od] = val - hi;
                 }
-                if (kPush && do_push) {
-                  // A warp stores 32 consecutive elements of one row into each rank's slot.
-                  const long long e = static_cast<long long>(row) * N + col;
-                  for (int r = 0; r < push.num_peers; ++r) {
-                    void* dst = reinterpret_cast<void*>(push.base[r] + push_offset);
-                    if (push.dtype == 1) {
-                      static_cast<__nv_bfloat16*>(dst)[e] = __float2bfloat16_rn(val);
-                    } else if (push.dtype == 2) {
-                      static_cast<__half*>(dst)[e] = __float2half_rn(val);
-                    } else {
-                      static_cast<float*>(dst)[e] = val;
-                    }
-                  }
-                }
-                sq += val * val;
+                sq_chunk += val * val;
               }
-              o += packed ? (N - row - 1) : ldc;
             }
+            __syncwarp();
+          } else if (mirror) {
+            // Element (row0 + lane, col0 + j) goes to (col0 + j, row0 + lane): lanes run along the
+            // destination row, and the odd staging pitch keeps the column read conflict-free.
+            const int rows = min(32, M - row0), cols = min(32, N - col0);
+            if (lane < rows) {
+              const bool write_c = !(flags & kFlagNoC);
+              for (int j = 0; j < cols; ++j) {
+                const float val = st[lane * kStagePitch + j];
+                const int drow = col0 + j, dcol = row0 + lane;
+                if (write_c) Cp[static_cast<long long>(drow) * ldc + dcol] = val;
+                if (flags & kFlagSplitOut) {
+                  const long long od = static_cast<long long>(drow) * ldd + dcol;
+                  const float hi = tf32_round(val);
+                  Dhi[od] = hi;
+                  Dlo[od] = val - hi;
+                }
+              }
+            }
+            __syncwarp();
+            sq_chunk *= 2.f;
           }
-          __syncwarp();
+          sq += sq_chunk;
         }
       }
       tc_fence_before_sync();
@@ -255,6 +316,11 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
         if (lane == 0 && sq != 0.f) atomicAdd(p->sumsq, sq);
+      }
+      if (flags & kFlagTrace) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tr += __shfl_xor_sync(0xffffffffu, tr, o);
+        if (lane == 0 && tr != 0.f) atomicAdd(p->sumsq + 1, tr);
       }
     }
   }
@@ -278,7 +344,7 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
 
 template <int kSplit, bool kPush>
 void launch_impl(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
-                 int* status, int max_ctas, cudaStream_t stream, const PeerPush& push) {
+                 float gamma, int* status, int max_ctas, cudaStream_t stream, const PeerPush& push) {
   using C = Cfg<kSplit>;
   static bool configured = false;
   if (!configured) {
@@ -287,23 +353,23 @@ void launch_impl(const GemmProblem* problems, const GemmTile* tiles, int num_til
   }
   const int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
   grouped_gemm_kernel<kSplit, kPush><<<grid, kThreads, C::kSmemBytes, stream>>>(problems, tiles, num_tiles, alpha,
-                                                                               beta, status, push);
+                                                                               beta, gamma, status, push);
 }
 
 }  // namespace
 
 void launch_grouped_gemm(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
-                         bool split, int* status, int max_ctas, cudaStream_t stream, const PeerPush* push) {
+                         bool split, int* status, int max_ctas, cudaStream_t stream, const PeerPush* push, float gamma) {
   if (num_tiles <= 0) return;
   PeerPush none{};
   const PeerPush& pp = push != nullptr ? *push : none;
   const bool pushing = pp.num_peers > 0;
   if (split) {
-    if (pushing) launch_impl<1, true>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
-    else launch_impl<1, false>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
+    if (pushing) launch_impl<1, true>(problems, tiles, num_tiles, alpha, beta, gamma, status, max_ctas, stream, pp);
+    else launch_impl<1, false>(problems, tiles, num_tiles, alpha, beta, gamma, status, max_ctas, stream, pp);
   } else {
-    if (pushing) launch_impl<0, true>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
-    else launch_impl<0, false>(problems, tiles, num_tiles, alpha, beta, status, max_ctas, stream, pp);
+    if (pushing) launch_impl<0, true>(problems, tiles, num_tiles, alpha, beta, gamma, status, max_ctas, stream, pp);
+    else launch_impl<0, false>(problems, tiles, num_tiles, alpha, beta, gamma, status, max_ctas, stream, pp);
   }
 }
 

@@ -25,6 +25,14 @@
 //                   buffer over NVLink (fused all-gather of the search directions)
 //   kFlagSquareAcc  the accumulator is squared before alpha/beta are applied: with C the running
 //                   second moment V this is V <- beta2 V + w (Q_L^T G Q_R)^2 fused into the projection
+//   kFlagMirror     the result is symmetric (products of commuting symmetric matrices, Grams): the
+//                   tile list holds only tiles on or above the diagonal and every tile strictly
+//                   above it is also stored transposed (C, d_hi, d_lo), so the full matrix is an
+//                   operand of the next product at half the tensor-core work; sumsq counts such
+//                   a tile twice
+//   kFlagAddDiag    gamma (a launch scalar) is added to the diagonal entries: C = alpha A B^T +
+//                   beta C + gamma I, the polynomial steps of the matrix sign iteration
+//   kFlagTrace      add the diagonal entries of the result to sumsq[1] (trace)
 #pragma once
 
 #include <cstdint>
@@ -37,6 +45,9 @@ constexpr int kFlagSplitOut = 2;
 constexpr int kFlagSumSq = 4;
 constexpr int kFlagNoC = 8;
 constexpr int kFlagSquareAcc = 16;  // C = beta * C + alpha * acc^2 (second moment in the eigenbasis)
+constexpr int kFlagMirror = 64;     // symmetric result: upper tiles computed, mirrored into the lower triangle
+constexpr int kFlagAddDiag = 128;   // + gamma on the diagonal
+constexpr int kFlagTrace = 256;     // sumsq[1] += trace of the result
 constexpr int kFlagPeerPush = 32;   // also store the result, cast to the communication dtype, into the
                                     // problem's slot of every rank's gather buffer (PeerPush): the
                                     // all-gather of the search directions happens tile by tile from
@@ -45,7 +56,15 @@ constexpr int kFlagPeerPush = 32;   // also store the result, cast to the commun
 constexpr int kErrPipelineTimeout = 1;  // a bounded mbarrier wait expired
 
 struct alignas(128) GemmProblem {
-  CUtensorMap a_hi, a_lo, b_hi, b_lo;  // 2-D maps: dim0 = K (contiguous), dim1 = rows
+  // 2-D tensor maps (dim0 = K, contiguous; dim1 = rows) of the arrays the operands are views of.
+  // They live in device memory next to the problem table; several problems (the panels of a
+  // blocked factorisation) may share one map and differ only in the view origin below.
+  const CUtensorMap* a_hi;
+  const CUtensorMap* a_lo;
+  const CUtensorMap* b_hi;
+  const CUtensorMap* b_lo;
+  int a_row0, a_k0;  // origin of the A view inside its array (a_k0 a multiple of 4: TMA alignment)
+  int b_row0, b_k0;  // a view that does not end where its array ends along K must have K % kBK == 0
   float* c;
   float* d_hi;
   float* d_lo;
@@ -79,6 +98,7 @@ constexpr int kBK = 32;  // fp32 elements = 128 bytes = one swizzle row
 
 // Host-side launch.  `status` is a device int the kernel writes a non-zero error code to.
 void launch_grouped_gemm(const GemmProblem* problems, const GemmTile* tiles, int num_tiles, float alpha, float beta,
-                         bool split, int* status, int max_ctas, cudaStream_t stream, const PeerPush* push = nullptr);
+                         bool split, int* status, int max_ctas, cudaStream_t stream, const PeerPush* push = nullptr,
+                         float gamma = 0.f);
 
 }  // namespace ob200

@@ -1,0 +1,88 @@
+"""The divide-and-conquer eigensolver through its plain-tensor backend (runs on CPU): the same
+driver, split-point, retry and closing logic that the sm_100a backend executes."""
+
+import pytest
+import torch
+
+from optimizers_b200.matrix.eigh_dc import SIGN_SCHEDULE, TorchBackend, eigh_divide_and_conquer
+
+
+def _orth(d, gen):
+    q, _ = torch.linalg.qr(torch.randn(d, d, dtype=torch.float64, generator=gen))
+    return q
+
+
+def _matrix(kind, d, gen):
+    if kind == "lowrank":
+        G = torch.randn(d, d // 3, dtype=torch.float64, generator=gen)
+        return G @ G.T / d
+    lam = {
+        "power": 1.0 / torch.arange(1, d + 1, dtype=torch.float64) ** 2,
+        "uniform": torch.rand(d, dtype=torch.float64, generator=gen),
+        "clustered": torch.cat([torch.ones(d // 2), torch.full((d - d // 2,), 1e-3)]).double(),
+        "scalar": torch.full((d,), 0.37, dtype=torch.float64),
+    }[kind]
+    q = _orth(d, gen)
+    return (q * lam) @ q.T
+
+
+def test_sign_schedule_maps_the_unit_interval_to_one():
+    x = torch.cat([torch.logspace(-7, 0, 2001, dtype=torch.float64), torch.linspace(0.9, 1.0005, 200, dtype=torch.float64)])
+    for a, b, c in SIGN_SCHEDULE:
+        x = a * x + b * x**3 + c * x**5
+        assert x.max() < 1.0 + 1e-6 and x.min() > 0.0  # never leaves (0, 1]: no blow-up, no sign change
+    for a, b, c in SIGN_SCHEDULE[:14]:
+        t = torch.linspace(0, 0.5, 501, dtype=torch.float64)
+        assert torch.all(a + 3 * b * t**2 + 5 * c * t**4 >= -1e-9)  # increasing until the band [0.5, 1]
+    assert (x - 1).abs().max() < 1e-8
+
+
+@pytest.mark.parametrize("kind", ["power", "uniform", "clustered", "lowrank", "scalar"])
+def test_divide_and_conquer_matches_fp64_eigh(kind):
+    gen = torch.Generator().manual_seed(3)
+    d = 200
+    A64 = _matrix(kind, d, gen)
+    lams, vecs, info = eigh_divide_and_conquer(TorchBackend(torch.device("cpu")), [A64.float()], leaf=32)
+    assert info["failed"] == []
+    lam, Q = lams[0].double(), vecs[0].double()
+    ref = torch.linalg.eigvalsh(A64)
+    scale = float(ref.abs().max())
+    assert torch.all(lam[1:] >= lam[:-1])  # ascending
+    assert float((lam - ref).abs().max()) <= 2e-6 * scale
+    assert float(torch.linalg.norm(Q.T @ Q - torch.eye(d, dtype=torch.float64))) < 2e-4
+    assert float(torch.linalg.norm((Q * lam) @ Q.T - A64)) <= 3e-4 * float(torch.linalg.norm(A64))
+
+
+def test_batch_of_mixed_sizes_and_small_roots():
+    gen = torch.Generator().manual_seed(5)
+    mats = [_matrix("power", 150, gen), _matrix("uniform", 20, gen), _matrix("lowrank", 97, gen)]
+    lams, vecs, info = eigh_divide_and_conquer(TorchBackend(torch.device("cpu")), [m.float() for m in mats], leaf=32)
+    assert info["failed"] == []
+    for A, lam, Q in zip(mats, lams, vecs):
+        ref = torch.linalg.eigvalsh(A)
+        assert float((lam.double() - ref).abs().max()) <= 2e-6 * float(ref.abs().max())
+        assert Q.shape == A.shape
+
+
+def test_unconverged_sign_is_retried_then_reported(monkeypatch):
+    """A sign iteration that never yields a projector: the root is given up after the retries and
+    reported, the other matrix of the batch is still solved."""
+    gen = torch.Generator().manual_seed(7)
+    mats = [_matrix("uniform", 80, gen).float(), _matrix("power", 80, gen).float()]
+    backend = TorchBackend(torch.device("cpu"))
+    original = backend.sign_projector
+    attempts = []
+
+    def broken(subs):
+        original(subs)
+        for s in subs:
+            if s.root == 0:
+                attempts.append(s.attempt)
+                s.idem_err = 1.0  # pretend an eigenvalue sits on the split point
+
+    monkeypatch.setattr(backend, "sign_projector", broken)
+    lams, vecs, info = eigh_divide_and_conquer(backend, mats, leaf=32)
+    assert info["failed"] == [0] and lams[0] is None and vecs[0] is None
+    assert attempts[:3] == [0, 1, 2]
+    ref = torch.linalg.eigvalsh(mats[1].double())
+    assert float((lams[1].double() - ref).abs().max()) <= 2e-6 * float(ref.abs().max())
