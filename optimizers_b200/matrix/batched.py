@@ -5,10 +5,12 @@ per factor.  Here all factors of a refresh are processed together:
 
 1. one pass prepares the bias-corrected (optionally trace-scaled) factor matrices and a single
    device->host read checks all of them for NaN/Inf;
-2. the symmetric eigendecompositions run concurrently on a pool of CUDA streams, one Python
-   thread per stream (``torch.linalg.eigh`` blocks its calling thread on an error code, so
-   threads, not just streams, are needed for overlap); the eigenvalue stabilisation and the
-   scaling ``Q·diag(λ^(-1/p))`` run on the same stream without host synchronisation;
+2. the symmetric eigendecompositions run batched on this framework's own kernels: factors up to
+   128 x 128 in one launch of the shared-memory Jacobi kernel, larger ones by the spectral
+   divide-and-conquer solver of ``eigh_dc`` (tensor-core products, Householder panels, Jacobi
+   leaves); a matrix either gives up on goes to ``torch.linalg.eigh`` on a pool of CUDA streams,
+   one Python thread per stream, which is also where the double-precision retry lives; the
+   eigenvalue stabilisation and the scaling ``Q·diag(λ^(-1/p))`` need no host synchronisation;
 3. the reconstruction ``X = (Q·λ^(-1/p)) Qᵀ`` of every factor is one grouped tcgen05 launch;
 4. the packed checkpoint state is refreshed from the result, a second single read checks it, and
    the caller rebuilds the (hi, lo) operand mirrors from the state.
@@ -73,6 +75,47 @@ def _all_finite(tensors: list[Tensor]) -> list[bool]:
     return torch.isfinite(torch.stack(torch._foreach_norm(tensors, float("inf")))).cpu().tolist()
 
 
+# Sum of d^2 over the factors advanced together by the divide-and-conquer eigensolver (its
+# workspace is about 25 arrays of that size); OB200_EIGH_CHUNK_ELEMS overrides.
+_DC_CHUNK_ELEMS = int(_os.environ.get("OB200_EIGH_CHUNK_ELEMS", str(96 * 1024 * 1024)))
+# OB200_EIGH=library sends every factor larger than the Jacobi kernel's limit to the library eigensolver.
+_DC_ENABLED = _os.environ.get("OB200_EIGH", "native") != "library"
+
+
+def native_eigh(ext: Any, mats: list[Tensor], status: Tensor) -> list[tuple[Tensor, Tensor] | None]:
+    """Eigendecompositions of symmetric fp32 matrices larger than the Jacobi kernel's limit with the
+    divide-and-conquer solver on the tensor cores, in chunks of bounded workspace, largest first.
+    An entry is ``None`` where the solver gave the matrix up (the caller falls back to the library)."""
+    from optimizers_b200.matrix.eigh_dc import NativeBackend, eigh_divide_and_conquer
+
+    out: list[tuple[Tensor, Tensor] | None] = [None] * len(mats)
+    if not mats or not _DC_ENABLED:
+        return out
+    order = sorted(range(len(mats)), key=lambda i: -mats[i].shape[0])
+    chunks: list[list[int]] = [[]]
+    size = 0
+    for i in order:
+        d2 = mats[i].shape[0] ** 2
+        if chunks[-1] and size + d2 > _DC_CHUNK_ELEMS:
+            chunks.append([])
+            size = 0
+        chunks[-1].append(i)
+        size += d2
+    for chunk in chunks:
+        backend = NativeBackend(ext, mats[chunk[0]].device, status)
+        lams, vecs, info = eigh_divide_and_conquer(backend, [mats[i] for i in chunk])
+        for i, lam, Q in zip(chunk, lams, vecs, strict=True):
+            if lam is not None:
+                out[i] = (lam, Q)
+        given_up = sorted(set(info["failed"]) | set(backend.failed_in_finish))
+        if given_up:
+            logger.warning(
+                "The divide-and-conquer eigensolver gave up on %d of %d matrices; the library eigensolver takes them.",
+                len(given_up), len(chunk),
+            )
+    return out
+
+
 class _Item:
     __slots__ = ("block", "k", "A", "root", "qs_hi", "qs_lo", "q_hi", "q_lo", "error", "done", "lam", "Q")
 
@@ -128,7 +171,12 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
     # 2. eigendecompositions on the stream pool (largest first for balance)
     ready = torch.cuda.Event()
     ready.record(main)
-    executor, streams = _pool(device)
+    lazy_pool: list = []  # the stream pool is only set up when a factor falls back to the library
+
+    def pool():
+        if not lazy_pool:
+            lazy_pool.extend(_pool(device))
+        return lazy_pool
 
     def finish(it: _Item, lam: Tensor, Q: Tensor) -> None:
         """Eigenpairs -> the two GEMM operands of the reconstruction, (Q s) and Q, as (hi, lo) pairs."""
@@ -156,7 +204,7 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
     def work(it: _Item, slot: int) -> None:
         kf = it.block.factors
         cfg = kf.amortized_computation_config  # EigenConfig, or EighEigendecompositionConfig (eigendecomposed)
-        stream = streams[slot]
+        stream = pool()[1][slot]
         with torch.cuda.device(device), torch.cuda.stream(stream):
             stream.wait_event(ready)
             try:
@@ -241,8 +289,31 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
         pooled = [i for i in pooled if i not in done_here]
         ready.record(main)
 
+    # Larger factors: the batched divide-and-conquer eigensolver; the library takes what it gives up.
+    large = [i for i in pooled if items[i].A.shape[0] > ext.JACOBI_MAX_N and items[i].A.dtype == torch.float32]
+    if large:
+        ridged = []
+        for i in large:
+            kf = items[i].block.factors
+            stability = kf.amortized_computation_config.rank_deficient_stability_config
+            ridged.append(mf._ridge(items[i].A, kf.epsilon * getattr(stability, "perturb_before_computation", 0)))
+        solved = native_eigh(ext, ridged, status)
+        done_here = set()
+        for i, pair in zip(large, solved, strict=True):
+            if pair is None:
+                continue
+            try:
+                finish(items[i], *pair)
+            except Exception as exception:
+                items[i].error = exception
+            items[i].done = torch.cuda.Event()
+            items[i].done.record(main)
+            done_here.add(i)
+        pooled = [i for i in pooled if i not in done_here]
+        ready.record(main)
+
     order = sorted(pooled, key=lambda i: -items[i].A.shape[0])
-    futures = [executor.submit(work, items[i], n % _POOL_SIZE) for n, i in enumerate(order)]
+    futures = [pool()[0].submit(work, items[i], n % _POOL_SIZE) for n, i in enumerate(order)]
     for f in futures:
         f.result()
     for it in items:
@@ -717,11 +788,16 @@ def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | flo
             )
     ready = torch.cuda.Event()
     ready.record(main)
-    executor, streams = _pool(device)
+    lazy_pool: list = []  # the stream pool is only set up when a factor falls back to the library
+
+    def pool():
+        if not lazy_pool:
+            lazy_pool.extend(_pool(device))
+        return lazy_pool
 
     def work(it: _Item, slot: int) -> None:
         kf = it.block.factors
-        stream = streams[slot]
+        stream = pool()[1][slot]
         with torch.cuda.device(device), torch.cuda.stream(stream):
             stream.wait_event(ready)
             old_q = kf.factor_matrices_eigenvectors[it.k]
@@ -761,8 +837,30 @@ def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | flo
                 done_here.add(i)
             pooled = [i for i in pooled if i not in done_here]
             ready.record(main)
+        large = [i for i in pooled if items[i].A.shape[0] > ext.JACOBI_MAX_N and items[i].A.dtype == torch.float32]
+        if large:
+            stability = cfg0.rank_deficient_stability_config
+            ridged = [
+                mf._ridge(items[i].A, items[i].block.factors.epsilon * getattr(stability, "perturb_before_computation", 0))
+                for i in large
+            ]
+            status = torch.zeros(1, dtype=torch.int32, device=device)
+            solved = native_eigh(ext, ridged, status)
+            done_here = set()
+            for i, pair in zip(large, solved, strict=True):
+                if pair is None:
+                    continue
+                it = items[i]
+                it.q_hi = pair[1].to(dtype=it.block.factors.factor_matrices_eigenvectors[it.k].dtype)
+                it.done = torch.cuda.Event()
+                it.done.record(main)
+                done_here.add(i)
+            pooled = [i for i in pooled if i not in done_here]
+            ready.record(main)
+            if int(status.item()) & 1:
+                raise RuntimeError("grouped GEMM pipeline wait timed out (device-side bounded wait expired)")
     order = sorted(pooled, key=lambda i: -items[i].A.shape[0])
-    futures = [executor.submit(work, items[i], n % _POOL_SIZE) for n, i in enumerate(order)]
+    futures = [pool()[0].submit(work, items[i], n % _POOL_SIZE) for n, i in enumerate(order)]
     for f in futures:
         f.result()
     for it in items:

@@ -301,10 +301,12 @@ class _Mat:
     def __init__(self, rows: int, cols: int, device: torch.device, plain: bool = True, pair: bool = True) -> None:
         self.rows, self.cols = rows, cols
         ld = _pad4(cols)
-        mk = lambda: torch.empty(rows, ld, device=device, dtype=torch.float32)[:, :cols]  # noqa: E731
-        self.plain = mk() if plain else None
-        self.hi = mk() if pair else None
-        self.lo = mk() if pair else None
+        count = int(plain) + 2 * int(pair)
+        # one allocation for the arrays of this matrix; each array starts on a 16-byte boundary
+        block = torch.empty(count * rows * ld, device=device, dtype=torch.float32)
+        views = [torch.as_strided(block, (rows, cols), (ld, 1), k * rows * ld) for k in range(count)]
+        self.plain = views.pop(0) if plain else None
+        self.hi, self.lo = (views[0], views[1]) if pair else (None, None)
 
 
 _OMEGA_CACHE: dict[tuple, _Mat] = {}
@@ -438,12 +440,12 @@ class NativeBackend:
         for s in subs:
             k, n = s.rank, s.n
             P = s.extra.pop("P")
-            Yt = _Mat(k, n, dev)  # rows: the columns of P Omega
+            Yt = _Mat(k, n, dev, pair=False)  # rows: the columns of P Omega
             Zt = _Mat(n, n, dev)
             s.extra["Qt"] = Zt
-            g.append((om.hi, om.lo, P.hi, P.lo, Yt.plain, Yt.hi, Yt.lo, None, Yt.plain.stride(0), Yt.hi.stride(0),
-                      ext.FLAG_SPLIT_OUT, False, None, (0, 0, 0, 0, k, n, n)))
-            qr_specs.append((Yt.plain, Yt.hi, Yt.lo, n, k, Zt.plain, Zt.hi, Zt.lo))
+            g.append((om.hi, om.lo, P.hi, P.lo, Yt.plain, None, None, None, Yt.plain.stride(0), 0,
+                      0, False, None, (0, 0, 0, 0, k, n, n)))
+            qr_specs.append((Yt.plain, n, k, Zt.plain, Zt.hi, Zt.lo))
             s.extra["P_keep"] = P
         # the Omega view ends before its array along K unless n == dmax: K = n must then be a multiple of 32;
         # otherwise fall back to a sliced operand (its own tensor map)
@@ -455,21 +457,21 @@ class NativeBackend:
             else:
                 fixed.append((om.hi[:k, :n], om.lo[:k, :n]) + spec[2:13] + (None,))
         self._gemm(fixed)
-        ext.householder_qr(qr_specs, self.status)
+        ext.householder_qr(qr_specs)
         for _ in range(self.range_passes - 1):
             # One more pass from the orthonormal basis just found: Y <- P V1, whose conditioning is 1.
             g, qr_specs = [], []
             for s in subs:
                 k, n = s.rank, s.n
                 P, Zt_old = s.extra["P_keep"], s.extra["Qt"]
-                Yt, Zt = _Mat(k, n, dev), _Mat(n, n, dev)
+                Yt, Zt = _Mat(k, n, dev, pair=False), _Mat(n, n, dev)
                 v1 = _Mat.__new__(_Mat)
                 v1.rows, v1.cols, v1.plain, v1.hi, v1.lo = k, n, None, Zt_old.hi[:k], Zt_old.lo[:k]
-                g.append(self._spec(v1, P, Yt, c=Yt.plain))
-                qr_specs.append((Yt.plain, Yt.hi, Yt.lo, n, k, Zt.plain, Zt.hi, Zt.lo))
+                g.append(self._spec(v1, P, None, c=Yt.plain))
+                qr_specs.append((Yt.plain, n, k, Zt.plain, Zt.hi, Zt.lo))
                 s.extra["Qt"] = Zt
             self._gemm(g)
-            ext.householder_qr(qr_specs, self.status)
+            ext.householder_qr(qr_specs)
         for s in subs:
             s.extra.pop("P_keep")
 

@@ -72,10 +72,13 @@ float* fptr(const std::optional<torch::Tensor>& t) {
   return t->data_ptr<float>();
 }
 
+// Host table -> device, asynchronously on the current stream: the staging buffer is pinned and
+// torch's host allocator keeps it alive until the copy has run, so building a launch table never
+// drains the stream.
 torch::Tensor upload_bytes(const void* src, size_t bytes, const torch::Device& device) {
-  auto host = torch::empty({static_cast<int64_t>(std::max<size_t>(bytes, 1))}, torch::dtype(torch::kUInt8));
+  auto host = torch::empty({static_cast<int64_t>(std::max<size_t>(bytes, 1))}, torch::dtype(torch::kUInt8).pinned_memory(true));
   std::memcpy(host.data_ptr(), src, bytes);
-  return host.to(device);
+  return host.to(device, /*non_blocking=*/true);
 }
 
 // Host-side assembly of grouped-GEMM launch tables.  Problems of any number of launches go into
@@ -200,10 +203,10 @@ class PlanBuilder {
       p.b_hi = dev_maps + ix[2];
       p.b_lo = dev_maps + (ix[3] >= 0 ? ix[3] : ix[2]);
     }
-    auto host = torch::empty({static_cast<int64_t>(table_bytes + map_bytes)}, torch::dtype(torch::kUInt8));
+    auto host = torch::empty({static_cast<int64_t>(table_bytes + map_bytes)}, torch::dtype(torch::kUInt8).pinned_memory(true));
     std::memcpy(host.data_ptr(), problems_.data(), table_bytes);
     std::memcpy(static_cast<uint8_t*>(host.data_ptr()) + table_bytes, maps_.data(), map_bytes);
-    buffer.copy_(host);
+    buffer.copy_(host, /*non_blocking=*/true);
     auto d_tiles = upload_bytes(tiles_.data(), tiles_.size() * sizeof(GemmTile), device_);
     return {buffer, d_tiles};
   }
@@ -730,15 +733,14 @@ torch::Tensor jacobi_eigh_into(const std::vector<torch::Tensor>& mats, const std
   return sweeps;
 }
 
-// Panels of the blocked Householder QR.  Each spec: (ct, n, c0, c1, v_hi, v_lo, ttv_hi, ttv_lo, tv_hi, tv_lo)
-// with ct the transposed storage (rows are columns of the factored matrix; ct.stride(0) is the pitch),
-// v_* of shape [n - c0, QR_PANEL] contiguous and ttv_* / tv_* of shape [c1 - c0, n - c0] with a common pitch.
+// Panels of the blocked Householder QR, for driving the panel kernel on its own.
+// Each spec: (ct, n, c0, c1, vt, ttv, tv) with vt / ttv / tv of shape [QR_PANEL, n - c0] and one pitch.
 torch::Tensor build_qr_panel_table(const std::vector<py::tuple>& specs) {
   std::vector<QrPanelDesc> descs(specs.size());
   torch::Device device(torch::kCPU);
   for (size_t i = 0; i < specs.size(); ++i) {
     const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 10, "QR panel spec must have 10 fields");
+    TORCH_CHECK(s.size() == 7, "QR panel spec must have 7 fields");
     auto ct = s[0].cast<torch::Tensor>();
     TORCH_CHECK(ct.is_cuda() && ct.scalar_type() == torch::kFloat32 && ct.dim() == 2 && ct.stride(1) == 1);
     device = ct.device();
@@ -751,25 +753,20 @@ torch::Tensor build_qr_panel_table(const std::vector<py::tuple>& specs) {
     d.c1 = s[3].cast<int>();
     TORCH_CHECK(d.c0 >= 0 && d.c1 > d.c0 && d.c1 - d.c0 <= kQrPanel && d.c1 <= d.n && d.c1 <= ct.size(0) && d.n <= ct.size(1),
                 "QR panel bounds");
-    const int L = d.n - d.c0, nb = d.c1 - d.c0;
-    auto get = [&](int k, int64_t rows, int64_t cols) {
+    const int L = d.n - d.c0;
+    auto get = [&](int k) {
       auto t = s[k].cast<torch::Tensor>();
       TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.dim() == 2 && t.stride(1) == 1 &&
-                      t.size(0) >= rows && t.size(1) >= cols,
+                      t.size(0) >= kQrPanel && t.size(1) >= L,
                   "QR panel operand ", k, " too small");
       return t;
     };
-    auto v_hi = get(4, L, kQrPanel), v_lo = get(5, L, kQrPanel);
-    TORCH_CHECK(v_hi.stride(0) == kQrPanel && v_lo.stride(0) == kQrPanel, "V must have pitch QR_PANEL");
-    auto ttv_hi = get(6, nb, L), ttv_lo = get(7, nb, L), tv_hi = get(8, nb, L), tv_lo = get(9, nb, L);
-    d.ldw = static_cast<int>(ttv_hi.stride(0));
-    TORCH_CHECK(ttv_lo.stride(0) == d.ldw && tv_hi.stride(0) == d.ldw && tv_lo.stride(0) == d.ldw, "common pitch");
-    d.v_hi = v_hi.data_ptr<float>();
-    d.v_lo = v_lo.data_ptr<float>();
-    d.ttv_hi = ttv_hi.data_ptr<float>();
-    d.ttv_lo = ttv_lo.data_ptr<float>();
-    d.tv_hi = tv_hi.data_ptr<float>();
-    d.tv_lo = tv_lo.data_ptr<float>();
+    auto vt = get(4), ttv = get(5), tv = get(6);
+    d.ldw = static_cast<int>(vt.stride(0));
+    TORCH_CHECK(ttv.stride(0) == d.ldw && tv.stride(0) == d.ldw, "common pitch");
+    d.vt = vt.data_ptr<float>();
+    d.ttv = ttv.data_ptr<float>();
+    d.tv = tv.data_ptr<float>();
   }
   return upload_bytes(descs.data(), descs.size() * sizeof(QrPanelDesc), device);
 }
@@ -783,48 +780,43 @@ void householder_panel(const torch::Tensor& table, int64_t count) {
 
 // Blocked Householder QR of a batch of matrices, entirely on the device and without host
 // synchronisation: for every panel of kQrPanel columns one launch of the panel kernel over all
-// matrices that still have such a panel, then two grouped tensor-core GEMM launches that apply the
-// block reflector to the remaining columns (C <- C - (C V T) V^T in the transposed storage); a
-// second sweep over the panels in reverse accumulates Q^T the same way, touching only the trailing
-// block each reflector acts on.  All launch tables are assembled here and uploaded once.
+// matrices that still have such a panel, then one launch of the block-reflector kernel that
+// applies it to the remaining columns (C <- C - (C V T) V^T in the transposed storage); a second
+// sweep over the panels in reverse accumulates Q^T the same way, touching only the trailing block
+// each reflector acts on.  All launch tables are assembled here and uploaded once.
 //
-// Each spec: (ct, ct_hi, ct_lo, n, k, zt, zt_hi, zt_lo)
-//   ct, ct_hi, ct_lo  [>= k, n] views (row pitch a multiple of 4): row c is column c of the n x k matrix
-//                     to factor, plain and as a tf32 (hi, lo) pair; overwritten (R and reflectors)
-//   zt, zt_hi, zt_lo  [n, n] views: receive Q^T of the full n x n orthogonal factor, plain and split;
-//                     its first k rows span the columns of the matrix, the others their complement
+// Each spec: (ct, n, k, zt, zt_hi, zt_lo)
+//   ct                [>= k, n] view (row pitch a multiple of 4): row c is column c of the n x k matrix
+//                     to factor; overwritten (R and reflectors, LAPACK geqrf layout transposed)
+//   zt, zt_hi, zt_lo  [n, n] views of one pitch: receive Q^T of the full n x n orthogonal factor, plain
+//                     and as a tf32 (hi, lo) pair; its first k rows span the columns of the matrix, the
+//                     others their complement
 // Replaces torch.linalg.qr (cuSOLVER geqrf + orgqr) of the reference's QR iteration
 // (distributed_shampoo/preconditioner/matrix_functions.py:843).
-void householder_qr(const std::vector<py::tuple>& specs, torch::Tensor status) {
+void householder_qr(const std::vector<py::tuple>& specs) {
   TORCH_CHECK(!specs.empty(), "householder_qr: empty batch");
   struct Item {
-    torch::Tensor ct, ct_hi, ct_lo, zt, zt_hi, zt_lo;
-    torch::Tensor v_hi, v_lo, ttv_hi, ttv_lo, tv_hi, tv_lo, u_hi, u_lo;
-    torch::Tensor ttv_hi_v, ttv_lo_v, tv_hi_v, tv_lo_v;  // [k16, n] views of the padded arrays
+    torch::Tensor ct, zt, zt_hi, zt_lo, vt, ttv, tv;
     int n = 0, k = 0, npan = 0;
-    std::vector<int64_t> voff;  // first row of panel j inside v_hi / v_lo
   };
   std::vector<Item> items(specs.size());
   int max_pan = 0;
   torch::Device device(torch::kCPU);
   for (size_t i = 0; i < specs.size(); ++i) {
     const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 8, "householder_qr spec must have 8 fields");
+    TORCH_CHECK(s.size() == 6, "householder_qr spec must have 6 fields");
     Item& it = items[i];
     it.ct = s[0].cast<torch::Tensor>();
-    it.ct_hi = s[1].cast<torch::Tensor>();
-    it.ct_lo = s[2].cast<torch::Tensor>();
-    it.n = s[3].cast<int>();
-    it.k = s[4].cast<int>();
-    it.zt = s[5].cast<torch::Tensor>();
-    it.zt_hi = s[6].cast<torch::Tensor>();
-    it.zt_lo = s[7].cast<torch::Tensor>();
+    it.n = s[1].cast<int>();
+    it.k = s[2].cast<int>();
+    it.zt = s[3].cast<torch::Tensor>();
+    it.zt_hi = s[4].cast<torch::Tensor>();
+    it.zt_lo = s[5].cast<torch::Tensor>();
     TORCH_CHECK(it.k >= 1 && it.k <= it.n, "householder_qr: need 1 <= k <= n");
-    for (const torch::Tensor* t : {&it.ct, &it.ct_hi, &it.ct_lo}) {
-      TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->dim() == 2 && t->stride(1) == 1 &&
-                      t->size(0) >= it.k && t->size(1) == it.n && t->stride(0) == it.ct.stride(0),
-                  "householder_qr: ct arrays must be [>= k, n] fp32 views with one pitch");
-    }
+    TORCH_CHECK(it.n <= kReflectSmemFloats, "householder_qr: n too large for the row-tile kernel");
+    TORCH_CHECK(it.ct.is_cuda() && it.ct.scalar_type() == torch::kFloat32 && it.ct.dim() == 2 && it.ct.stride(1) == 1 &&
+                    it.ct.size(0) >= it.k && it.ct.size(1) == it.n,
+                "householder_qr: ct must be a [>= k, n] fp32 view");
     for (const torch::Tensor* t : {&it.zt, &it.zt_hi, &it.zt_lo}) {
       TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->dim() == 2 && t->stride(1) == 1 &&
                       t->size(0) == it.n && t->size(1) == it.n && t->stride(0) == it.zt.stride(0),
@@ -833,138 +825,108 @@ void householder_qr(const std::vector<py::tuple>& specs, torch::Tensor status) {
     device = it.ct.device();
     it.npan = (it.k + kQrPanel - 1) / kQrPanel;
     max_pan = std::max(max_pan, it.npan);
-    int64_t rows = 0;
-    for (int j = 0; j < it.npan; ++j) {
-      it.voff.push_back(rows);
-      rows += it.n - j * kQrPanel;
-    }
-    const auto opts = it.ct.options();
-    const int64_t k16 = static_cast<int64_t>(it.npan) * kQrPanel, ldw = (it.n + 3) / 4 * 4;
-    it.v_hi = torch::empty({rows, kQrPanel}, opts);
-    it.v_lo = torch::empty({rows, kQrPanel}, opts);
-    it.ttv_hi = torch::empty({k16, ldw}, opts);
-    it.ttv_lo = torch::empty({k16, ldw}, opts);
-    it.tv_hi = torch::empty({k16, ldw}, opts);
-    it.tv_lo = torch::empty({k16, ldw}, opts);
-    it.ttv_hi_v = it.ttv_hi.narrow(1, 0, it.n);
-    it.ttv_lo_v = it.ttv_lo.narrow(1, 0, it.n);
-    it.tv_hi_v = it.tv_hi.narrow(1, 0, it.n);
-    it.tv_lo_v = it.tv_lo.narrow(1, 0, it.n);
-    it.u_hi = torch::zeros({it.n, kQrPanel}, opts);
-    it.u_lo = torch::zeros({it.n, kQrPanel}, opts);
+    // kReflectChunk columns of slack per row: the reflector kernel copies whole chunks
+    const int64_t k16 = static_cast<int64_t>(it.npan) * kQrPanel, ldw = (it.n + 3) / 4 * 4 + kReflectChunk;
+    it.vt = torch::empty({k16, ldw}, it.ct.options());
+    it.ttv = torch::empty({k16, ldw}, it.ct.options());
+    it.tv = torch::empty({k16, ldw}, it.ct.options());
   }
   c10::cuda::CUDAGuard guard(device);
   auto stream = at::cuda::getCurrentCUDAStream();
 
-  // Panel descriptors, panel-major.
+  // Launch tables, panel-major: panel descriptors, then the reflector applications of the forward
+  // and of the backward sweep with their row tiles.
   std::vector<QrPanelDesc> panels;
-  std::vector<std::pair<int, int>> panel_range(max_pan);
-  for (int j = 0; j < max_pan; ++j) {
-    const int first = static_cast<int>(panels.size());
-    for (const Item& it : items) {
-      if (j >= it.npan) continue;
-      QrPanelDesc d;
-      std::memset(&d, 0, sizeof(d));
-      d.ct = it.ct.data_ptr<float>();
-      d.ld = static_cast<int>(it.ct.stride(0));
-      d.n = it.n;
-      d.c0 = j * kQrPanel;
-      d.c1 = std::min(it.k, d.c0 + kQrPanel);
-      d.v_hi = it.v_hi.data_ptr<float>() + it.voff[j] * kQrPanel;
-      d.v_lo = it.v_lo.data_ptr<float>() + it.voff[j] * kQrPanel;
-      d.ldw = static_cast<int>(it.ttv_hi.stride(0));
-      const int64_t row = static_cast<int64_t>(d.c0) * d.ldw;  // the kernel indexes columns from c0 itself
-      d.ttv_hi = it.ttv_hi.data_ptr<float>() + row + d.c0;
-      d.ttv_lo = it.ttv_lo.data_ptr<float>() + row + d.c0;
-      d.tv_hi = it.tv_hi.data_ptr<float>() + row + d.c0;
-      d.tv_lo = it.tv_lo.data_ptr<float>() + row + d.c0;
-      panels.push_back(d);
+  std::vector<ReflectDesc> reflect;
+  std::vector<int2> tiles;
+  struct Range {
+    int first = 0, count = 0;
+  };
+  std::vector<Range> panel_range(max_pan), fwd_range(max_pan), bwd_range(max_pan);
+  auto add_reflect = [&](float* x, float* x_hi, float* x_lo, int ldx, int rows, int L, const float* w, const float* vt,
+                         int ldw) {
+    ReflectDesc r;
+    std::memset(&r, 0, sizeof(r));
+    r.x = x;
+    r.x_hi = x_hi;
+    r.x_lo = x_lo;
+    r.w = w;
+    r.vt = vt;
+    r.ldx = ldx;
+    r.ldw = ldw;
+    r.rows = rows;
+    r.L = L;
+    r.rows_per_tile = std::max(1, std::min(kReflectMaxRows, kReflectSmemFloats / L));
+    const int idx = static_cast<int>(reflect.size());
+    reflect.push_back(r);
+    for (int row0 = 0; row0 < rows; row0 += r.rows_per_tile) tiles.push_back(make_int2(idx, row0));
+  };
+  for (int sweep = 0; sweep < 2; ++sweep) {
+    for (int j = 0; j < max_pan; ++j) {
+      const int panel_first = static_cast<int>(panels.size());
+      const int tile_first = static_cast<int>(tiles.size());
+      for (const Item& it : items) {
+        if (j >= it.npan) continue;
+        const int c0 = j * kQrPanel, c1 = std::min(it.k, c0 + kQrPanel), L = it.n - c0;
+        const int ldw = static_cast<int>(it.vt.stride(0));
+        const int64_t w_off = static_cast<int64_t>(c0) * ldw + c0;  // panel row 0, column c0
+        if (sweep == 0) {
+          QrPanelDesc d;
+          std::memset(&d, 0, sizeof(d));
+          d.ct = it.ct.data_ptr<float>();
+          d.ld = static_cast<int>(it.ct.stride(0));
+          d.n = it.n;
+          d.c0 = c0;
+          d.c1 = c1;
+          d.ldw = ldw;
+          d.vt = it.vt.data_ptr<float>() + w_off;
+          d.ttv = it.ttv.data_ptr<float>() + w_off;
+          d.tv = it.tv.data_ptr<float>() + w_off;
+          panels.push_back(d);
+          if (it.k > c1) {
+            const int64_t ld = it.ct.stride(0);
+            add_reflect(it.ct.data_ptr<float>() + c1 * ld + c0, nullptr, nullptr, static_cast<int>(ld), it.k - c1, L,
+                        it.ttv.data_ptr<float>() + w_off, it.vt.data_ptr<float>() + w_off, ldw);
+          }
+        } else {
+          const int64_t ld = it.zt.stride(0);
+          const int64_t off = c0 * ld + c0;
+          const bool last = j == 0;  // covers the whole matrix: also emit the (hi, lo) pair
+          add_reflect(it.zt.data_ptr<float>() + off, last ? it.zt_hi.data_ptr<float>() : nullptr,
+                      last ? it.zt_lo.data_ptr<float>() : nullptr, static_cast<int>(ld), L, L,
+                      it.tv.data_ptr<float>() + w_off, it.vt.data_ptr<float>() + w_off, ldw);
+        }
+      }
+      if (sweep == 0) {
+        panel_range[j] = {panel_first, static_cast<int>(panels.size()) - panel_first};
+        fwd_range[j] = {tile_first, static_cast<int>(tiles.size()) - tile_first};
+      } else {
+        bwd_range[j] = {tile_first, static_cast<int>(tiles.size()) - tile_first};
+      }
     }
-    panel_range[j] = {first, static_cast<int>(panels.size()) - first};
   }
   auto d_panels = upload_bytes(panels.data(), panels.size() * sizeof(QrPanelDesc), device);
+  auto d_reflect = upload_bytes(reflect.data(), reflect.size() * sizeof(ReflectDesc), device);
+  auto d_tiles = upload_bytes(tiles.data(), tiles.size() * sizeof(int2), device);
   const auto* panel_table = reinterpret_cast<const QrPanelDesc*>(d_panels.data_ptr());
+  const auto* reflect_table = reinterpret_cast<const ReflectDesc*>(d_reflect.data_ptr());
+  const auto* tile_table = reinterpret_cast<const int2*>(d_tiles.data_ptr());
 
-  PlanBuilder builder;
-  using Range = std::pair<int64_t, int64_t>;
-  std::vector<Range> fwd1(max_pan), fwd2(max_pan), bwd1(max_pan), bwd2(max_pan);
-  auto stage = [&](bool forward, bool second, int j) {
-    builder.begin_launch();
-    for (Item& it : items) {
-      if (j >= it.npan) continue;
-      const int c0 = j * kQrPanel, c1 = std::min(it.k, c0 + kQrPanel), nb = c1 - c0;
-      const int L = it.n - c0;
-      const int rows = forward ? it.k - c1 : L;  // rows of the updated block
-      if (rows <= 0) continue;
-      const int row0 = forward ? c1 : c0;
-      torch::Tensor& x = forward ? it.ct : it.zt;
-      torch::Tensor& x_hi = forward ? it.ct_hi : it.zt_hi;
-      torch::Tensor& x_lo = forward ? it.ct_lo : it.zt_lo;
-      PlanBuilder::Problem q;
-      if (!second) {  // U = X[row0:, c0:] (W^T)[c0:c1, c0:]^T with W^T = T^T V^T (forward) or T V^T (backward)
-        q.a = {&x_hi, &x_lo, row0, c0};
-        q.b = {forward ? &it.ttv_hi_v : &it.tv_hi_v, forward ? &it.ttv_lo_v : &it.tv_lo_v, c0, c0};
-        q.M = rows;
-        q.N = nb;
-        q.K = L;
-        q.d_hi = it.u_hi.data_ptr<float>();
-        q.d_lo = it.u_lo.data_ptr<float>();
-        q.ldd = kQrPanel;
-        q.flags = kFlagNoC | kFlagSplitOut;
-      } else {  // X[row0:, c0:] -= U V^T
-        q.a = {&it.u_hi, &it.u_lo, 0, 0};
-        q.b = {&it.v_hi, &it.v_lo, static_cast<int>(it.voff[j]), 0};
-        q.M = rows;
-        q.N = L;
-        q.K = kQrPanel;
-        const int64_t off = static_cast<int64_t>(row0) * x.stride(0) + c0;
-        q.c = x.data_ptr<float>() + off;
-        q.ldc = static_cast<int>(x.stride(0));
-        q.d_hi = x_hi.data_ptr<float>() + off;
-        q.d_lo = x_lo.data_ptr<float>() + off;
-        q.ldd = static_cast<int>(x.stride(0));
-        q.flags = kFlagSplitOut;
-      }
-      builder.add(q);
-    }
-    return builder.end_launch();
-  };
-  for (int j = 0; j < max_pan; ++j) {
-    fwd1[j] = stage(true, false, j);
-    fwd2[j] = stage(true, true, j);
-  }
-  for (int j = 0; j < max_pan; ++j) {
-    bwd1[j] = stage(false, false, j);
-    bwd2[j] = stage(false, true, j);
-  }
-  auto [table, tiles] = builder.finalize();
-  const auto* problems = reinterpret_cast<const GemmProblem*>(table.data_ptr());
-  const auto* tile_list = reinterpret_cast<const GemmTile*>(tiles.data_ptr());
-  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  auto gemm = [&](const Range& r, float alpha, float beta) {
-    if (r.second <= 0) return;
-    launch_grouped_gemm(problems, tile_list + r.first, static_cast<int>(r.second), alpha, beta, /*split=*/true,
-                        status.data_ptr<int>(), sms, stream);
-  };
-
-  // Z = I (plain and split) in one launch.
+  // Z = I in one launch.
   std::vector<SymOp> eye_ops;
   std::vector<int2> eye_chunks;
   for (const Item& it : items) {
-    for (int which = 0; which < 2; ++which) {
-      SymOp op;
-      std::memset(&op, 0, sizeof(op));
-      op.src = it.zt.data_ptr<float>();
-      op.n = it.n;
-      op.ld_src = op.ld_dst = static_cast<int>(it.zt.stride(0));
-      op.dst_hi = which == 0 ? it.zt.data_ptr<float>() : it.zt_hi.data_ptr<float>();
-      op.dst_lo = which == 0 ? nullptr : it.zt_lo.data_ptr<float>();
-      op.a = 0.f;  // the source is not read
-      op.b = 1.f;
-      const int idx = static_cast<int>(eye_ops.size());
-      eye_ops.push_back(op);
-      for (int r = 0; r < (op.n + kSymRowsPerChunk - 1) / kSymRowsPerChunk; ++r) eye_chunks.push_back(make_int2(idx, r));
-    }
+    SymOp op;
+    std::memset(&op, 0, sizeof(op));
+    op.src = it.zt.data_ptr<float>();
+    op.n = it.n;
+    op.ld_src = op.ld_dst = static_cast<int>(it.zt.stride(0));
+    op.dst_hi = it.zt.data_ptr<float>();
+    op.a = 0.f;  // the source is not read
+    op.b = 1.f;
+    const int idx = static_cast<int>(eye_ops.size());
+    eye_ops.push_back(op);
+    for (int r = 0; r < (op.n + kSymRowsPerChunk - 1) / kSymRowsPerChunk; ++r) eye_chunks.push_back(make_int2(idx, r));
   }
   auto d_eye_ops = upload_bytes(eye_ops.data(), eye_ops.size() * sizeof(SymOp), device);
   auto d_eye_chunks = upload_bytes(eye_chunks.data(), eye_chunks.size() * sizeof(int2), device);
@@ -972,13 +934,11 @@ void householder_qr(const std::vector<py::tuple>& specs, torch::Tensor status) {
                            reinterpret_cast<const int2*>(d_eye_chunks.data_ptr()), static_cast<int>(eye_chunks.size()), stream);
 
   for (int j = 0; j < max_pan; ++j) {
-    launch_householder_panel(panel_table + panel_range[j].first, panel_range[j].second, stream);
-    gemm(fwd1[j], 1.f, 0.f);
-    gemm(fwd2[j], -1.f, 1.f);
+    launch_householder_panel(panel_table + panel_range[j].first, panel_range[j].count, stream);
+    launch_apply_block_reflector(reflect_table, tile_table + fwd_range[j].first, fwd_range[j].count, stream);
   }
   for (int j = max_pan - 1; j >= 0; --j) {
-    gemm(bwd1[j], 1.f, 0.f);
-    gemm(bwd2[j], -1.f, 1.f);
+    launch_apply_block_reflector(reflect_table, tile_table + bwd_range[j].first, bwd_range[j].count, stream);
   }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   // The launch tables and the workspace are referenced by kernels still in flight: torch's caching

@@ -14,7 +14,7 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
-__device__ __forceinline__ void store_split(float* hi, float* lo, long long o, float x) {
+__device__ __forceinline__ void store_split(float* __restrict__ hi, float* __restrict__ lo, long long o, float x) {
   const float h = tf32_round(x);
   hi[o] = h;
   lo[o] = x - h;
@@ -140,25 +140,205 @@ __global__ void __launch_bounds__(kQrThreads, 1) householder_panel_kernel(const 
       v[jj] = x;
     }
 #pragma unroll
-    for (int jj = 0; jj < kQrPanel; ++jj) store_split(d.v_hi, d.v_lo, static_cast<long long>(i) * kQrPanel + jj, v[jj]);
-#pragma unroll
     for (int jj = 0; jj < kQrPanel; ++jj) {
+      float ttv = 0.f, tv = 0.f;
       if (jj < nb) {
-        float ttv = 0.f, tv = 0.f;
 #pragma unroll
         for (int m = 0; m < kQrPanel; ++m) {
           if (m <= jj) ttv = fmaf(tmat[m][jj], v[m], ttv);
           if (m >= jj) tv = fmaf(tmat[jj][m], v[m], tv);
         }
-        const long long o = static_cast<long long>(jj) * d.ldw + i;  // ttv_* / tv_* point at (row c0, column c0)
-        store_split(d.ttv_hi, d.ttv_lo, o, ttv);
-        store_split(d.tv_hi, d.tv_lo, o, tv);
       }
+      const long long o = static_cast<long long>(jj) * d.ldw + i;  // all kQrPanel rows are written
+      d.vt[o] = v[jj];
+      d.ttv[o] = ttv;
+      d.tv[o] = tv;
     }
   }
   if (in_smem) {
     for (int j = 0; j < nb; ++j)
       for (int i = tid; i < L; i += kQrThreads) gpanel[static_cast<long long>(j) * d.ld + i] = P[j * pitch + i];
+  }
+}
+
+constexpr int kReflectThreads = 256;
+constexpr int kReflectGroupRows = 4;                                   // rows whose sums one thread keeps in registers
+constexpr int kReflectGroups = kReflectMaxRows / kReflectGroupRows;    // row groups of a tile
+constexpr int kReflectGroupThreads = kReflectThreads / kReflectGroups;
+constexpr int kReflectGroupWarps = kReflectGroupThreads / 32;
+static_assert(kReflectChunk % kReflectGroupThreads == 0, "every thread of a group owns whole columns of a chunk");
+
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
+// Stage columns [c0, c0 + kReflectChunk) of the kQrPanel rows of `src` (pitch ldw) into `dst`.  The
+// arrays are allocated with kReflectChunk columns of slack per row, so a chunk never leaves its
+// row's storage; entries beyond L are garbage that no thread uses.
+__device__ __forceinline__ void stage_chunk(float* dst, const float* __restrict__ src, int ldw, int c0) {
+  constexpr int kVecs = kReflectChunk / 4;
+  for (int e = threadIdx.x; e < kQrPanel * kVecs; e += blockDim.x) {
+    const int j = e / kVecs, i4 = e % kVecs;
+    cp_async16(dst + j * kReflectChunk + 4 * i4, src + static_cast<long long>(j) * ldw + c0 + 4 * i4);
+  }
+  cp_async_commit();
+}
+
+// A tile of up to kReflectMaxRows whole rows stays in shared memory between the two passes.  The
+// threads are split into row groups of four rows; a thread owns columns i = t, t + 128, ... of its
+// group, keeps the 16 entries W[:, i] (then Vt[:, i]) in registers and runs them against its four
+// rows, so a shared-memory load feeds 16 multiply-adds instead of one.  The chunks of W and Vt are
+// double buffered with cp.async: the next chunk travels while the current one is consumed.
+__global__ void __launch_bounds__(kReflectThreads, 2) apply_block_reflector_kernel(const ReflectDesc* __restrict__ descs,
+                                                                                  const int2* __restrict__ tiles,
+                                                                                  int num_tiles) {
+  extern __shared__ float rsm[];
+  float* ws = rsm;                                 // [2][kQrPanel][kReflectChunk] chunks of W, then of Vt
+  float* xs = rsm + 2 * kQrPanel * kReflectChunk;  // [rows_per_tile][L]
+  __shared__ float part[kReflectGroups][kReflectGroupWarps][kReflectGroupRows * kQrPanel];
+  __shared__ float us[kReflectGroups][kReflectGroupRows * kQrPanel];
+  constexpr int kBuf = kQrPanel * kReflectChunk;
+  const int lane = threadIdx.x & 31;
+  const int g = threadIdx.x / kReflectGroupThreads, t = threadIdx.x % kReflectGroupThreads;
+  const int gw = t >> 5;  // warp inside the group
+  for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    const int2 ref = tiles[tile];
+    const ReflectDesc d = descs[ref.x];
+    const int row0 = ref.y;
+    const int R = min(d.rows_per_tile, d.rows - row0);
+    const int L = d.L;
+    const int num_chunks = (L + kReflectChunk - 1) / kReflectChunk;
+    float* xg = d.x + static_cast<long long>(row0) * d.ldx;
+    stage_chunk(ws, d.w, d.ldw, 0);
+    const bool vec = (L & 3) == 0 && (d.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(xg) & 15) == 0;
+    if (vec) {
+      const int L4 = L >> 2;
+      for (int e = threadIdx.x; e < R * L4; e += kReflectThreads) {
+        const int r = e / L4, i4 = e % L4;
+        reinterpret_cast<float4*>(xs + r * L)[i4] = reinterpret_cast<const float4*>(xg + static_cast<long long>(r) * d.ldx)[i4];
+      }
+    } else {
+      for (int e = threadIdx.x; e < R * L; e += kReflectThreads) {
+        const int r = e / L, i = e % L;
+        xs[r * L + i] = xg[static_cast<long long>(r) * d.ldx + i];
+      }
+    }
+    const int rbase = g * kReflectGroupRows;  // first row of this thread's group inside the tile
+    // ---- pass 1: u[r][j] = sum_i X[r][i] W[j][i]
+    float acc[kReflectGroupRows][kQrPanel];
+#pragma unroll
+    for (int q = 0; q < kReflectGroupRows; ++q)
+#pragma unroll
+      for (int j = 0; j < kQrPanel; ++j) acc[q][j] = 0.f;
+    for (int c = 0; c < num_chunks; ++c) {
+      const int c0 = c * kReflectChunk;
+      const int cw = min(kReflectChunk, L - c0);
+      const float* wb = ws + (c & 1) * kBuf;
+      // next chunk of W, or the first chunk of Vt for the second pass
+      if (c + 1 < num_chunks) stage_chunk(ws + ((c + 1) & 1) * kBuf, d.w, d.ldw, c0 + kReflectChunk);
+      else stage_chunk(ws + ((c + 1) & 1) * kBuf, d.vt, d.ldw, 0);
+      cp_async_wait<1>();
+      __syncthreads();  // chunk c (and, at c = 0, the rows) visible to all threads
+      if (rbase < R) {
+        for (int i = t; i < cw; i += kReflectGroupThreads) {
+          float w[kQrPanel];
+#pragma unroll
+          for (int j = 0; j < kQrPanel; ++j) w[j] = wb[j * kReflectChunk + i];
+#pragma unroll
+          for (int q = 0; q < kReflectGroupRows; ++q) {
+            const float x = rbase + q < R ? xs[(rbase + q) * L + c0 + i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < kQrPanel; ++j) acc[q][j] = fmaf(x, w[j], acc[q][j]);
+          }
+        }
+      }
+      __syncthreads();  // buffer (c & 1) may be refilled by the next iteration's prefetch
+    }
+    // sums over the threads of the group: inside each warp, then across the group's warps
+#pragma unroll
+    for (int q = 0; q < kReflectGroupRows; ++q)
+#pragma unroll
+      for (int j = 0; j < kQrPanel; ++j) {
+        const float sum = warp_sum(acc[q][j]);
+        if (lane == 0) part[g][gw][q * kQrPanel + j] = sum;
+      }
+    __syncthreads();
+    if (t < kReflectGroupRows * kQrPanel) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kReflectGroupWarps; ++w) sum += part[g][w][t];
+      us[g][t] = sum;
+    }
+    __syncthreads();
+    float u[kReflectGroupRows][kQrPanel];
+#pragma unroll
+    for (int q = 0; q < kReflectGroupRows; ++q)
+#pragma unroll
+      for (int j = 0; j < kQrPanel; ++j) u[q][j] = us[g][q * kQrPanel + j];
+    // ---- pass 2: X[r][i] -= sum_j u[r][j] Vt[j][i]; chunk c of Vt sits in buffer (num_chunks + c) & 1
+    for (int c = 0; c < num_chunks; ++c) {
+      const int c0 = c * kReflectChunk;
+      const int cw = min(kReflectChunk, L - c0);
+      const float* vb = ws + ((num_chunks + c) & 1) * kBuf;
+      if (c + 1 < num_chunks) {
+        stage_chunk(ws + ((num_chunks + c + 1) & 1) * kBuf, d.vt, d.ldw, c0 + kReflectChunk);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      if (rbase < R) {
+        for (int i = t; i < cw; i += kReflectGroupThreads) {
+          float v[kQrPanel];
+#pragma unroll
+          for (int j = 0; j < kQrPanel; ++j) v[j] = vb[j * kReflectChunk + i];
+#pragma unroll
+          for (int q = 0; q < kReflectGroupRows; ++q) {
+            if (rbase + q < R) {
+              float sum = 0.f;
+#pragma unroll
+              for (int j = 0; j < kQrPanel; ++j) sum = fmaf(u[q][j], v[j], sum);
+              xs[(rbase + q) * L + c0 + i] -= sum;
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    // rows back to global memory (and their (hi, lo) pair)
+    const bool split = d.x_hi != nullptr;
+    float* hg = split ? d.x_hi + static_cast<long long>(row0) * d.ldx : nullptr;
+    float* lg = split ? d.x_lo + static_cast<long long>(row0) * d.ldx : nullptr;
+    const bool vec_out = vec && (!split || (((reinterpret_cast<uintptr_t>(hg) | reinterpret_cast<uintptr_t>(lg)) & 15) == 0));
+    if (vec_out) {
+      const int L4 = L >> 2;
+      for (int e = threadIdx.x; e < R * L4; e += kReflectThreads) {
+        const int r = e / L4, i4 = e % L4;
+        const float4 x = reinterpret_cast<const float4*>(xs + r * L)[i4];
+        reinterpret_cast<float4*>(xg + static_cast<long long>(r) * d.ldx)[i4] = x;
+        if (split) {
+          float4 h, l;
+          h.x = tf32_round(x.x); h.y = tf32_round(x.y); h.z = tf32_round(x.z); h.w = tf32_round(x.w);
+          l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
+          reinterpret_cast<float4*>(hg + static_cast<long long>(r) * d.ldx)[i4] = h;
+          reinterpret_cast<float4*>(lg + static_cast<long long>(r) * d.ldx)[i4] = l;
+        }
+      }
+    } else {
+      for (int e = threadIdx.x; e < R * L; e += kReflectThreads) {
+        const int r = e / L, i = e % L;
+        const float x = xs[r * L + i];
+        const long long o = static_cast<long long>(r) * d.ldx + i;
+        xg[o] = x;
+        if (split) store_split(hg, lg, o, x);
+      }
+    }
+    __syncthreads();  // xs is reused by the next tile
   }
 }
 
@@ -281,6 +461,18 @@ void launch_householder_panel(const QrPanelDesc* descs, int count, cudaStream_t 
     configured = true;
   }
   householder_panel_kernel<<<count, kQrThreads, kBytes, stream>>>(descs);
+}
+
+void launch_apply_block_reflector(const ReflectDesc* descs, const int2* tiles, int num_tiles, cudaStream_t stream) {
+  if (num_tiles <= 0) return;
+  static bool configured = false;
+  constexpr int kBytes = (2 * kQrPanel * kReflectChunk + kReflectSmemFloats) * 4;
+  if (!configured) {
+    cudaFuncSetAttribute(apply_block_reflector_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+    configured = true;
+  }
+  const int cap = 2 * sm_count();  // two CTAs per SM: one loads or stores its rows while the other computes
+  apply_block_reflector_kernel<<<num_tiles < cap ? num_tiles : cap, kReflectThreads, kBytes, stream>>>(descs, tiles, num_tiles);
 }
 
 void launch_sym_measure(const SymOp* ops, int count, cudaStream_t stream) {

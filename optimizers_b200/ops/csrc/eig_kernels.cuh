@@ -26,26 +26,49 @@ constexpr int kQrSmemFloats = 3072 * kQrPanel;  // panels up to this many floats
 // of the matrix being factored, a vector of length n.  The panel covers columns c0 .. c1-1
 // (c1 - c0 <= kQrPanel, c0 a multiple of kQrPanel); entries [0, c0) of its rows are finished R
 // entries and are not touched.  On return rows c0..c1-1 hold R on and before the diagonal position
-// and the reflector below it (LAPACK geqrf layout), and, for i in [c0, n):
-//   v       [(i - c0) * kQrPanel + j]      = V[i, j]          (n - c0) x kQrPanel, zero padded
-//   ttv     [j * ldw + (i - c0)]           = (T^T V^T)[j, i]  operand of the trailing update
-//   tv      [j * ldw + (i - c0)]           = (T V^T)[j, i]    operand of the accumulation of Q
-// (the caller points ttv_* / tv_* at the entry of panel row 0 and column c0 of a larger array)
-// each as a tf32 (hi, lo) pair.  H_c0 ... H_{c1-1} = I - V T V^T with T upper triangular.
+// and the reflector below it (LAPACK geqrf layout), and three kQrPanel x (n - c0) arrays of common
+// row pitch ldw (rows beyond the panel's columns are zero) hold, for i in [c0, n):
+//   vt  [j * ldw + (i - c0)] = V[i, j]            the reflectors
+//   ttv [j * ldw + (i - c0)] = (T^T V^T)[j, i]    left factor of the trailing update
+//   tv  [j * ldw + (i - c0)] = (T V^T)[j, i]      left factor of the accumulation of Q
+// with H_c0 ... H_{c1-1} = I - V T V^T and T upper triangular.  (The caller points vt / ttv / tv at
+// the entry of panel row 0 and column c0 of larger arrays.)
 struct QrPanelDesc {
   float* ct;
-  float* v_hi;
-  float* v_lo;
-  float* ttv_hi;
-  float* ttv_lo;
-  float* tv_hi;
-  float* tv_lo;
+  float* vt;
+  float* ttv;
+  float* tv;
   int ld, n, c0, c1;
-  int ldw;  // row pitch of tt_v / t_v (>= n - c0, multiple of 4)
+  int ldw;
   int pad_[3];
 };
 
 void launch_householder_panel(const QrPanelDesc* descs, int count, cudaStream_t stream);
+
+// Application of a block reflector to a block of rows:  X <- X - (X W^T) Vt  with X rows x L
+// (pitch ldx), W and Vt kQrPanel x L (pitch ldw a multiple of 4, 16-byte aligned rows, and at least
+// kReflectChunk columns of addressable slack after column L of every row: chunks are copied whole).  In the transposed storage of the QR this is
+// C <- (I - V T V^T)^T C on trailing columns (W = T^T V^T) and Z <- Z (I - V T^T V^T) on the
+// accumulated Q^T (W = T V^T).  A rank-16 update moves 8 bytes per element for 64 flops: it is
+// bound by HBM, so it runs on the CUDA cores in exact fp32, each CTA holding a tile of whole rows in
+// shared memory between the two passes (inner products, update); x_hi / x_lo, when given, also
+// receive the tf32 (hi, lo) pair of the updated block (same pitch).
+struct ReflectDesc {
+  float* x;
+  float* x_hi;  // may be null
+  float* x_lo;
+  const float* w;
+  const float* vt;
+  int ldx, ldw, rows, L;
+  int rows_per_tile;  // whole rows held by one CTA: at most kReflectMaxRows, rows_per_tile * L <= kReflectSmemFloats
+  int pad_[3];
+};
+
+constexpr int kReflectMaxRows = 8;
+constexpr int kReflectSmemFloats = 16384;  // row tile: 64 KB, two CTAs per SM
+constexpr int kReflectChunk = 256;         // columns of W / Vt staged per step
+
+void launch_apply_block_reflector(const ReflectDesc* descs, const int2* tiles, int num_tiles, cudaStream_t stream);
 
 // One square matrix of a batched pass.
 struct SymOp {
