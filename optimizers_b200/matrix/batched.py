@@ -75,9 +75,12 @@ def _all_finite(tensors: list[Tensor]) -> list[bool]:
     return torch.isfinite(torch.stack(torch._foreach_norm(tensors, float("inf")))).cpu().tolist()
 
 
-# Sum of d^2 over the factors advanced together by the divide-and-conquer eigensolver (its
-# workspace is about 25 arrays of that size); OB200_EIGH_CHUNK_ELEMS overrides.
-_DC_CHUNK_ELEMS = int(_os.environ.get("OB200_EIGH_CHUNK_ELEMS", str(96 * 1024 * 1024)))
+# Upper bound on the sum of d^2 over the factors advanced together by the divide-and-conquer
+# eigensolver (OB200_EIGH_CHUNK_ELEMS overrides).  Its workspace is about 25 fp32 arrays of that
+# size; the bound actually used is further limited to a third of the memory free at the refresh.
+# The more factors advance together, the fuller the grouped launches of the deep levels are.
+_DC_CHUNK_ELEMS = int(_os.environ.get("OB200_EIGH_CHUNK_ELEMS", str(512 * 1024 * 1024)))
+_DC_WORKSPACE_ARRAYS = 25
 # OB200_EIGH=library sends every factor larger than the Jacobi kernel's limit to the library eigensolver.
 _DC_ENABLED = _os.environ.get("OB200_EIGH", "native") != "library"
 
@@ -92,11 +95,14 @@ def native_eigh(ext: Any, mats: list[Tensor], status: Tensor) -> list[tuple[Tens
     if not mats or not _DC_ENABLED:
         return out
     order = sorted(range(len(mats)), key=lambda i: -mats[i].shape[0])
+    free_bytes, _ = torch.cuda.mem_get_info(mats[0].device)
+    free_bytes += torch.cuda.memory_reserved(mats[0].device) - torch.cuda.memory_allocated(mats[0].device)  # cached blocks are reusable
+    limit = max(min(_DC_CHUNK_ELEMS, free_bytes // (3 * 4 * _DC_WORKSPACE_ARRAYS)), 1)
     chunks: list[list[int]] = [[]]
     size = 0
     for i in order:
         d2 = mats[i].shape[0] ** 2
-        if chunks[-1] and size + d2 > _DC_CHUNK_ELEMS:
+        if chunks[-1] and size + d2 > limit:
             chunks.append([])
             size = 0
         chunks[-1].append(i)
@@ -107,11 +113,16 @@ def native_eigh(ext: Any, mats: list[Tensor], status: Tensor) -> list[tuple[Tens
         for i, lam, Q in zip(chunk, lams, vecs, strict=True):
             if lam is not None:
                 out[i] = (lam, Q)
+        logger.info(
+            "divide-and-conquer eigh: %d matrices (largest %d), %d rounds, %d sign computations, work %.2f x sum d^3, %d leaves retried",
+            len(chunk), mats[chunk[0]].shape[0], info["rounds"], info["sign_computations"],
+            info["sign_cubes"] / sum(float(mats[i].shape[0]) ** 3 for i in chunk), backend.leaves_retried,
+        )
         given_up = sorted(set(info["failed"]) | set(backend.failed_in_finish))
         if given_up:
             logger.warning(
-                "The divide-and-conquer eigensolver gave up on %d of %d matrices; the library eigensolver takes them.",
-                len(given_up), len(chunk),
+                "The divide-and-conquer eigensolver gave up on %d of %d matrices; the library eigensolver takes them. %s",
+                len(given_up), len(chunk), "; ".join(f"[{chunk[r]}] {why}" for r, why in info["reasons"].items()) or "(leaf Jacobi sweeps exhausted)",
             )
     return out
 
@@ -758,6 +769,90 @@ def eigenbasis_refresh_supported(cfg: Any) -> bool:
     return isinstance(cfg, EighEigendecompositionConfig) and cfg.eigendecomposition_offload_device == ""
 
 
+def native_qr_iteration(
+    ext: Any, mats: list[Tensor], estimates: list[Tensor], max_iterations: int, tolerance: float, status: Tensor
+) -> list[Tensor]:
+    """The reference's warm-started QR iteration (``matrix_functions.py:799-852``) for all factors
+    of a refresh at once, on this framework's kernels only.
+
+    With V the previous eigenvectors of A:  B = V^T A V;  while the off-diagonal criterion
+    ``||B - diag B||_F <= tolerance ||B||_F`` fails (and iterations remain):  Q R = B,  B <- Q^T B Q
+    (= R Q),  V <- V Q;  finally the columns are ordered by ascending diag(B).  The products are
+    grouped tensor-core launches over all factors (symmetric ones compute the upper tiles only), the
+    QR factorisations one call of the batched Householder driver (panel kernel + block-reflector
+    kernel), the criterion one reduction launch whose results the host reads once per iteration for
+    all factors together.  Returns the new eigenvector matrices (columns)."""
+    from optimizers_b200.matrix.eigh_dc import _Mat
+
+    device = mats[0].device
+    F = ext
+    n_all = [m.shape[0] for m in mats]
+
+    def pair_of(x: Tensor) -> _Mat:
+        n0, n1 = x.shape
+        m = _Mat(n0, n1, device)
+        m.plain.copy_(x)
+        ext.tf32_split(m.plain, m.hi, m.lo)
+        return m
+
+    A = [pair_of(a) for a in mats]
+    V = [pair_of(v) for v in estimates]  # columns are eigenvectors; K-major operand over the eigenvector index
+    Vt = [_Mat(n, n, device, plain=False) for n in n_all]
+    table = ext.build_transpose_table([(v.hi, vt.hi, None, None) for v, vt in zip(V, Vt)] + [(v.lo, vt.lo, None, None) for v, vt in zip(V, Vt)])
+    ext.transpose_split(*table)
+
+    def run(specs: list[tuple], alpha: float = 1.0, beta: float = 0.0) -> None:
+        if specs:
+            ext.run_gemm_plan(*ext.build_gemm_plan(specs), alpha, beta, True, status)
+
+    def product(a: _Mat, b: _Mat, out: _Mat, sym: bool = False, plain: bool = True) -> tuple:
+        """out = a b^T as plain array and (hi, lo) pair."""
+        flags = F.FLAG_SPLIT_OUT | (F.FLAG_MIRROR if sym else 0) | (0 if plain else F.FLAG_NO_C)
+        c = out.plain if plain else None
+        return (a.hi, a.lo, b.hi, b.lo, c, out.hi, out.lo, None, out.hi.stride(0), out.hi.stride(0), flags, sym)
+
+    def congruence(Wt: list[_Mat], M: list[_Mat], idx: list[int]) -> list[_Mat]:
+        """W^T M W for symmetric M, W given by its transpose (rows = columns of W)."""
+        T = {i: _Mat(n_all[i], n_all[i], device, plain=False) for i in idx}
+        out = {i: _Mat(n_all[i], n_all[i], device) for i in idx}
+        run([product(Wt[i], M[i], T[i], plain=False) for i in idx])
+        run([product(T[i], Wt[i], out[i], sym=True) for i in idx])
+        return out
+
+    everyone = list(range(len(mats)))
+    B = congruence(Vt, A, everyone)
+    active = everyone
+    for _ in range(max_iterations):
+        if not active:
+            break
+        stats = torch.zeros(len(active), 2, device=device)
+        ops = ext.build_sym_table([(B[i].plain, None, None, stats[k], 0.0, 0.0) for k, i in enumerate(active)])
+        ext.sq_offdiag(ops[0], len(active))
+        still = []
+        for i, (total2, diag2) in zip(active, stats.cpu().tolist(), strict=True):  # the host read of this iteration
+            off = max(total2 - diag2, 0.0) ** 0.5
+            if not off <= tolerance * total2**0.5:  # also true for NaN: let the QR run, the caller's finiteness check reports it
+                still.append(i)
+        active = still
+        if not active:
+            break
+        # Q R = B on the batched Householder driver; B is symmetric, so it is its own transposed storage.
+        Zt = {i: _Mat(n_all[i], n_all[i], device) for i in active}
+        work = {i: B[i].plain.clone() for i in active}
+        ext.householder_qr([(work[i], n_all[i], n_all[i], Zt[i].plain, Zt[i].hi, Zt[i].lo) for i in active])
+        newB = congruence(Zt, B, active)
+        newV = {i: _Mat(n_all[i], n_all[i], device) for i in active}
+        newVt = {i: _Mat(n_all[i], n_all[i], device, plain=False) for i in active}
+        run([product(V[i], Zt[i], newV[i]) for i in active] + [product(Zt[i], V[i], newVt[i], plain=False) for i in active])
+        for i in active:
+            B[i], V[i], Vt[i] = newB[i], newV[i], newVt[i]
+    out = []
+    for i in everyone:
+        _, order = torch.diagonal(B[i].plain).sort(stable=True)
+        out.append(V[i].plain.index_select(1, order))
+    return out
+
+
 def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | float, ext: Any = None) -> None:
     """Recompute ``factor_matrices_eigenvectors`` of every block (eigh, or the warm-started QR
     iteration of ``matrix_functions.py:799-852``) with the factors spread over a pool of streams,
@@ -816,6 +911,32 @@ def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | flo
 
     pooled = list(range(len(items)))
     cfg0 = blocks[0].factors.amortized_computation_config
+    from optimizers_b200.config import QREigendecompositionConfig
+
+    if ext is not None and isinstance(cfg0, QREigendecompositionConfig) and _DC_ENABLED:
+        native = [
+            i for i in pooled
+            if items[i].A.dtype == torch.float32 and items[i].A.shape[0] >= 2
+            and items[i].block.factors.factor_matrices_eigenvectors[items[i].k].dtype == torch.float32
+        ]
+        if native:
+            stability = cfg0.rank_deficient_stability_config
+            ridged = [
+                mf._ridge(items[i].A, items[i].block.factors.epsilon * getattr(stability, "perturb_before_computation", 0))
+                for i in native
+            ]
+            old = [items[i].block.factors.factor_matrices_eigenvectors[items[i].k] for i in native]
+            status = torch.zeros(1, dtype=torch.int32, device=device)
+            results = native_qr_iteration(ext, ridged, old, cfg0.max_iterations, cfg0.tolerance, status)
+            for i, Q in zip(native, results, strict=True):
+                items[i].q_hi = Q
+                items[i].done = torch.cuda.Event()
+                items[i].done.record(main)
+            if int(status.item()) & 1:
+                raise RuntimeError("grouped GEMM pipeline wait timed out (device-side bounded wait expired)")
+            done = set(native)
+            pooled = [i for i in pooled if i not in done]
+            ready.record(main)
     if ext is not None and isinstance(cfg0, EighEigendecompositionConfig) and cfg0.tolerance == 0.0:
         # Small factors: one launch of the shared-memory Jacobi eigensolver for all of them.
         small = [i for i in pooled if items[i].A.shape[0] <= ext.JACOBI_MAX_N]

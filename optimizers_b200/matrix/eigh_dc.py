@@ -174,12 +174,30 @@ class TorchBackend:
             )
 
     def close_leaves(self, subs: list[Sub]) -> list[int]:
-        """Eigendecomposition of the small problems; returns the roots of those that failed."""
-        for s in subs:
-            lam, Q = torch.linalg.eigh(s.A)
-            self.lams[s.root][s.offset : s.offset + s.n] = lam
-            self.vecs[s.root][:, s.offset : s.offset + s.n] = Q if s.B is None else s.B @ Q
-        return []
+        self._run_leaves(subs, shift=0.0)
+        return []  # convergence of the leaves is read once, in finish()
+
+    def _run_leaves(self, subs: list[Sub], shift: float) -> None:
+        ext, dev = self.ext, self.device
+        direct = [s for s in subs if s.B is None]  # a root that is itself a leaf: eigenvectors as columns
+        based = [s for s in subs if s.B is not None]
+        lam_of = lambda s: self.lams[s.root][s.offset : s.offset + s.n]  # noqa: E731
+        if direct:
+            sweeps = ext.jacobi_eigh_into(
+                [s.A.plain for s in direct], [self.vecs[s.root] for s in direct], [lam_of(s) for s in direct], False,
+                self.jacobi_max_sweeps, self.jacobi_tolerance, shift)
+            self._leaf_sweeps.append((direct, sweeps))
+        if based:
+            holders = [_Mat(s.n, s.n, dev) for s in based]
+            sweeps = ext.jacobi_eigh_into(
+                [s.A.plain for s in based], [h.plain for h in holders], [lam_of(s) for s in based], True,
+                self.jacobi_max_sweeps, self.jacobi_tolerance, shift)
+            self._leaf_sweeps.append((based, sweeps))
+            table = ext.build_sym_table([(h.plain, h.hi, h.lo, None, 1.0, 0.0) for h in holders])
+            ext.shift_scale_split(*table)  # the (hi, lo) pairs of all leaves in one launch
+            self._gemm([
+                self._spec(s.B, h, None, c=self.vecs[s.root][:, s.offset : s.offset + s.n]) for s, h in zip(based, holders)
+            ])
 
     def finish(self, roots_ok: list[bool]) -> tuple[list[Tensor | None], list[Tensor | None]]:
         lams: list[Tensor | None] = []
@@ -237,6 +255,7 @@ def eigh_divide_and_conquer(
     backend = _Timed(backend) if getattr(backend, "profile", None) is not None else backend
     work = backend.begin(mats)
     failed: set[int] = set()
+    reasons: dict[int, str] = {}
     rounds = 0
     signs = 0
     cubes = 0.0  # sum of n^3 over all sign computations: the unit the cost of a refresh scales with
@@ -250,7 +269,9 @@ def eigh_divide_and_conquer(
         if not big:
             break
         if rounds > _MAX_ROUNDS:
-            failed.update(s.root for s in big)
+            for s in big:
+                failed.add(s.root)
+                reasons.setdefault(s.root, f"still splitting after {_MAX_ROUNDS} rounds (subproblem of size {s.n})")
             break
         backend.measure(big)
         scalar = [s for s in big if s.spread <= scalar_tol * eps * backend.root_norms[s.root] or s.spread == 0.0]
@@ -273,6 +294,11 @@ def eigh_divide_and_conquer(
             s.extra.clear()
             if s.attempt >= _MAX_ATTEMPTS:
                 failed.add(s.root)
+                reasons.setdefault(
+                    s.root,
+                    f"no projector after {_MAX_ATTEMPTS} sign computations: subproblem n={s.n} rank={s.rank} "
+                    f"idempotency defect={s.idem_err:.3g} spread={s.spread:.3g} (root norm {backend.root_norms[s.root]:.3g})",
+                )
             else:
                 retry.append(s)
         children: list[Sub] = []
@@ -282,7 +308,7 @@ def eigh_divide_and_conquer(
         work = retry + children
     ok = [i not in failed for i in range(len(mats))]
     lams, vecs = backend.finish(ok)
-    return lams, vecs, {"failed": sorted(failed), "rounds": rounds, "sign_computations": signs, "sign_cubes": cubes}
+    return lams, vecs, {"failed": sorted(failed), "rounds": rounds, "sign_computations": signs, "sign_cubes": cubes, "reasons": reasons}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -310,6 +336,9 @@ class _Mat:
 
 
 _OMEGA_CACHE: dict[tuple, _Mat] = {}
+import os as _os
+
+_SPLIT_RULE = _os.environ.get("OB200_DC_SPLIT", "mean")
 
 
 class NativeBackend:
@@ -327,6 +356,8 @@ class NativeBackend:
         self.profile: dict[str, float] | None = None  # set to {} to collect per-phase times
         self.jacobi_max_sweeps = 24
         self.jacobi_tolerance = 2e-6
+        self.jacobi_shift = 1.5  # second attempt of a leaf the Jacobi kernel did not settle on (see finish)
+        self.leaves_retried = 0
 
     # -- helpers ----------------------------------------------------------------------------
     def _gemm(self, specs: list[tuple], alpha: float = 1.0, beta: float = 0.0, gamma: float = 0.0) -> None:
@@ -384,6 +415,15 @@ class NativeBackend:
         table = ext.build_sym_table([(s.A.plain, None, None, stats[i], 0.0, 0.0) for i, s in enumerate(subs)])
         ext.sym_measure(table[0], len(subs))
         for s, (sigma, spread) in zip(subs, stats.cpu().tolist(), strict=True):
+            if _SPLIT_RULE == "moment" and sigma > 0.0 and not s.attempt:
+                # heavy tail: most of the trace sits in a few eigenvalues and the mean lies far above
+                # the median; lower the split point by the square root of n / participation ratio
+                m2 = (spread * spread + s.n * sigma * sigma) / s.n
+                ratio = max(m2 / (sigma * sigma), 1.0)
+                lowered = sigma / math.sqrt(ratio)
+                shift = lowered - sigma
+                spread = math.sqrt(spread * spread + s.n * shift * shift)
+                sigma = lowered
             if s.attempt:
                 shift = _NUDGE * s.attempt * spread * (1 if s.attempt % 2 else -1)
                 # trace(A - sigma I) = 0, so the shifted spread follows without another pass
@@ -542,11 +582,11 @@ class NativeBackend:
         if direct:
             sweeps.append(([subs[i] for i in direct], ext.jacobi_eigh_into(
                 [mats[i] for i in direct], [qs[i] for i in direct], [lams[i] for i in direct], False,
-                self.jacobi_max_sweeps, self.jacobi_tolerance)))
+                self.jacobi_max_sweeps, self.jacobi_tolerance, self.jacobi_shift)))
         if with_basis:
             sweeps.append(([subs[i] for i in with_basis], ext.jacobi_eigh_into(
                 [mats[i] for i in with_basis], [qs[i] for i in with_basis], [lams[i] for i in with_basis], True,
-                self.jacobi_max_sweeps, self.jacobi_tolerance)))
+                self.jacobi_max_sweeps, self.jacobi_tolerance, self.jacobi_shift)))
             g = []
             for i in with_basis:
                 s, Qt = subs[i], holders[i]
@@ -559,11 +599,23 @@ class NativeBackend:
 
     def finish(self, roots_ok: list[bool]) -> tuple[list[Tensor | None], list[Tensor | None]]:
         roots_ok = list(roots_ok)
-        for subs, sweeps in self._leaf_sweeps:
-            for s, used in zip(subs, sweeps.cpu().tolist(), strict=True):
-                if used > self.jacobi_max_sweeps:
-                    roots_ok[s.root] = False
-        self._leaf_sweeps = []
+        # One-sided Jacobi does not settle on a leaf that is singular or indefinite to working
+        # precision (columns of A V that are pure rounding noise): such leaves run once more on
+        # A + 1.5 ||A||_F I, which costs them the relative accuracy of their smallest eigenvalues,
+        # already lost, and nothing else.
+        pending, self._leaf_sweeps = self._leaf_sweeps, []
+        stuck = [
+            s for subs, sweeps in pending for s, used in zip(subs, sweeps.cpu().tolist(), strict=True)
+            if used > self.jacobi_max_sweeps and roots_ok[s.root]
+        ]
+        if stuck:
+            self._run_leaves(stuck, shift=self.jacobi_shift)
+            for subs, sweeps in self._leaf_sweeps:
+                for s, used in zip(subs, sweeps.cpu().tolist(), strict=True):
+                    if used > self.jacobi_max_sweeps:
+                        roots_ok[s.root] = False
+            self._leaf_sweeps = []
+        self.leaves_retried = len(stuck)
         self.failed_in_finish = [i for i, ok in enumerate(roots_ok) if not ok]
         lams: list[Tensor | None] = []
         vecs: list[Tensor | None] = []

@@ -692,7 +692,7 @@ std::tuple<std::vector<torch::Tensor>, std::vector<torch::Tensor>, torch::Tensor
     lams.push_back(torch::empty({n}, a.options()));
     qs.push_back(torch::empty({n, n}, a.options()));
     descs[i] = {a.data_ptr<float>(), qs.back().data_ptr<float>(), lams.back().data_ptr<float>(), static_cast<int>(n),
-                static_cast<int>(a.stride(0)), static_cast<int>(n), 0};
+                static_cast<int>(a.stride(0)), static_cast<int>(n), 0, 0.f, 0};
   }
   auto d_descs = upload_bytes(descs.data(), descs.size() * sizeof(JacobiDesc), device);
   auto sweeps = torch::zeros({static_cast<int64_t>(mats.size())}, torch::dtype(torch::kInt32).device(device));
@@ -705,8 +705,11 @@ std::tuple<std::vector<torch::Tensor>, std::vector<torch::Tensor>, torch::Tensor
 
 // jacobi_eigh writing into caller-provided storage: qs[i] is an n x n view (any row pitch) that
 // receives the eigenvectors as columns (or as rows with `transposed`), lams[i] an n-vector.
+// `shift_scale` > 0 (JacobiDesc::shift_scale) makes the kernel robust on singular and indefinite
+// matrices at the price of absolute instead of relative accuracy of the small eigenvalues.
 torch::Tensor jacobi_eigh_into(const std::vector<torch::Tensor>& mats, const std::vector<torch::Tensor>& qs,
-                               const std::vector<torch::Tensor>& lams, bool transposed, int64_t max_sweeps, double tol) {
+                               const std::vector<torch::Tensor>& lams, bool transposed, int64_t max_sweeps, double tol,
+                               double shift_scale) {
   TORCH_CHECK(!mats.empty() && mats.size() == qs.size() && mats.size() == lams.size(), "jacobi_eigh_into: list sizes");
   const auto device = mats[0].device();
   c10::cuda::CUDAGuard guard(device);
@@ -722,7 +725,8 @@ torch::Tensor jacobi_eigh_into(const std::vector<torch::Tensor>& mats, const std
     TORCH_CHECK(q.scalar_type() == torch::kFloat32 && q.dim() == 2 && q.size(0) == n && q.size(1) == n && q.stride(1) == 1);
     TORCH_CHECK(l.scalar_type() == torch::kFloat32 && l.dim() == 1 && l.size(0) == n && l.stride(0) == 1);
     descs[i] = {a.data_ptr<float>(), q.data_ptr<float>(), l.data_ptr<float>(), static_cast<int>(n),
-                static_cast<int>(a.stride(0)), static_cast<int>(q.stride(0)), transposed ? 1 : 0};
+                static_cast<int>(a.stride(0)), static_cast<int>(q.stride(0)), transposed ? 1 : 0,
+                static_cast<float>(shift_scale), 0};
   }
   auto d_descs = upload_bytes(descs.data(), descs.size() * sizeof(JacobiDesc), device);
   auto sweeps = torch::zeros({static_cast<int64_t>(mats.size())}, torch::dtype(torch::kInt32).device(device));

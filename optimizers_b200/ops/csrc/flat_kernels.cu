@@ -196,6 +196,29 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
     }
   }
   __syncthreads();
+  float shift = 0.f;
+  if (d.shift_scale > 0.f) {
+    __shared__ float fro_parts[kWarps];
+    __shared__ float shift_s;
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < n * n; e += kJacobiThreads) {
+      const float x = a[(e / n) * kJacobiPitch + (e % n)];
+      ss = fmaf(x, x, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) fro_parts[warp] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float total = 0.f;
+      for (int w = 0; w < kWarps; ++w) total += fro_parts[w];
+      shift_s = d.shift_scale * sqrtf(total);
+    }
+    __syncthreads();
+    shift = shift_s;
+    for (int j = threadIdx.x; j < n; j += kJacobiThreads) a[j * kJacobiPitch + j] += shift;
+    __syncthreads();
+  }
 
   int sweep = 0;
   bool converged = false;
@@ -302,7 +325,7 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
     int rank = 0;
     for (int k = 0; k < n; ++k) rank += (lam_s[k] < x) || (lam_s[k] == x && k < j);
     rank_of[j] = rank;
-    d.lam[rank] = x;
+    d.lam[rank] = x - shift;
   }
   __syncthreads();
   // Q[i][rank(j)] = v_j[i]; lanes run over j so that the scattered destination stays within a row.

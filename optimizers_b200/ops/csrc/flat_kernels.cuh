@@ -48,7 +48,12 @@ struct JacobiDesc {
   float* q;        // n x n, row pitch ldq: eigenvectors as columns, ascending eigenvalue order
   float* lam;      // n eigenvalues, ascending
   int n, lda, ldq;
-  int transposed;  // 1: eigenvectors are written as the rows of q instead
+  int transposed;     // 1: eigenvectors are written as the rows of q instead
+  float shift_scale;  // s > 0: the kernel works on A + s ||A||_F I (same eigenvectors, every eigenvalue at least
+                      // (s - 1) ||A||_F) and subtracts the shift from the eigenvalues at the end.  One-sided Jacobi
+                      // orthogonalises the columns of A V; on a singular or indefinite matrix the columns that
+                      // belong to eigenvalues near zero are rounding noise and never pass the relative test.
+  int pad_;
 };
 
 constexpr int kJacobiMaxN = 128;

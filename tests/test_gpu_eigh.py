@@ -217,3 +217,39 @@ def test_native_divide_and_conquer_eigh_matches_fp64(ext, d):
         err = float(torch.linalg.norm(got - want) / torch.linalg.norm(want))
         # fp32 eigensolvers resolve eigenvalues to ~1e-7 of the largest one; the library's fp32 eigh gives 1e-2 here
         assert err < 5e-2, (kind, err)
+
+
+@pytest.mark.parametrize("d", [96, 300, 1024])
+def test_native_qr_iteration_matches_torch_path(ext, d):
+    """Warm-started QR iteration on ill-conditioned factors (condition number 1e8) against the
+    torch formulation in fp64: same eigenvalue estimates, an orthonormal basis, and an off-diagonal
+    residue that is no worse."""
+    from optimizers_b200.matrix import functions as mf
+    from optimizers_b200.matrix.batched import native_qr_iteration
+
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(d)
+    mats, starts = [], []
+    for k in range(3):
+        q, _ = torch.linalg.qr(torch.randn(d, d, device=dev, dtype=torch.float64, generator=gen))
+        lam = torch.logspace(0, -8, d, device=dev, dtype=torch.float64)
+        A = (q * lam) @ q.T
+        # previous eigenvectors: the true ones rotated a little (a refresh interval later)
+        S = 0.05 * torch.randn(d, d, device=dev, dtype=torch.float64, generator=gen)
+        rot, _ = torch.linalg.qr(torch.eye(d, device=dev, dtype=torch.float64) + (S - S.T))
+        mats.append(A)
+        starts.append((q @ rot).contiguous())
+    status = _status(dev)
+    got = native_qr_iteration(ext, [m.float() for m in mats], [v.float() for v in starts], 2, 1e-6, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    eye = torch.eye(d, device=dev, dtype=torch.float64)
+    for A, V0, V in zip(mats, starts, got):
+        lam_ref, V_ref = mf._qr_iteration(A, V0, 2, 1e-6)
+        V = V.double()
+        assert float((V.T @ V - eye).abs().max()) < 1e-4
+        B, B_ref = V.T @ A @ V, V_ref.T @ A @ V_ref
+        assert torch.allclose(torch.diagonal(B), lam_ref, atol=2e-4 * float(lam_ref.abs().max()), rtol=0)
+        off = torch.linalg.norm(B - torch.diag(torch.diagonal(B)))
+        off_ref = torch.linalg.norm(B_ref - torch.diag(torch.diagonal(B_ref)))
+        assert float(off) <= 1.5 * float(off_ref) + 2e-4 * float(torch.linalg.norm(A))
