@@ -11,15 +11,25 @@ AdaGrad grafting.  Data is synthetic (uniform token ids) and weights are randoml
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
 
-The step counter of the optimizer is preset to ``start_preconditioning_step - 1`` (in both
-arms) so that the first warm-up step performs the root-inverse refresh and every timed step
-runs the preconditioned path; further refreshes fall in the timed region whenever the step
-count crosses a multiple of ``precondition_frequency``.
+What is reported is what training costs per step once the preconditioner refresh is counted:
 
-Rank 0 prints one JSON line.  ``value`` is timed on the device with CUDA events around the K
-steps (inputs already on the device); ``e2e`` repeats the K steps through the public API with a
-pinned-host -> device copy of each step's tokens and a device -> host read of each step's loss
-inside the timed region.
+    amortized ms/step = steady ms/step + (refresh step ms - steady ms/step) / precondition_frequency
+
+``steady`` is the device time of the K timed steps, none of which recomputes the inverse roots
+(the step counter of the optimizer is preset to ``start_preconditioning_step - 1``, in both arms,
+so that the first warm-up step performs the first refresh and every later step runs the
+preconditioned path).  ``refresh step`` is one more step, timed on the device after the timed
+regions with the counter set so that it recomputes every inverse root (the refresh of a run in
+progress: allocator and kernels warm; the first, cold one is reported separately).  ``value`` is
+tokens/s at the amortised step time.
+
+Rank 0 prints one JSON line.  The K steps are timed on the device with CUDA events (inputs
+already on the device); ``optimizer_step_ms`` is the device time of ``optimizer.step()`` inside
+those steps; ``e2e`` repeats the K steps through the public API with a pinned-host -> device copy
+of each step's tokens and a device -> host read of each step's loss inside the timed region and
+is amortised the same way.  ``plain_model`` (this framework's arm only) repeats the steady
+measurement with the plain PyTorch GPT-2 that the reference arm uses, which isolates the
+optimizer's share of the difference between the arms.
 """
 
 from __future__ import annotations
@@ -58,6 +68,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--model", choices=["fused", "plain"], default="fused",
                     help="this framework's arm: its GPT-2 with the fused norm / LM-head-loss kernels, or the plain "
                     "PyTorch model that the reference arm always uses")
+    ap.add_argument("--no-plain", action="store_true", help="skip the extra plain-model measurement of this framework's arm")
     ap.add_argument("--layers", type=int, default=12, help="debug only; the reported config needs 12")
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="debug only; the reported config needs 16")
     return ap.parse_args()
@@ -264,38 +275,42 @@ def main() -> None:
     torch.manual_seed(1234)
     torch.backends.cuda.matmul.allow_tf32 = False  # optimizer math of the reference stays fp32
     fused_model = args.impl == "ours" and args.model == "fused"
-    if fused_model:
-        # Same architecture, initialisation and autocast numerics as make_gpt2; the normalisations
-        # and the LM head + cross-entropy run through this framework's CUDA kernels.
-        from optimizers_b200.models import GPT2, GPT2Config
-
-        model = GPT2(GPT2Config(n_layer=args.layers)).to(dev)
-    else:
-        model = make_gpt2(args.layers).to(dev)
-    train_model = model
-    # This framework's p2p path reduces the gradients inside the optimizer's prologue kernel
-    # (owners pull their blocks from peer memory), so the model is not wrapped in DDP there.
     hsdp = world > 1 and args.parallelism == "hsdp"
-    mesh = None
     fused_comm = args.impl == "ours" and world > 1 and args.comm == "p2p" and args.backend != "torch" and not hsdp
-    if hsdp:
-        from torch.distributed.device_mesh import init_device_mesh
-        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy
 
-        shard = min(world, 4)
-        mesh = init_device_mesh("cuda", (world // shard, shard), mesh_dim_names=("replicate", "shard"))
-        train_model = model = FSDP(
-            model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True,
-            device_id=local_rank,
-        )
-    elif world > 1 and not fused_comm:
-        train_model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
-    elif world > 1:
-        for p in model.parameters():
-            dist.broadcast(p.data, src=0)
-    opt = build_optimizer(args.impl, model, world, args, mesh)
-    if hasattr(opt, "train"):
-        opt.train()
+    def build(use_fused_model: bool):
+        """Model, its training wrapper and the optimizer of one arm."""
+        if use_fused_model:
+            # Same architecture, initialisation and autocast numerics as make_gpt2; the normalisations
+            # and the LM head + cross-entropy run through this framework's CUDA kernels.
+            from optimizers_b200.models import GPT2, GPT2Config
+
+            model = GPT2(GPT2Config(n_layer=args.layers)).to(dev)
+        else:
+            model = make_gpt2(args.layers).to(dev)
+        train_model = model
+        mesh = None
+        # This framework's p2p path reduces the gradients inside the optimizer's prologue kernel
+        # (owners pull their blocks from peer memory), so the model is not wrapped in DDP there.
+        if hsdp:
+            from torch.distributed.device_mesh import init_device_mesh
+            from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy
+
+            shard = min(world, 4)
+            mesh = init_device_mesh("cuda", (world // shard, shard), mesh_dim_names=("replicate", "shard"))
+            train_model = model = FSDP(
+                model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True,
+                device_id=local_rank,
+            )
+        elif world > 1 and not fused_comm:
+            train_model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
+        elif world > 1:
+            for p in model.parameters():
+                dist.broadcast(p.data, src=0)
+        opt = build_optimizer(args.impl, model, world, args, mesh)
+        if hasattr(opt, "train"):
+            opt.train()
+        return train_model, opt
 
     B = args.batch
     gen = torch.Generator().manual_seed(100 + rank)
@@ -303,86 +318,138 @@ def main() -> None:
     host_tokens = [torch.randint(0, VOCAB, (B, SEQ + 1), generator=gen).pin_memory() for _ in range(n_batches)]
     dev_tokens = [t.to(dev) for t in host_tokens]
 
-    def train_step(tokens: torch.Tensor) -> torch.Tensor:
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = train_model(tokens[:, :-1], tokens[:, 1:])
-        loss.backward()
-        opt.step()
-        opt.zero_grad(set_to_none=not fused_comm)
-        return loss
-
     def barrier() -> None:
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (untimed); the first step performs the root-inverse refresh
-    refresh_ms = None
-    for i in range(max(args.warmup, 1)):
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        train_step(dev_tokens[i % n_batches])
-        torch.cuda.synchronize()
-        if i == 0:
-            refresh_ms = (time.perf_counter() - t0) * 1e3
+    def set_step_counter(opt, value: int) -> None:
+        # Resume-style preset of the shared step counter (a CPU tensor aliased under every parameter).
+        for state in opt.state.values():
+            if "step" in state:
+                state["step"].fill_(value)
+                break
 
-    # ---- device-timed region: K steps, inputs resident on the device
+    def measure(train_model, opt, steps: int, warmup: int, with_refresh: bool) -> dict:
+        opt_start = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        opt_stop = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+
+        def train_step(tokens: torch.Tensor, k: int | None = None) -> torch.Tensor:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = train_model(tokens[:, :-1], tokens[:, 1:])
+            loss.backward()
+            if k is not None:
+                opt_start[k].record()
+            opt.step()
+            if k is not None:
+                opt_stop[k].record()
+            opt.zero_grad(set_to_none=not fused_comm)
+            return loss
+
+        # ---- warm-up (untimed); the first step performs the first (cold) refresh
+        first_ms = None
+        for i in range(max(warmup, 1)):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            train_step(dev_tokens[i % n_batches])
+            torch.cuda.synchronize()
+            if i == 0:
+                first_ms = (time.perf_counter() - t0) * 1e3
+
+        # ---- device-timed region: K steps, inputs resident on the device
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            train_step(dev_tokens[i % n_batches], i)
+        stop.record()
+        barrier()
+        out = {
+            "first_step_ms": first_ms,
+            "steady_ms": start.elapsed_time(stop) / steps,
+            "optimizer_ms": sum(a.elapsed_time(b) for a, b in zip(opt_start, opt_stop)) / steps,
+        }
+        if not with_refresh:
+            return out
+
+        # ---- end-to-end region: pinned host tokens in, loss out, every step
+        barrier()
+        h2d = d2h = 0
+        e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_wall = time.perf_counter()
+        e_start.record()
+        last = 0.0
+        for i in range(steps):
+            src = host_tokens[i % n_batches]
+            tokens = src.to(dev, non_blocking=True)
+            h2d += src.numel() * src.element_size()
+            loss = train_step(tokens)
+            last = loss.item()
+            d2h += loss.element_size()
+        e_stop.record()
+        barrier()
+        out["e2e_ms"] = max(e_start.elapsed_time(e_stop), (time.perf_counter() - t_wall) * 1e3 if world == 1 else 0.0) / steps
+        out["h2d"], out["d2h"], out["final_loss"] = h2d // max(steps, 1), d2h // max(steps, 1), last
+
+        # ---- one refresh step of the run in progress (every inverse root recomputed), device-timed
+        set_step_counter(opt, 3 * PRECOND_FREQ - 1)
+        barrier()
+        r_start, r_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r_start.record()
+        train_step(dev_tokens[0])
+        r_stop.record()
+        barrier()
+        out["refresh_ms"] = r_start.elapsed_time(r_stop)
+        return out
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    train_model, opt = build(fused_model)
     model_launches = 0
     if fused_model:
         from optimizers_b200.models import fused_ops
 
         model_launches = -fused_ops.launch_count
-    start.record()
-    for i in range(args.steps):
-        train_step(dev_tokens[i % n_batches])
-    stop.record()
+    m = measure(train_model, opt, args.steps, args.warmup, with_refresh=True)
     if fused_model:
-        model_launches += fused_ops.launch_count
-    barrier()
-    dev_ms = start.elapsed_time(stop)
-
-    # ---- end-to-end region: pinned host tokens in, loss out, every step
-    barrier()
-    h2d = d2h = 0
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_wall = time.perf_counter()
-    e_start.record()
-    last = 0.0
-    for i in range(args.steps):
-        src = host_tokens[i % n_batches]
-        tokens = src.to(dev, non_blocking=True)
-        h2d += src.numel() * src.element_size()
-        loss = train_step(tokens)
-        last = loss.item()
-        d2h += loss.element_size()
-    e_stop.record()
-    barrier()
-    e2e_ms = max(e_start.elapsed_time(e_stop), (time.perf_counter() - t_wall) * 1e3 if world == 1 else 0.0)
+        # launches of the model kernels per step, from the whole measured run
+        steps_run = max(args.warmup, 1) + 2 * args.steps + 1
+        model_launches = (model_launches + fused_ops.launch_count) // steps_run
     clocks = sampler.stop() if rank == 0 else {}
+    launches_per_step = (count_native_launches(opt) + model_launches) if args.impl == "ours" else 0
 
-    times = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
+    plain = None
+    if args.impl == "ours" and fused_model and not args.no_plain and not hsdp:
+        del train_model, opt
+        torch.cuda.empty_cache()
+        torch.manual_seed(1234)
+        plain_model, plain_opt = build(False)
+        plain = measure(plain_model, plain_opt, args.steps, args.warmup, with_refresh=False)
+        del plain_model, plain_opt
+
+    keys = ["steady_ms", "optimizer_ms", "e2e_ms", "refresh_ms", "first_step_ms"]
+    times = torch.tensor([m[k] for k in keys] + ([plain["steady_ms"], plain["optimizer_ms"]] if plain else [0.0, 0.0]),
+                         device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = times.tolist()
+    steady_ms, optimizer_ms, e2e_ms, refresh_ms, first_ms, plain_ms, plain_opt_ms = times.tolist()
+
+    def amortized(step_ms: float) -> float:
+        return step_ms + max(refresh_ms - steady_ms, 0.0) / PRECOND_FREQ
 
     tokens_per_step = B * SEQ * world
-    value = tokens_per_step * args.steps / (dev_ms / 1e3)
-    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
-    launches = count_native_launches(opt) * args.steps + model_launches if args.impl == "ours" else 0
+    value = tokens_per_step / (amortized(steady_ms) / 1e3)
+    e2e_value = tokens_per_step / (amortized(e2e_ms) / 1e3)
     if rank == 0:
         out = {
-            "metric": "train tokens/sec (GPT-2 124M, Distributed Shampoo)",
+            "metric": "train tokens/sec (GPT-2 124M, Distributed Shampoo), preconditioner refresh amortised over precondition_frequency steps",
             "value": value,
             "unit": "tokens/s",
             "n_gpus": world,
             "steps": args.steps,
             "warmup": args.warmup,
-            "ms_per_step": dev_ms / args.steps,
+            "ms_per_step": amortized(steady_ms),
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
@@ -403,18 +470,30 @@ def main() -> None:
                 "l2_policy": "working set (params, grads, optimizer state, activations: several GB) exceeds the 126 MB L2",
                 "step_counter_preset": PRECOND_FREQ - 1,
             },
+            "steady_ms_per_step": steady_ms,
+            "optimizer_step_ms": optimizer_ms,
             "refresh_step_ms": refresh_ms,
-            "final_loss": last,
+            "first_refresh_step_ms": first_ms,
+            "amortized_ms_per_step": amortized(steady_ms),
+            "precondition_frequency": PRECOND_FREQ,
+            "final_loss": m["final_loss"],
             "clocks": clocks,
             "e2e": {
                 "value": e2e_value,
                 "unit": "tokens/s",
-                "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": h2d // max(args.steps, 1),
-                "d2h_bytes_per_step": d2h // max(args.steps, 1),
+                "ms_per_step": amortized(e2e_ms),
+                "steady_ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": m["h2d"],
+                "d2h_bytes_per_step": m["d2h"],
             },
-            "gpu_launches": launches,
+            "gpu_launches": launches_per_step * args.steps,
         }
+        if plain is not None:
+            out["plain_model"] = {
+                "what": "this framework's optimizer under the plain PyTorch GPT-2 of the reference arm (steady steps)",
+                "steady_ms_per_step": plain_ms,
+                "optimizer_step_ms": plain_opt_ms,
+            }
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
