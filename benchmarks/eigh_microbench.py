@@ -104,7 +104,9 @@ def main() -> None:
     if args.profile:
         backend.profile = {}
         _, (_, _, info) = timed(lambda: (backend.profile.clear(), eigh_divide_and_conquer(backend, big))[1])
+        calls = backend.profile.pop("calls", [])
         print(json.dumps({"arm": "divide_and_conquer phases (ms, serialised)", **{k: round(v, 2) for k, v in backend.profile.items()}}), flush=True)
+        print(json.dumps({"arm": "divide_and_conquer calls (phase, subproblems, mean size, ms)", "calls": calls}), flush=True)
     if not args.skip_library:
         ms_lib, _ = timed(lambda: [torch.linalg.eigh(m) for m in big])
         print(json.dumps({"arm": "torch.linalg.eigh loop", "ms": ms_lib, "matrices": len(big)}), flush=True)

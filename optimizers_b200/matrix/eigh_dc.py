@@ -80,9 +80,16 @@ class Sub:
     offset: int
     A: Any = None  # backend handle of the matrix
     B: Any = None  # backend handle of the basis; None for a root (identity)
-    attempt: int = 0
-    sigma: float = 0.0
-    spread: float = 0.0
+    attempt: int = 0  # sign computations of this subproblem that did not yield a projector
+    mean: float = 0.0  # trace / n
+    mean_spread: float = 0.0  # ||A - mean I||_F
+    sigma: float = 0.0  # split point
+    spread: float = 0.0  # ||A - sigma I||_F
+    lo: float = -math.inf  # known bounds of the eigenvalues (from the splits that produced the subproblem)
+    hi: float = math.inf
+    span: tuple[int, int] | None = None  # positions of its eigenvalues in the root's hint, descending order
+    rule: str = "mean"  # how sigma was chosen: "mean", "hint", "geometric"
+    one_sided: bool = False  # a hinted or geometric split point failed here: the mean from now on
     rank: int = 0
     idem_err: float = 0.0
     extra: dict = field(default_factory=dict)  # backend scratch
@@ -109,15 +116,11 @@ class TorchBackend:
 
     # -- one round ----------------------------------------------------------------------------
     def measure(self, subs: list[Sub]) -> None:
-        """sigma = trace / n (nudged on a repeated attempt) and spread = ||A - sigma I||_F."""
+        """mean = trace / n and spread = ||A - mean I||_F (the driver derives the split point)."""
         for s in subs:
-            sigma = float(torch.trace(s.A)) / s.n
-            shifted = s.A - sigma * torch.eye(s.n, device=self.device, dtype=self.dtype)
-            spread = float(torch.linalg.norm(shifted))
-            if s.attempt:
-                sigma += _NUDGE * s.attempt * spread * (1 if s.attempt % 2 else -1)
-                spread = float(torch.linalg.norm(s.A - sigma * torch.eye(s.n, device=self.device, dtype=self.dtype)))
-            s.sigma, s.spread = sigma, spread
+            mean = float(torch.trace(s.A)) / s.n
+            shifted = s.A - mean * torch.eye(s.n, device=self.device, dtype=self.dtype)
+            s.mean, s.mean_spread = mean, float(torch.linalg.norm(shifted))
 
     def sign_projector(self, subs: list[Sub]) -> None:
         """P = (I + sign(A - sigma I)) / 2, rank = ||P||_F^2, idem_err = trace(P) - ||P||_F^2."""
@@ -174,30 +177,12 @@ class TorchBackend:
             )
 
     def close_leaves(self, subs: list[Sub]) -> list[int]:
-        self._run_leaves(subs, shift=0.0)
-        return []  # convergence of the leaves is read once, in finish()
-
-    def _run_leaves(self, subs: list[Sub], shift: float) -> None:
-        ext, dev = self.ext, self.device
-        direct = [s for s in subs if s.B is None]  # a root that is itself a leaf: eigenvectors as columns
-        based = [s for s in subs if s.B is not None]
-        lam_of = lambda s: self.lams[s.root][s.offset : s.offset + s.n]  # noqa: E731
-        if direct:
-            sweeps = ext.jacobi_eigh_into(
-                [s.A.plain for s in direct], [self.vecs[s.root] for s in direct], [lam_of(s) for s in direct], False,
-                self.jacobi_max_sweeps, self.jacobi_tolerance, shift)
-            self._leaf_sweeps.append((direct, sweeps))
-        if based:
-            holders = [_Mat(s.n, s.n, dev) for s in based]
-            sweeps = ext.jacobi_eigh_into(
-                [s.A.plain for s in based], [h.plain for h in holders], [lam_of(s) for s in based], True,
-                self.jacobi_max_sweeps, self.jacobi_tolerance, shift)
-            self._leaf_sweeps.append((based, sweeps))
-            table = ext.build_sym_table([(h.plain, h.hi, h.lo, None, 1.0, 0.0) for h in holders])
-            ext.shift_scale_split(*table)  # the (hi, lo) pairs of all leaves in one launch
-            self._gemm([
-                self._spec(s.B, h, None, c=self.vecs[s.root][:, s.offset : s.offset + s.n]) for s, h in zip(based, holders)
-            ])
+        """Eigendecomposition of the small problems; returns the roots of those that failed."""
+        for s in subs:
+            lam, Q = torch.linalg.eigh(s.A)
+            self.lams[s.root][s.offset : s.offset + s.n] = lam
+            self.vecs[s.root][:, s.offset : s.offset + s.n] = Q if s.B is None else s.B @ Q
+        return []
 
     def finish(self, roots_ok: list[bool]) -> tuple[list[Tensor | None], list[Tensor | None]]:
         lams: list[Tensor | None] = []
@@ -211,6 +196,63 @@ class TorchBackend:
             lams.append(lam[order])
             vecs.append(Q[:, order].contiguous())
         return lams, vecs
+
+
+_HEAVY_TAIL = 8.0  # n * sum(lambda^2) / sum(lambda)^2 above which the mean says little about the median
+_SAFE_GAP = 4e-6  # smallest gap, relative to the spread, in which a hinted split point is placed
+_WIDE_RANGE = 1e3  # hi / lo above which a heavy-tailed spectrum is split at the geometric mean of its bounds
+
+
+def plan_split(s: Sub, hint: Any, floor: float) -> None:
+    """Choose the split point ``s.sigma`` (and ``s.spread = ||A - sigma I||_F``) of a measured
+    subproblem.  The mean of the eigenvalues always has eigenvalues on both sides, but on the
+    heavy-tailed spectra of Kronecker factors (a handful of dominant eigenvalues, many decades of
+    tail, often a numerically null cluster) it isolates a few eigenvalues per round.  In order:
+
+    - after a split point that left everything on one side, or without better knowledge: the mean;
+    - with a hint (eigenvalue estimates of the same matrix from an earlier decomposition, any
+      positive scale, sorted descending): the largest gap in the middle third of the subproblem's
+      part of the hint, rescaled by the current trace: balanced splits and the null cluster comes
+      off in one piece;
+    - heavy tail and bounds (from the splits above, the norm, and the rounding floor) that span more
+      than three decades: the geometric mean of the bounds;
+    - a sign iteration that did not converge is repeated with the point nudged by 3e-5 of the spread.
+    """
+    n, mean, spread = s.n, s.mean, s.mean_spread
+    sigma, rule = mean, "mean"
+    hi = min(s.hi, mean + spread)
+    lo = max(s.lo, mean - spread)
+    if not s.one_sided:
+        span = s.span
+        if hint is not None and span is not None and span[1] - span[0] == n and n >= 4:
+            part = hint[span[0] : span[1]]
+            total = float(part.sum())
+            if total > 0.0 and mean > 0.0:
+                scale = mean * n / total
+                # Splitting between positions m - 1 and m (m eigenvalues above) is only safe where the
+                # gap is resolved by the sign iteration: eigenvalues closer to the split point than
+                # ~1e-7 of the spread do not converge.  Among the safe positions take the one that
+                # balances the two halves best (cost m^3 + (n - m)^3).
+                gaps = (part[:-1] - part[1:]) * scale  # gaps[m - 1]: between positions m - 1 and m
+                safe = torch.nonzero(gaps >= _SAFE_GAP * spread).flatten() + 1
+                if safe.numel():
+                    m = int(safe[(safe - n / 2).abs().argmin()])
+                    if min(m, n - m) >= max(2, n // 16):  # a split that moves less is left to the other rules
+                        cand = 0.5 * float(part[m - 1] + part[m]) * scale
+                        if lo < cand < hi:
+                            sigma, rule = cand, "hint"
+        if rule == "mean" and mean > 0.0:
+            ratio = (spread * spread + n * mean * mean) / (n * mean * mean)
+            low = max(lo, floor)
+            if ratio > _HEAVY_TAIL and hi > 0.0 and hi / low > _WIDE_RANGE:
+                cand = math.sqrt(hi * low)
+                if cand < mean:
+                    sigma, rule = cand, "geometric"
+    if s.attempt:
+        sigma += _NUDGE * s.attempt * max(spread, abs(sigma - mean)) * (1 if s.attempt % 2 else -1)
+    shift = sigma - mean
+    s.sigma, s.rule = sigma, rule
+    s.spread = math.sqrt(spread * spread + n * shift * shift)  # trace(A - mean I) = 0
 
 
 class _Timed:
@@ -235,14 +277,18 @@ class _Timed:
             if torch.cuda.is_available():
                 torch.cuda.synchronize()
             prof = self._backend.profile
-            prof[name] = prof.get(name, 0.0) + (time.perf_counter() - t0) * 1e3
+            ms = (time.perf_counter() - t0) * 1e3
+            prof[name] = prof.get(name, 0.0) + ms
+            if args and isinstance(args[0], list) and args[0] and isinstance(args[0][0], Sub):
+                # per call: number of subproblems, their mean size, milliseconds
+                prof.setdefault("calls", []).append((name, len(args[0]), round(sum(s.n for s in args[0]) / len(args[0])), round(ms, 2)))
             return out
 
         return timed
 
 
 def eigh_divide_and_conquer(
-    backend: Any, mats: list[Tensor], leaf: int = LEAF, scalar_tol: float = 4.0
+    backend: Any, mats: list[Tensor], leaf: int = LEAF, scalar_tol: float = 4.0, hints: list[Any] | None = None
 ) -> tuple[list[Tensor | None], list[Tensor | None], dict[str, Any]]:
     """Eigendecompositions (ascending eigenvalues, eigenvectors as columns) of the symmetric
     matrices ``mats``, all advanced together.  Returns ``(eigenvalues, eigenvectors, info)``; the
@@ -250,10 +296,23 @@ def eigh_divide_and_conquer(
     ``info["failed"]``.
 
     ``scalar_tol``: a subproblem is closed as a multiple eigenvalue when its spread is below
-    ``scalar_tol * eps * ||root matrix||_F``."""
+    ``scalar_tol * eps * ||root matrix||_F``.
+
+    ``hints``: per matrix ``None`` or a 1-D CPU tensor of eigenvalue estimates of the same size (any
+    positive scale, any order), e.g. the eigenvalues found at the previous refresh; they only steer
+    the choice of split points (``plan_split``)."""
     eps = torch.finfo(torch.float32).eps
     backend = _Timed(backend) if getattr(backend, "profile", None) is not None else backend
     work = backend.begin(mats)
+    plans: list[Any] = [None] * len(mats)
+    if hints is not None:
+        for i, h in enumerate(hints):
+            if h is not None and h.numel() == mats[i].shape[0]:
+                plans[i] = torch.sort(h.detach().to(device="cpu", dtype=torch.float64), descending=True).values
+    for s in work:
+        if plans[s.root] is not None:
+            s.span = (0, s.n)
+    one_sided = 0
     failed: set[int] = set()
     reasons: dict[int, str] = {}
     rounds = 0
@@ -274,10 +333,13 @@ def eigh_divide_and_conquer(
                 reasons.setdefault(s.root, f"still splitting after {_MAX_ROUNDS} rounds (subproblem of size {s.n})")
             break
         backend.measure(big)
-        scalar = [s for s in big if s.spread <= scalar_tol * eps * backend.root_norms[s.root] or s.spread == 0.0]
+        is_scalar = lambda s: s.mean_spread <= scalar_tol * eps * backend.root_norms[s.root] or s.mean_spread == 0.0  # noqa: E731
+        scalar = [s for s in big if is_scalar(s)]
         if scalar:
             backend.close_scalar(scalar)
-        active = [s for s in big if not (s.spread <= scalar_tol * eps * backend.root_norms[s.root] or s.spread == 0.0)]
+        active = [s for s in big if not is_scalar(s)]
+        for s in active:
+            plan_split(s, plans[s.root], scalar_tol * eps * backend.root_norms[s.root])
         if not active:
             work = []
             continue
@@ -286,9 +348,22 @@ def eigh_divide_and_conquer(
         cubes += sum(float(s.n) ** 3 for s in active)
         good, retry = [], []
         for s in active:
-            bad = not (abs(s.idem_err) <= _IDEMPOTENCY_TOL) or s.rank <= 0 or s.rank >= s.n  # also catches NaN
-            if not bad:
+            converged = abs(s.idem_err) <= _IDEMPOTENCY_TOL  # False for NaN
+            if converged and 0 < s.rank < s.n:
                 good.append(s)
+                continue
+            if s.rule != "mean":
+                # A hinted or geometric split point that left every eigenvalue on one side (a bound
+                # learned) or landed where eigenvalues crowd (no projector): a sign computation
+                # spent; the subproblem continues with the mean, which cannot fail the first way.
+                if converged and s.rank <= 0:
+                    s.hi = min(s.hi, s.sigma)
+                elif converged:
+                    s.lo = max(s.lo, s.sigma)
+                s.one_sided = True
+                s.extra.clear()
+                retry.append(s)
+                one_sided += 1
                 continue
             s.attempt += 1
             s.extra.clear()
@@ -304,11 +379,21 @@ def eigh_divide_and_conquer(
         children: list[Sub] = []
         if good:
             backend.split_basis(good)
+            split_of = {(s.root, s.offset): s for s in good}
             children = backend.project(good)
+            for c in children:
+                parent = split_of.get((c.root, c.offset))
+                above = parent is not None  # the child of the eigenvalues above sigma keeps the parent's offset
+                if parent is None:
+                    parent = next(p for p in good if p.root == c.root and p.offset + p.rank == c.offset)
+                c.lo, c.hi = (parent.sigma, parent.hi) if above else (parent.lo, parent.sigma)
+                if parent.span is not None:
+                    a = parent.span[0]
+                    c.span = (a, a + parent.rank) if above else (a + parent.rank, parent.span[1])
         work = retry + children
     ok = [i not in failed for i in range(len(mats))]
     lams, vecs = backend.finish(ok)
-    return lams, vecs, {"failed": sorted(failed), "rounds": rounds, "sign_computations": signs, "sign_cubes": cubes, "reasons": reasons}
+    return lams, vecs, {"failed": sorted(failed), "rounds": rounds, "sign_computations": signs, "sign_cubes": cubes, "reasons": reasons, "one_sided_splits": one_sided}  # one_sided_splits: hinted / geometric points that had to be abandoned
 
 
 # ----------------------------------------------------------------------------------------------
@@ -336,9 +421,7 @@ class _Mat:
 
 
 _OMEGA_CACHE: dict[tuple, _Mat] = {}
-import os as _os
 
-_SPLIT_RULE = _os.environ.get("OB200_DC_SPLIT", "mean")
 
 
 class NativeBackend:
@@ -414,22 +497,8 @@ class NativeBackend:
         stats = torch.zeros(len(subs), 2, device=self.device)
         table = ext.build_sym_table([(s.A.plain, None, None, stats[i], 0.0, 0.0) for i, s in enumerate(subs)])
         ext.sym_measure(table[0], len(subs))
-        for s, (sigma, spread) in zip(subs, stats.cpu().tolist(), strict=True):
-            if _SPLIT_RULE == "moment" and sigma > 0.0 and not s.attempt:
-                # heavy tail: most of the trace sits in a few eigenvalues and the mean lies far above
-                # the median; lower the split point by the square root of n / participation ratio
-                m2 = (spread * spread + s.n * sigma * sigma) / s.n
-                ratio = max(m2 / (sigma * sigma), 1.0)
-                lowered = sigma / math.sqrt(ratio)
-                shift = lowered - sigma
-                spread = math.sqrt(spread * spread + s.n * shift * shift)
-                sigma = lowered
-            if s.attempt:
-                shift = _NUDGE * s.attempt * spread * (1 if s.attempt % 2 else -1)
-                # trace(A - sigma I) = 0, so the shifted spread follows without another pass
-                spread = math.sqrt(spread * spread + s.n * shift * shift)
-                sigma += shift
-            s.sigma, s.spread = sigma, spread
+        for s, (mean, spread) in zip(subs, stats.cpu().tolist(), strict=True):
+            s.mean, s.mean_spread = mean, spread
 
     def sign_projector(self, subs: list[Sub]) -> None:
         ext, dev, F = self.ext, self.device, self.ext
@@ -563,39 +632,30 @@ class NativeBackend:
                 cols.copy_(s.B.plain)
 
     def close_leaves(self, subs: list[Sub]) -> list[int]:
-        ext, dev = self.ext, self.device
-        mats, qs, lams = [], [], []
-        holders = []
-        for s in subs:
-            mats.append(s.A.plain)
-            lams.append(self.lams[s.root][s.offset : s.offset + s.n])
-            if s.B is None:
-                qs.append(self.vecs[s.root])  # a root that is itself a leaf: eigenvectors as columns
-                holders.append(None)
-            else:
-                Qt = _Mat(s.n, s.n, dev)
-                qs.append(Qt.plain)
-                holders.append(Qt)
-        with_basis = [i for i, h in enumerate(holders) if h is not None]
-        direct = [i for i, h in enumerate(holders) if h is None]
-        sweeps = []
-        if direct:
-            sweeps.append(([subs[i] for i in direct], ext.jacobi_eigh_into(
-                [mats[i] for i in direct], [qs[i] for i in direct], [lams[i] for i in direct], False,
-                self.jacobi_max_sweeps, self.jacobi_tolerance, self.jacobi_shift)))
-        if with_basis:
-            sweeps.append(([subs[i] for i in with_basis], ext.jacobi_eigh_into(
-                [mats[i] for i in with_basis], [qs[i] for i in with_basis], [lams[i] for i in with_basis], True,
-                self.jacobi_max_sweeps, self.jacobi_tolerance, self.jacobi_shift)))
-            g = []
-            for i in with_basis:
-                s, Qt = subs[i], holders[i]
-                ext.tf32_split(Qt.plain, Qt.hi, Qt.lo)
-                cols = self.vecs[s.root][:, s.offset : s.offset + s.n]
-                g.append(self._spec(s.B, Qt, None, c=cols))
-            self._gemm(g)
-        self._leaf_sweeps.extend(sweeps)
+        self._run_leaves(subs, shift=0.0)
         return []  # convergence of the leaves is read once, in finish()
+
+    def _run_leaves(self, subs: list[Sub], shift: float) -> None:
+        ext, dev = self.ext, self.device
+        direct = [s for s in subs if s.B is None]  # a root that is itself a leaf: eigenvectors as columns
+        based = [s for s in subs if s.B is not None]
+        lam_of = lambda s: self.lams[s.root][s.offset : s.offset + s.n]  # noqa: E731
+        if direct:
+            sweeps = ext.jacobi_eigh_into(
+                [s.A.plain for s in direct], [self.vecs[s.root] for s in direct], [lam_of(s) for s in direct], False,
+                self.jacobi_max_sweeps, self.jacobi_tolerance, shift)
+            self._leaf_sweeps.append((direct, sweeps))
+        if based:
+            holders = [_Mat(s.n, s.n, dev) for s in based]
+            sweeps = ext.jacobi_eigh_into(
+                [s.A.plain for s in based], [h.plain for h in holders], [lam_of(s) for s in based], True,
+                self.jacobi_max_sweeps, self.jacobi_tolerance, shift)
+            self._leaf_sweeps.append((based, sweeps))
+            table = ext.build_sym_table([(h.plain, h.hi, h.lo, None, 1.0, 0.0) for h in holders])
+            ext.shift_scale_split(*table)  # the (hi, lo) pairs of all leaves in one launch
+            self._gemm([
+                self._spec(s.B, h, None, c=self.vecs[s.root][:, s.offset : s.offset + s.n]) for s, h in zip(based, holders)
+            ])
 
     def finish(self, roots_ok: list[bool]) -> tuple[list[Tensor | None], list[Tensor | None]]:
         roots_ok = list(roots_ok)

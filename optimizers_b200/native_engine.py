@@ -164,6 +164,7 @@ class _Block:
         "m1", "v", "mom", "z", "g_hi", "g_lo", "gt_hi", "gt_lo", "f_hi", "f_lo", "tt_hi", "tt_lo", "p",
         "inv_hi", "inv_lo", "ev", "qt_hi", "qt_lo", "t2_hi", "t2_lo",
         "dims3", "view2d", "y_hi", "y_lo", "zt_hi", "zt_lo", "aux_g_hi", "aux_g_lo", "aux_gt_hi", "aux_gt_lo", "d1_hi", "d1_lo", "d2_hi", "d2_lo",
+        "eig_hints",  # factor index -> eigenvalues found at the previous refresh (host tensor; steers the eigensolver)
     )
 
 
@@ -268,6 +269,7 @@ class NativeGroupEngine:
 
         for i, (view, info) in enumerate(zip(dist.local_blocked_params, dist.local_block_info_list, strict=True)):
             b = _Block()
+            b.eig_hints = None
             b.index = i
             b.param_view = view
             b.grad_slot = local_owner[i]

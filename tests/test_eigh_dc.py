@@ -86,3 +86,41 @@ def test_unconverged_sign_is_retried_then_reported(monkeypatch):
     assert attempts[:3] == [0, 1, 2]
     ref = torch.linalg.eigvalsh(mats[1].double())
     assert float((lams[1].double() - ref).abs().max()) <= 2e-6 * float(ref.abs().max())
+
+
+def _heavy_tailed(d, gen):
+    """A handful of dominant eigenvalues, a power-law tail and a numerically null cluster: the
+    shape of a Kronecker factor a few hundred steps into training."""
+    lam = torch.cat([1.0 / torch.arange(1, d // 3 + 1, dtype=torch.float64) ** 3, torch.full((d - d // 3,), 1e-12, dtype=torch.float64)])
+    q = _orth(d, gen)
+    return (q * lam) @ q.T, lam
+
+
+def test_hints_from_a_previous_decomposition_balance_the_splits():
+    gen = torch.Generator().manual_seed(11)
+    d = 256
+    A64, lam_true = _heavy_tailed(d, gen)
+    A = A64.float()
+    plain = eigh_divide_and_conquer(TorchBackend(torch.device("cpu")), [A], leaf=32)
+    # the hint: last refresh's eigenvalues, at another scale and slightly off
+    hint = 3.0 * lam_true * (1 + 0.05 * torch.randn(d, dtype=torch.float64, generator=gen))
+    hinted = eigh_divide_and_conquer(TorchBackend(torch.device("cpu")), [A], leaf=32, hints=[hint])
+    for lams, vecs, info in (plain, hinted):
+        assert info["failed"] == []
+        ref = torch.linalg.eigvalsh(A64)
+        assert float((lams[0].double() - ref).abs().max()) <= 2e-6 * float(ref.abs().max())
+        Q = vecs[0].double()
+        assert float(torch.linalg.norm((Q * lams[0].double()) @ Q.T - A64)) <= 3e-4 * float(torch.linalg.norm(A64))
+    assert hinted[2]["sign_cubes"] < 0.8 * plain[2]["sign_cubes"]  # less work: the null cluster comes off at once
+
+
+def test_misleading_hint_costs_one_sign_computation_not_the_result():
+    gen = torch.Generator().manual_seed(13)
+    d = 120
+    A64 = _matrix("uniform", d, gen)
+    # a hint whose every gap lies far below the actual spectrum after rescaling by the trace
+    hint = torch.cat([torch.full((d // 2,), 1.0), torch.full((d - d // 2,), 1e-9)]).double()
+    lams, vecs, info = eigh_divide_and_conquer(TorchBackend(torch.device("cpu")), [A64.float()], leaf=32, hints=[hint])
+    assert info["failed"] == []
+    ref = torch.linalg.eigvalsh(A64)
+    assert float((lams[0].double() - ref).abs().max()) <= 2e-6 * float(ref.abs().max())
