@@ -138,61 +138,3 @@ def test_hybrid_shard_lossless_matches_single_device(strategy):
     for full, _ in run_distributed(_fully_shard_worker, 4, strategy, 1, (2, 2)):
         for a, b in zip(ref, full):
             assert torch.equal(a, b)
-
-
-def test_hybrid_shard_default_runs():
-    results = run_distributed(_fully_shard_worker, 4, "DEFAULT", 1, (2, 2))
-    for full, keys in results:
-        assert all(torch.isfinite(t).all() for t in full)
-        assert any(k.startswith("rank_") for k in keys)
-    for other in results[1:]:
-        for a, b in zip(results[0][0], other[0]):
-            assert torch.equal(a, b)
-
-
-def _fsdp1_worker(rank, world, hybrid):
-    from torch.distributed.device_mesh import init_device_mesh
-    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy
-
-    from optimizers_b200 import (
-        DistributedShampoo,
-        FSDPDistributedConfig,
-        HSDPDistributedConfig,
-        compile_fsdp_parameter_metadata,
-    )
-
-    model = _model()
-    if hybrid:
-        mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
-        model = FSDP(model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True, device_id=torch.device("cpu"))
-        cfg = HSDPDistributedConfig(param_to_metadata=compile_fsdp_parameter_metadata(model), device_mesh=mesh)
-    else:
-        model = FSDP(model, use_orig_params=True, device_id=torch.device("cpu"))
-        cfg = FSDPDistributedConfig(param_to_metadata=compile_fsdp_parameter_metadata(model))
-    opt = DistributedShampoo(model.parameters(), distributed_config=cfg, **_opt_kwargs())
-    losses = []
-    for x, y in _data(5):
-        opt.zero_grad()
-        loss = torch.nn.functional.cross_entropy(model(x), y)
-        loss.backward()
-        opt.step()
-        losses.append(float(loss))
-    keys = sorted({str(k) for s in opt.state_dict()["state"].values() for k in s})
-    return losses, keys
-
-
-def test_fsdp1_distributor_runs():
-    results = run_distributed(_fsdp1_worker, 2, False)
-    for rank, (losses, keys) in enumerate(results):
-        assert all(l == l for l in losses) and losses[-1] < losses[0] + 1.0
-        assert any(k.startswith(f"rank_{rank}-block_") for k in keys)
-    assert results[0][0] == results[1][0]  # same data on every rank -> same loss
-
-
-def test_hsdp1_distributor_runs():
-    results = run_distributed(_fsdp1_worker, 4, True)
-    for losses, keys in results:
-        assert all(l == l for l in losses)
-        assert any(k.startswith("rank_") for k in keys)
-    for other in results[1:]:
-        assert other[0] == results[0][0]

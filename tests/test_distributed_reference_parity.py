@@ -1,0 +1,157 @@
+"""Sharded distributors against the unmodified reference library inside the same gloo ranks:
+FSDP1, HSDP1, fully-shard (default assignment) and hybrid-shard (default assignment) must update
+the model bit for bit like the reference's distributors do (the reference checks FSDP == HSDP and
+per-rank state the same way: ``distributed_shampoo/distributor/gpu_tests/``).  Also the DDP corner
+cases of ``shampoo_ddp_distributor_test.py:318-362, 782-858``: ranks without blocks, parameters
+without gradients, layers that never receive one."""
+
+import pytest
+import torch
+
+from dist_utils_for_tests import run_distributed
+from ref_oracle import REF_DIR, reference_available
+
+needs_reference = pytest.mark.skipif(not reference_available(), reason="reference library is not installed under baseline/_ref")
+
+
+def _model():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(
+        torch.nn.Linear(12, 20, bias=True), torch.nn.ReLU(), torch.nn.Linear(20, 9, bias=False), torch.nn.ReLU(), torch.nn.Linear(9, 5)
+    )
+
+
+def _data(steps):
+    g = torch.Generator().manual_seed(3)
+    return [(torch.randn(8, 12, generator=g), torch.randint(0, 5, (8,), generator=g)) for _ in range(steps)]
+
+
+def _parity_worker(rank, world, strategy):
+    import sys
+
+    sys.path.insert(0, REF_DIR)
+    import distributed_shampoo as ref_lib
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy, fully_shard
+    from torch.distributed.tensor import DTensor
+
+    import optimizers_b200 as our_lib
+
+    def train(lib):
+        model = _model()
+        cpu = torch.device("cpu")
+        if strategy == "fsdp":
+            model = FSDP(model, use_orig_params=True, device_id=cpu)
+            cfg = lib.FSDPDistributedConfig(param_to_metadata=lib.compile_fsdp_parameter_metadata(model))
+        elif strategy == "hsdp":
+            mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+            model = FSDP(model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True, device_id=cpu)
+            cfg = lib.HSDPDistributedConfig(param_to_metadata=lib.compile_fsdp_parameter_metadata(model), device_mesh=mesh)
+        elif strategy == "fully_shard":
+            fully_shard(model, mesh=init_device_mesh("cpu", (world,)))
+            cfg = lib.FullyShardDistributedConfig()
+        else:
+            mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+            fully_shard(model, mesh=mesh)
+            cfg = lib.HybridShardDistributedConfig(device_mesh=mesh)
+        opt = lib.DistributedShampoo(
+            model.parameters(), lr=0.01, betas=(0.9, 0.999), epsilon=1e-8, max_preconditioner_dim=8,
+            precondition_frequency=2, start_preconditioning_step=2, weight_decay=1e-3,
+            grafting_config=lib.AdamPreconditionerConfig(), distributed_config=cfg,
+        )
+        for x, y in _data(6):
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+        local = [
+            (p.to_local() if isinstance(p, DTensor) else p).detach().clone() for p in model.parameters()
+        ]
+        state_keys = sorted(str(k) for s in opt.state_dict()["state"].values() for k in s)
+        return local, state_keys
+
+    theirs, their_keys = train(ref_lib)
+    ours, our_keys = train(our_lib)
+    return theirs, ours, their_keys, our_keys
+
+
+@needs_reference
+@pytest.mark.parametrize("strategy,world", [("fsdp", 2), ("hsdp", 4), ("fully_shard", 2), ("hybrid_shard", 4)])
+def test_sharded_distributor_matches_reference_bitwise(strategy, world):
+    for theirs, ours, their_keys, our_keys in run_distributed(_parity_worker, world, strategy):
+        assert len(theirs) == len(ours)
+        for a, b in zip(theirs, ours):
+            assert a.shape == b.shape and torch.equal(a, b), (a - b).abs().max()
+        assert their_keys == our_keys  # same per-rank block ids and state names
+
+
+def _ddp_corner_worker(rank, world, case):
+    import optimizers_b200 as lib
+
+    torch.manual_seed(0)
+    if case == "few_blocks":
+        # one parameter, one block: every rank but its owner holds no block at all
+        model = torch.nn.Sequential(torch.nn.Linear(6, 4, bias=False))
+    else:
+        model = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.ReLU(), torch.nn.Linear(8, 4), torch.nn.Linear(4, 3))
+    def make(cfg):
+        return lib.DistributedShampoo(
+            model.parameters(), lr=0.01, betas=(0.9, 0.999), epsilon=1e-8, max_preconditioner_dim=8,
+            precondition_frequency=2, start_preconditioning_step=2, grafting_config=lib.AdaGradPreconditionerConfig(epsilon=1e-8),
+            distributed_config=cfg,
+        )
+
+    opt = make(lib.DDPDistributedConfig(communication_dtype=torch.float32, num_trainers_per_group=world))
+    g = torch.Generator().manual_seed(5)
+    for step in range(5):
+        x = torch.randn(8, 6, generator=g)
+        opt.zero_grad(set_to_none=True)
+        if case == "dead_layer":
+            out = model[1](model[0](x))
+            out = model[2](out)  # the last layer never takes part: its gradients stay None
+        else:
+            out = model(x)
+        out.square().mean().backward()
+        if case == "missing_grads" and step % 2 == 1:
+            # gradients vanish on some steps (same on every rank), as under gradient accumulation masks
+            list(model.parameters())[0].grad = None
+        opt.step()
+    return [p.detach().clone() for p in model.parameters()]
+
+
+def _single_corner(case):
+    """The same training loop on one process with the single-device distributor."""
+    import optimizers_b200 as lib
+
+    class _Stub:
+        pass
+
+    torch.manual_seed(0)
+    if case == "few_blocks":
+        model = torch.nn.Sequential(torch.nn.Linear(6, 4, bias=False))
+    else:
+        model = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.ReLU(), torch.nn.Linear(8, 4), torch.nn.Linear(4, 3))
+    opt = lib.DistributedShampoo(
+        model.parameters(), lr=0.01, betas=(0.9, 0.999), epsilon=1e-8, max_preconditioner_dim=8,
+        precondition_frequency=2, start_preconditioning_step=2, grafting_config=lib.AdaGradPreconditionerConfig(epsilon=1e-8),
+    )
+    g = torch.Generator().manual_seed(5)
+    for step in range(5):
+        x = torch.randn(8, 6, generator=g)
+        opt.zero_grad(set_to_none=True)
+        if case == "dead_layer":
+            out = model[2](model[1](model[0](x)))
+        else:
+            out = model(x)
+        out.square().mean().backward()
+        if case == "missing_grads" and step % 2 == 1:
+            list(model.parameters())[0].grad = None
+        opt.step()
+    return [p.detach().clone() for p in model.parameters()]
+
+
+@pytest.mark.parametrize("case,world", [("few_blocks", 3), ("missing_grads", 2), ("dead_layer", 2)])
+def test_ddp_ranks_without_blocks_and_parameters_without_gradients(case, world):
+    ref = _single_corner(case)
+    for params in run_distributed(_ddp_corner_worker, world, case):
+        for a, b in zip(ref, params):
+            assert torch.equal(a, b), (a - b).abs().max()
