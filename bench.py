@@ -200,11 +200,13 @@ def build_optimizer(impl: str, model, world: int, args, mesh=None):
     else:
         import optimizers_b200 as lib
 
-        fused = world > 1 and args.comm == "p2p" and args.backend != "torch" and mesh is None
+        p2p = world > 1 and args.comm == "p2p" and args.backend != "torch"
         extra = {
             "native_runtime_config": lib.NativeRuntimeConfig(
-                backend=args.backend, gemm_mode=args.gemm_mode, comm_path="p2p" if fused else "nccl",
-                fuse_gradient_reduction=fused,
+                backend=args.backend, gemm_mode=args.gemm_mode, comm_path="p2p" if p2p else "nccl",
+                # DDP: owners pull and sum the peers' gradients in the prologue kernel; under HSDP the
+                # FSDP wrapper has already reduced them, only the all-gather of the directions is fused
+                fuse_gradient_reduction=p2p and mesh is None,
             )
         }
     if mesh is not None:
@@ -464,7 +466,9 @@ def main() -> None:
                 "seq_len": SEQ,
                 "parallelism": (f"hsdp{world} (replicate {world // min(world, 4)} x shard {min(world, 4)})" if hsdp
                                 else f"dp{world}") if world > 1 else "single",
-                "comm": ("p2p fused reduce-scatter + all-gather kernels" if fused_comm else "nccl") if world > 1 else "none",
+                "comm": ("p2p fused reduce-scatter + all-gather kernels" if fused_comm
+                         else "p2p all-gather of the directions over the replicate group (fused into the epilogue kernel)"
+                         if (hsdp and args.impl == "ours" and args.comm == "p2p" and args.backend != "torch") else "nccl") if world > 1 else "none",
                 "optimizer": "DistributedShampoo max_preconditioner_dim=2048 precondition_frequency=100 AdaGrad grafting, fp32 factors",
                 "gemm_mode": args.gemm_mode if args.impl == "ours" else "fp32 (cuBLAS)",
                 "l2_policy": "working set (params, grads, optimizer state, activations: several GB) exceeds the 126 MB L2",

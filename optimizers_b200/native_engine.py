@@ -24,8 +24,9 @@ Coverage: fp32 parameters on CUDA, blocks of order 1 or 2 (and contiguous order-
 root-inverse Shampoo) with every dim preconditioned,
 root-inverse, eigendecomposed, KL or eigenvalue-corrected Shampoo with no / SGD / AdaGrad / RMSprop / Adam grafting,
 any weight decay type,
-classic momentum, GPA / Schedule-Free, single-device and DDP distributors (NCCL all-gather, or
-peer-to-peer stores and loads over NVLink with ``comm_path="p2p"``).  Anything else makes
+classic momentum, GPA / Schedule-Free, every distributor; the DDP family (DDP, and the replicate
+groups of HSDP and hybrid shard) gathers the search directions with NCCL or, with
+``comm_path="p2p"``, by stores into the peers' buffers over NVLink.  Anything else makes
 ``build_native_engine`` return ``None`` (torch step) or raise with ``backend="native"``.
 """
 
@@ -212,8 +213,12 @@ class NativeGroupEngine:
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._status_event: torch.cuda.Event | None = None
         self._ddp = isinstance(group[DISTRIBUTED_CONFIG], DDPDistributedConfig)
-        self._p2p = type(group[DISTRIBUTED_CONFIG]) is DDPDistributedConfig and cfg.comm_path == "p2p"
-        self._pull = self._p2p and cfg.fuse_gradient_reduction
+        # Every distributor of the DDP family (DDP itself, and the replicate groups of the HSDP and
+        # hybrid-shard distributors) can deliver its search directions by peer stores instead of an
+        # all-gather.  The fused gradient reduction only exists where the optimizer sees replicated,
+        # unreduced gradients: plain DDP (the sharded wrappers reduce-scatter their own).
+        self._p2p = self._ddp and cfg.comm_path == "p2p"
+        self._pull = self._p2p and cfg.fuse_gradient_reduction and type(group[DISTRIBUTED_CONFIG]) is DDPDistributedConfig
         self._comm_params = bool(getattr(group[DISTRIBUTED_CONFIG], "communicate_params", False)) and self._ddp
         self._gemm_push = self._p2p and cfg.fuse_direction_push and not self._soap and not self._comm_params
         self.gemm_push_steps = 0  # steps whose all-gather ran from the GEMM epilogue

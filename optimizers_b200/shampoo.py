@@ -817,8 +817,10 @@ class DistributedShampoo(Optimizer):
             if engine is not None and engine.mode_switch(coeff):
                 rec[TRAIN_MODE].fill_(to_train)
                 continue
-            delta = torch._foreach_sub(rec[WEIGHT_BUFFER_LIST], rec[DISTRIBUTOR].local_blocked_params)
-            torch._foreach_mul_(delta, (1 - mu_y) if to_train else (1 - torch.reciprocal(mu_y)))
+            delta: list[torch.Tensor] = []
+            if rec[WEIGHT_BUFFER_LIST]:  # a rank that owns no block still joins the distributor's collective
+                delta = list(torch._foreach_sub(rec[WEIGHT_BUFFER_LIST], rec[DISTRIBUTOR].local_blocked_params))
+                torch._foreach_mul_(delta, (1 - mu_y) if to_train else (1 - torch.reciprocal(mu_y)))
             rec[DISTRIBUTOR].update_params(blocked_search_directions=tuple(delta), use_masked_tensors=False)
             rec[TRAIN_MODE].fill_(to_train)
 

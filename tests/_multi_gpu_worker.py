@@ -158,6 +158,10 @@ def sharded_main() -> None:
     if comm_path == "p2p":
         for rec in opt._per_group_state_lists:
             d = rec["distributor"]
+            if getattr(d, "_gather_grads_ctx", None) is None:
+                # DDP-family distributor: the engine stores the directions into the peers' buffers
+                assert rec["native_engine"] is None or rec["native_engine"]._p2p
+                continue
             if d._gather_grads_ctx._group_size > 1:  # a shard group of one rank has nothing to exchange
                 assert d._gather_grads_ctx._p2p and d._redistribute_ctx._p2p
             d._gather_grads_ctx.check_status()

@@ -138,3 +138,42 @@ def test_hybrid_shard_lossless_matches_single_device(strategy):
     for full, _ in run_distributed(_fully_shard_worker, 4, strategy, 1, (2, 2)):
         for a, b in zip(ref, full):
             assert torch.equal(a, b)
+
+
+def _gpa_idle_rank_worker(rank, world):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import optimizers_b200 as lib
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(12, 20, bias=False), torch.nn.ReLU(), torch.nn.Linear(20, 9, bias=False))
+    if world > 1:
+        fully_shard(model, mesh=init_device_mesh("cpu", (world,)))
+        extra = {"distributed_config": lib.FullyShardDistributedConfig(param_assignment_strategy=lib.FSDPParamAssignmentStrategy.ROUND_ROBIN)}
+    else:
+        extra = {}
+    opt = lib.DistributedShampoo(
+        model.parameters(), lr=0.01, max_preconditioner_dim=8, precondition_frequency=2, start_preconditioning_step=2,
+        grafting_config=lib.AdaGradPreconditionerConfig(epsilon=1e-8),
+        iterate_averaging_config=lib.GeneralizedPrimalAveragingConfig(eval_interp_coeff=0.9, train_interp_coeff=0.7), **extra,
+    )
+    opt.train()
+    g = torch.Generator().manual_seed(1)
+    for _ in range(4):
+        x = torch.randn(8, 12, generator=g)
+        opt.zero_grad()
+        model(x).square().sum().backward()
+        opt.step()
+    opt.eval()  # a rank that owns no parameter still takes part in the switch's collective
+    return [(p.full_tensor() if world > 1 else p).detach().clone() for p in model.parameters()]
+
+
+def test_primal_averaging_mode_switch_with_a_rank_that_owns_nothing():
+    """Two parameters, four ranks, ROUND_ROBIN ownership: two ranks hold no block; train()/eval()
+    and the steps must neither fail on them nor change the result (four ranks: the gradient
+    average of identical shards is exact)."""
+    ref = _gpa_idle_rank_worker(0, 1)
+    for params in run_distributed(_gpa_idle_rank_worker, 4):
+        for a, b in zip(ref, params):
+            assert torch.equal(a, b), (a - b).abs().max()

@@ -103,3 +103,15 @@ def test_lossless_peer_memory_exchange_matches_all_to_all(tmp_path, strategy):
     # The exchange moves bits; the engine's norm reductions use atomics, so two runs agree to an ulp.
     for a, b in zip(torch.load(ref), torch.load(got)):
         assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (a - b).abs().max()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs (replicate groups of two)")
+@pytest.mark.parametrize("strategy", ["hsdp", "hybrid_shard"])
+def test_replicate_group_peer_push_matches_nccl_all_gather(tmp_path, strategy):
+    """HSDP / hybrid shard: the owners of a replicate group store their search directions straight
+    into the other members' gather buffers (comm_path="p2p") instead of the NCCL all-gather."""
+    ref, got = str(tmp_path / "ref.pt"), str(tmp_path / "got.pt")
+    _run(f"torch:{strategy}", 4, ref, 29555)
+    _run(f"native:{strategy}:p2p", 4, got, 29556)
+    for a, b in zip(torch.load(ref), torch.load(got)):
+        assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
