@@ -62,9 +62,11 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--backend", choices=["auto", "native", "torch"], default="native")
     ap.add_argument("--gemm-mode", choices=["tf32x3", "tf32"], default="tf32x3")
     ap.add_argument("--comm", choices=["p2p", "nccl"], default="p2p", help="multi-GPU path of this framework")
-    ap.add_argument("--parallelism", choices=["ddp", "hsdp"], default="ddp",
-                    help="N > 1: DDP distributor (default; the same strategy at every N) or the hybrid-sharded "
-                    "distributor over FSDP HYBRID_SHARD with a (N / min(N, 4)) x min(N, 4) replicate x shard mesh")
+    ap.add_argument("--parallelism", choices=["ddp", "hsdp"], default="hsdp",
+                    help="N > 1: the hybrid-sharded distributor over FSDP HYBRID_SHARD with a (N / min(N, 4)) x min(N, 4) "
+                    "replicate x shard mesh (default: the benchmark configuration, 2 x 4 on eight GPUs) or the DDP distributor; "
+                    "the other one is measured as well and reported under other_parallelism")
+    ap.add_argument("--single-parallelism", action="store_true", help="N > 1: measure only --parallelism")
     ap.add_argument("--model", choices=["fused", "plain"], default="fused",
                     help="this framework's arm: its GPT-2 with the fused norm / LM-head-loss kernels, or the plain "
                     "PyTorch model that the reference arm always uses")
@@ -277,172 +279,215 @@ def main() -> None:
     torch.manual_seed(1234)
     torch.backends.cuda.matmul.allow_tf32 = False  # optimizer math of the reference stays fp32
     fused_model = args.impl == "ours" and args.model == "fused"
-    hsdp = world > 1 and args.parallelism == "hsdp"
-    fused_comm = args.impl == "ours" and world > 1 and args.comm == "p2p" and args.backend != "torch" and not hsdp
+    p2p_requested = args.impl == "ours" and world > 1 and args.comm == "p2p" and args.backend != "torch"
 
-    def build(use_fused_model: bool):
-        """Model, its training wrapper and the optimizer of one arm."""
-        if use_fused_model:
-            # Same architecture, initialisation and autocast numerics as make_gpt2; the normalisations
-            # and the LM head + cross-entropy run through this framework's CUDA kernels.
-            from optimizers_b200.models import GPT2, GPT2Config
+    def run_arm(parallelism: str, with_plain: bool) -> dict:
+        """Build model + optimizer under one parallelism, measure, and return the figures (maxima
+        over ranks)."""
+        hsdp = world > 1 and parallelism == "hsdp"
+        fused_comm = p2p_requested and not hsdp
 
-            model = GPT2(GPT2Config(n_layer=args.layers)).to(dev)
-        else:
-            model = make_gpt2(args.layers).to(dev)
-        train_model = model
-        mesh = None
-        # This framework's p2p path reduces the gradients inside the optimizer's prologue kernel
-        # (owners pull their blocks from peer memory), so the model is not wrapped in DDP there.
-        if hsdp:
-            from torch.distributed.device_mesh import init_device_mesh
-            from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy
+        def build(use_fused_model: bool):
+            """Model, its training wrapper and the optimizer of one arm."""
+            if use_fused_model:
+                # Same architecture, initialisation and autocast numerics as make_gpt2; the normalisations
+                # and the LM head + cross-entropy run through this framework's CUDA kernels.
+                from optimizers_b200.models import GPT2, GPT2Config
 
-            shard = min(world, 4)
-            mesh = init_device_mesh("cuda", (world // shard, shard), mesh_dim_names=("replicate", "shard"))
-            train_model = model = FSDP(
-                model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True,
-                device_id=local_rank,
-            )
-        elif world > 1 and not fused_comm:
-            train_model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
-        elif world > 1:
-            for p in model.parameters():
-                dist.broadcast(p.data, src=0)
-        opt = build_optimizer(args.impl, model, world, args, mesh)
-        if hasattr(opt, "train"):
-            opt.train()
-        return train_model, opt
+                model = GPT2(GPT2Config(n_layer=args.layers)).to(dev)
+            else:
+                model = make_gpt2(args.layers).to(dev)
+            train_model = model
+            mesh = None
+            # This framework's p2p path reduces the gradients inside the optimizer's prologue kernel
+            # (owners pull their blocks from peer memory), so the model is not wrapped in DDP there.
+            if hsdp:
+                from torch.distributed.device_mesh import init_device_mesh
+                from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy
 
-    B = args.batch
-    gen = torch.Generator().manual_seed(100 + rank)
-    n_batches = 8
-    host_tokens = [torch.randint(0, VOCAB, (B, SEQ + 1), generator=gen).pin_memory() for _ in range(n_batches)]
-    dev_tokens = [t.to(dev) for t in host_tokens]
+                shard = min(world, 4)
+                mesh = init_device_mesh("cuda", (world // shard, shard), mesh_dim_names=("replicate", "shard"))
+                train_model = model = FSDP(
+                    model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True,
+                    device_id=local_rank,
+                )
+            elif world > 1 and not fused_comm:
+                train_model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
+            elif world > 1:
+                for p in model.parameters():
+                    dist.broadcast(p.data, src=0)
+            opt = build_optimizer(args.impl, model, world, args, mesh)
+            if hasattr(opt, "train"):
+                opt.train()
+            return train_model, opt
 
-    def barrier() -> None:
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+        B = args.batch
+        gen = torch.Generator().manual_seed(100 + rank)
+        n_batches = 8
+        host_tokens = [torch.randint(0, VOCAB, (B, SEQ + 1), generator=gen).pin_memory() for _ in range(n_batches)]
+        dev_tokens = [t.to(dev) for t in host_tokens]
 
-    def set_step_counter(opt, value: int) -> None:
-        # Resume-style preset of the shared step counter (a CPU tensor aliased under every parameter).
-        for state in opt.state.values():
-            if "step" in state:
-                state["step"].fill_(value)
-                break
-
-    def measure(train_model, opt, steps: int, warmup: int, with_refresh: bool) -> dict:
-        opt_start = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-        opt_stop = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-
-        def train_step(tokens: torch.Tensor, k: int | None = None) -> torch.Tensor:
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss = train_model(tokens[:, :-1], tokens[:, 1:])
-            loss.backward()
-            if k is not None:
-                opt_start[k].record()
-            opt.step()
-            if k is not None:
-                opt_stop[k].record()
-            opt.zero_grad(set_to_none=not fused_comm)
-            return loss
-
-        # ---- warm-up (untimed); the first step performs the first (cold) refresh
-        first_ms = None
-        for i in range(max(warmup, 1)):
+        def barrier() -> None:
+            if world > 1:
+                dist.barrier()
             torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            train_step(dev_tokens[i % n_batches])
-            torch.cuda.synchronize()
-            if i == 0:
-                first_ms = (time.perf_counter() - t0) * 1e3
 
-        # ---- device-timed region: K steps, inputs resident on the device
-        barrier()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(steps):
-            train_step(dev_tokens[i % n_batches], i)
-        stop.record()
-        barrier()
-        out = {
-            "first_step_ms": first_ms,
-            "steady_ms": start.elapsed_time(stop) / steps,
-            "optimizer_ms": sum(a.elapsed_time(b) for a, b in zip(opt_start, opt_stop)) / steps,
-        }
-        if not with_refresh:
+        def set_step_counter(opt, value: int) -> None:
+            # Resume-style preset of the shared step counter (a CPU tensor aliased under every parameter).
+            for state in opt.state.values():
+                if "step" in state:
+                    state["step"].fill_(value)
+                    break
+
+        def measure(train_model, opt, steps: int, warmup: int, with_refresh: bool) -> dict:
+            opt_start = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            opt_stop = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+
+            def train_step(tokens: torch.Tensor, k: int | None = None) -> torch.Tensor:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss = train_model(tokens[:, :-1], tokens[:, 1:])
+                loss.backward()
+                if k is not None:
+                    opt_start[k].record()
+                opt.step()
+                if k is not None:
+                    opt_stop[k].record()
+                opt.zero_grad(set_to_none=not fused_comm)
+                return loss
+
+            # ---- warm-up (untimed); the first step performs the first (cold) refresh
+            first_ms = None
+            for i in range(max(warmup, 1)):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                train_step(dev_tokens[i % n_batches])
+                torch.cuda.synchronize()
+                if i == 0:
+                    first_ms = (time.perf_counter() - t0) * 1e3
+
+            # ---- device-timed region: K steps, inputs resident on the device
+            barrier()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(steps):
+                train_step(dev_tokens[i % n_batches], i)
+            stop.record()
+            barrier()
+            out = {
+                "first_step_ms": first_ms,
+                "steady_ms": start.elapsed_time(stop) / steps,
+                "optimizer_ms": sum(a.elapsed_time(b) for a, b in zip(opt_start, opt_stop)) / steps,
+            }
+            if not with_refresh:
+                return out
+
+            # ---- end-to-end region: pinned host tokens in, loss out, every step
+            barrier()
+            h2d = d2h = 0
+            e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_wall = time.perf_counter()
+            e_start.record()
+            last = 0.0
+            for i in range(steps):
+                src = host_tokens[i % n_batches]
+                tokens = src.to(dev, non_blocking=True)
+                h2d += src.numel() * src.element_size()
+                loss = train_step(tokens)
+                last = loss.item()
+                d2h += loss.element_size()
+            e_stop.record()
+            barrier()
+            out["e2e_ms"] = max(e_start.elapsed_time(e_stop), (time.perf_counter() - t_wall) * 1e3 if world == 1 else 0.0) / steps
+            out["h2d"], out["d2h"], out["final_loss"] = h2d // max(steps, 1), d2h // max(steps, 1), last
+
+            # ---- one refresh step of the run in progress (every inverse root recomputed), device-timed
+            set_step_counter(opt, 3 * PRECOND_FREQ - 1)
+            barrier()
+            r_start, r_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r_start.record()
+            train_step(dev_tokens[0])
+            r_stop.record()
+            barrier()
+            out["refresh_ms"] = r_start.elapsed_time(r_stop)
             return out
 
-        # ---- end-to-end region: pinned host tokens in, loss out, every step
-        barrier()
-        h2d = d2h = 0
-        e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t_wall = time.perf_counter()
-        e_start.record()
-        last = 0.0
-        for i in range(steps):
-            src = host_tokens[i % n_batches]
-            tokens = src.to(dev, non_blocking=True)
-            h2d += src.numel() * src.element_size()
-            loss = train_step(tokens)
-            last = loss.item()
-            d2h += loss.element_size()
-        e_stop.record()
-        barrier()
-        out["e2e_ms"] = max(e_start.elapsed_time(e_stop), (time.perf_counter() - t_wall) * 1e3 if world == 1 else 0.0) / steps
-        out["h2d"], out["d2h"], out["final_loss"] = h2d // max(steps, 1), d2h // max(steps, 1), last
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        train_model, opt = build(fused_model)
+        model_launches = 0
+        if fused_model:
+            from optimizers_b200.models import fused_ops
 
-        # ---- one refresh step of the run in progress (every inverse root recomputed), device-timed
-        set_step_counter(opt, 3 * PRECOND_FREQ - 1)
-        barrier()
-        r_start, r_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        r_start.record()
-        train_step(dev_tokens[0])
-        r_stop.record()
-        barrier()
-        out["refresh_ms"] = r_start.elapsed_time(r_stop)
-        return out
+            model_launches = -fused_ops.launch_count
+        m = measure(train_model, opt, args.steps, args.warmup, with_refresh=True)
+        if fused_model:
+            # launches of the model kernels per step, from the whole measured run
+            steps_run = max(args.warmup, 1) + 2 * args.steps + 1
+            model_launches = (model_launches + fused_ops.launch_count) // steps_run
+        clocks = sampler.stop() if rank == 0 else {}
+        launches_per_step = (count_native_launches(opt) + model_launches) if args.impl == "ours" else 0
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    train_model, opt = build(fused_model)
-    model_launches = 0
-    if fused_model:
-        from optimizers_b200.models import fused_ops
+        plain = None
+        if with_plain and args.impl == "ours" and fused_model and not args.no_plain:
+            del train_model, opt
+            torch.cuda.empty_cache()
+            torch.manual_seed(1234)
+            plain_model, plain_opt = build(False)
+            plain = measure(plain_model, plain_opt, args.steps, args.warmup, with_refresh=False)
+            del plain_model, plain_opt
 
-        model_launches = -fused_ops.launch_count
-    m = measure(train_model, opt, args.steps, args.warmup, with_refresh=True)
-    if fused_model:
-        # launches of the model kernels per step, from the whole measured run
-        steps_run = max(args.warmup, 1) + 2 * args.steps + 1
-        model_launches = (model_launches + fused_ops.launch_count) // steps_run
-    clocks = sampler.stop() if rank == 0 else {}
-    launches_per_step = (count_native_launches(opt) + model_launches) if args.impl == "ours" else 0
+        keys = ["steady_ms", "optimizer_ms", "e2e_ms", "refresh_ms", "first_step_ms"]
+        times = torch.tensor([m[k] for k in keys] + ([plain["steady_ms"], plain["optimizer_ms"]] if plain else [0.0, 0.0]),
+                             device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        steady_ms, optimizer_ms, e2e_ms, refresh_ms, first_ms, plain_ms, plain_opt_ms = times.tolist()
 
-    plain = None
-    if args.impl == "ours" and fused_model and not args.no_plain and not hsdp:
-        del train_model, opt
-        torch.cuda.empty_cache()
-        torch.manual_seed(1234)
-        plain_model, plain_opt = build(False)
-        plain = measure(plain_model, plain_opt, args.steps, args.warmup, with_refresh=False)
-        del plain_model, plain_opt
+        def amortized(step_ms: float) -> float:
+            return step_ms + max(refresh_ms - steady_ms, 0.0) / PRECOND_FREQ
 
-    keys = ["steady_ms", "optimizer_ms", "e2e_ms", "refresh_ms", "first_step_ms"]
-    times = torch.tensor([m[k] for k in keys] + ([plain["steady_ms"], plain["optimizer_ms"]] if plain else [0.0, 0.0]),
-                         device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    steady_ms, optimizer_ms, e2e_ms, refresh_ms, first_ms, plain_ms, plain_opt_ms = times.tolist()
+        tokens_per_step = B * SEQ * world
+        value = tokens_per_step / (amortized(steady_ms) / 1e3)
+        e2e_value = tokens_per_step / (amortized(e2e_ms) / 1e3)
+        tokens = B * SEQ * world
+        return {
+            "hsdp": hsdp, "fused_comm": fused_comm, "steady_ms": steady_ms, "optimizer_ms": optimizer_ms, "e2e_ms": e2e_ms,
+            "refresh_ms": refresh_ms, "first_ms": first_ms, "plain": (plain_ms, plain_opt_ms) if plain is not None else None,
+            "amortized_ms": amortized(steady_ms), "e2e_amortized_ms": amortized(e2e_ms),
+            "value": tokens / (amortized(steady_ms) / 1e3), "e2e_value": tokens / (amortized(e2e_ms) / 1e3),
+            "final_loss": m["final_loss"], "h2d": m["h2d"], "d2h": m["d2h"], "clocks": clocks,
+            "launches_per_step": launches_per_step, "batch": B,
+        }
+
+    def describe(r: dict) -> tuple[str, str]:
+        if world == 1:
+            return "single", "none"
+        if r["hsdp"]:
+            par = f"hsdp{world} (replicate {world // min(world, 4)} x shard {min(world, 4)})"
+            comm = ("FSDP reduce-scatter (NCCL); directions all-gathered over the replicate group by peer stores fused into the epilogue kernel"
+                    if p2p_requested else "nccl")
+        else:
+            par = f"dp{world}"
+            comm = "p2p fused reduce-scatter + all-gather kernels" if r["fused_comm"] else "nccl"
+        return par, comm
+
+    main_par = args.parallelism if world > 1 else "ddp"
+    r = run_arm(main_par, with_plain=True)
+    other = None
+    if world > 1 and not args.single_parallelism:
+        other = run_arm("ddp" if main_par == "hsdp" else "hsdp", with_plain=False)
+    B = r["batch"]
+    value, e2e_value = r["value"], r["e2e_value"]
+    steady_ms, optimizer_ms, e2e_ms, refresh_ms, first_ms = (r[k] for k in ("steady_ms", "optimizer_ms", "e2e_ms", "refresh_ms", "first_ms"))
+    clocks, launches_per_step, hsdp, fused_comm = r["clocks"], r["launches_per_step"], r["hsdp"], r["fused_comm"]
+    plain = r["plain"]
+    plain_ms, plain_opt_ms = plain if plain is not None else (0.0, 0.0)
+    m = {"final_loss": r["final_loss"], "h2d": r["h2d"], "d2h": r["d2h"]}
 
     def amortized(step_ms: float) -> float:
         return step_ms + max(refresh_ms - steady_ms, 0.0) / PRECOND_FREQ
 
-    tokens_per_step = B * SEQ * world
-    value = tokens_per_step / (amortized(steady_ms) / 1e3)
-    e2e_value = tokens_per_step / (amortized(e2e_ms) / 1e3)
     if rank == 0:
         out = {
             "metric": "train tokens/sec (GPT-2 124M, Distributed Shampoo), preconditioner refresh amortised over precondition_frequency steps",
@@ -464,11 +509,8 @@ def main() -> None:
                 else "plain PyTorch modules",
                 "global_batch": B * world,
                 "seq_len": SEQ,
-                "parallelism": (f"hsdp{world} (replicate {world // min(world, 4)} x shard {min(world, 4)})" if hsdp
-                                else f"dp{world}") if world > 1 else "single",
-                "comm": ("p2p fused reduce-scatter + all-gather kernels" if fused_comm
-                         else "p2p all-gather of the directions over the replicate group (fused into the epilogue kernel)"
-                         if (hsdp and args.impl == "ours" and args.comm == "p2p" and args.backend != "torch") else "nccl") if world > 1 else "none",
+                "parallelism": describe(r)[0],
+                "comm": describe(r)[1],
                 "optimizer": "DistributedShampoo max_preconditioner_dim=2048 precondition_frequency=100 AdaGrad grafting, fp32 factors",
                 "gemm_mode": args.gemm_mode if args.impl == "ours" else "fp32 (cuBLAS)",
                 "l2_policy": "working set (params, grads, optimizer state, activations: several GB) exceeds the 126 MB L2",
@@ -492,6 +534,13 @@ def main() -> None:
             },
             "gpu_launches": launches_per_step * args.steps,
         }
+        if other is not None:
+            out["other_parallelism"] = {
+                "parallelism": describe(other)[0], "comm": describe(other)[1], "value": other["value"], "unit": "tokens/s",
+                "amortized_ms_per_step": other["amortized_ms"], "steady_ms_per_step": other["steady_ms"],
+                "optimizer_step_ms": other["optimizer_ms"], "refresh_step_ms": other["refresh_ms"],
+                "e2e_value": other["e2e_value"],
+            }
         if plain is not None:
             out["plain_model"] = {
                 "what": "this framework's optimizer under the plain PyTorch GPT-2 of the reference arm (steady steps)",
