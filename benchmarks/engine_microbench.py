@@ -42,6 +42,12 @@ def main() -> None:
     ap.add_argument("--refreshes", type=int, default=2)
     ap.add_argument("--backend", default="native")
     ap.add_argument("--gemm-mode", default="tf32x3")
+    ap.add_argument("--fuse-grads", action="store_true",
+                    help="with --comm p2p: owners sum the peers' gradients inside the prologue kernel (the gradients "
+                    "live in the peer-addressable arena)")
+    ap.add_argument("--phases", action="store_true",
+                    help="also print the device time between the phase boundaries of the native step (max over ranks) "
+                    "and the bytes that cross NVLink per rank")
     ap.add_argument("--comm", choices=["nccl", "p2p"], default="nccl",
                     help="under torchrun (N > 1, DDP distributor, bf16 search directions): NCCL all-gather or the "
                     "epilogue's stores into every peer's gather buffer")
@@ -84,7 +90,8 @@ def main() -> None:
         extra = {}
         if args.impl == "ours":
             extra["native_runtime_config"] = lib.NativeRuntimeConfig(
-                backend=args.backend, gemm_mode=args.gemm_mode, comm_path=args.comm if world > 1 else "nccl"
+                backend=args.backend, gemm_mode=args.gemm_mode, comm_path=args.comm if world > 1 else "nccl",
+                fuse_gradient_reduction=args.fuse_grads and world > 1 and args.comm == "p2p",
             )
         if world > 1:
             extra["distributed_config"] = lib.DDPDistributedConfig(
@@ -109,9 +116,14 @@ def main() -> None:
         step_counter = next(s["step"] for s in opt.state.values() if "step" in s)
         step_counter.fill_(period - 1)
 
+    fused_grads = args.impl == "ours" and args.optimizer != "gpa" and args.fuse_grads and world > 1 and args.comm == "p2p"
+
     def one_step(i: int) -> float:
         for p, g in zip(params, grads[i % 2]):
-            p.grad = g
+            if fused_grads:
+                p.grad.copy_(g)  # .grad is the parameter's view of the shared gradient arena
+            else:
+                p.grad = g
         flush.zero_()
         if world > 1:
             dist.barrier()  # ranks enter the step together
@@ -149,6 +161,30 @@ def main() -> None:
     if args.impl == "ours" and args.optimizer != "gpa":
         eng = opt._per_group_state_lists[0].get("native_engine")
         out["native_launches_per_step"] = eng.launches_per_step if eng is not None else 0
+    if args.phases and args.impl == "ours" and args.optimizer != "gpa":
+        eng = opt._per_group_state_lists[0].get("native_engine")
+        if eng is not None:
+            samples: dict[str, list[float]] = {}
+            for i in range(args.steps):
+                eng.phase_events = []
+                one_step(i)
+                marks = eng.phase_events
+                for (_, a), (name, b) in zip(marks, marks[1:]):
+                    samples.setdefault(name, []).append(a.elapsed_time(b))
+            eng.phase_events = None
+            names = list(samples)
+            med = torch.tensor([statistics.median(samples[n]) for n in names], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(med, op=dist.ReduceOp.MAX)
+            out["phase_ms"] = {n: round(v, 4) for n, v in zip(names, med.tolist())}
+            # NVLink bytes per rank and step: an owner pulls the other ranks' fp32 gradients of its blocks
+            # and stores its bf16 directions into the other ranks' gather buffers
+            owned = nb / world
+            elems = owned * d * d
+            out["nvlink_bytes_per_rank"] = {
+                "gradient_pull_fp32": int(elems * 4 * (world - 1)) if fused_grads else 0,
+                "direction_push_bf16": int(elems * 2 * (world - 1)) if (world > 1 and args.comm == "p2p") else 0,
+            }
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

@@ -197,6 +197,9 @@ class NativeGroupEngine:
             RootInvKLShampooPreconditionerConfig, EigendecomposedKLShampooPreconditionerConfig
         )
         self.launches_per_step = 0
+        # Diagnostics: assign a list to ``phase_events`` and every step appends (name, CUDA event)
+        # pairs at the boundaries of its phases (benchmarks/engine_microbench.py --phases).
+        self.phase_events: list[tuple[str, torch.cuda.Event]] | None = None
 
         gc = group[GRAFTING_CONFIG]
         if gc is None:
@@ -411,6 +414,12 @@ class NativeGroupEngine:
                 table.extend(b + cursor * 4 for b in bases)
                 cursor += p.numel()
             self._grad_ptrs_dev = torch.tensor(table, dtype=torch.int64, device=self._device)
+
+    def _mark(self, name: str) -> None:
+        if self.phase_events is not None:
+            event = torch.cuda.Event(enable_timing=True)
+            event.record()
+            self.phase_events.append((name, event))
 
     def _peer_barrier(self, which: int) -> None:
         self._barrier_seq += 1
@@ -779,10 +788,12 @@ class NativeGroupEngine:
             self.launches_per_step = 0
             self._finish_update(scaled)
             return
+        self._mark("start")
         if self._p2p:
             # Every rank has finished its backward pass (its gradients are complete) and has applied
             # the previous step's directions (its gather buffer may be overwritten).
             self._peer_barrier(0)
+            self._mark("barrier_entry")
         t = int(step.item())
         launches = 0
 
@@ -806,14 +817,17 @@ class NativeGroupEngine:
             self._arena.world if self._pull else 0, 1.0 / self._arena.world if self._pull else 1.0,
         )
         launches += 2
+        self._mark("grad_prologue")
         if not self._soap and self._kl_plan is not None:
             ext.run_gemm_plan(*self._kl_plan, 1.0, 0.0, self._split, self._status)
             launches += 1
         ext.run_gemm_plan(*self._syrk_plan, plist._weighting_factor, plist._beta2, self._split, self._status)
         launches += 1
+        self._mark("factor_syrk")
 
         if refresh:
             self._refresh(self._active_blocks)
+            self._mark("refresh")
 
         if self._soap:
             launches += self._soap_step(plist, graft_only)
@@ -833,6 +847,7 @@ class NativeGroupEngine:
                 ext.run_gemm_plan(*self._gemm2_plan, 1.0, 0.0, self._split, self._status)
             launches += 1
 
+        self._mark("preconditioner_gemms")
         if use_push:
             launches += self._push_scales(has_grafting)
             self.gemm_push_steps += 1
@@ -849,6 +864,7 @@ class NativeGroupEngine:
             self._gather_bases if self._p2p else [], self._comm_params,
         )
         launches += 1
+        self._mark("direction_epilogue")
         self.launches_per_step = launches
         self._finish_update()
 
@@ -945,10 +961,12 @@ class NativeGroupEngine:
             if self.launches_per_step == 0:
                 self._peer_barrier(0)
             self._peer_barrier(1)
+            self._mark("barrier_exit")
             self.launches_per_step += 1
             recv = self._gather_local
         else:
             dist_._all_gather()
+            self._mark("all_gather")
             recv = dist_._global_dist_buffer
         sel = dist_._global_grad_selector
         if self._gather_for != sel:
@@ -974,6 +992,7 @@ class NativeGroupEngine:
                 self._ext.gathered_apply_scaled(*self._gather_table, self._comm_dtype_code, scaled[0], scaled[1], guard)
             else:
                 self._ext.gathered_apply(*self._gather_table, self._comm_dtype_code, self._comm_params, guard)
+            self._mark("gathered_apply")
             self.launches_per_step += 1
         if hasattr(dist_, "_write_back"):
             dist_._write_back()

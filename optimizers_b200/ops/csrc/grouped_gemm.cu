@@ -195,11 +195,93 @@ grouped_gemm_kernel(const GemmProblem* __restrict__ problems, const GemmTile* __
           const bool diag_chunk = diag_tile && c == q;
           float v[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kBN + c * 32, v);
+          float sq_chunk = 0.f;
+          // Fast path: the thread that holds row (row0 + lane) of the accumulator stores its 32
+          // consecutive columns itself with 16-byte accesses (C, then the (hi, lo) pair), and
+          // stores the transposed copy of a symmetric result one column at a time, where the 32
+          // lanes are 32 consecutive addresses.  No staging through shared memory.  It needs a full
+          // chunk, 16-byte alignment of every row segment and none of the per-element layouts
+          // (packed triangle, peer push, the symmetrised diagonal chunk).
+          const bool fast_c = (flags & kFlagNoC) || ((ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(Cp) & 15) == 0);
+          const bool fast_d = !(flags & kFlagSplitOut) ||
+                              ((ldd & 3) == 0 && ((reinterpret_cast<uintptr_t>(Dhi) | reinterpret_cast<uintptr_t>(Dlo)) & 15) == 0);
+          if (col0 + 32 <= N && !(flags & kFlagPackedC) && !do_push && !diag_chunk && fast_c && fast_d) {
+            const int row = row0 + lane;
+            if (row < M) {
+              const bool write_c = !(flags & kFlagNoC);
+              if (flags & kFlagSquareAcc) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] *= v[j];
+              }
+              if (write_c && beta != 0.f) {
+                const float4* src = reinterpret_cast<const float4*>(Cp + static_cast<long long>(row) * ldc + col0);
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                  const float4 o = src[j4];
+                  v[4 * j4 + 0] = alpha * v[4 * j4 + 0] + beta * o.x;
+                  v[4 * j4 + 1] = alpha * v[4 * j4 + 1] + beta * o.y;
+                  v[4 * j4 + 2] = alpha * v[4 * j4 + 2] + beta * o.z;
+                  v[4 * j4 + 3] = alpha * v[4 * j4 + 3] + beta * o.w;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] *= alpha;
+              }
+              if (flags & (kFlagAddDiag | kFlagTrace)) {
+                const int dj = row - col0;  // position of the diagonal entry in this segment, if any
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j == dj) {
+                    if (flags & kFlagAddDiag) v[j] += gamma;
+                    if (flags & kFlagTrace) tr += v[j];
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) sq_chunk = fmaf(v[j], v[j], sq_chunk);
+              if (write_c) {
+                float4* dst = reinterpret_cast<float4*>(Cp + static_cast<long long>(row) * ldc + col0);
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) dst[j4] = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+              }
+              if (flags & kFlagSplitOut) {
+                float4* dh = reinterpret_cast<float4*>(Dhi + static_cast<long long>(row) * ldd + col0);
+                float4* dl = reinterpret_cast<float4*>(Dlo + static_cast<long long>(row) * ldd + col0);
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                  float h[4], l[4];
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    h[k] = tf32_round(v[4 * j4 + k]);
+                    l[k] = v[4 * j4 + k] - h[k];
+                  }
+                  dh[j4] = make_float4(h[0], h[1], h[2], h[3]);
+                  dl[j4] = make_float4(l[0], l[1], l[2], l[3]);
+                }
+              }
+              if (mirror) {
+                // (row, col0 + j) -> (col0 + j, row): for a fixed j the warp writes 32 consecutive floats
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const long long oc = static_cast<long long>(col0 + j) * ldc + row;
+                  if (write_c) Cp[oc] = v[j];
+                  if (flags & kFlagSplitOut) {
+                    const long long od = static_cast<long long>(col0 + j) * ldd + row;
+                    const float hi = tf32_round(v[j]);
+                    Dhi[od] = hi;
+                    Dlo[od] = v[j] - hi;
+                  }
+                }
+                sq_chunk *= 2.f;
+              }
+            }
+            sq += sq_chunk;
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) st[lane * kStagePitch + j] = v[j];
           __syncwarp();
           const int col = col0 + lane;
-          float sq_chunk = 0.f;
           if (col < N) {
             const int rows = min(32, M - row0);
             const bool packed = (flags & kFlagPackedC) != 0;
