@@ -785,9 +785,10 @@ void householder_panel(const torch::Tensor& table, int64_t count) {
 // Blocked Householder QR of a batch of matrices, entirely on the device and without host
 // synchronisation: for every panel of kQrPanel columns one launch of the panel kernel over all
 // matrices that still have such a panel, then one launch of the block-reflector kernel that
-// applies it to the remaining columns (C <- C - (C V T) V^T in the transposed storage); a second
-// sweep over the panels in reverse accumulates Q^T the same way, touching only the trailing block
-// each reflector acts on.  All launch tables are assembled here and uploaded once.
+// applies it to the remaining columns (C <- C - (C V T) V^T in the transposed storage); one more
+// launch then accumulates Q^T of every matrix, each CTA carrying a tile of rows of the identity
+// through all panels' reflectors in shared memory.  All launch tables are assembled here and
+// uploaded once.
 //
 // Each spec: (ct, n, k, zt, zt_hi, zt_lo)
 //   ct                [>= k, n] view (row pitch a multiple of 4): row c is column c of the n x k matrix
@@ -839,14 +840,14 @@ void householder_qr(const std::vector<py::tuple>& specs) {
   auto stream = at::cuda::getCurrentCUDAStream();
 
   // Launch tables, panel-major: panel descriptors, then the reflector applications of the forward
-  // and of the backward sweep with their row tiles.
+  // with their row tiles.
   std::vector<QrPanelDesc> panels;
   std::vector<ReflectDesc> reflect;
   std::vector<int2> tiles;
   struct Range {
     int first = 0, count = 0;
   };
-  std::vector<Range> panel_range(max_pan), fwd_range(max_pan), bwd_range(max_pan);
+  std::vector<Range> panel_range(max_pan), fwd_range(max_pan);
   auto add_reflect = [&](float* x, float* x_hi, float* x_lo, int ldx, int rows, int L, const float* w, const float* vt,
                          int ldw) {
     ReflectDesc r;
@@ -865,49 +866,54 @@ void householder_qr(const std::vector<py::tuple>& specs) {
     reflect.push_back(r);
     for (int row0 = 0; row0 < rows; row0 += r.rows_per_tile) tiles.push_back(make_int2(idx, row0));
   };
-  for (int sweep = 0; sweep < 2; ++sweep) {
-    for (int j = 0; j < max_pan; ++j) {
-      const int panel_first = static_cast<int>(panels.size());
-      const int tile_first = static_cast<int>(tiles.size());
-      for (const Item& it : items) {
-        if (j >= it.npan) continue;
-        const int c0 = j * kQrPanel, c1 = std::min(it.k, c0 + kQrPanel), L = it.n - c0;
-        const int ldw = static_cast<int>(it.vt.stride(0));
-        const int64_t w_off = static_cast<int64_t>(c0) * ldw + c0;  // panel row 0, column c0
-        if (sweep == 0) {
-          QrPanelDesc d;
-          std::memset(&d, 0, sizeof(d));
-          d.ct = it.ct.data_ptr<float>();
-          d.ld = static_cast<int>(it.ct.stride(0));
-          d.n = it.n;
-          d.c0 = c0;
-          d.c1 = c1;
-          d.ldw = ldw;
-          d.vt = it.vt.data_ptr<float>() + w_off;
-          d.ttv = it.ttv.data_ptr<float>() + w_off;
-          d.tv = it.tv.data_ptr<float>() + w_off;
-          panels.push_back(d);
-          if (it.k > c1) {
-            const int64_t ld = it.ct.stride(0);
-            add_reflect(it.ct.data_ptr<float>() + c1 * ld + c0, nullptr, nullptr, static_cast<int>(ld), it.k - c1, L,
-                        it.ttv.data_ptr<float>() + w_off, it.vt.data_ptr<float>() + w_off, ldw);
-          }
-        } else {
-          const int64_t ld = it.zt.stride(0);
-          const int64_t off = c0 * ld + c0;
-          const bool last = j == 0;  // covers the whole matrix: also emit the (hi, lo) pair
-          add_reflect(it.zt.data_ptr<float>() + off, last ? it.zt_hi.data_ptr<float>() : nullptr,
-                      last ? it.zt_lo.data_ptr<float>() : nullptr, static_cast<int>(ld), L, L,
-                      it.tv.data_ptr<float>() + w_off, it.vt.data_ptr<float>() + w_off, ldw);
-        }
-      }
-      if (sweep == 0) {
-        panel_range[j] = {panel_first, static_cast<int>(panels.size()) - panel_first};
-        fwd_range[j] = {tile_first, static_cast<int>(tiles.size()) - tile_first};
-      } else {
-        bwd_range[j] = {tile_first, static_cast<int>(tiles.size()) - tile_first};
+  for (int j = 0; j < max_pan; ++j) {
+    const int panel_first = static_cast<int>(panels.size());
+    const int tile_first = static_cast<int>(tiles.size());
+    for (const Item& it : items) {
+      if (j >= it.npan) continue;
+      const int c0 = j * kQrPanel, c1 = std::min(it.k, c0 + kQrPanel), L = it.n - c0;
+      const int ldw = static_cast<int>(it.vt.stride(0));
+      const int64_t w_off = static_cast<int64_t>(c0) * ldw + c0;  // panel row 0, column c0
+      QrPanelDesc d;
+      std::memset(&d, 0, sizeof(d));
+      d.ct = it.ct.data_ptr<float>();
+      d.ld = static_cast<int>(it.ct.stride(0));
+      d.n = it.n;
+      d.c0 = c0;
+      d.c1 = c1;
+      d.ldw = ldw;
+      d.vt = it.vt.data_ptr<float>() + w_off;
+      d.ttv = it.ttv.data_ptr<float>() + w_off;
+      d.tv = it.tv.data_ptr<float>() + w_off;
+      panels.push_back(d);
+      if (it.k > c1) {
+        const int64_t ld = it.ct.stride(0);
+        add_reflect(it.ct.data_ptr<float>() + c1 * ld + c0, nullptr, nullptr, static_cast<int>(ld), it.k - c1, L,
+                    it.ttv.data_ptr<float>() + w_off, it.vt.data_ptr<float>() + w_off, ldw);
       }
     }
+    panel_range[j] = {panel_first, static_cast<int>(panels.size()) - panel_first};
+    fwd_range[j] = {tile_first, static_cast<int>(tiles.size()) - tile_first};
+  }
+  // Accumulation of Q^T: one descriptor per matrix, tiles of whole rows.
+  std::vector<AccumulateDesc> accumulate;
+  std::vector<int2> acc_tiles;
+  for (const Item& it : items) {
+    AccumulateDesc a;
+    std::memset(&a, 0, sizeof(a));
+    a.zt = it.zt.data_ptr<float>();
+    a.zt_hi = it.zt_hi.data_ptr<float>();
+    a.zt_lo = it.zt_lo.data_ptr<float>();
+    a.vt = it.vt.data_ptr<float>();
+    a.tv = it.tv.data_ptr<float>();
+    a.ldz = static_cast<int>(it.zt.stride(0));
+    a.ldw = static_cast<int>(it.vt.stride(0));
+    a.n = it.n;
+    a.npan = it.npan;
+    a.rows_per_tile = std::max(1, std::min(kReflectMaxRows, kReflectSmemFloats / it.n));
+    const int idx = static_cast<int>(accumulate.size());
+    accumulate.push_back(a);
+    for (int row0 = 0; row0 < it.n; row0 += a.rows_per_tile) acc_tiles.push_back(make_int2(idx, row0));
   }
   auto d_panels = upload_bytes(panels.data(), panels.size() * sizeof(QrPanelDesc), device);
   auto d_reflect = upload_bytes(reflect.data(), reflect.size() * sizeof(ReflectDesc), device);
@@ -916,34 +922,15 @@ void householder_qr(const std::vector<py::tuple>& specs) {
   const auto* reflect_table = reinterpret_cast<const ReflectDesc*>(d_reflect.data_ptr());
   const auto* tile_table = reinterpret_cast<const int2*>(d_tiles.data_ptr());
 
-  // Z = I in one launch.
-  std::vector<SymOp> eye_ops;
-  std::vector<int2> eye_chunks;
-  for (const Item& it : items) {
-    SymOp op;
-    std::memset(&op, 0, sizeof(op));
-    op.src = it.zt.data_ptr<float>();
-    op.n = it.n;
-    op.ld_src = op.ld_dst = static_cast<int>(it.zt.stride(0));
-    op.dst_hi = it.zt.data_ptr<float>();
-    op.a = 0.f;  // the source is not read
-    op.b = 1.f;
-    const int idx = static_cast<int>(eye_ops.size());
-    eye_ops.push_back(op);
-    for (int r = 0; r < (op.n + kSymRowsPerChunk - 1) / kSymRowsPerChunk; ++r) eye_chunks.push_back(make_int2(idx, r));
-  }
-  auto d_eye_ops = upload_bytes(eye_ops.data(), eye_ops.size() * sizeof(SymOp), device);
-  auto d_eye_chunks = upload_bytes(eye_chunks.data(), eye_chunks.size() * sizeof(int2), device);
-  launch_shift_scale_split(reinterpret_cast<const SymOp*>(d_eye_ops.data_ptr()),
-                           reinterpret_cast<const int2*>(d_eye_chunks.data_ptr()), static_cast<int>(eye_chunks.size()), stream);
+  auto d_accumulate = upload_bytes(accumulate.data(), accumulate.size() * sizeof(AccumulateDesc), device);
+  auto d_acc_tiles = upload_bytes(acc_tiles.data(), acc_tiles.size() * sizeof(int2), device);
 
   for (int j = 0; j < max_pan; ++j) {
     launch_householder_panel(panel_table + panel_range[j].first, panel_range[j].count, stream);
     launch_apply_block_reflector(reflect_table, tile_table + fwd_range[j].first, fwd_range[j].count, stream);
   }
-  for (int j = max_pan - 1; j >= 0; --j) {
-    launch_apply_block_reflector(reflect_table, tile_table + bwd_range[j].first, bwd_range[j].count, stream);
-  }
+  launch_accumulate_q(reinterpret_cast<const AccumulateDesc*>(d_accumulate.data_ptr()),
+                      reinterpret_cast<const int2*>(d_acc_tiles.data_ptr()), static_cast<int>(acc_tiles.size()), stream);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   // The launch tables and the workspace are referenced by kernels still in flight: torch's caching
   // allocator only reuses their memory for work queued later on this same stream.

@@ -189,30 +189,154 @@ __device__ __forceinline__ void stage_chunk(float* dst, const float* __restrict_
   cp_async_commit();
 }
 
-// A tile of up to kReflectMaxRows whole rows stays in shared memory between the two passes.  The
-// threads are split into row groups of four rows; a thread owns columns i = t, t + 128, ... of its
-// group, keeps the 16 entries W[:, i] (then Vt[:, i]) in registers and runs them against its four
-// rows, so a shared-memory load feeds 16 multiply-adds instead of one.  The chunks of W and Vt are
-// double buffered with cp.async: the next chunk travels while the current one is consumed.
+// One block reflector applied to a tile of rows resident in shared memory:
+//   xs[r][i] -= sum_j (sum_i' xs[r][i'] W[j][i']) Vt[j][i],   r < R, i < L  (xs row pitch `pitch`).
+// The threads are split into row groups of four rows; a thread owns columns i = t, t + 128, ... of
+// its group, keeps the 16 entries W[:, i] (then Vt[:, i]) in registers and runs them against its
+// four rows, so a shared-memory load feeds 16 multiply-adds instead of one.  The chunks of W and Vt
+// are double buffered with cp.async: the next chunk travels while the current one is consumed.
+// Chunk 0 of W must already have been staged into ws (and committed) by the caller, so that its
+// latency overlaps whatever the caller does before (loading the rows).  Ends with a barrier.
+struct ReflectScratch {
+  float part[kReflectGroups][kReflectGroupWarps][kReflectGroupRows * kQrPanel];
+  float us[kReflectGroups][kReflectGroupRows * kQrPanel];
+};
+
+__device__ __forceinline__ void reflect_tile(float* ws, float* xs, int pitch, int R, int L, const float* __restrict__ w,
+                                             const float* __restrict__ vt, int ldw, ReflectScratch& sc) {
+  constexpr int kBuf = kQrPanel * kReflectChunk;
+  const int lane = threadIdx.x & 31;
+  const int g = threadIdx.x / kReflectGroupThreads, t = threadIdx.x % kReflectGroupThreads;
+  const int gw = t >> 5;  // warp inside the group
+  const int num_chunks = (L + kReflectChunk - 1) / kReflectChunk;
+  const int rbase = g * kReflectGroupRows;  // first row of this thread's group inside the tile
+  // ---- pass 1: u[r][j] = sum_i X[r][i] W[j][i]
+  float acc[kReflectGroupRows][kQrPanel];
+#pragma unroll
+  for (int q = 0; q < kReflectGroupRows; ++q)
+#pragma unroll
+    for (int j = 0; j < kQrPanel; ++j) acc[q][j] = 0.f;
+  for (int c = 0; c < num_chunks; ++c) {
+    const int c0 = c * kReflectChunk;
+    const int cw = min(kReflectChunk, L - c0);
+    const float* wb = ws + (c & 1) * kBuf;
+    // next chunk of W, or the first chunk of Vt for the second pass
+    if (c + 1 < num_chunks) stage_chunk(ws + ((c + 1) & 1) * kBuf, w, ldw, c0 + kReflectChunk);
+    else stage_chunk(ws + ((c + 1) & 1) * kBuf, vt, ldw, 0);
+    cp_async_wait<1>();
+    __syncthreads();  // chunk c (and, at c = 0, the rows) visible to all threads
+    if (rbase < R) {
+      for (int i = t; i < cw; i += kReflectGroupThreads) {
+        float wv[kQrPanel];
+#pragma unroll
+        for (int j = 0; j < kQrPanel; ++j) wv[j] = wb[j * kReflectChunk + i];
+#pragma unroll
+        for (int q = 0; q < kReflectGroupRows; ++q) {
+          const float x = rbase + q < R ? xs[(rbase + q) * pitch + c0 + i] : 0.f;
+#pragma unroll
+          for (int j = 0; j < kQrPanel; ++j) acc[q][j] = fmaf(x, wv[j], acc[q][j]);
+        }
+      }
+    }
+    __syncthreads();  // buffer (c & 1) may be refilled by the next iteration's prefetch
+  }
+  // sums over the threads of the group: inside each warp, then across the group's warps
+#pragma unroll
+  for (int q = 0; q < kReflectGroupRows; ++q)
+#pragma unroll
+    for (int j = 0; j < kQrPanel; ++j) {
+      const float sum = warp_sum(acc[q][j]);
+      if (lane == 0) sc.part[g][gw][q * kQrPanel + j] = sum;
+    }
+  __syncthreads();
+  if (t < kReflectGroupRows * kQrPanel) {
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < kReflectGroupWarps; ++k) sum += sc.part[g][k][t];
+    sc.us[g][t] = sum;
+  }
+  __syncthreads();
+  float u[kReflectGroupRows][kQrPanel];
+#pragma unroll
+  for (int q = 0; q < kReflectGroupRows; ++q)
+#pragma unroll
+    for (int j = 0; j < kQrPanel; ++j) u[q][j] = sc.us[g][q * kQrPanel + j];
+  // ---- pass 2: X[r][i] -= sum_j u[r][j] Vt[j][i]; chunk c of Vt sits in buffer (num_chunks + c) & 1
+  for (int c = 0; c < num_chunks; ++c) {
+    const int c0 = c * kReflectChunk;
+    const int cw = min(kReflectChunk, L - c0);
+    const float* vb = ws + ((num_chunks + c) & 1) * kBuf;
+    if (c + 1 < num_chunks) {
+      stage_chunk(ws + ((num_chunks + c + 1) & 1) * kBuf, vt, ldw, c0 + kReflectChunk);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (rbase < R) {
+      for (int i = t; i < cw; i += kReflectGroupThreads) {
+        float v[kQrPanel];
+#pragma unroll
+        for (int j = 0; j < kQrPanel; ++j) v[j] = vb[j * kReflectChunk + i];
+#pragma unroll
+        for (int q = 0; q < kReflectGroupRows; ++q) {
+          if (rbase + q < R) {
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < kQrPanel; ++j) sum = fmaf(u[q][j], v[j], sum);
+            xs[(rbase + q) * pitch + c0 + i] -= sum;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Rows of a resident tile back to global memory, optionally also as the tf32 (hi, lo) pair.
+__device__ __forceinline__ void store_tile(const float* xs, int R, int L, float* xg, float* hg, float* lg, int ldx) {
+  const bool split = hg != nullptr;
+  const bool vec = (L & 3) == 0 && (ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(xg) & 15) == 0 &&
+                   (!split || (((reinterpret_cast<uintptr_t>(hg) | reinterpret_cast<uintptr_t>(lg)) & 15) == 0));
+  if (vec) {
+    const int L4 = L >> 2;
+    for (int e = threadIdx.x; e < R * L4; e += kReflectThreads) {
+      const int r = e / L4, i4 = e % L4;
+      const float4 x = reinterpret_cast<const float4*>(xs + r * L)[i4];
+      reinterpret_cast<float4*>(xg + static_cast<long long>(r) * ldx)[i4] = x;
+      if (split) {
+        float4 h, l;
+        h.x = tf32_round(x.x); h.y = tf32_round(x.y); h.z = tf32_round(x.z); h.w = tf32_round(x.w);
+        l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
+        reinterpret_cast<float4*>(hg + static_cast<long long>(r) * ldx)[i4] = h;
+        reinterpret_cast<float4*>(lg + static_cast<long long>(r) * ldx)[i4] = l;
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < R * L; e += kReflectThreads) {
+      const int r = e / L, i = e % L;
+      const float x = xs[r * L + i];
+      const long long o = static_cast<long long>(r) * ldx + i;
+      xg[o] = x;
+      if (split) store_split(hg, lg, o, x);
+    }
+  }
+}
+
+// A tile of up to kReflectMaxRows whole rows stays in shared memory between the two passes.
 __global__ void __launch_bounds__(kReflectThreads, 2) apply_block_reflector_kernel(const ReflectDesc* __restrict__ descs,
                                                                                   const int2* __restrict__ tiles,
                                                                                   int num_tiles) {
   extern __shared__ float rsm[];
   float* ws = rsm;                                 // [2][kQrPanel][kReflectChunk] chunks of W, then of Vt
   float* xs = rsm + 2 * kQrPanel * kReflectChunk;  // [rows_per_tile][L]
-  __shared__ float part[kReflectGroups][kReflectGroupWarps][kReflectGroupRows * kQrPanel];
-  __shared__ float us[kReflectGroups][kReflectGroupRows * kQrPanel];
-  constexpr int kBuf = kQrPanel * kReflectChunk;
-  const int lane = threadIdx.x & 31;
-  const int g = threadIdx.x / kReflectGroupThreads, t = threadIdx.x % kReflectGroupThreads;
-  const int gw = t >> 5;  // warp inside the group
+  __shared__ ReflectScratch sc;
   for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
     const int2 ref = tiles[tile];
     const ReflectDesc d = descs[ref.x];
     const int row0 = ref.y;
     const int R = min(d.rows_per_tile, d.rows - row0);
     const int L = d.L;
-    const int num_chunks = (L + kReflectChunk - 1) / kReflectChunk;
     float* xg = d.x + static_cast<long long>(row0) * d.ldx;
     stage_chunk(ws, d.w, d.ldw, 0);
     const bool vec = (L & 3) == 0 && (d.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(xg) & 15) == 0;
@@ -228,117 +352,52 @@ __global__ void __launch_bounds__(kReflectThreads, 2) apply_block_reflector_kern
         xs[r * L + i] = xg[static_cast<long long>(r) * d.ldx + i];
       }
     }
-    const int rbase = g * kReflectGroupRows;  // first row of this thread's group inside the tile
-    // ---- pass 1: u[r][j] = sum_i X[r][i] W[j][i]
-    float acc[kReflectGroupRows][kQrPanel];
-#pragma unroll
-    for (int q = 0; q < kReflectGroupRows; ++q)
-#pragma unroll
-      for (int j = 0; j < kQrPanel; ++j) acc[q][j] = 0.f;
-    for (int c = 0; c < num_chunks; ++c) {
-      const int c0 = c * kReflectChunk;
-      const int cw = min(kReflectChunk, L - c0);
-      const float* wb = ws + (c & 1) * kBuf;
-      // next chunk of W, or the first chunk of Vt for the second pass
-      if (c + 1 < num_chunks) stage_chunk(ws + ((c + 1) & 1) * kBuf, d.w, d.ldw, c0 + kReflectChunk);
-      else stage_chunk(ws + ((c + 1) & 1) * kBuf, d.vt, d.ldw, 0);
-      cp_async_wait<1>();
-      __syncthreads();  // chunk c (and, at c = 0, the rows) visible to all threads
-      if (rbase < R) {
-        for (int i = t; i < cw; i += kReflectGroupThreads) {
-          float w[kQrPanel];
-#pragma unroll
-          for (int j = 0; j < kQrPanel; ++j) w[j] = wb[j * kReflectChunk + i];
-#pragma unroll
-          for (int q = 0; q < kReflectGroupRows; ++q) {
-            const float x = rbase + q < R ? xs[(rbase + q) * L + c0 + i] : 0.f;
-#pragma unroll
-            for (int j = 0; j < kQrPanel; ++j) acc[q][j] = fmaf(x, w[j], acc[q][j]);
-          }
-        }
-      }
-      __syncthreads();  // buffer (c & 1) may be refilled by the next iteration's prefetch
-    }
-    // sums over the threads of the group: inside each warp, then across the group's warps
-#pragma unroll
-    for (int q = 0; q < kReflectGroupRows; ++q)
-#pragma unroll
-      for (int j = 0; j < kQrPanel; ++j) {
-        const float sum = warp_sum(acc[q][j]);
-        if (lane == 0) part[g][gw][q * kQrPanel + j] = sum;
-      }
-    __syncthreads();
-    if (t < kReflectGroupRows * kQrPanel) {
-      float sum = 0.f;
-#pragma unroll
-      for (int w = 0; w < kReflectGroupWarps; ++w) sum += part[g][w][t];
-      us[g][t] = sum;
-    }
-    __syncthreads();
-    float u[kReflectGroupRows][kQrPanel];
-#pragma unroll
-    for (int q = 0; q < kReflectGroupRows; ++q)
-#pragma unroll
-      for (int j = 0; j < kQrPanel; ++j) u[q][j] = us[g][q * kQrPanel + j];
-    // ---- pass 2: X[r][i] -= sum_j u[r][j] Vt[j][i]; chunk c of Vt sits in buffer (num_chunks + c) & 1
-    for (int c = 0; c < num_chunks; ++c) {
-      const int c0 = c * kReflectChunk;
-      const int cw = min(kReflectChunk, L - c0);
-      const float* vb = ws + ((num_chunks + c) & 1) * kBuf;
-      if (c + 1 < num_chunks) {
-        stage_chunk(ws + ((num_chunks + c + 1) & 1) * kBuf, d.vt, d.ldw, c0 + kReflectChunk);
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
-      __syncthreads();
-      if (rbase < R) {
-        for (int i = t; i < cw; i += kReflectGroupThreads) {
-          float v[kQrPanel];
-#pragma unroll
-          for (int j = 0; j < kQrPanel; ++j) v[j] = vb[j * kReflectChunk + i];
-#pragma unroll
-          for (int q = 0; q < kReflectGroupRows; ++q) {
-            if (rbase + q < R) {
-              float sum = 0.f;
-#pragma unroll
-              for (int j = 0; j < kQrPanel; ++j) sum = fmaf(u[q][j], v[j], sum);
-              xs[(rbase + q) * L + c0 + i] -= sum;
-            }
-          }
-        }
-      }
-      __syncthreads();
-    }
-    // rows back to global memory (and their (hi, lo) pair)
+    reflect_tile(ws, xs, L, R, L, d.w, d.vt, d.ldw, sc);
     const bool split = d.x_hi != nullptr;
-    float* hg = split ? d.x_hi + static_cast<long long>(row0) * d.ldx : nullptr;
-    float* lg = split ? d.x_lo + static_cast<long long>(row0) * d.ldx : nullptr;
-    const bool vec_out = vec && (!split || (((reinterpret_cast<uintptr_t>(hg) | reinterpret_cast<uintptr_t>(lg)) & 15) == 0));
-    if (vec_out) {
-      const int L4 = L >> 2;
-      for (int e = threadIdx.x; e < R * L4; e += kReflectThreads) {
-        const int r = e / L4, i4 = e % L4;
-        const float4 x = reinterpret_cast<const float4*>(xs + r * L)[i4];
-        reinterpret_cast<float4*>(xg + static_cast<long long>(r) * d.ldx)[i4] = x;
-        if (split) {
-          float4 h, l;
-          h.x = tf32_round(x.x); h.y = tf32_round(x.y); h.z = tf32_round(x.z); h.w = tf32_round(x.w);
-          l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
-          reinterpret_cast<float4*>(hg + static_cast<long long>(r) * d.ldx)[i4] = h;
-          reinterpret_cast<float4*>(lg + static_cast<long long>(r) * d.ldx)[i4] = l;
-        }
-      }
-    } else {
-      for (int e = threadIdx.x; e < R * L; e += kReflectThreads) {
-        const int r = e / L, i = e % L;
-        const float x = xs[r * L + i];
-        const long long o = static_cast<long long>(r) * d.ldx + i;
-        xg[o] = x;
-        if (split) store_split(hg, lg, o, x);
+    store_tile(xs, R, L, xg, split ? d.x_hi + static_cast<long long>(row0) * d.ldx : nullptr,
+               split ? d.x_lo + static_cast<long long>(row0) * d.ldx : nullptr, d.ldx);
+    __syncthreads();  // xs is reused by the next tile
+  }
+}
+
+// Accumulation of Q^T in one launch: Z = I (I - V_last T_last^T V_last^T) ... (I - V_0 T_0^T V_0^T).
+// Every row of Z is transformed independently of the others, so a CTA keeps a tile of rows in
+// shared memory, starts it as rows of the identity and applies every panel's reflector in turn
+// (last panel first); Z is never read and written once, and the panels' W / Vt operands are shared
+// by all tiles of a matrix through the L2.  Panel j only acts on columns >= 16 j, and rows above
+// 16 j are still rows of the identity there, so a tile starts at the last panel that reaches it.
+__global__ void __launch_bounds__(kReflectThreads, 2) accumulate_q_kernel(const AccumulateDesc* __restrict__ descs,
+                                                                         const int2* __restrict__ tiles, int num_tiles) {
+  extern __shared__ float rsm[];
+  float* ws = rsm;
+  float* xs = rsm + 2 * kQrPanel * kReflectChunk;  // [rows_per_tile][n]
+  __shared__ ReflectScratch sc;
+  for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    const int2 ref = tiles[tile];
+    const AccumulateDesc d = descs[ref.x];
+    const int row0 = ref.y, n = d.n;
+    const int R = min(d.rows_per_tile, n - row0);
+    const int first = min(d.npan - 1, (row0 + R - 1) / kQrPanel);  // last panel whose columns reach the tile's rows
+    {
+      const long long off = static_cast<long long>(first) * kQrPanel * d.ldw + first * kQrPanel;
+      stage_chunk(ws, d.tv + off, d.ldw, 0);
+    }
+    for (int e = threadIdx.x; e < R * n; e += kReflectThreads) {
+      const int r = e / n, i = e % n;
+      xs[e] = (i == row0 + r) ? 1.f : 0.f;
+    }
+    for (int j = first; j >= 0; --j) {
+      const int c0 = j * kQrPanel;
+      const long long off = static_cast<long long>(c0) * d.ldw + c0;  // panel row 0, column c0
+      reflect_tile(ws, xs + c0, n, R, n - c0, d.tv + off, d.vt + off, d.ldw, sc);
+      if (j > 0) {
+        const long long next = static_cast<long long>(c0 - kQrPanel) * d.ldw + (c0 - kQrPanel);
+        stage_chunk(ws, d.tv + next, d.ldw, 0);  // reflect_tile left both chunk buffers free
       }
     }
-    __syncthreads();  // xs is reused by the next tile
+    float* zg = d.zt + static_cast<long long>(row0) * d.ldz;
+    store_tile(xs, R, n, zg, d.zt_hi + static_cast<long long>(row0) * d.ldz, d.zt_lo + static_cast<long long>(row0) * d.ldz, d.ldz);
+    __syncthreads();
   }
 }
 
@@ -473,6 +532,18 @@ void launch_apply_block_reflector(const ReflectDesc* descs, const int2* tiles, i
   }
   const int cap = 2 * sm_count();  // two CTAs per SM: one loads or stores its rows while the other computes
   apply_block_reflector_kernel<<<num_tiles < cap ? num_tiles : cap, kReflectThreads, kBytes, stream>>>(descs, tiles, num_tiles);
+}
+
+void launch_accumulate_q(const AccumulateDesc* descs, const int2* tiles, int num_tiles, cudaStream_t stream) {
+  if (num_tiles <= 0) return;
+  static bool configured = false;
+  constexpr int kBytes = (2 * kQrPanel * kReflectChunk + kReflectSmemFloats) * 4;
+  if (!configured) {
+    cudaFuncSetAttribute(accumulate_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+    configured = true;
+  }
+  const int cap = 2 * sm_count();
+  accumulate_q_kernel<<<num_tiles < cap ? num_tiles : cap, kReflectThreads, kBytes, stream>>>(descs, tiles, num_tiles);
 }
 
 void launch_sym_measure(const SymOp* ops, int count, cudaStream_t stream) {

@@ -70,6 +70,22 @@ constexpr int kReflectChunk = 256;         // columns of W / Vt staged per step
 
 void launch_apply_block_reflector(const ReflectDesc* descs, const int2* tiles, int num_tiles, cudaStream_t stream);
 
+// Q^T of a factored matrix (all of its panels) in one pass over its rows; see accumulate_q_kernel.
+// vt / tv are the [npan * kQrPanel, ldw] arrays the panel kernel filled (row 16 j + m = reflector m of
+// panel j, indexed by absolute column), zt / zt_hi / zt_lo the n x n outputs of pitch ldz.
+struct AccumulateDesc {
+  float* zt;
+  float* zt_hi;
+  float* zt_lo;
+  const float* vt;
+  const float* tv;
+  int ldz, ldw, n, npan;
+  int rows_per_tile;
+  int pad_[3];
+};
+
+void launch_accumulate_q(const AccumulateDesc* descs, const int2* tiles, int num_tiles, cudaStream_t stream);
+
 // One square matrix of a batched pass.
 struct SymOp {
   const float* src;  // n x n, row pitch ld_src
