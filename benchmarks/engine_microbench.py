@@ -81,8 +81,13 @@ def main() -> None:
 
     if args.optimizer == "gpa":
         if args.impl == "reference":
-            raise SystemExit("the reference wheel does not ship its gpa package")
-        from optimizers_b200.gpa_adamw import GPAAdamW
+            # The reference's wheel ships distributed_shampoo only; its gpa package is copied beside it
+            # (cp -r <reference>/gpa baseline/_ref/gpa), unmodified.
+            if not os.path.isdir(os.path.join(REPO, "baseline", "_ref", "gpa")):
+                raise SystemExit("baseline/_ref/gpa is missing: copy the reference's gpa package there")
+            from gpa.gpa_adamw import GPAAdamW
+        else:
+            from optimizers_b200.gpa_adamw import GPAAdamW
 
         opt = GPAAdamW(params, lr=1e-3, weight_decay=1e-2)
         opt.train()

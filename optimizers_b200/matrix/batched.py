@@ -67,6 +67,57 @@ def _pad4(n: int) -> int:
     return (n + 3) // 4 * 4
 
 
+def _prepared_factors(ext: Any, blocks: list[Any], bias_correction2: Tensor | float) -> list[tuple[Any, int, Tensor]]:
+    """``(block, k, A)`` for every factor of ``blocks`` with ``A`` the full, bias-corrected (and,
+    if configured, trace-scaled) factor matrix.  fp32 state is unpacked by one grouped launch and
+    divided by one multi-tensor launch; other dtypes take the per-factor tensor path."""
+    out: list[tuple[Any, int, Tensor]] = []
+    specs, native = [], []
+    for b in blocks:
+        kf = b.factors
+        for k, factor in enumerate(kf.factor_matrices):
+            if ext is not None and factor.is_cuda and factor.dtype == torch.float32 and (factor.dim() == 1 or factor.stride(-1) == 1):
+                d = kf._packed_dim(factor) if factor.dim() == 1 else factor.shape[0]
+                A = torch.empty(d, d, dtype=torch.float32, device=factor.device)
+                specs.append((factor, d, A, None))
+                native.append(A)
+            else:
+                A = kf.unpack(factor / bias_correction2)
+            out.append((b, k, A))
+    if specs:
+        ext.unpack_split(*ext.build_unpack_table(specs))
+        torch._foreach_div_(native, float(bias_correction2))
+    for n, (b, k, A) in enumerate(out):
+        kf = b.factors
+        if kf.use_trace_scaling:
+            out[n] = (b, k, A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent))
+    return out
+
+
+class _PhaseClock:
+    """OB200_REFRESH_TIMING=1: log the wall time of the phases of a refresh, each bracketed by a
+    device synchronisation (diagnostics; the synchronisations cost a little themselves)."""
+
+    enabled = _os.environ.get("OB200_REFRESH_TIMING", "0") == "1"
+
+    def __init__(self, what: str) -> None:
+        self.what, self.marks = what, []
+        self.tick("start")
+
+    def tick(self, name: str) -> None:
+        if not self.enabled:
+            return
+        import time
+
+        torch.cuda.synchronize()
+        self.marks.append((name, time.perf_counter()))
+
+    def report(self) -> None:
+        if self.enabled:
+            parts = [f"{b[0]} {1e3 * (b[1] - a[1]):.1f}" for a, b in zip(self.marks, self.marks[1:])]
+            logger.warning("%s phases (ms): %s", self.what, ", ".join(parts))
+
+
 def _all_finite(tensors: list[Tensor]) -> list[bool]:
     """Per-tensor finiteness with one multi-tensor launch and one host read: a norm is finite
     exactly when every element is (the max norm cannot overflow)."""
@@ -204,15 +255,9 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
     device = blocks[0].inv_hi[0].device
     main = torch.cuda.current_stream(device)
 
+    clock = _PhaseClock("eigen refresh")
     # 1. prepare + one finiteness read
-    items: list[_Item] = []
-    for b in blocks:
-        kf = b.factors
-        for k, factor in enumerate(kf.factor_matrices):
-            A = kf.unpack(factor / bias_correction2)
-            if kf.use_trace_scaling:
-                A = A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent)
-            items.append(_Item(b, k, A, kf.roots[k]))
+    items: list[_Item] = [_Item(b, k, A, b.factors.roots[k]) for b, k, A in _prepared_factors(ext, blocks, bias_correction2)]
     finite = _all_finite([it.A for it in items])
     for it, ok in zip(items, finite):
         if not ok:
@@ -223,6 +268,7 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
                 "Otherwise, in some cases, this may be due to divergence of the algorithm. To mitigate, try decreasing the learning rate or increasing grafting epsilon."
             )
 
+    clock.tick("prepare")
     # 2. eigendecompositions on the stream pool (largest first for balance)
     ready = torch.cuda.Event()
     ready.record(main)
@@ -344,6 +390,7 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
         pooled = [i for i in pooled if i not in done_here]
         ready.record(main)
 
+    clock.tick("small factors (jacobi + scaling)")
     # Larger factors: the batched divide-and-conquer eigensolver; the library takes what it gives up.
     large = [i for i in pooled if items[i].A.shape[0] > ext.JACOBI_MAX_N and items[i].A.dtype == torch.float32]
     if large:
@@ -353,6 +400,7 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
             stability = kf.amortized_computation_config.rank_deficient_stability_config
             ridged.append(mf._ridge(items[i].A, kf.epsilon * getattr(stability, "perturb_before_computation", 0)))
         solved = native_eigh(ext, ridged, status, _hints_of(items, large))
+        clock.tick("large factors: eigensolver")
         _remember_eigenvalues(items, large, solved)
         done_here = set()
         for i, pair in zip(large, solved, strict=True):
@@ -376,6 +424,7 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
         assert it.done is not None
         main.wait_event(it.done)
 
+    clock.tick("scaling + operand split, library fallback")
     # 3. grouped reconstruction X = (Q s) Q^T, written as plain fp32 into the hi mirror
     specs = []
     good = [it for it in items if it.error is None]
@@ -390,9 +439,11 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
         plan = ext.build_gemm_plan(specs)
         ext.run_gemm_plan(*plan, 1.0, 0.0, split, status)
 
+    clock.tick("reconstruction")
     # 4. checkpoint state (packed upper triangle) from the result + one finiteness read; the
     #    operand mirrors are then rebuilt from the state so that both always agree exactly
     checked: list[Tensor] = []
+    pack_specs: list[tuple[Tensor, Tensor]] = []  # fp32 state: one grouped launch writes every packed triangle
     for it in good:
         d = it.A.shape[0]
         kf = it.block.factors
@@ -405,8 +456,13 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
                 ext.tf32_split(mirror, mirror, it.block.inv_lo[it.k][:, :d])
             continue
         state = kf.inv_factor_matrices[it.k]
-        state.copy_(kf.pack(it.block.inv_hi[it.k][:, :d]).to(dtype=state.dtype))
+        if state.dtype == torch.float32 and (state.dim() == 1 or state.stride(-1) == 1):
+            pack_specs.append((it.block.inv_hi[it.k][:, :d], state))
+        else:
+            state.copy_(kf.pack(it.block.inv_hi[it.k][:, :d]).to(dtype=state.dtype))
         checked.append(state)
+    if pack_specs:
+        ext.pack_upper(*ext.build_pack_table(pack_specs))
     for it, ok in zip(good, _all_finite(checked)):
         if not ok:
             index = it.block.factors.factor_matrix_indices[it.k]
@@ -415,6 +471,8 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
                 "To mitigate, check factor matrix before the matrix computation."
             )
     main.synchronize()  # scratch allocated on the pool streams may now be reused
+    clock.tick("state packing + finiteness")
+    clock.report()
 
     # failure bookkeeping per block
     last_error: dict[int, Exception | None] = {}
@@ -504,15 +562,12 @@ def batched_newton_refresh(
     max_iterations, tolerance = cfg.max_iterations, cfg.tolerance
 
     items: list[_NewtonItem] = []
-    for b in blocks:
+    for b, k, A in _prepared_factors(ext, blocks, bias_correction2):
         kf = b.factors
-        for k, factor in enumerate(kf.factor_matrices):
+        if True:
             root = Fraction(kf.roots[k])
             if root.denominator != 1:
                 raise ValueError(f"root.denominator={root.denominator} must be equal to 1 to use coupled inverse Newton iteration!")
-            A = kf.unpack(factor / bias_correction2)
-            if kf.use_trace_scaling:
-                A = A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent)
             it = _NewtonItem()
             it.block, it.k, it.d, it.root, it.A = b, k, A.shape[0], root.numerator, A
             it.converged, it.last_err, it.iters = False, float("inf"), 0
@@ -909,14 +964,7 @@ def batched_eigenbasis_refresh(blocks: list[Any], bias_correction2: Tensor | flo
         return
     device = blocks[0].factors.factor_matrices[0].device
     main = torch.cuda.current_stream(device)
-    items: list[_Item] = []
-    for b in blocks:
-        kf = b.factors
-        for k, factor in enumerate(kf.factor_matrices):
-            A = kf.unpack(factor / bias_correction2)
-            if kf.use_trace_scaling:
-                A = A * torch.pow(torch.clamp(torch.trace(A), min=kf.epsilon), -kf.trace_scaling_exponent)
-            items.append(_Item(b, k, A, 0.0))
+    items: list[_Item] = [_Item(b, k, A, 0.0) for b, k, A in _prepared_factors(ext, blocks, bias_correction2)]
     finite = _all_finite([it.A for it in items])
     for it, ok in zip(items, finite):
         if not ok:

@@ -157,6 +157,33 @@ def build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, An
     return NativeGroupEngine(optimizer, rec, group, cfg)
 
 
+class _ZeroPool:
+    """Zero-initialised fp32 scratch carved out of a few large allocations: the operand arrays of a
+    group are hundreds of tensors, and one fill launch per tensor made engine construction the
+    bulk of a short run's kernel launches.  Every array starts on a 256-byte boundary."""
+
+    CHUNK_ELEMS = 64 * 1024 * 1024  # 256 MB
+
+    def __init__(self, device: torch.device) -> None:
+        self._device = device
+        self._chunk: Tensor | None = None
+        self._cursor = 0
+
+    def zeros(self, *shape: int) -> Tensor:
+        numel = 1
+        for n in shape:
+            numel *= n
+        padded = (numel + 63) // 64 * 64
+        if padded > self.CHUNK_ELEMS // 4:  # large arrays get their own allocation
+            return torch.zeros(*shape, dtype=torch.float32, device=self._device)
+        if self._chunk is None or self._cursor + padded > self._chunk.numel():
+            self._chunk = torch.zeros(self.CHUNK_ELEMS, dtype=torch.float32, device=self._device)
+            self._cursor = 0
+        out = self._chunk[self._cursor : self._cursor + numel].view(*shape)
+        self._cursor += padded
+        return out
+
+
 class _Block:
     """Host-side record of one local block: views, state, scratch operands."""
 
@@ -272,8 +299,8 @@ class NativeGroupEngine:
         vs = self._glist._local_preconditioner_list if self._graft_kind == _GRAFT_ADAGRAD else None
         self._norms = torch.zeros(max(len(dist.local_blocked_params), 1), 2, dtype=torch.float32, device=dev)
 
-        def zeros(*shape: int) -> Tensor:
-            return torch.zeros(*shape, dtype=torch.float32, device=dev)
+        pool = _ZeroPool(dev)
+        zeros = pool.zeros
 
         for i, (view, info) in enumerate(zip(dist.local_blocked_params, dist.local_block_info_list, strict=True)):
             b = _Block()
@@ -599,18 +626,28 @@ class NativeGroupEngine:
     def refresh_inverse_mirrors(self, blocks: list[_Block] | None = None) -> None:
         """Rebuild the full (hi, lo) operand copies of the inverse roots (or, for the
         eigenvalue-corrected variant, of the eigenvector matrices and their transposes) from the
-        state tensors."""
+        state tensors: one grouped launch over every factor of every block (two for the
+        eigenvalue-corrected variant)."""
+        ext, sp = self._ext, self._split
+        todo = self._blocks if blocks is None else blocks
+        if not todo:
+            return
         if self._soap:
-            for b in self._blocks if blocks is None else blocks:
+            plain, transposed = [], []
+            for b in todo:
                 for k, Q in enumerate(b.factors.factor_matrices_eigenvectors):
                     d = Q.shape[0]
-                    for src, hi, lo in ((Q, b.inv_hi[k], b.inv_lo[k]), (Q.T.contiguous(), b.qt_hi[k], b.qt_lo[k])):
-                        if self._split:
-                            self._ext.tf32_split(src.contiguous(), hi[:, :d], lo[:, :d])
-                        else:
-                            hi[:, :d].copy_(src)
+                    Q = Q if Q.stride(-1) == 1 else Q.contiguous()
+                    plain.append((Q, d, b.inv_hi[k][:, :d], b.inv_lo[k][:, :d] if sp else None))
+                    if sp:
+                        transposed.append((Q, None, b.qt_hi[k][:, :d], b.qt_lo[k][:, :d]))
+                    else:
+                        transposed.append((Q, b.qt_hi[k][:, :d], None, None))
+            ext.unpack_split(*ext.build_unpack_table(plain))
+            ext.transpose_split(*ext.build_transpose_table(transposed))
             return
-        for b in self._blocks if blocks is None else blocks:
+        specs = []
+        for b in todo:
             if self._eigdec:
                 from fractions import Fraction
 
@@ -618,20 +655,19 @@ class NativeGroupEngine:
 
                 kf = b.factors
                 stability = kf.amortized_computation_config.rank_deficient_stability_config
-                invs = [
+                sources = [
                     mf.matrix_inverse_root_from_eigendecomposition(
                         L=lam, Q=Q, root=Fraction(root), epsilon=kf.epsilon, rank_deficient_stability_config=stability
-                    )
+                    ).contiguous()
                     for Q, lam, root in zip(kf.factor_matrices_eigenvectors, kf.factor_matrices_eigenvalues, kf.roots, strict=True)
                 ]
             else:
-                invs = b.factors.get_unpacked_inv_factor_matrices()
-            for k, inv in enumerate(invs):
-                d = inv.shape[0]
-                if self._split:
-                    self._ext.tf32_split(inv, b.inv_hi[k][:, :d], b.inv_lo[k][:, :d])
-                else:
-                    b.inv_hi[k][:, :d].copy_(inv)
+                # the state itself: the packed upper triangle or the full matrix
+                sources = [m if m.dim() == 1 or m.stride(-1) == 1 else m.contiguous() for m in b.factors.inv_factor_matrices]
+            for k, src in enumerate(sources):
+                d = b.inv_hi[k].shape[0]
+                specs.append((src, d, b.inv_hi[k][:, :d], b.inv_lo[k][:, :d] if sp else None))
+        ext.unpack_split(*ext.build_unpack_table(specs))
 
     # ------------------------------------------------------------------------------------------
     # Hooks called by the optimizer
@@ -918,7 +954,12 @@ class NativeGroupEngine:
         else:
             for b in blocks:
                 b.factors.amortized_computation(bias_correction2=plist._bias_correction2)
+        from optimizers_b200.matrix.batched import _PhaseClock
+
+        clock = _PhaseClock("engine refresh tail")
         self.refresh_inverse_mirrors(blocks)
+        clock.tick("operand mirrors from the state")
+        clock.report()
         self.check_status()
 
     def _push_scales(self, has_grafting: bool) -> int:

@@ -997,6 +997,93 @@ void shift_scale_split(const torch::Tensor& ops, const torch::Tensor& chunks, in
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// Each spec: (src, d, dst_hi, dst_lo | None): src is the packed upper triangle (1-D, d (d + 1) / 2
+// elements) or the full d x d matrix (2-D) of a symmetric matrix; dst_* are d x d views.
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_unpack_table(const std::vector<py::tuple>& specs) {
+  std::vector<UnpackOp> ops(specs.size());
+  std::vector<int2> chunks;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 4, "unpack spec must have 4 fields");
+    auto src = s[0].cast<torch::Tensor>();
+    TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32, "unpack source must be an fp32 CUDA tensor");
+    device = src.device();
+    UnpackOp& op = ops[i];
+    std::memset(&op, 0, sizeof(op));
+    op.src = src.data_ptr<float>();
+    op.d = s[1].cast<int>();
+    if (src.dim() == 1) {
+      TORCH_CHECK(src.is_contiguous() && src.numel() == static_cast<int64_t>(op.d) * (op.d + 1) / 2, "packed source size");
+      op.packed = 1;
+    } else {
+      TORCH_CHECK(src.dim() == 2 && src.stride(1) == 1 && src.size(0) == op.d && src.size(1) == op.d, "full source shape");
+      op.ld_src = static_cast<int>(src.stride(0));
+    }
+    auto hi = s[2].cast<torch::Tensor>();
+    auto lo = s[3].cast<std::optional<torch::Tensor>>();
+    TORCH_CHECK(hi.dim() == 2 && hi.stride(1) == 1 && hi.size(0) >= op.d && hi.size(1) >= op.d, "unpack destination shape");
+    op.dst_hi = hi.data_ptr<float>();
+    op.ld_dst = static_cast<int>(hi.stride(0));
+    if (lo.has_value()) {
+      TORCH_CHECK(lo->stride(0) == hi.stride(0), "dst_hi and dst_lo share one pitch");
+      op.dst_lo = lo->data_ptr<float>();
+    }
+    for (int r = 0; r < (op.d + kSymRowsPerChunk - 1) / kSymRowsPerChunk; ++r) chunks.push_back(make_int2(static_cast<int>(i), r));
+  }
+  auto d_ops = upload_bytes(ops.data(), ops.size() * sizeof(UnpackOp), device);
+  auto d_chunks = upload_bytes(chunks.data(), chunks.size() * sizeof(int2), device);
+  return {d_ops, d_chunks, static_cast<int64_t>(chunks.size())};
+}
+
+// Each spec: (src [d, d], dst): dst is 1-D (the packed upper triangle) or a [d, d] view.
+std::tuple<torch::Tensor, torch::Tensor, int64_t> build_pack_table(const std::vector<py::tuple>& specs) {
+  std::vector<UnpackOp> ops(specs.size());
+  std::vector<int2> chunks;
+  torch::Device device(torch::kCPU);
+  for (size_t i = 0; i < specs.size(); ++i) {
+    const py::tuple& s = specs[i];
+    TORCH_CHECK(s.size() == 2, "pack spec must have 2 fields");
+    auto src = s[0].cast<torch::Tensor>();
+    auto dst = s[1].cast<torch::Tensor>();
+    TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1 &&
+                    src.size(0) == src.size(1) && dst.scalar_type() == torch::kFloat32,
+                "pack source must be a square fp32 CUDA matrix");
+    device = src.device();
+    UnpackOp& op = ops[i];
+    std::memset(&op, 0, sizeof(op));
+    op.src = src.data_ptr<float>();
+    op.d = static_cast<int>(src.size(0));
+    op.ld_src = static_cast<int>(src.stride(0));
+    op.dst_hi = dst.data_ptr<float>();
+    if (dst.dim() == 1) {
+      TORCH_CHECK(dst.is_contiguous() && dst.numel() == static_cast<int64_t>(op.d) * (op.d + 1) / 2, "packed destination size");
+      op.packed = 1;
+    } else {
+      TORCH_CHECK(dst.dim() == 2 && dst.stride(1) == 1 && dst.size(0) == op.d && dst.size(1) == op.d, "full destination shape");
+      op.ld_dst = static_cast<int>(dst.stride(0));
+    }
+    for (int r = 0; r < (op.d + kSymRowsPerChunk - 1) / kSymRowsPerChunk; ++r) chunks.push_back(make_int2(static_cast<int>(i), r));
+  }
+  auto d_ops = upload_bytes(ops.data(), ops.size() * sizeof(UnpackOp), device);
+  auto d_chunks = upload_bytes(chunks.data(), chunks.size() * sizeof(int2), device);
+  return {d_ops, d_chunks, static_cast<int64_t>(chunks.size())};
+}
+
+void pack_upper(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_pack_upper(reinterpret_cast<const UnpackOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
+                    static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+void unpack_split(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  c10::cuda::CUDAGuard guard(ops.device());
+  launch_unpack_split(reinterpret_cast<const UnpackOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
+                      static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 // Each spec: (src [rows, cols], dst | None, dst_hi | None, dst_lo | None); destinations are [cols, rows].
 std::tuple<torch::Tensor, torch::Tensor, int64_t> build_transpose_table(const std::vector<py::tuple>& specs) {
   std::vector<TransposeOp> ops(specs.size());
@@ -1078,6 +1165,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sym_measure", &sym_measure);
   m.def("sq_offdiag", &sq_offdiag);
   m.def("shift_scale_split", &shift_scale_split);
+  m.def("build_unpack_table", &build_unpack_table);
+  m.def("unpack_split", &unpack_split);
+  m.def("build_pack_table", &build_pack_table);
+  m.def("pack_upper", &pack_upper);
   m.def("build_transpose_table", &build_transpose_table);
   m.def("transpose_split", &transpose_split);
   m.def("jacobi_eigh_into", &jacobi_eigh_into);

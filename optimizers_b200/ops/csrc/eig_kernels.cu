@@ -483,6 +483,51 @@ __global__ void __launch_bounds__(256) shift_scale_split_kernel(const SymOp* __r
   }
 }
 
+__global__ void __launch_bounds__(256) unpack_split_kernel(const UnpackOp* __restrict__ ops, const int2* __restrict__ chunks,
+                                                           int num_chunks) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const UnpackOp op = ops[ref.x];
+    const int row0 = ref.y * kSymRowsPerChunk;
+    const int rows = min(kSymRowsPerChunk, op.d - row0);
+    for (int e = threadIdx.x; e < rows * op.d; e += blockDim.x) {
+      const int i = row0 + e / op.d, j = e % op.d;
+      float x;
+      if (op.packed) {
+        const long long a = i < j ? i : j, b = i < j ? j : i;  // (a, b) with a <= b lies in the stored triangle
+        x = op.src[a * op.d - a * (a - 1) / 2 + (b - a)];
+      } else {
+        x = op.src[static_cast<long long>(i) * op.ld_src + j];
+      }
+      const long long o = static_cast<long long>(i) * op.ld_dst + j;
+      if (op.dst_lo != nullptr) {
+        store_split(op.dst_hi, op.dst_lo, o, x);
+      } else {
+        op.dst_hi[o] = x;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) pack_upper_kernel(const UnpackOp* __restrict__ ops, const int2* __restrict__ chunks,
+                                                         int num_chunks) {
+  for (int c = blockIdx.x; c < num_chunks; c += gridDim.x) {
+    const int2 ref = chunks[c];
+    const UnpackOp op = ops[ref.x];
+    const int row0 = ref.y * kSymRowsPerChunk;
+    const int rows = min(kSymRowsPerChunk, op.d - row0);
+    for (int e = threadIdx.x; e < rows * op.d; e += blockDim.x) {
+      const int i = row0 + e / op.d, j = e % op.d;
+      const float x = op.src[static_cast<long long>(i) * op.ld_src + j];
+      if (op.packed) {
+        if (j >= i) op.dst_hi[static_cast<long long>(i) * op.d - static_cast<long long>(i) * (i - 1) / 2 + (j - i)] = x;
+      } else {
+        op.dst_hi[static_cast<long long>(i) * op.ld_dst + j] = x;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) transpose_split_kernel(const TransposeOp* __restrict__ ops,
                                                               const int4* __restrict__ tiles, int num_tiles) {
   __shared__ float tile[32][33];
@@ -560,6 +605,18 @@ void launch_shift_scale_split(const SymOp* ops, const int2* chunks, int num_chun
   if (num_chunks <= 0) return;
   const int cap = sm_count() * 8;
   shift_scale_split_kernel<<<num_chunks < cap ? num_chunks : cap, 256, 0, stream>>>(ops, chunks, num_chunks);
+}
+
+void launch_unpack_split(const UnpackOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  const int cap = sm_count() * 8;
+  unpack_split_kernel<<<num_chunks < cap ? num_chunks : cap, 256, 0, stream>>>(ops, chunks, num_chunks);
+}
+
+void launch_pack_upper(const UnpackOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream) {
+  if (num_chunks <= 0) return;
+  const int cap = sm_count() * 8;
+  pack_upper_kernel<<<num_chunks < cap ? num_chunks : cap, 256, 0, stream>>>(ops, chunks, num_chunks);
 }
 
 void launch_transpose_split(const TransposeOp* ops, const int4* tiles, int num_tiles, cudaStream_t stream) {

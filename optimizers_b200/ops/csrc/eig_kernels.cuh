@@ -104,6 +104,22 @@ void launch_sq_offdiag(const SymOp* ops, int count, cudaStream_t stream);
 // Chunked over (matrix, 8-row band) pairs.
 void launch_shift_scale_split(const SymOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream);
 
+// dst = the symmetric d x d matrix held in `src`, either as its row-major packed upper triangle
+// (packed = 1; the checkpoint layout of the factor and inverse-root state) or in full (pitch ld_src),
+// written as a tf32 (hi, lo) pair, or plain into dst_hi when dst_lo is null.  One launch rebuilds
+// the GEMM operand mirrors of every factor of a parameter group from the state, instead of an
+// index_put and two copies per factor.
+struct UnpackOp {
+  const float* src;
+  float* dst_hi;
+  float* dst_lo;
+  int d, ld_src, ld_dst, packed;
+};
+void launch_unpack_split(const UnpackOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream);
+// The reverse for the checkpoint state: dst_hi (packed = 1: the packed upper triangle, else a full
+// d x d array of pitch ld_dst) = the d x d matrix at src (pitch ld_src); dst_lo is not used.
+void launch_pack_upper(const UnpackOp* ops, const int2* chunks, int num_chunks, cudaStream_t stream);
+
 // Transposed copy of a rows x cols matrix (pitch ld_src) into dst (cols x rows, pitch ld_dst),
 // optionally also as a (hi, lo) pair.  One launch covers a table of matrices.
 struct TransposeOp {

@@ -29,6 +29,8 @@ Reference counterpart: ``distributed_shampoo/preconditioner/shampoo_precondition
 
 from __future__ import annotations
 
+import functools
+
 import logging
 import math
 from collections.abc import Callable, Mapping
@@ -67,12 +69,19 @@ EIGENVALUES = "factor_matrices_eigenvalues"
 CORRECTED_EIGENVALUES = "corrected_eigenvalues"
 
 
+@functools.cache
+def _packed_diagonal_offsets(d: int, device_type: str, device_index: int | None) -> Tensor:
+    """Offsets of the diagonal entries in the packed upper triangle of a d x d matrix, computed on
+    the host once per size and device (building them on the device took six launches per factor)."""
+    i = torch.arange(d)
+    return (i * d - i * (i - 1) // 2).to(torch.device(device_type, device_index))
+
+
 def _packed_eye(info: BlockInfo, d: int, dtype: torch.dtype, device: torch.device) -> Tensor:
     """Identity in packed form: ones at the offsets of the diagonal entries."""
     t = info.allocate_zeros_tensor(size=(packed_size(d),), dtype=dtype, device=device)
     local = info.get_tensor(t)
-    i = torch.arange(d, device=local.device)
-    local[i * d - i * (i - 1) // 2] = 1.0
+    local.index_fill_(0, _packed_diagonal_offsets(d, local.device.type, local.device.index), 1.0)
     return t
 
 
