@@ -36,6 +36,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--backend", default="auto", help="native runtime back-end of this framework")
+    ap.add_argument("--comm", choices=["nccl", "p2p"], default="p2p",
+                    help="N > 1, this framework: gather the search directions with NCCL or by peer stores (DDP family)")
     ap.add_argument("--layers", type=int, default=None, help="debug: fewer decoder layers")
     args = ap.parse_args()
 
@@ -59,7 +61,7 @@ def main() -> None:
     else:
         import optimizers_b200 as lib
 
-        extra = {"native_runtime_config": lib.NativeRuntimeConfig(backend=args.backend)}
+        extra = {"native_runtime_config": lib.NativeRuntimeConfig(backend=args.backend, comm_path=args.comm if world > 1 else "nccl")}
     from optimizers_b200 import models as M
 
     if not hasattr(lib, "ClassicMomentumConfig"):  # the reference defines it but does not re-export it
