@@ -70,6 +70,7 @@ from optimizers_b200.config import (
     WeightDecayType,
 )
 from optimizers_b200.utils.blocking import compress_list, generate_pairwise_indices
+from optimizers_b200.utils import tracing
 
 logger: logging.Logger = logging.getLogger(__name__)
 
@@ -443,6 +444,8 @@ class NativeGroupEngine:
             self._grad_ptrs_dev = torch.tensor(table, dtype=torch.int64, device=self._device)
 
     def _mark(self, name: str) -> None:
+        if tracing.nvtx_enabled():
+            torch.cuda.nvtx.mark(f"ob200::phase::{name}")
         if self.phase_events is not None:
             event = torch.cuda.Event(enable_timing=True)
             event.record()

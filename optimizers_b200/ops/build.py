@@ -87,4 +87,7 @@ def load() -> ModuleType:
     spec.loader.exec_module(module)
     sys.modules[_NAME] = module
     _module = module
+    from optimizers_b200.utils import tracing
+
+    tracing.configure_from_environment()
     return module

@@ -7,6 +7,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <array>
@@ -15,6 +16,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <optional>
+#include <string>
 #include <vector>
 
 #include "block_kernels.cuh"
@@ -70,6 +72,80 @@ float* fptr(const std::optional<torch::Tensor>& t) {
   if (!t.has_value()) return nullptr;
   TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32, "expected an fp32 CUDA tensor");
   return t->data_ptr<float>();
+}
+
+// Tracing of the native launches.  Bit 0 of the mode wraps every binding that launches kernels in
+// an NVTX range named after it (visible to Nsight Systems / Nsight Compute range filters); bit 1
+// brackets it with CUDA events on the current stream and accumulates the device time per name,
+// read (after a synchronisation of the pending events) with launch_timings().  Both are off by
+// default and cost one branch per call.
+int g_trace_mode = 0;
+constexpr int kTraceNvtx = 1, kTraceTiming = 2;
+
+struct LaunchStat {
+  int64_t count = 0;
+  double ms = 0.0;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;
+};
+std::map<std::string, LaunchStat>& launch_stats() {
+  static std::map<std::string, LaunchStat> stats;
+  return stats;
+}
+
+void drain(LaunchStat& st) {
+  for (auto& [begin, end] : st.pending) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(end) == cudaSuccess && cudaEventElapsedTime(&ms, begin, end) == cudaSuccess) st.ms += ms;
+    cudaEventDestroy(begin);
+    cudaEventDestroy(end);
+  }
+  st.pending.clear();
+}
+
+class LaunchScope {
+ public:
+  explicit LaunchScope(const char* name) : name_(name), mode_(g_trace_mode) {
+    if (mode_ == 0) return;
+    if (mode_ & kTraceNvtx) nvtxRangePushA(name_);
+    if (mode_ & kTraceTiming) {
+      cudaEventCreate(&begin_);
+      cudaEventCreate(&end_);
+      cudaEventRecord(begin_, at::cuda::getCurrentCUDAStream());
+    }
+  }
+  ~LaunchScope() {
+    if (mode_ == 0) return;
+    if (mode_ & kTraceTiming) {
+      cudaEventRecord(end_, at::cuda::getCurrentCUDAStream());
+      LaunchStat& st = launch_stats()[name_];
+      st.count += 1;
+      st.pending.emplace_back(begin_, end_);
+      if (st.pending.size() >= 4096) drain(st);
+    }
+    if (mode_ & kTraceNvtx) nvtxRangePop();
+  }
+  LaunchScope(const LaunchScope&) = delete;
+  LaunchScope& operator=(const LaunchScope&) = delete;
+
+ private:
+  const char* name_;
+  int mode_;
+  cudaEvent_t begin_ = nullptr, end_ = nullptr;
+};
+
+void set_launch_tracing(bool nvtx, bool timing) {
+  g_trace_mode = (nvtx ? kTraceNvtx : 0) | (timing ? kTraceTiming : 0);
+}
+
+// name -> (calls, device milliseconds) since the last reset.
+std::map<std::string, std::pair<int64_t, double>> launch_timings(bool reset) {
+  std::map<std::string, std::pair<int64_t, double>> out;
+  for (auto& [name, st] : launch_stats()) {
+    drain(st);
+    out[name] = {st.count, st.ms};
+  }
+  if (reset) launch_stats().clear();
+  return out;
 }
 
 // Host table -> device, asynchronously on the current stream: the staging buffer is pinned and
@@ -318,6 +394,7 @@ std::tuple<torch::Tensor, torch::Tensor, std::vector<std::pair<int64_t, int64_t>
 
 void run_gemm_range(const torch::Tensor& problems, const torch::Tensor& tiles, int64_t first_tile, int64_t num_tiles,
                     double alpha, double beta, bool split, torch::Tensor status, double gamma) {
+  LaunchScope scope("ob200::grouped_gemm");
   if (num_tiles <= 0) return;
   c10::cuda::CUDAGuard guard(problems.device());
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
@@ -330,6 +407,7 @@ void run_gemm_range(const torch::Tensor& problems, const torch::Tensor& tiles, i
 
 void run_gemm_plan(const torch::Tensor& problems, const torch::Tensor& tiles, int64_t num_tiles, double alpha,
                    double beta, bool split, torch::Tensor status, double gamma) {
+  LaunchScope scope("ob200::grouped_gemm");
   c10::cuda::CUDAGuard guard(problems.device());
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   launch_grouped_gemm(reinterpret_cast<const GemmProblem*>(problems.data_ptr()),
@@ -343,6 +421,7 @@ void run_gemm_plan(const torch::Tensor& problems, const torch::Tensor& tiles, in
 void run_gemm_plan_push(const torch::Tensor& problems, const torch::Tensor& tiles, int64_t num_tiles, double alpha,
                         double beta, bool split, torch::Tensor status, const std::vector<int64_t>& peer_bases,
                         int64_t send_dtype) {
+  LaunchScope scope("ob200::grouped_gemm_push");
   c10::cuda::CUDAGuard guard(problems.device());
   TORCH_CHECK(peer_bases.size() <= 8, "at most 8 peers");
   PeerPush push{};
@@ -422,6 +501,7 @@ void grad_prologue(const torch::Tensor& blocks, const torch::Tensor& tiles, int6
                    double bias_correction1, int64_t graft_kind, double graft_beta2, double graft_weight,
                    double graft_bc2, double graft_eps, bool write_split, torch::Tensor status,
                    int64_t num_grad_peers, double grad_scale) {
+  LaunchScope scope("ob200::grad_prologue");
   c10::cuda::CUDAGuard guard(blocks.device());
   PrologueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
@@ -451,6 +531,7 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
                         const torch::Tensor& mu_x, bool classic_momentum, double momentum, double dampening,
                         bool nesterov, int64_t send_dtype, bool split_input, const std::vector<int64_t>& peer_bases,
                         bool send_params) {
+  LaunchScope scope("ob200::direction_epilogue");
   c10::cuda::CUDAGuard guard(blocks.device());
   EpilogueArgs a;
   a.blocks = reinterpret_cast<const BlockDesc*>(blocks.data_ptr());
@@ -481,6 +562,7 @@ void direction_epilogue(const torch::Tensor& blocks, const torch::Tensor& tiles,
 
 void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype,
                     bool copy_params, const std::optional<torch::Tensor>& status) {
+  LaunchScope scope("ob200::gathered_apply");
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
                         static_cast<int>(num_tiles), static_cast<int>(dtype), nullptr, 0.f, copy_params,
@@ -492,6 +574,7 @@ void gathered_apply(const torch::Tensor& blocks, const torch::Tensor& tiles, int
 // points at the block's grafting scale: W <- W - lr (scale P + wd_alpha W).
 void gathered_apply_scaled(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, int64_t dtype,
                            const torch::Tensor& lr, double wd_alpha, const std::optional<torch::Tensor>& status) {
+  LaunchScope scope("ob200::gathered_apply_scaled");
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_gathered_apply(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
                         static_cast<int>(num_tiles), static_cast<int>(dtype), lr.data_ptr<float>(),
@@ -502,6 +585,7 @@ void gathered_apply_scaled(const torch::Tensor& blocks, const torch::Tensor& til
 
 void eig_scale(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double bc2, double inv_root,
                double eps, bool write_split) {
+  LaunchScope scope("ob200::eig_scale");
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_eig_scale(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
                    static_cast<int>(num_tiles), static_cast<float>(bc2), static_cast<float>(inv_root),
@@ -510,6 +594,7 @@ void eig_scale(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t 
 }
 
 void mode_switch(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_t num_tiles, double coeff, int64_t send_dtype) {
+  LaunchScope scope("ob200::mode_switch");
   c10::cuda::CUDAGuard guard(blocks.device());
   launch_mode_switch(reinterpret_cast<const BlockDesc*>(blocks.data_ptr()), tile_ptr(tiles),
                      static_cast<int>(num_tiles), static_cast<float>(coeff), static_cast<int>(send_dtype),
@@ -519,6 +604,7 @@ void mode_switch(const torch::Tensor& blocks, const torch::Tensor& tiles, int64_
 
 void peer_barrier(torch::Tensor local_flags, const torch::Tensor& peer_flag_bases, int64_t my_rank, int64_t world,
                   int64_t seq, torch::Tensor status) {
+  LaunchScope scope("ob200::peer_barrier");
   c10::cuda::CUDAGuard guard(local_flags.device());
   TORCH_CHECK(world <= 32, "peer barrier supports up to 32 ranks");
   launch_peer_barrier(local_flags.data_ptr<int>(),
@@ -563,6 +649,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_mat_table(const std::vec
 }
 
 void affine_identity_split(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks, double a, double b) {
+  LaunchScope scope("ob200::affine_identity_split");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_affine_identity_split(reinterpret_cast<const MatOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
                                static_cast<int>(num_chunks), static_cast<float>(a), static_cast<float>(b),
@@ -571,6 +658,7 @@ void affine_identity_split(const torch::Tensor& ops, const torch::Tensor& chunks
 }
 
 void identity_error(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  LaunchScope scope("ob200::identity_error");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_identity_error(reinterpret_cast<const MatOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
                         static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
@@ -579,6 +667,7 @@ void identity_error(const torch::Tensor& ops, const torch::Tensor& chunks, int64
 
 // Exact-fp32 P = L G R for one block; the m x n intermediate comes from torch's allocator.
 torch::Tensor two_sided_apply(const torch::Tensor& L, const torch::Tensor& G, const torch::Tensor& R) {
+  LaunchScope scope("ob200::two_sided_apply");
   TORCH_CHECK(L.is_cuda() && G.is_cuda() && R.is_cuda(), "operands must be CUDA tensors");
   TORCH_CHECK(L.scalar_type() == torch::kFloat32 && G.scalar_type() == torch::kFloat32 && R.scalar_type() == torch::kFloat32);
   TORCH_CHECK(L.is_contiguous() && G.is_contiguous() && R.is_contiguous() && G.dim() == 2);
@@ -594,6 +683,7 @@ torch::Tensor two_sided_apply(const torch::Tensor& L, const torch::Tensor& G, co
 }
 
 void tf32_split(const torch::Tensor& src, torch::Tensor hi, torch::Tensor lo) {
+  LaunchScope scope("ob200::tf32_split");
   TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1);
   TORCH_CHECK(hi.dim() == 2 && lo.dim() == 2 && hi.stride(1) == 1 && lo.stride(1) == 1);
   c10::cuda::CUDAGuard guard(src.device());
@@ -605,6 +695,7 @@ void tf32_split(const torch::Tensor& src, torch::Tensor hi, torch::Tensor lo) {
 void gpa_adamw_step(const torch::Tensor& table, int64_t total_chunks, const torch::Tensor& chunk_map, double lr,
                     double beta1, double beta2, double eps, double bias_correction1, double bias_correction2,
                     double weight_decay, bool wd_on_y, double avg_coeff, double train_interp_coeff) {
+  LaunchScope scope("ob200::gpa_adamw_step");
   c10::cuda::CUDAGuard guard(table.device());
   launch_gpa_adamw(reinterpret_cast<const GpaTensorDesc*>(table.data_ptr()),
                    reinterpret_cast<const int2*>(chunk_map.data_ptr()), static_cast<int>(total_chunks),
@@ -616,6 +707,7 @@ void gpa_adamw_step(const torch::Tensor& table, int64_t total_chunks, const torc
 }
 
 void gpa_lerp(const torch::Tensor& table, int64_t total_chunks, const torch::Tensor& chunk_map, double weight) {
+  LaunchScope scope("ob200::gpa_lerp");
   c10::cuda::CUDAGuard guard(table.device());
   launch_gpa_lerp(reinterpret_cast<const GpaTensorDesc*>(table.data_ptr()), reinterpret_cast<const int2*>(chunk_map.data_ptr()),
                   static_cast<int>(total_chunks), static_cast<float>(weight), at::cuda::getCurrentCUDAStream());
@@ -678,6 +770,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_copy_table(const std::ve
 // Returns (eigenvalue tensors, eigenvector tensors, sweeps used per matrix as a device int tensor).
 std::tuple<std::vector<torch::Tensor>, std::vector<torch::Tensor>, torch::Tensor> jacobi_eigh(
     const std::vector<torch::Tensor>& mats, int64_t max_sweeps, double tol) {
+  LaunchScope scope("ob200::jacobi_eigh");
   TORCH_CHECK(!mats.empty(), "jacobi_eigh: empty batch");
   const auto device = mats[0].device();
   c10::cuda::CUDAGuard guard(device);
@@ -710,6 +803,7 @@ std::tuple<std::vector<torch::Tensor>, std::vector<torch::Tensor>, torch::Tensor
 torch::Tensor jacobi_eigh_into(const std::vector<torch::Tensor>& mats, const std::vector<torch::Tensor>& qs,
                                const std::vector<torch::Tensor>& lams, bool transposed, int64_t max_sweeps, double tol,
                                double shift_scale) {
+  LaunchScope scope("ob200::jacobi_eigh_into");
   TORCH_CHECK(!mats.empty() && mats.size() == qs.size() && mats.size() == lams.size(), "jacobi_eigh_into: list sizes");
   const auto device = mats[0].device();
   c10::cuda::CUDAGuard guard(device);
@@ -776,6 +870,7 @@ torch::Tensor build_qr_panel_table(const std::vector<py::tuple>& specs) {
 }
 
 void householder_panel(const torch::Tensor& table, int64_t count) {
+  LaunchScope scope("ob200::householder_panel");
   c10::cuda::CUDAGuard guard(table.device());
   launch_householder_panel(reinterpret_cast<const QrPanelDesc*>(table.data_ptr()), static_cast<int>(count),
                            at::cuda::getCurrentCUDAStream());
@@ -799,6 +894,7 @@ void householder_panel(const torch::Tensor& table, int64_t count) {
 // Replaces torch.linalg.qr (cuSOLVER geqrf + orgqr) of the reference's QR iteration
 // (distributed_shampoo/preconditioner/matrix_functions.py:843).
 void householder_qr(const std::vector<py::tuple>& specs) {
+  LaunchScope scope("ob200::householder_qr");
   TORCH_CHECK(!specs.empty(), "householder_qr: empty batch");
   struct Item {
     torch::Tensor ct, zt, zt_hi, zt_lo, vt, ttv, tv;
@@ -979,18 +1075,21 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_sym_table(const std::vec
 }
 
 void sym_measure(const torch::Tensor& ops, int64_t count) {
+  LaunchScope scope("ob200::sym_measure");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_sym_measure(reinterpret_cast<const SymOp*>(ops.data_ptr()), static_cast<int>(count), at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 void sq_offdiag(const torch::Tensor& ops, int64_t count) {
+  LaunchScope scope("ob200::sq_offdiag");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_sq_offdiag(reinterpret_cast<const SymOp*>(ops.data_ptr()), static_cast<int>(count), at::cuda::getCurrentCUDAStream());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 void shift_scale_split(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  LaunchScope scope("ob200::shift_scale_split");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_shift_scale_split(reinterpret_cast<const SymOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
                            static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
@@ -1071,6 +1170,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_pack_table(const std::ve
 }
 
 void pack_upper(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  LaunchScope scope("ob200::pack_upper");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_pack_upper(reinterpret_cast<const UnpackOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
                     static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
@@ -1078,6 +1178,7 @@ void pack_upper(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t n
 }
 
 void unpack_split(const torch::Tensor& ops, const torch::Tensor& chunks, int64_t num_chunks) {
+  LaunchScope scope("ob200::unpack_split");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_unpack_split(reinterpret_cast<const UnpackOp*>(ops.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
                       static_cast<int>(num_chunks), at::cuda::getCurrentCUDAStream());
@@ -1127,6 +1228,7 @@ std::tuple<torch::Tensor, torch::Tensor, int64_t> build_transpose_table(const st
 }
 
 void transpose_split(const torch::Tensor& ops, const torch::Tensor& tiles, int64_t num_tiles) {
+  LaunchScope scope("ob200::transpose_split");
   c10::cuda::CUDAGuard guard(ops.device());
   launch_transpose_split(reinterpret_cast<const TransposeOp*>(ops.data_ptr()), reinterpret_cast<const int4*>(tiles.data_ptr()),
                          static_cast<int>(num_tiles), at::cuda::getCurrentCUDAStream());
@@ -1134,6 +1236,7 @@ void transpose_split(const torch::Tensor& ops, const torch::Tensor& tiles, int64
 }
 
 void peer_copy(const torch::Tensor& table, const torch::Tensor& chunks, int64_t num_chunks) {
+  LaunchScope scope("ob200::peer_copy");
   if (num_chunks == 0) return;
   c10::cuda::CUDAGuard guard(table.device());
   launch_peer_copy(reinterpret_cast<const CopyDesc*>(table.data_ptr()), reinterpret_cast<const int2*>(chunks.data_ptr()),
@@ -1148,6 +1251,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("FLAG_SPLIT_OUT") = kFlagSplitOut;
   m.attr("FLAG_SUMSQ") = kFlagSumSq;
   m.attr("FLAG_NO_C") = kFlagNoC;
+  m.def("set_launch_tracing", &set_launch_tracing, py::arg("nvtx"), py::arg("timing"));
+  m.def("launch_timings", &launch_timings, py::arg("reset") = false);
   m.def("build_gemm_plan", &build_gemm_plan);
   m.def("run_gemm_plan", &run_gemm_plan, py::arg("problems"), py::arg("tiles"), py::arg("num_tiles"), py::arg("alpha"),
         py::arg("beta"), py::arg("split"), py::arg("status"), py::arg("gamma") = 0.0);

@@ -61,6 +61,8 @@ def main() -> None:
     for rec in opt._per_group_state_lists:
         if rec.get("native_engine") is not None:
             rec["native_engine"].check_status()
+            arena = getattr(rec["native_engine"], "_arena", None)
+            assert arena is None or arena.overrun_regions() == [], arena.overrun_regions()
             pushed = rec["native_engine"].gemm_push_steps
             # 8 steps, preconditioning from step 3: six steps gather from the GEMM epilogue
             assert pushed == (6 if mode == "p2p_gemm" else 0), pushed
@@ -166,11 +168,16 @@ def sharded_main() -> None:
                 assert d._gather_grads_ctx._p2p and d._redistribute_ctx._p2p
             d._gather_grads_ctx.check_status()
             d._redistribute_ctx.check_status()
+            for ctx in (d._gather_grads_ctx, d._redistribute_ctx):
+                arena = getattr(ctx, "_arena", None)
+                assert arena is None or arena.overrun_regions() == [], arena.overrun_regions()
     engines = [rec.get("native_engine") for rec in opt._per_group_state_lists]
     assert all((e is not None) == (backend == "native") for e in engines), engines
     for e in engines:
         if e is not None:
             e.check_status()
+            arena = getattr(e, "_arena", None)
+            assert arena is None or arena.overrun_regions() == [], arena.overrun_regions()
     torch.cuda.synchronize()
     if strategy in ("fsdp", "hsdp"):
         with FSDP.summon_full_params(model):
