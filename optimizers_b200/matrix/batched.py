@@ -493,16 +493,29 @@ def batched_eigen_refresh(ext: Any, blocks: list[Any], bias_correction2: Tensor 
 # Coupled Newton inverse root, all factors at once, on the grouped tensor-core GEMM
 # ----------------------------------------------------------------------------------------------
 def newton_refresh_supported(cfg: Any) -> bool:
-    from optimizers_b200.config import CoupledNewtonConfig
+    from optimizers_b200.config import CoupledHigherOrderConfig, CoupledNewtonConfig
 
-    return isinstance(cfg, CoupledNewtonConfig)
+    return isinstance(cfg, (CoupledNewtonConfig, CoupledHigherOrderConfig))
+
+
+def _taylor_coefficients(p: int, order: int) -> list[float]:
+    """Coefficients of 1, x, ..., x^(order-1) in the Taylor series of (1 - x)^(-1/p)."""
+    coeff = [1.0]
+    num = den = 1
+    for i in range(1, order):
+        num *= 1 + (i - 1) * p
+        den *= i * p
+        coeff.append(num / den)
+    return coeff
 
 
 class _NewtonItem:
     """Iteration buffers of one factor.  Every matrix is kept as a (hi, lo) tf32 pair in padded
     storage so that it can be an operand of the next grouped GEMM; ``X`` and ``M`` ping-pong."""
 
-    __slots__ = ("block", "k", "d", "root", "A", "X", "M", "Mp", "pw", "err", "converged", "last_err", "iters")
+    __slots__ = (
+        "block", "k", "d", "root", "power", "A", "Ar", "X", "M", "Mp", "R", "T", "pw", "err", "converged", "last_err", "iters",
+    )
 
 
 def _pair(d: int, device: torch.device, split: bool) -> tuple[Tensor, Tensor | None]:
@@ -550,7 +563,18 @@ def batched_newton_refresh(
     when its error is below the configured tolerance, when the iteration limit is reached
     (warning, as in the reference), or when the error stalls above the tolerance at the
     rounding floor of the tensor-core accumulation (error below 1e-3 and not improved by 10 %
-    between two checks)."""
+    between two checks).
+
+    ``CoupledHigherOrderConfig`` runs through the same loop (reference:
+    distributed_shampoo/preconditioner/matrix_functions.py:439-661): the ridge is
+    ``max(rel_epsilon * ||A||_inf, abs_epsilon)``, the start is ``z = 1 / trace``, the first step is a
+    Newton step and every later one builds ``M_p = sum_i c_i (I - M)^i`` (Taylor coefficients of
+    ``(1 - x)^(-1/p)``) by Horner products whose ``+ c_i I`` is the GEMM epilogue's diagonal term;
+    the error is read every iteration, an increase by 20 % stops the factor, and at the end
+    ``max |A_r X^p - I| <= 0.1`` is verified on the device and ``X^q`` formed for a fractional
+    root ``p / q``."""
+    from optimizers_b200.config import CoupledHigherOrderConfig
+
     if not blocks:
         return
     # The iteration amplifies operand rounding: a single tf32 product per multiply does not
@@ -560,18 +584,23 @@ def batched_newton_refresh(
     device = blocks[0].inv_hi[0].device
     cfg = blocks[0].factors.amortized_computation_config
     max_iterations, tolerance = cfg.max_iterations, cfg.tolerance
+    higher = cfg if isinstance(cfg, CoupledHigherOrderConfig) else None
 
     items: list[_NewtonItem] = []
     for b, k, A in _prepared_factors(ext, blocks, bias_correction2):
         kf = b.factors
-        if True:
-            root = Fraction(kf.roots[k])
-            if root.denominator != 1:
-                raise ValueError(f"root.denominator={root.denominator} must be equal to 1 to use coupled inverse Newton iteration!")
-            it = _NewtonItem()
-            it.block, it.k, it.d, it.root, it.A = b, k, A.shape[0], root.numerator, A
-            it.converged, it.last_err, it.iters = False, float("inf"), 0
-            items.append(it)
+        root = Fraction(kf.roots[k])
+        if higher is None and root.denominator != 1:
+            raise ValueError(f"root.denominator={root.denominator} must be equal to 1 to use coupled inverse Newton iteration!")
+        if higher is not None and min(abs(root.numerator), abs(root.denominator)) >= 10:
+            logger.warning(
+                f"abs(root.numerator)={abs(root.numerator)} and abs(root.denominator)={abs(root.denominator)} are probably too big for best performance."
+            )
+        it = _NewtonItem()
+        it.block, it.k, it.d, it.root, it.power, it.A = b, k, A.shape[0], root.numerator, root.denominator, A
+        it.converged, it.last_err, it.iters = False, float("inf"), 0
+        it.Ar = None
+        items.append(it)
     finite = _all_finite([it.A for it in items])
     for it, ok in zip(items, finite):
         if not ok:
@@ -582,10 +611,16 @@ def batched_newton_refresh(
     errs = torch.zeros(len(items), device=device)
     for n, it in enumerate(items):
         d, p = it.d, it.root
-        eps = it.block.factors.epsilon
         A_r = it.A.clone()
-        A_r.diagonal().add_(eps)
-        z = (p + 1) / (2 * torch.linalg.norm(A_r))
+        if higher is None:
+            A_r.diagonal().add_(it.block.factors.epsilon)
+            z = (p + 1) / (2 * torch.linalg.norm(A_r))
+        else:
+            lam = torch.linalg.matrix_norm(it.A, torch.inf)
+            A_r.diagonal().add_(torch.clamp(lam * higher.rel_epsilon, min=higher.abs_epsilon))
+            z = torch.reciprocal(torch.trace(A_r))
+            it.Ar = _pair(d, device, split)  # the verification at the end multiplies X^p by it
+            ext.tf32_split(A_r, *_v(it.Ar, d))
         it.X = [_pair(d, device, split), _pair(d, device, split)]
         it.M = [_pair(d, device, split), _pair(d, device, split)]
         it.Mp = _pair(d, device, split)
@@ -601,28 +636,29 @@ def batched_newton_refresh(
             else:
                 hi.copy_(src)
         it.err = errs[n : n + 1]
-    return _newton_iterate(ext, items, errs, split, status, max_iterations, tolerance, check_every, blocks)
+    order = higher.order if higher is not None else 0
+    return _newton_iterate(ext, items, errs, split, status, max_iterations, tolerance, check_every, blocks, order)
 
 
 _NEWTON_CHUNK_ELEMS = 64 * 1024 * 1024  # sum of d^2 iterated together (16 arrays of that size are live)
 
 
-def _newton_iterate(ext, items, errs, split, status, max_iterations, tolerance, check_every, blocks) -> None:
+def _newton_iterate(ext, items, errs, split, status, max_iterations, tolerance, check_every, blocks, order=0) -> None:
     failures: dict[int, Exception] = {}
     by_root: dict[int, list[_NewtonItem]] = {}
     for it in items:
-        by_root.setdefault(it.root, []).append(it)
+        by_root.setdefault(it.root, []).append(it)  # grouped by the numerator p; q only matters at the end
     for p, group in by_root.items():
         chunk: list[_NewtonItem] = []
         size = 0
         for it in sorted(group, key=lambda x: -x.d):
             if chunk and size + it.d * it.d > _NEWTON_CHUNK_ELEMS:
-                _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures)
+                _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures, order)
                 chunk, size = [], 0
             chunk.append(it)
             size += it.d * it.d
         if chunk:
-            _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures)
+            _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures, order)
 
     # results -> packed checkpoint state; one finiteness read
     good = [it for it in items if id(it) not in failures]
@@ -653,10 +689,14 @@ def _newton_iterate(ext, items, errs, split, status, max_iterations, tolerance, 
         b.factors.note_refresh_outcome(last_error.get(id(b)))
 
 
-def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures) -> None:
+def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolerance, check_every, failures, order=0) -> None:
     device = errs.device
     alpha = -1.0 / p
     chain = _power_chain(p)
+    coeff = _taylor_coefficients(p, order) if order else None
+    horner = max(order - 2, 0)  # products per higher-order step that build M_p
+    if order:
+        check_every = 1  # the stopping rule compares consecutive errors
     for it in chunk:
         d = it.d
         it.pw = {e: _pair(d, device, split) for e, _, _ in chain}
@@ -664,20 +704,46 @@ def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolera
         it.A = [torch.zeros(d, _pad4(d), device=device), torch.zeros(d, _pad4(d), device=device)]
         hi, lo = _v(it.M[0], d)
         it.A[0][:, :d].copy_(hi + lo if lo is not None else hi)
+        if horner:
+            it.R = _pair(d, device, split)
+            it.T = [_pair(d, device, split) for _ in range(min(horner, 2))]
 
-    def gemm(a, b, out, d, c_full=None):
+    def gemm(a, b, out, d, c_full=None, flags=0):
+        # Every product here is a polynomial in one symmetric matrix, hence symmetric: only the
+        # upper tiles are computed and mirrored bit for bit.  Without that, the antisymmetric part
+        # of the rounding errors is amplified from step to step (the kernel multiplies by B^T) and
+        # the error of an ill-conditioned factor stalls near 1e-3.
         a_hi, a_lo = _v(a, d)
         b_hi, b_lo = _v(b, d)
+        flags |= ext.FLAG_MIRROR
         if split:
-            flags = ext.FLAG_SPLIT_OUT | (0 if c_full is not None else ext.FLAG_NO_C)
-            return (a_hi, a_lo, b_hi, b_lo, c_full, out[0], out[1], None, out[0].stride(0), out[0].stride(0), flags, False)
+            flags |= ext.FLAG_SPLIT_OUT | (0 if c_full is not None else ext.FLAG_NO_C)
+            return (a_hi, a_lo, b_hi, b_lo, c_full, out[0], out[1], None, out[0].stride(0), out[0].stride(0), flags, True)
         # single-pass mode: the plain result is the operand of the next product
-        return (a_hi, None, b_hi, None, out[0], None, None, None, out[0].stride(0), 0, 0, False)
+        return (a_hi, None, b_hi, None, out[0], None, None, None, out[0].stride(0), 0, flags, True)
 
-    def build(active, cur):
+    def build(active, cur, newton_step):
         nxt = cur ^ 1
         full_m = lambda it, which: it.A[which][:, : it.d] if split else it.M[which][0][:, : it.d]  # noqa: E731
-        affine = ext.build_mat_table([(full_m(it, cur), *_v(it.Mp, it.d), None) for it in active])
+        pre = []  # (table, a, b) pointwise passes, then (plan, gamma) products that end in M_p
+        if newton_step or not horner:
+            # Newton: (1 - a) I + a M;  order 2: c0 I + c1 (I - M)
+            lin = (alpha, 1.0 - alpha) if (newton_step or not order) else (-coeff[1], coeff[0] + coeff[1])
+            pre.append((ext.build_mat_table([(full_m(it, cur), *_v(it.Mp, it.d), None) for it in active]), *lin))
+            products = []
+        else:
+            # R = I - M;  T = c_{o-1} R + c_{o-2} I;  T <- c_i I + T R for i = o-3 .. 0, the last one into M_p
+            pre.append((ext.build_mat_table([(full_m(it, cur), *_v(it.R, it.d), None) for it in active]), -1.0, 1.0))
+            pre.append((
+                ext.build_mat_table([(full_m(it, cur), *_v(it.T[0], it.d), None) for it in active]),
+                -coeff[order - 1], coeff[order - 1] + coeff[order - 2],
+            ))
+            products = []
+            for n, i in enumerate(reversed(range(order - 2))):
+                src = lambda it: it.T[n % 2]  # noqa: E731
+                dst = (lambda it: it.Mp) if i == 0 else (lambda it: it.T[(n + 1) % 2])  # noqa: E731
+                specs = [gemm(src(it), it.R, dst(it), it.d, flags=ext.FLAG_ADD_DIAG) for it in active]
+                products.append((ext.build_gemm_plan(specs), coeff[i]))
         stages = [[gemm(it.X[cur], it.Mp, it.X[nxt], it.d) for it in active]]
         for n, (e, l, r) in enumerate(chain):
             specs = [gemm(it.Mp if l == 1 else it.pw[l], it.Mp if r == 1 else it.pw[r], it.pw[e], it.d) for it in active]
@@ -693,17 +759,21 @@ def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolera
         stages.append(last)
         plans = [ext.build_gemm_plan(s) for s in stages]
         err_src = [(full_m(it, nxt), None, None, it.err) for it in active]
-        return affine, plans, ext.build_mat_table(err_src)
+        return pre, products, plans, ext.build_mat_table(err_src)
 
     active = list(chunk)
     cur = 0
     tables = {}
     iteration = 0
     while active:
-        if cur not in tables:
-            tables[cur] = build(active, cur)
-        affine, plans, err_table = tables[cur]
-        ext.affine_identity_split(*affine, alpha, 1.0 - alpha)
+        key = (cur, bool(order) and iteration == 0)
+        if key not in tables:
+            tables[key] = build(active, cur, key[1])
+        pre, products, plans, err_table = tables[key]
+        for table, a, b in pre:
+            ext.affine_identity_split(*table, a, b)
+        for plan, gamma in products:
+            ext.run_gemm_plan(*plan, 1.0, 0.0, split, status, gamma)
         for plan in plans:
             ext.run_gemm_plan(*plan, 1.0, 0.0, split, status)
         iteration += 1
@@ -717,11 +787,15 @@ def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolera
         for it, e in zip(active, values):
             it.iters = iteration
             stalled = e < 1e-3 and e > 0.9 * it.last_err
+            grew = bool(order) and e > 1.2 * it.last_err  # the reference's early stop of the higher-order iteration
             if e != e or e == float("inf"):
                 failures[id(it)] = ArithmeticError("coupled Newton iteration produced NaN/Inf")
-            elif e <= tolerance or stalled or iteration >= max_iterations:
+            elif e <= tolerance or stalled or grew or iteration >= max_iterations:
                 if e > tolerance and iteration >= max_iterations:
-                    logger.warning("Newton did not converge and reached maximum number of iterations!")
+                    logger.warning(
+                        "Higher order method did not converge and reached maximum number of iterations!"
+                        if order else "Newton did not converge and reached maximum number of iterations!"
+                    )
             else:
                 it.last_err = e
                 still.append(it)
@@ -730,8 +804,53 @@ def _newton_run_chunk(ext, chunk, p, errs, split, status, max_iterations, tolera
         if len(still) != len(active):
             tables = {}
         active = still
+    if order:
+        _verify_and_power(ext, [it for it in chunk if id(it) not in failures], p, chain, gemm, errs, split, status, failures)
     for it in chunk:  # release iteration buffers
-        it.M = it.Mp = it.pw = it.A = None
+        it.M = it.Mp = it.pw = it.A = it.R = it.T = it.Ar = None
+
+
+def _verify_and_power(ext, items, p, chain, gemm, errs, split, status, failures) -> None:
+    """End of the higher-order iteration: fail the factors with ``max |A_r X^p - I| > 0.1``
+    (reference: matrix_functions.py:628-640) and raise X to the denominator of a fractional root."""
+    if not items:
+        return
+    device = errs.device
+
+    def run(specs):
+        if specs:
+            ext.run_gemm_plan(*ext.build_gemm_plan(specs), 1.0, 0.0, split, status)
+
+    for e, l, r in chain:  # X^p through the buffers of the power chain
+        run([gemm(it.X if l == 1 else it.pw[l], it.X if r == 1 else it.pw[r], it.pw[e], it.d) for it in items])
+    specs = []
+    for it in items:
+        top = it.X if p == 1 else it.pw[p]
+        a_hi, a_lo = _v(top, it.d)
+        b_hi, b_lo = _v(it.Ar, it.d)
+        specs.append((a_hi, a_lo if split else None, b_hi, b_lo if split else None, it.A[0][:, : it.d], None, None, None,
+                      it.A[0].stride(0), 0, ext.FLAG_MIRROR, True))
+    run(specs)
+    errs.zero_()
+    ext.identity_error(*ext.build_mat_table([(it.A[0][:, : it.d], None, None, it.err) for it in items]))
+    values = torch.stack([it.err[0] for it in items]).cpu().tolist()
+    for it, e in zip(items, values):
+        if not e <= 1e-1:
+            failures[id(it)] = ArithmeticError(
+                f"Error in matrix inverse root (before powering for fractions) {e} exceeds threshold 1e-1, raising an exception!"
+            )
+    by_power: dict[int, list] = {}
+    for it in items:
+        if it.power > 1 and id(it) not in failures:
+            by_power.setdefault(it.power, []).append(it)
+    for q, group in by_power.items():
+        steps = _power_chain(q)
+        for it in group:
+            it.pw = {e: _pair(it.d, device, split) for e, _, _ in steps}
+        for e, l, r in steps:
+            run([gemm(it.X if l == 1 else it.pw[l], it.X if r == 1 else it.pw[r], it.pw[e], it.d) for it in group])
+        for it in group:
+            it.X = it.pw[q]
 
 
 # --------------------------------------------------------------------------------------------------

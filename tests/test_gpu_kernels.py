@@ -303,6 +303,49 @@ def test_native_newton_refresh_matches_eigen_roots(split):
     assert checked >= 6
 
 
+@pytest.mark.parametrize("order,exponent", [(3, 0.25), (2, 0.25), (4, 0.5), (3, 2.0 / 3.0)])
+def test_native_higher_order_refresh_matches_eigen_roots(order, exponent):
+    """Batched coupled higher-order iteration on the grouped GEMM (Horner products in I - M, Newton
+    first step, verification of A_r X^p and the q-th power of a fractional root p / q) against the
+    fp64 eigendecomposition of the same ridged matrix."""
+    from fractions import Fraction
+
+    from optimizers_b200 import CoupledHigherOrderConfig, DistributedShampoo, NativeRuntimeConfig, RootInvShampooPreconditionerConfig
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(150, 200), torch.nn.ReLU(), torch.nn.Linear(200, 40)).to(dev)
+    cfg = CoupledHigherOrderConfig(rel_epsilon=1e-4, abs_epsilon=1e-8, order=order, tolerance=1e-6)
+    opt = DistributedShampoo(
+        model.parameters(), lr=1e-3, epsilon=1e-4, max_preconditioner_dim=128, precondition_frequency=1,
+        preconditioner_config=RootInvShampooPreconditionerConfig(
+            amortized_computation_config=cfg, inverse_exponent_override={2: exponent}
+        ),
+        native_runtime_config=NativeRuntimeConfig(backend="native"),
+    )
+    x = torch.randn(256, 150, device=dev)
+    model(x).square().mean().backward()
+    opt.step()
+    engine = opt._per_group_state_lists[0]["native_engine"]
+    assert engine is not None
+    engine.check_status()
+    checked = 0
+    for b in engine._blocks:
+        kf = b.factors
+        if len(kf.roots) != 2:
+            continue
+        for F, X, root in zip(kf.get_unpacked_factor_matrices(), kf.get_unpacked_inv_factor_matrices(), kf.roots):
+            assert Fraction(root).limit_denominator(64) == Fraction(1 / exponent).limit_denominator(64)
+            F = F.double()
+            ridge = max(F.abs().sum(dim=1).max().item() * 1e-4, 1e-8)
+            lam, Q = torch.linalg.eigh(F + ridge * torch.eye(F.shape[0], device=dev, dtype=torch.float64))
+            want = (Q * lam.pow(-exponent)) @ Q.T
+            rel = (X.double() - want).abs().max() / want.abs().max()
+            assert rel < 2e-3, (F.shape, root, rel)
+            checked += 1
+    assert checked >= 4
+
+
 @pytest.mark.parametrize("split", [True, False])
 def test_batched_newton_schulz_matches_torch(split):
     from optimizers_b200.matrix import functions as mf
