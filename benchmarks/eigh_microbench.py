@@ -55,6 +55,7 @@ def main() -> None:
     ap.add_argument("--preset", choices=["", "gpt2"], default="")
     ap.add_argument("--spectrum", choices=["gram", "lowrank", "power1", "power2"], default="gram")
     ap.add_argument("--passes", type=int, default=2)
+    ap.add_argument("--polish", choices=["householder", "newton_schulz"], default="householder")
     ap.add_argument("--skip-library", action="store_true")
     ap.add_argument("--profile", action="store_true", help="also print the time per phase of the driver")
     ap.add_argument("--check", action="store_true", help="accuracy against fp64 eigh (slow)")
@@ -80,7 +81,7 @@ def main() -> None:
         torch.cuda.synchronize()
         return start.elapsed_time(stop), out
 
-    backend = NativeBackend(ext, dev, range_passes=args.passes)
+    backend = NativeBackend(ext, dev, range_passes=args.passes, polish=args.polish)
     ms, (lams, vecs, info) = timed(lambda: eigh_divide_and_conquer(backend, big))
     line = {
         "arm": "divide_and_conquer", "ms": ms, "matrices": len(big), "sizes": sizes, "input_bytes": total_bytes,

@@ -19,57 +19,8 @@ from optimizers_b200 import (
     DistributedShampoo,
     RootInvShampooPreconditionerConfig,
 )
+from fake_ext import FakeExt
 from optimizers_b200.matrix import batched, functions as mf
-
-
-class FakeExt:
-    """The subset of the extension's interface that the coupled iterations use."""
-
-    FLAG_PACKED_C, FLAG_SPLIT_OUT, FLAG_SUMSQ, FLAG_NO_C = 1, 2, 4, 8
-    FLAG_MIRROR, FLAG_ADD_DIAG = 64, 128
-
-    def __init__(self):
-        self.gemm_launches = 0
-
-    def tf32_split(self, src, hi, lo):
-        hi.copy_(src)
-        lo.zero_()
-
-    def build_mat_table(self, specs):
-        return (list(specs), None, 0)
-
-    def affine_identity_split(self, specs, _chunks, _n, a, b):
-        for src, hi, lo, _err in specs:
-            hi.copy_(a * src + b * torch.eye(src.shape[0]))
-            if lo is not None:
-                lo.zero_()
-
-    def identity_error(self, specs, _chunks, _n):
-        for src, _hi, _lo, err in specs:
-            err[0] = (src - torch.eye(src.shape[0])).abs().max()
-
-    def build_gemm_plan(self, specs):
-        return (list(specs), None, 0)
-
-    def run_gemm_plan(self, specs, _tiles, _n, alpha, beta, split, status, gamma=0.0):
-        self.gemm_launches += 1
-        for a_hi, a_lo, b_hi, b_lo, c, d_hi, d_lo, _sumsq, _ldc, _ldd, flags, _upper in specs:
-            A = a_hi + (a_lo if a_lo is not None else 0)
-            B = b_hi + (b_lo if b_lo is not None else 0)
-            out = alpha * (A.double() @ B.double().T).float()
-            m, n = out.shape  # outputs may be handed over in their padded storage
-            if flags & self.FLAG_MIRROR:
-                assert _upper and m == n
-                out = torch.triu(out) + torch.triu(out, 1).T
-            if c is not None and not flags & self.FLAG_NO_C and beta != 0.0:
-                out = out + beta * c[:m, :n]
-            if flags & self.FLAG_ADD_DIAG:
-                out = out + gamma * torch.eye(m)
-            if c is not None and not flags & self.FLAG_NO_C:
-                c[:m, :n].copy_(out)
-            if flags & self.FLAG_SPLIT_OUT:
-                d_hi[:m, :n].copy_(out)
-                d_lo.zero_()
 
 
 def _blocks(config, exponent=None, seed=0):
@@ -149,3 +100,42 @@ def test_higher_order_verification_rejects_a_wrong_root():
         torch.equal(m, old) for b, olds in zip(blocks, before) for m, old in zip(b.factors.inv_factor_matrices, olds)
     )
     assert kept >= 1
+
+
+@pytest.mark.parametrize("max_iterations", [1, 3])
+def test_qr_iteration_loop_matches_the_per_factor_function(max_iterations):
+    """The batched warm-started QR iteration against the per-factor torch function: same number of
+    sweeps (the criterion is evaluated the same way), hence the same bases up to column signs."""
+    gen = torch.Generator().manual_seed(5)
+    mats, estimates = [], []
+    for n in (12, 40, 7):
+        q, _ = torch.linalg.qr(torch.randn(n, n, generator=gen))
+        lam = torch.linspace(1.0, 3.0, n)
+        mats.append((q * lam) @ q.T)
+        # previous eigenvectors: the true ones rotated a little
+        skew = torch.randn(n, n, generator=gen) * 0.03
+        estimates.append(q @ torch.linalg.matrix_exp(skew - skew.T))
+    estimates[2] = torch.linalg.eigh(mats[2])[1]  # already diagonalising: must be left alone
+    status = torch.zeros(1, dtype=torch.int32)
+    got = batched.native_qr_iteration(FakeExt(), mats, estimates, max_iterations, 1e-4, status)
+    for A, V0, V in zip(mats, estimates, got):
+        _, want = mf._qr_iteration(A, V0, max_iterations, 1e-4)
+        n = A.shape[0]
+        assert torch.allclose(V.T @ V, torch.eye(n), atol=1e-5)
+        overlap = (want.T @ V).abs()
+        assert torch.allclose(overlap, torch.eye(n), atol=2e-3), overlap
+    assert torch.allclose(got[2].abs(), estimates[2].abs(), atol=1e-6)
+
+
+@pytest.mark.parametrize("split", [True, False])
+def test_newton_schulz_loop_matches_the_per_factor_function(split):
+    gen = torch.Generator().manual_seed(6)
+    shapes = [(20, 12), (9, 30), (16, 16)]
+    mats = [torch.randn(*s, generator=gen) for s in shapes]
+    coefficients = (3.4445, -4.7750, 2.0315)
+    runner = batched.BatchedNewtonSchulz(FakeExt(), shapes, torch.device("cpu"), split=split)
+    got = runner(mats, 5, coefficients)
+    for A, X in zip(mats, got):
+        want = mf.newton_schulz(A, 5, coefficients)
+        assert X.shape == A.shape
+        assert torch.allclose(X, want, rtol=1e-4, atol=1e-4)
