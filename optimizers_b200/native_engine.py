@@ -117,8 +117,8 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     ):
         if block.dim() > 3 or (block.dim() == 3 and not _order3_ok(block, pc)):
             return f"block of order {block.dim()} and shape {tuple(block.shape)} has no native step yet"
-        if not all(sel):
-            return "blocks with unpreconditioned dims have no native step yet"
+        if not all(sel) and (block.dim() > 2 or type(pc) not in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig)):
+            return "blocks with unpreconditioned dims have a native step only for 1-D / 2-D blocks of (eigendecomposed) root-inverse Shampoo"
         if block.numel() == 0:
             return "empty blocks"
     if any(b.dim() > 3 or b.numel() == 0 or (b.dim() == 3 and not b.is_contiguous()) for b in rec[DISTRIBUTOR]._global_blocked_params):
@@ -193,6 +193,7 @@ class _Block:
         "m1", "v", "mom", "z", "g_hi", "g_lo", "gt_hi", "gt_lo", "f_hi", "f_lo", "tt_hi", "tt_lo", "p",
         "inv_hi", "inv_lo", "ev", "qt_hi", "qt_lo", "t2_hi", "t2_lo",
         "dims3", "view2d", "y_hi", "y_lo", "zt_hi", "zt_lo", "aux_g_hi", "aux_g_lo", "aux_gt_hi", "aux_gt_lo", "d1_hi", "d1_lo", "d2_hi", "d2_lo",
+        "sel",  # per dim of the block: has a Kronecker factor (inverse_exponent_override 0 switches a dim off)
         "eig_hints",  # factor index -> eigenvalues found at the previous refresh (host tensor; steers the eigensolver)
     )
 
@@ -251,7 +252,15 @@ class NativeGroupEngine:
         self._p2p = self._ddp and cfg.comm_path == "p2p"
         self._pull = self._p2p and cfg.fuse_gradient_reduction and type(group[DISTRIBUTED_CONFIG]) is DDPDistributedConfig
         self._comm_params = bool(getattr(group[DISTRIBUTED_CONFIG], "communicate_params", False)) and self._ddp
-        self._gemm_push = self._p2p and cfg.fuse_direction_push and not self._soap and not self._comm_params
+        # Every rank must take the same decision, so the rule looks at the configuration only: a dim
+        # switched off by an exponent of 0 leaves blocks without a final product to push from.
+        overrides = getattr(group[PRECONDITIONER_CONFIG], "inverse_exponent_override", {}).values()
+        some_dim_off = any(
+            0.0 in (o.values() if isinstance(o, dict) else (o,)) for o in overrides
+        )
+        self._gemm_push = (
+            self._p2p and cfg.fuse_direction_push and not self._soap and not self._comm_params and not some_dim_off
+        )
         self.gemm_push_steps = 0  # steps whose all-gather ran from the GEMM epilogue
         self._comm_dtype_code = 0
         self._gather_table = None
@@ -303,8 +312,10 @@ class NativeGroupEngine:
         pool = _ZeroPool(dev)
         zeros = pool.zeros
 
+        selectors = self._plist._local_preconditioned_dims_selector_list
         for i, (view, info) in enumerate(zip(dist.local_blocked_params, dist.local_block_info_list, strict=True)):
             b = _Block()
+            b.sel = tuple(selectors[i])
             b.eig_hints = None
             b.index = i
             b.param_view = view
@@ -329,7 +340,9 @@ class NativeGroupEngine:
             b.mom = moms[i] if moms is not None else None
             b.z = zs[i] if zs is not None else None
             two_d = b.order == 2
-            need_g = two_d or self._soap
+            left = two_d and b.sel[0]  # a factor on the rows
+            right = b.sel[-1]  # a factor on the columns (the only dim of a 1-D block)
+            need_g = left or self._soap
             if b.dims3 is not None:
                 self._alloc_order3(b, zeros)
                 blocks.append(b)
@@ -337,8 +350,9 @@ class NativeGroupEngine:
             b.aux_g_hi = b.aux_g_lo = b.aux_gt_hi = b.aux_gt_lo = b.d1_hi = b.d1_lo = b.d2_hi = b.d2_lo = None
             b.g_hi = zeros(b.m, b.n_pad) if need_g else None
             b.g_lo = zeros(b.m, b.n_pad) if need_g and self._split else None
-            b.gt_hi = zeros(b.n, b.m_pad)
-            b.gt_lo = zeros(b.n, b.m_pad) if self._split else None
+            need_gt = right or self._soap
+            b.gt_hi = zeros(b.n, b.m_pad) if need_gt else None
+            b.gt_lo = zeros(b.n, b.m_pad) if need_gt and self._split else None
             b.f_hi = zeros(b.m, b.n_pad)
             b.f_lo = zeros(b.m, b.n_pad) if self._split else None
             # The chain intermediate T^T [n, m_pad] takes over the memory of G^T, whose last reader
@@ -349,11 +363,15 @@ class NativeGroupEngine:
                 b.y_hi, b.zt_hi = zeros(b.m, b.n_pad), zeros(b.n, b.m_pad)
                 if self._split:
                     b.y_lo, b.zt_lo = zeros(b.m, b.n_pad), zeros(b.n, b.m_pad)
-            b.tt_hi = b.gt_hi if two_d else None
-            b.tt_lo = b.gt_lo if two_d and self._split else None
+            if left and not right:  # (F I)^T = F^T has no G^T to reuse
+                b.tt_hi = zeros(b.n, b.m_pad)
+                b.tt_lo = zeros(b.n, b.m_pad) if self._split else None
+            else:
+                b.tt_hi = b.gt_hi if left else None
+                b.tt_lo = b.gt_lo if left and self._split else None
             # Likewise the search direction P [m, n] reuses G (hi part) when the pitches agree.
             b.p = b.g_hi if (b.g_hi is not None and b.n_pad == b.n) else zeros(b.m, b.n)
-            dims = (b.m, b.n) if two_d else (b.n,)
+            dims = tuple(d for d, on in zip((b.m, b.n) if two_d else (b.n,), b.sel, strict=True) if on)
             b.inv_hi = [zeros(d, _pad4(d)) for d in dims]
             b.inv_lo = [zeros(d, _pad4(d)) if self._split else None for d in dims]
             b.ev = b.qt_hi = b.qt_lo = b.t2_hi = b.t2_lo = None
@@ -473,7 +491,7 @@ class NativeGroupEngine:
                 (
                     b.view2d, b.grad_offset, b.grad_slot, b.m, b.n, b.n_pad, b.m_pad, b.m1, b.v, b.mom, b.z,
                     b.g_hi, b.g_lo, b.gt_hi, b.gt_lo, b.f_hi, b.f_lo, b.p, self._norms[b.index], self._send_ptr(b),
-                    self._slot_offset(b), b.ev, 0,
+                    self._slot_offset(b), b.ev, 0 if (self._soap or any(b.sel)) else 2,
                 )
             )
         for b in blocks:
@@ -494,6 +512,7 @@ class NativeGroupEngine:
             return t[:, :k] if t.shape[1] != k else t
 
         syrk, gemm0, gemm1, gemm2, kl = [], [], [], [], []
+        f_transposes = []  # (F hi|lo -> T^T hi|lo) of the blocks preconditioned on the rows only
         pack_flag = F.FLAG_PACKED_C if self._packing else 0
         sp = self._split
 
@@ -522,7 +541,12 @@ class NativeGroupEngine:
                 gemm2.append((*inv[0], *d2, b.p, None, None, self._norms[b.index, 1:2], bb * c, 0, F.FLAG_SUMSQ, False))
                 continue
             two_d = b.order == 2
-            t_hi, t_lo = op(b.gt_hi, b.n, b.m), (op(b.gt_lo, b.n, b.m) if self._split else None)
+            left, right = two_d and b.sel[0], b.sel[-1]
+            if not (left or right):
+                continue  # the prologue itself delivers P = filtered gradient and ||P||^2
+            t_hi = t_lo = None
+            if right:
+                t_hi, t_lo = op(b.gt_hi, b.n, b.m), (op(b.gt_lo, b.n, b.m) if self._split else None)
             if two_d and self._kl:
                 # KL-Shampoo statistics: L <- Gram of G R^(-1/p), R <- Gram of L^(-1/p) G, with the
                 # current inverse roots (reference: shampoo_preconditioner_list.py:1945-2046).
@@ -536,14 +560,23 @@ class NativeGroupEngine:
                 syrk.append((*y, *y, fm[0], None, None, None, b.m, 0, pack_flag, self._packing))
                 syrk.append((*zt, *zt, fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
             else:
-                if two_d:
+                if left:
                     a_hi, a_lo = op(b.g_hi, b.m, b.n), (op(b.g_lo, b.m, b.n) if self._split else None)
                     syrk.append((a_hi, a_lo, a_hi, a_lo, fm[0], None, None, None, b.m, 0, pack_flag, self._packing))
-                syrk.append((t_hi, t_lo, t_hi, t_lo, fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
+                if right:
+                    syrk.append((t_hi, t_lo, t_hi, t_lo, fm[-1], None, None, None, b.n, 0, pack_flag, self._packing))
 
             f_hi, f_lo = op(b.f_hi, b.m, b.n), (op(b.f_lo, b.m, b.n) if self._split else None)
             sumsq = self._norms[b.index, 1:2]
-            if two_d:
+            if left and not right:
+                # P = L F: the chain's second product with T^T = F^T, made by a transposing copy
+                l_hi, l_lo = op(b.inv_hi[0], b.m, b.m), (op(b.inv_lo[0], b.m, b.m) if self._split else None)
+                tt_hi, tt_lo = op(b.tt_hi, b.n, b.m), (op(b.tt_lo, b.n, b.m) if self._split else None)
+                f_transposes.append((f_hi, tt_hi, None, None))
+                if self._split:  # tf32 rounding is elementwise: the transposed pair is the pair of the transpose
+                    f_transposes.append((f_lo, tt_lo, None, None))
+                gemm2.append((l_hi, l_lo, tt_hi, tt_lo, b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
+            elif left:
                 r_hi, r_lo = op(b.inv_hi[1], b.n, b.n), (op(b.inv_lo[1], b.n, b.n) if self._split else None)
                 l_hi, l_lo = op(b.inv_hi[0], b.m, b.m), (op(b.inv_lo[0], b.m, b.m) if self._split else None)
                 if self._split:
@@ -554,14 +587,17 @@ class NativeGroupEngine:
                     gemm1.append((r_hi, None, f_hi, None, b.tt_hi, None, None, None, b.m_pad, 0, 0, False))
                 tt_hi, tt_lo = op(b.tt_hi, b.n, b.m), (op(b.tt_lo, b.n, b.m) if self._split else None)
                 gemm2.append((l_hi, l_lo, tt_hi, tt_lo, b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
-            else:
-                r_hi, r_lo = op(b.inv_hi[0], b.n, b.n), (op(b.inv_lo[0], b.n, b.n) if self._split else None)
+            else:  # columns only: a 1-D block, or a 2-D block whose rows are not preconditioned
+                r_hi, r_lo = op(b.inv_hi[-1], b.n, b.n), (op(b.inv_lo[-1], b.n, b.n) if self._split else None)
                 gemm2.append((f_hi, f_lo, r_hi, r_lo, b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
-        self._syrk_plan = ext.build_gemm_plan(syrk)
+        self._f_transpose_table = ext.build_transpose_table(f_transposes) if f_transposes else None
+        # the pushing plan pairs one final product with every block (see the rule at _gemm_push)
+        assert not self._gemm_push or len(gemm2) == len(blocks)
+        self._syrk_plan = ext.build_gemm_plan(syrk) if syrk else None
         self._kl_plan = ext.build_gemm_plan(kl) if kl else None
         self._gemm0_plan = ext.build_gemm_plan(gemm0) if gemm0 else None
         self._gemm1_plan = ext.build_gemm_plan(gemm1) if gemm1 else None
-        self._gemm2_plan = ext.build_gemm_plan(gemm2)
+        self._gemm2_plan = ext.build_gemm_plan(gemm2) if gemm2 else None
         if self._gemm_push:
             # Same products; the result goes to the block's slot of every gather buffer instead of b.p.
             flags = F.FLAG_SUMSQ | F.FLAG_NO_C | F.FLAG_PEER_PUSH
@@ -670,7 +706,8 @@ class NativeGroupEngine:
             for k, src in enumerate(sources):
                 d = b.inv_hi[k].shape[0]
                 specs.append((src, d, b.inv_hi[k][:, :d], b.inv_lo[k][:, :d] if sp else None))
-        ext.unpack_split(*ext.build_unpack_table(specs))
+        if specs:
+            ext.unpack_split(*ext.build_unpack_table(specs))
 
     # ------------------------------------------------------------------------------------------
     # Hooks called by the optimizer
@@ -860,8 +897,9 @@ class NativeGroupEngine:
         if not self._soap and self._kl_plan is not None:
             ext.run_gemm_plan(*self._kl_plan, 1.0, 0.0, self._split, self._status)
             launches += 1
-        ext.run_gemm_plan(*self._syrk_plan, plist._weighting_factor, plist._beta2, self._split, self._status)
-        launches += 1
+        if self._syrk_plan is not None:
+            ext.run_gemm_plan(*self._syrk_plan, plist._weighting_factor, plist._beta2, self._split, self._status)
+            launches += 1
         self._mark("factor_syrk")
 
         if refresh:
@@ -877,12 +915,15 @@ class NativeGroupEngine:
             if self._gemm1_plan is not None:
                 ext.run_gemm_plan(*self._gemm1_plan, 1.0, 0.0, self._split, self._status)
                 launches += 1
+            if self._f_transpose_table is not None:
+                ext.transpose_split(*self._f_transpose_table)
+                launches += 1
             if use_push:
                 # The last preconditioner GEMM stores its tiles into every rank's gather buffer.
                 ext.run_gemm_plan_push(
                     *self._gemm2_push_plan, 1.0, 0.0, self._split, self._status, self._gather_bases, self._comm_dtype_code
                 )
-            else:
+            elif self._gemm2_plan is not None:
                 ext.run_gemm_plan(*self._gemm2_plan, 1.0, 0.0, self._split, self._status)
             launches += 1
 

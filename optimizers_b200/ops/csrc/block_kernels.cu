@@ -172,7 +172,8 @@ __global__ void __launch_bounds__(256, 3) grad_prologue_kernel(PrologueArgs a) {
     }
 
     // ---- compute and store
-    float sq = 0.f;
+    float sq = 0.f, psq = 0.f;
+    const bool identity_p = b.aux == 2;  // no dim is preconditioned: the direction is the filtered gradient
     bool bad = false;
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
@@ -213,10 +214,13 @@ __global__ void __launch_bounds__(256, 3) grad_prologue_kernel(PrologueArgs a) {
           const float gd = graft_direction(f, vn[k], a.graft_kind, a.graft_bias_correction2, a.graft_epsilon);
           if (live) sq += gd * gd;
         }
+        if (identity_p && live) psq += f * f;
+        if (identity_p) mo[r][k] = f;  // the loaded EMA has been consumed: reuse its registers
         if (!live) hi[k] = lo[k] = fh[k] = fl[k] = 0.f;
       }
       if (on) {
         const long long e = static_cast<long long>(i) * b.n + j;
+        if (identity_p) store4(b.p + e, mo[r], vec, cnt);
         const long long o = static_cast<long long>(i) * b.n_pad + j;  // n_pad % 4 == 0: always 16-byte stores
         if (b.g_hi != nullptr) {
           store4(b.g_hi + o, hi, true, 4);
@@ -270,6 +274,19 @@ __global__ void __launch_bounds__(256, 3) grad_prologue_kernel(PrologueArgs a) {
       if (s != 0.f) atomicAdd(&b.norms[0], s);
     }
     __syncthreads();
+    if (identity_p && b.norms != nullptr) {  // ||P||^2, which the last preconditioner GEMM reduces otherwise
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) psq += __shfl_xor_sync(0xffffffffu, psq, o);
+      if (lane == 0) red[warp] = psq;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += red[w];
+        if (s != 0.f) atomicAdd(&b.norms[1], s);
+      }
+      __syncthreads();
+    }
   }
 }
 
@@ -290,7 +307,7 @@ __global__ void __launch_bounds__(256, kPlain ? 3 : 2) direction_epilogue_kernel
     const BlockDesc& b = a.blocks[ref.block];
     const int i0 = ref.ti * kTile, j = ref.tj * kWide + 4 * lane;
     const int cnt = b.n - j < 4 ? b.n - j : 4;
-    if (cnt <= 0 || b.aux) continue;
+    if (cnt <= 0 || b.aux == 1) continue;
     float scale = 1.f;
     if (!a.graft_only && a.graft_kind != kGraftNone) scale = sqrtf(b.norms[0]) / (sqrtf(b.norms[1]) + 1e-16f);
     const bool has_v = a.graft_kind == kGraftAdaGrad;

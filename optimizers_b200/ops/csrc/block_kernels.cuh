@@ -49,6 +49,8 @@ struct BlockDesc {
   int aux;                // 1: a second 2-D view of an order-3 block that only needs the operand
                           // splits of its gradient (g_*, gt_*); it carries no state (m1, v, f_* and
                           // norms are null) and the epilogue kernels skip it
+                          // 2: a block none of whose dims is preconditioned: the prologue writes the
+                          // filtered gradient to p and its squared norm to norms[1] itself
   int pad_;
 };
 

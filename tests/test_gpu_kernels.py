@@ -236,6 +236,39 @@ def test_native_engine_matches_torch_step(name):
     walk(s_ref, s_nat)
 
 
+@pytest.mark.parametrize("eigdec", [False, True])
+@pytest.mark.parametrize(
+    "override",
+    [{2: {0: 0.25, 1: 0.0}}, {2: {0: 0.0, 1: 0.5}}, {2: 0.0}, {1: 0.0, 2: {0: 0.5, 1: 0.0}}, {1: 0.0, 2: 0.0}],
+    ids=["rows_only", "columns_only", "no_dim_of_matrices", "vectors_off_rows_only", "nothing"],
+)
+def test_native_engine_with_unpreconditioned_dims_matches_torch_step(override, eigdec):
+    """An exponent of 0 leaves a dim without a Kronecker factor (reference:
+    distributed_shampoo/preconditioner/shampoo_preconditioner_list.py:1749-1756): one-sided products,
+    and blocks whose direction is the filtered gradient itself."""
+    from optimizers_b200 import (
+        AdamPreconditionerConfig,
+        EigendecomposedShampooPreconditionerConfig,
+        RootInvShampooPreconditionerConfig,
+    )
+
+    cls = EigendecomposedShampooPreconditionerConfig if eigdec else RootInvShampooPreconditionerConfig
+    kw = dict(
+        lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64, precondition_frequency=3,
+        start_preconditioning_step=3, grafting_config=AdamPreconditionerConfig(beta2=0.999, epsilon=1e-8), weight_decay=1e-2,
+        preconditioner_config=cls(inverse_exponent_override=override),
+    )
+    m_ref, _, l_ref = _train("torch", 8, **kw)
+    m_nat, o_nat, l_nat = _train("native", 8, **kw)
+    for rec in o_nat._per_group_state_lists:
+        assert rec["native_engine"] is not None
+        rec["native_engine"].check_status()
+    for a, b in zip(l_ref, l_nat):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (l_ref, l_nat)
+    for p, q in zip(m_ref.parameters(), m_nat.parameters()):
+        assert torch.allclose(p, q, rtol=5e-3, atol=5e-4), (p - q).abs().max()
+
+
 @pytest.mark.parametrize("name", ["soap_adam_graft", "soap_qr_no_graft"])
 def test_native_soap_before_first_refresh_is_exact(name):
     """Before the first refresh the eigenbases are identities, so project / second-moment update /
