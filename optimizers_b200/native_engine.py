@@ -978,6 +978,9 @@ class NativeGroupEngine:
 
         plist = self._plist
         cfg = self._group[PRECONDITIONER_CONFIG].amortized_computation_config
+        blocks = [b for b in blocks if len(b.factors.factor_matrices) > 0]  # a block may have no preconditioned dim
+        if not blocks:
+            return
         if self._soap:
             if batched.eigenbasis_refresh_supported(cfg):
                 batched.batched_eigenbasis_refresh(blocks, plist._bias_correction2, self._ext)
