@@ -16,6 +16,10 @@ def main() -> None:
     mode = mode.removesuffix("+bf16")
     comm_params = mode.endswith("+params")  # updated parameters travel instead of search directions
     mode = mode.removesuffix("+params")
+    dead = mode.endswith("+dead")  # a registered layer that the forward pass never uses: its gradient stays None
+    mode = mode.removesuffix("+dead")
+    tiny = mode.endswith("+tiny")  # a single block: every rank but one owns nothing
+    mode = mode.removesuffix("+tiny")
     from optimizers_b200 import (
         AdamPreconditionerConfig,
         DDPDistributedConfig,
@@ -29,11 +33,28 @@ def main() -> None:
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(0)
-    model = torch.nn.Sequential(
-        torch.nn.Linear(96, 200), torch.nn.ReLU(), torch.nn.Linear(200, 72), torch.nn.ReLU(), torch.nn.Linear(72, 10)
-    ).to(dev)
+    features = 16 if tiny else 96
+
+    class Net(torch.nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            if tiny:
+                self.body = torch.nn.Sequential(torch.nn.Linear(features, 10, bias=False))
+            else:
+                self.body = torch.nn.Sequential(
+                    torch.nn.Linear(96, 200), torch.nn.ReLU(), torch.nn.Linear(200, 72), torch.nn.ReLU(), torch.nn.Linear(72, 10)
+                )
+            if dead:
+                self.unused = torch.nn.Linear(24, 40)
+
+        def forward(self, x):
+            return self.body(x)
+
+    model = Net().to(dev)
     fused = mode == "p2p_pull"
-    train_model = model if fused else torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index])
+    train_model = model if fused else torch.nn.parallel.DistributedDataParallel(
+        model, device_ids=[dev.index], find_unused_parameters=dead
+    )
     native = NativeRuntimeConfig(
         backend="torch" if mode == "torch" else "native",
         comm_path="p2p" if mode.startswith("p2p") else "nccl",
@@ -52,7 +73,7 @@ def main() -> None:
     )
     g = torch.Generator(device="cuda").manual_seed(1)
     for _ in range(8):
-        x = torch.randn(64, 96, device=dev, generator=g)
+        x = torch.randn(64, 96, device=dev, generator=g)[:, :features]
         y = torch.randint(0, 10, (64,), device=dev, generator=g)
         shard = slice(rank * 64 // world, (rank + 1) * 64 // world)
         opt.zero_grad(set_to_none=not fused)
@@ -149,7 +170,7 @@ def sharded_main() -> None:
         opt.train()
     g = torch.Generator(device="cuda").manual_seed(1)
     for _ in range(8):
-        x = torch.randn(64, 96, device=dev, generator=g)
+        x = torch.randn(64, 96, device=dev, generator=g)[:, :features]
         y = torch.randint(0, 10, (64,), device=dev, generator=g)
         shard = slice(rank * 64 // world, (rank + 1) * 64 // world)
         opt.zero_grad()

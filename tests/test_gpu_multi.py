@@ -36,6 +36,21 @@ def test_native_ddp_matches_torch_ddp(tmp_path, mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode", ["native_nccl+tiny", "p2p_push+tiny", "p2p_pull+tiny", "native_nccl+dead", "p2p_push+dead"])
+def test_native_ddp_with_idle_ranks_and_unused_parameters(tmp_path, mode):
+    """A model of one block leaves every rank but its owner without work (they still take part in the
+    barriers and receive the direction); a registered layer that never gets a gradient is skipped,
+    as in the reference (distributor/gpu_tests/shampoo_ddp_distributor_test.py:318-362)."""
+    n = min(torch.cuda.device_count(), 4)
+    suffix = mode[mode.index("+"):]
+    ref, got = str(tmp_path / "ref.pt"), str(tmp_path / "got.pt")
+    _run("torch" + suffix, n, ref, 29561)
+    _run(mode, n, got, 29562)
+    for a, b in zip(torch.load(ref), torch.load(got)):
+        assert torch.allclose(a, b, rtol=5e-3, atol=5e-4), (a - b).abs().max()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("mode", ["native_nccl", "p2p_push"])
 def test_native_ddp_communicate_params_matches_torch(tmp_path, mode):
     """communicate_params=True: owners apply their blocks' updates and the updated parameters
