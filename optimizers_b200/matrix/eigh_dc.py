@@ -56,11 +56,18 @@ logger: logging.Logger = logging.getLogger(__name__)
 # The last three polynomials are minimax on [0.5, 1] and [0.95, 1] (small oscillation, slopes < 1)
 # and the Newton-Schulz quintic.
 _BAND = (3.19298245614035, -5.543859649122806, 3.087719298245614)
-SIGN_SCHEDULE: tuple[tuple[float, float, float], ...] = (_BAND,) * 14 + (
+_FINISH = (
     (2.6073662581361705, -3.2052873333580942, 1.5974301564951396),
     (1.9203115684161138, -1.3422577427092492, 0.42194449535688716),
     (1.875, -1.25, 0.375),
 )
+SIGN_SCHEDULE: tuple[tuple[float, float, float], ...] = (_BAND,) * 14 + _FINISH
+# The 14 band iterations are what an eigenvalue 1e-7 away from the split point needs; the closest
+# eigenvalue of a real subproblem is typically 1e-5 to 1e-3 away (5 to 9 iterations).  So the
+# iteration runs in two stages: 9 band iterations and the finishing three, then, only for the
+# subproblems whose projector is not idempotent yet (an eigenvalue still between 0 and 1 shows in
+# trace(P) - ||P||_F^2), 5 more band iterations and the finishing three from X = 2 P - I.
+SIGN_STAGES: tuple[tuple[tuple[float, float, float], ...], ...] = ((_BAND,) * 9 + _FINISH, (_BAND,) * 5 + _FINISH)
 
 LEAF = 128  # largest problem the Jacobi kernel takes
 _MAX_ATTEMPTS = 3  # sign computations per subproblem before its root is given up
@@ -103,6 +110,7 @@ class TorchBackend:
         self._omega: Tensor | None = None
         self._seed = seed
         self.passes = 2
+        self.sign_stages_run = [0] * len(SIGN_STAGES)  # subproblems that went through each stage
 
     # -- set-up -----------------------------------------------------------------------------
     def begin(self, mats: list[Tensor]) -> list[Sub]:
@@ -127,20 +135,22 @@ class TorchBackend:
         for s in subs:
             eye = torch.eye(s.n, device=self.device, dtype=self.dtype)
             X = (s.A - s.sigma * eye) / s.spread
-            last = len(SIGN_SCHEDULE) - 1
-            for i, (a, b, c) in enumerate(SIGN_SCHEDULE):
-                Y = X @ X
-                Y = 0.5 * (Y + Y.T)
-                W = c * (Y @ Y) + b * Y + a * eye
-                W = 0.5 * (W + W.T)
-                X = X @ W
-                X = 0.5 * (X + X.T)
-                if i == last:
-                    X = 0.5 * X + 0.5 * eye
-            s.extra["P"] = X
-            fro2 = float((X * X).sum())
-            s.rank = int(round(fro2))
-            s.idem_err = float(torch.trace(X)) - fro2
+            for stage, schedule in enumerate(SIGN_STAGES):
+                for a, b, c in schedule:
+                    Y = X @ X
+                    Y = 0.5 * (Y + Y.T)
+                    W = c * (Y @ Y) + b * Y + a * eye
+                    W = 0.5 * (W + W.T)
+                    X = X @ W
+                    X = 0.5 * (X + X.T)
+                P = 0.5 * X + 0.5 * eye
+                fro2 = float((P * P).sum())
+                s.rank = int(round(fro2))
+                s.idem_err = float(torch.trace(P)) - fro2
+                self.sign_stages_run[stage] += 1
+                if abs(s.idem_err) <= _IDEMPOTENCY_TOL:
+                    break
+            s.extra["P"] = P
 
     def split_basis(self, subs: list[Sub]) -> None:
         """Qt (n x n, rows orthonormal): the first ``rank`` rows span range(P)."""
@@ -444,6 +454,7 @@ class NativeBackend:
         self.jacobi_tolerance = 2e-6
         self.jacobi_shift = 1.5  # second attempt of a leaf the Jacobi kernel did not settle on (see finish)
         self.leaves_retried = 0
+        self.sign_stages_run = [0] * len(SIGN_STAGES)  # subproblems that went through each stage
 
     # -- helpers ----------------------------------------------------------------------------
     def _gemm(self, specs: list[tuple], alpha: float = 1.0, beta: float = 0.0, gamma: float = 0.0) -> None:
@@ -504,15 +515,40 @@ class NativeBackend:
             s.mean, s.mean_spread = mean, spread
 
     def sign_projector(self, subs: list[Sub]) -> None:
+        ext, dev = self.ext, self.device
+        start = [_Mat(s.n, s.n, dev, plain=False) for s in subs]
+        table = ext.build_sym_table(
+            [(s.A.plain, start[i].hi, start[i].lo, None, 1.0 / s.spread, -s.sigma / s.spread) for i, s in enumerate(subs)]
+        )
+        ext.shift_scale_split(*table)
+        todo, X0 = list(subs), start
+        for stage, schedule in enumerate(SIGN_STAGES):
+            projectors = self._sign_stage(todo, X0, schedule)
+            self.sign_stages_run[stage] += len(todo)
+            again, again_x = [], []
+            for s, P in zip(todo, projectors, strict=True):
+                s.extra["P"] = P
+                if stage + 1 < len(SIGN_STAGES) and s.rank >= 0 and not abs(s.idem_err) <= _IDEMPOTENCY_TOL:
+                    # not a projector yet: X = 2 P - I goes through the next stage (an elementwise pass)
+                    X = _Mat(s.n, s.n, dev)
+                    torch.add(P.hi, P.lo, out=X.plain)
+                    again.append(s)
+                    again_x.append(X)
+            if not again:
+                break
+            table = ext.build_sym_table([(X.plain, X.hi, X.lo, None, 2.0, -1.0) for X in again_x])
+            ext.shift_scale_split(*table)
+            todo, X0 = again, again_x
+
+    def _sign_stage(self, subs: list[Sub], X0: list[_Mat], schedule: tuple) -> list[_Mat]:
+        """The polynomials of ``schedule`` applied to the iterates ``X0`` (operand pairs), the last
+        one fused with P = X / 2 + I / 2; sets ``rank`` and ``idem_err`` of ``subs`` from the
+        epilogue's ||P||_F^2 and trace(P) and returns the projectors."""
         ext, dev, F = self.ext, self.device, self.ext
-        X = [[_Mat(s.n, s.n, dev, plain=False) for s in subs] for _ in range(2)]
+        X = [X0, [_Mat(s.n, s.n, dev, plain=False) for s in subs]]
         Y = [_Mat(s.n, s.n, dev) for s in subs]
         W = [_Mat(s.n, s.n, dev, plain=False) for s in subs]
         stats = torch.zeros(len(subs), 2, device=dev)
-        table = ext.build_sym_table(
-            [(s.A.plain, X[0][i].hi, X[0][i].lo, None, 1.0 / s.spread, -s.sigma / s.spread) for i, s in enumerate(subs)]
-        )
-        ext.shift_scale_split(*table)
         idx = range(len(subs))
         plans = []
         for cur in (0, 1):
@@ -523,8 +559,8 @@ class NativeBackend:
             g3 = [self._spec(X[cur][i], W[i], X[nxt][i], sym=True) for i in idx]
             plans.append([ext.build_gemm_plan(g) for g in (g1, g2, g3)])
         cur = 0
-        last = len(SIGN_SCHEDULE) - 1
-        for it, (a, b, c) in enumerate(SIGN_SCHEDULE):
+        last = len(schedule) - 1
+        for it, (a, b, c) in enumerate(schedule):
             p1, p2, p3 = plans[cur]
             ext.run_gemm_plan(*p1, 1.0, 0.0, True, self.status)
             ext.run_gemm_plan(*p2, c, b, True, self.status, a)
@@ -539,11 +575,11 @@ class NativeBackend:
             else:
                 ext.run_gemm_plan(*p3, 1.0, 0.0, True, self.status)
             cur ^= 1
-        for i, (s, (fro2, trace)) in enumerate(zip(subs, stats.cpu().tolist(), strict=True)):
-            s.extra["P"] = X[cur][i]
+        for s, (fro2, trace) in zip(subs, stats.cpu().tolist(), strict=True):
             finite = fro2 == fro2 and abs(fro2) != float("inf")
             s.rank = int(round(fro2)) if finite else -1
             s.idem_err = trace - fro2 if finite else float("nan")
+        return [X[cur][i] for i in idx]
 
     def split_basis(self, subs: list[Sub]) -> None:
         ext, dev = self.ext, self.device
