@@ -85,7 +85,7 @@ def main() -> None:
     ms, (lams, vecs, info) = timed(lambda: eigh_divide_and_conquer(backend, big))
     line = {
         "arm": "divide_and_conquer", "ms": ms, "matrices": len(big), "sizes": sizes, "input_bytes": total_bytes,
-        "spectrum": args.spectrum, "rounds": info["rounds"], "sign_computations": info["sign_computations"],
+        "spectrum": args.spectrum, "rounds": info["rounds"], "sign_computations": info["sign_computations"], "sign_stages": info["sign_stages"],
         "work_over_sum_d3": info["sign_cubes"] / sum(float(m.shape[0]) ** 3 for m in big),
         "failed": info["failed"] + backend.failed_in_finish, "status": int(backend.status.item()),
     }

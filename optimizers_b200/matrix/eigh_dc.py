@@ -403,7 +403,11 @@ def eigh_divide_and_conquer(
         work = retry + children
     ok = [i not in failed for i in range(len(mats))]
     lams, vecs = backend.finish(ok)
-    return lams, vecs, {"failed": sorted(failed), "rounds": rounds, "sign_computations": signs, "sign_cubes": cubes, "reasons": reasons, "one_sided_splits": one_sided}  # one_sided_splits: hinted / geometric points that had to be abandoned
+    return lams, vecs, {
+        "failed": sorted(failed), "rounds": rounds, "sign_computations": signs, "sign_cubes": cubes, "reasons": reasons,
+        "one_sided_splits": one_sided,  # hinted / geometric points that had to be abandoned
+        "sign_stages": list(getattr(backend, "sign_stages_run", [])),  # subproblems through each stage of the schedule
+    }
 
 
 # ----------------------------------------------------------------------------------------------
