@@ -26,6 +26,37 @@ def _data(steps):
     return [(torch.randn(8, 12, generator=g), torch.randint(0, 5, (8,), generator=g)) for _ in range(steps)]
 
 
+def _flatten_state(tree, path=""):
+    """The state tree of this rank as ``(path, description)`` pairs: for a DTensor its local tensor
+    together with the ranks of its mesh and its placements, for a tensor itself, for anything else
+    its repr.  Picklable, so that the parent process compares what the ranks saw."""
+    from torch.distributed.tensor import DTensor
+
+    out = []
+    if isinstance(tree, dict):
+        for k in sorted(tree, key=str):
+            out += _flatten_state(tree[k], f"{path}/{k}")
+    elif isinstance(tree, DTensor):
+        out.append((path, ("dtensor", tree.to_local().detach().clone(), tree.device_mesh.mesh.tolist(),
+                           [str(p) for p in tree.placements], tuple(tree.shape))))
+    elif isinstance(tree, torch.Tensor):
+        out.append((path, ("tensor", tree.detach().clone())))
+    else:
+        out.append((path, ("other", repr(tree))))
+    return out
+
+
+def _assert_same_state(theirs, ours):
+    assert [p for p, _ in theirs] == [p for p, _ in ours]
+    for (path, a), (_, b) in zip(theirs, ours):
+        assert a[0] == b[0], (path, a[0], b[0])
+        if a[0] == "other":
+            assert a[1] == b[1], path
+            continue
+        assert a[1].dtype == b[1].dtype and a[1].shape == b[1].shape and torch.equal(a[1], b[1]), path
+        assert a[2:] == b[2:], (path, a[2:], b[2:])  # mesh ranks, placements and global shape of a DTensor
+
+
 def _parity_worker(rank, world, strategy):
     import sys
 
@@ -40,7 +71,10 @@ def _parity_worker(rank, world, strategy):
     def train(lib):
         model = _model()
         cpu = torch.device("cpu")
-        if strategy == "fsdp":
+        if strategy == "ddp":
+            model = torch.nn.parallel.DistributedDataParallel(model)
+            cfg = lib.DDPDistributedConfig(communication_dtype=torch.float32, num_trainers_per_group=world)
+        elif strategy == "fsdp":
             model = FSDP(model, use_orig_params=True, device_id=cpu)
             cfg = lib.FSDPDistributedConfig(param_to_metadata=lib.compile_fsdp_parameter_metadata(model))
         elif strategy == "hsdp":
@@ -67,21 +101,26 @@ def _parity_worker(rank, world, strategy):
             (p.to_local() if isinstance(p, DTensor) else p).detach().clone() for p in model.parameters()
         ]
         state_keys = sorted(str(k) for s in opt.state_dict()["state"].values() for k in s)
-        return local, state_keys
+        return local, state_keys, _flatten_state(opt.state_dict()["state"])
 
-    theirs, their_keys = train(ref_lib)
-    ours, our_keys = train(our_lib)
-    return theirs, ours, their_keys, our_keys
+    theirs, their_keys, their_state = train(ref_lib)
+    ours, our_keys, our_state = train(our_lib)
+    return theirs, ours, their_keys, our_keys, their_state, our_state
 
 
 @needs_reference
-@pytest.mark.parametrize("strategy,world", [("fsdp", 2), ("hsdp", 4), ("fully_shard", 2), ("hybrid_shard", 4)])
+@pytest.mark.parametrize("strategy,world", [("ddp", 2), ("ddp", 3), ("fsdp", 2), ("hsdp", 4), ("fully_shard", 2), ("hybrid_shard", 4)])
 def test_sharded_distributor_matches_reference_bitwise(strategy, world):
-    for theirs, ours, their_keys, our_keys in run_distributed(_parity_worker, world, strategy):
+    """Parameters and, leaf by leaf, the whole per-rank optimizer state (values, block ids, and for
+    DTensor state the mesh ranks, placements and global shapes) against the reference's distributor
+    run in the same processes (reference: distributor/gpu_tests/shampoo_ddp_distributor_test.py:364-780
+    pins the same trees as literals)."""
+    for theirs, ours, their_keys, our_keys, their_state, our_state in run_distributed(_parity_worker, world, strategy):
         assert len(theirs) == len(ours)
         for a, b in zip(theirs, ours):
             assert a.shape == b.shape and torch.equal(a, b), (a - b).abs().max()
         assert their_keys == our_keys  # same per-rank block ids and state names
+        _assert_same_state(their_state, our_state)
 
 
 def _ddp_corner_worker(rank, world, case):
