@@ -33,6 +33,7 @@ from __future__ import annotations
 
 import logging
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -67,7 +68,11 @@ SIGN_SCHEDULE: tuple[tuple[float, float, float], ...] = (_BAND,) * 14 + _FINISH
 # iteration runs in two stages: 9 band iterations and the finishing three, then, only for the
 # subproblems whose projector is not idempotent yet (an eigenvalue still between 0 and 1 shows in
 # trace(P) - ||P||_F^2), 5 more band iterations and the finishing three from X = 2 P - I.
-SIGN_STAGES: tuple[tuple[tuple[float, float, float], ...], ...] = ((_BAND,) * 9 + _FINISH, (_BAND,) * 5 + _FINISH)
+# OB200_SIGN_STAGE1 overrides the length of the first stage (14 gives the single fixed schedule).
+_STAGE1 = min(max(int(os.environ.get("OB200_SIGN_STAGE1", "9")), 1), 14)
+SIGN_STAGES: tuple[tuple[tuple[float, float, float], ...], ...] = ((_BAND,) * _STAGE1 + _FINISH,) + (
+    ((_BAND,) * (14 - _STAGE1) + _FINISH,) if _STAGE1 < 14 else ()
+)
 
 LEAF = 128  # largest problem the Jacobi kernel takes
 _MAX_ATTEMPTS = 3  # sign computations per subproblem before its root is given up
@@ -290,8 +295,13 @@ class _Timed:
             ms = (time.perf_counter() - t0) * 1e3
             prof[name] = prof.get(name, 0.0) + ms
             if args and isinstance(args[0], list) and args[0] and isinstance(args[0][0], Sub):
-                # per call: number of subproblems, their mean size, milliseconds
-                prof.setdefault("calls", []).append((name, len(args[0]), round(sum(s.n for s in args[0]) / len(args[0])), round(ms, 2)))
+                # per call: number of subproblems, their mean size, milliseconds, sum n^3 and sum n^2 rank (in 1e9)
+                subs = args[0]
+                prof.setdefault("calls", []).append((
+                    name, len(subs), round(sum(s.n for s in subs) / len(subs)), round(ms, 2),
+                    round(sum(float(s.n) ** 3 for s in subs) / 1e9, 2),
+                    round(sum(float(s.n) ** 2 * max(s.rank, 0) for s in subs) / 1e9, 2),
+                ))
             return out
 
         return timed
@@ -434,6 +444,23 @@ class _Mat:
         self.hi, self.lo = (views[0], views[1]) if pair else (None, None)
 
 
+def _mats(ext: Any, device: torch.device, shapes: list[tuple[int, int]], plain: bool = True, pair: bool = True) -> list[_Mat]:
+    """``_Mat(rows, cols, device, plain, pair)`` for every shape out of one allocation, the views
+    made by the extension: a refresh creates tens of thousands of scratch matrices, and one
+    allocation plus three views each in Python was a third of its host time.  The matrices of a
+    batch share their storage, so a batch should hold arrays of one lifetime."""
+    make = getattr(ext, "alloc_mat_batch", None)
+    if make is None or not shapes:
+        return [_Mat(r, c, device, plain=plain, pair=pair) for r, c in shapes]
+    out = []
+    new = _Mat.__new__
+    for (r, c), (p, hi, lo) in zip(shapes, make([r for r, _ in shapes], [c for _, c in shapes], plain, pair, device)):
+        m = new(_Mat)
+        m.rows, m.cols, m.plain, m.hi, m.lo = r, c, p, hi, lo
+        out.append(m)
+    return out
+
+
 _OMEGA_CACHE: dict[tuple, _Mat] = {}
 
 
@@ -500,9 +527,8 @@ class NativeBackend:
         self.vecs = [torch.zeros(m.shape[0], m.shape[0], device=dev) for m in mats]
         self.root_norms = torch.stack(torch._foreach_norm(list(mats))).cpu().tolist()
         subs = []
-        for i, m in enumerate(mats):
+        for i, (m, A) in enumerate(zip(mats, _mats(ext, dev, [(m.shape[0], m.shape[0]) for m in mats]), strict=True)):
             n = m.shape[0]
-            A = _Mat(n, n, dev)
             A.plain.copy_(m)
             ext.tf32_split(A.plain, A.hi, A.lo)
             subs.append(Sub(root=i, n=n, offset=0, A=A))
@@ -520,7 +546,7 @@ class NativeBackend:
 
     def sign_projector(self, subs: list[Sub]) -> None:
         ext, dev = self.ext, self.device
-        start = [_Mat(s.n, s.n, dev, plain=False) for s in subs]
+        start = _mats(ext, dev, [(s.n, s.n) for s in subs], plain=False)
         table = ext.build_sym_table(
             [(s.A.plain, start[i].hi, start[i].lo, None, 1.0 / s.spread, -s.sigma / s.spread) for i, s in enumerate(subs)]
         )
@@ -549,9 +575,10 @@ class NativeBackend:
         one fused with P = X / 2 + I / 2; sets ``rank`` and ``idem_err`` of ``subs`` from the
         epilogue's ||P||_F^2 and trace(P) and returns the projectors."""
         ext, dev, F = self.ext, self.device, self.ext
-        X = [X0, [_Mat(s.n, s.n, dev, plain=False) for s in subs]]
-        Y = [_Mat(s.n, s.n, dev) for s in subs]
-        W = [_Mat(s.n, s.n, dev, plain=False) for s in subs]
+        square = [(s.n, s.n) for s in subs]
+        X = [X0, _mats(ext, dev, square, plain=False)]
+        Y = _mats(ext, dev, square)
+        W = _mats(ext, dev, square, plain=False)
         stats = torch.zeros(len(subs), 2, device=dev)
         idx = range(len(subs))
         plans = []
@@ -589,11 +616,11 @@ class NativeBackend:
         ext, dev = self.ext, self.device
         om = self._omega_t
         qr_specs, g = [], []
-        for s in subs:
+        Yts = _mats(ext, dev, [(s.rank, s.n) for s in subs], pair=False)  # rows: the columns of P Omega
+        Zts = _mats(ext, dev, [(s.n, s.n) for s in subs])
+        for s, Yt, Zt in zip(subs, Yts, Zts, strict=True):
             k, n = s.rank, s.n
             P = s.extra.pop("P")
-            Yt = _Mat(k, n, dev, pair=False)  # rows: the columns of P Omega
-            Zt = _Mat(n, n, dev)
             s.extra["Qt"] = Zt
             g.append((om.hi, om.lo, P.hi, P.lo, Yt.plain, None, None, None, Yt.plain.stride(0), 0,
                       0, False, None, (0, 0, 0, 0, k, n, n)))
@@ -615,10 +642,11 @@ class NativeBackend:
         for _ in range(self.range_passes - 1 if self.polish == "householder" else 0):
             # One more pass from the orthonormal basis just found: Y <- P V1, whose conditioning is 1.
             g, qr_specs = [], []
-            for s in subs:
+            Yts = _mats(ext, dev, [(s.rank, s.n) for s in subs], pair=False)
+            Zts = _mats(ext, dev, [(s.n, s.n) for s in subs])
+            for s, Yt, Zt in zip(subs, Yts, Zts, strict=True):
                 k, n = s.rank, s.n
                 P, Zt_old = s.extra["P_keep"], s.extra["Qt"]
-                Yt, Zt = _Mat(k, n, dev, pair=False), _Mat(n, n, dev)
                 v1 = _Mat.__new__(_Mat)
                 v1.rows, v1.cols, v1.plain, v1.hi, v1.lo = k, n, None, Zt_old.hi[:k], Zt_old.lo[:k]
                 g.append(self._spec(v1, P, None, c=Yt.plain))
@@ -667,6 +695,10 @@ class NativeBackend:
         ext, dev = self.ext, self.device
         children: list[Sub] = []
         g1, g2, g3 = [], [], []
+        halves = [(m, s.n, self.lams[s.root].shape[0]) for s in subs for m in (s.rank, s.n - s.rank)]
+        Ts = iter(_mats(ext, dev, [(m, n) for m, n, _ in halves], plain=False))
+        Acs = iter(_mats(ext, dev, [(m, m) for m, _, _ in halves]))
+        Bcs = iter(_mats(ext, dev, [(d, m) for m, _, d in halves]))
         for s in subs:
             Qt = s.extra.pop("Qt")
             k, n = s.rank, s.n
@@ -674,12 +706,9 @@ class NativeBackend:
                 m = r1 - r0
                 vt = _Mat.__new__(_Mat)
                 vt.rows, vt.cols, vt.plain, vt.hi, vt.lo = m, n, None, Qt.hi[r0:r1], Qt.lo[r0:r1]
-                T = _Mat(m, n, dev, plain=False)  # V^T A
-                Ac = _Mat(m, m, dev)
+                T, Ac, Bc = next(Ts), next(Acs), next(Bcs)  # V^T A, the child, its basis
                 g1.append(self._spec(vt, s.A, T))
                 g2.append(self._spec(T, vt, Ac, c=Ac.plain, sym=True))
-                d = self.lams[s.root].shape[0]
-                Bc = _Mat(d, m, dev, plain=True)
                 if s.B is None:
                     # B = I V: a transposed copy of V^T
                     s.extra.setdefault("transposes", []).append((vt, Bc))
@@ -725,7 +754,7 @@ class NativeBackend:
                 self.jacobi_max_sweeps, self.jacobi_tolerance, shift)
             self._leaf_sweeps.append((direct, sweeps))
         if based:
-            holders = [_Mat(s.n, s.n, dev) for s in based]
+            holders = _mats(ext, dev, [(s.n, s.n) for s in based])
             sweeps = ext.jacobi_eigh_into(
                 [s.A.plain for s in based], [h.plain for h in holders], [lam_of(s) for s in based], True,
                 self.jacobi_max_sweeps, self.jacobi_tolerance, shift)

@@ -19,6 +19,21 @@ class FakeExt:
         self.gemm_launches = 0
         self.calls = []
 
+    # -- scratch matrices ------------------------------------------------------------------------
+    def alloc_mat_batch(self, rows, cols, plain, pair, device):
+        count = int(plain) + 2 * int(pair)
+        pitch = [(c + 3) // 4 * 4 for c in cols]
+        block = torch.full((max(sum(count * r * ld for r, ld in zip(rows, pitch)), 1),), float("nan"), device=device)
+        out, offset = [], 0
+        for r, c, ld in zip(rows, cols, pitch):
+            views = [None, None, None]
+            for k in range(3):
+                if plain if k == 0 else pair:
+                    views[k] = torch.as_strided(block, (r, c), (ld, 1), offset)
+                    offset += r * ld
+            out.append(tuple(views))
+        return out
+
     # -- operand split -------------------------------------------------------------------------
     def tf32_split(self, src, hi, lo):
         hi.copy_(src)
