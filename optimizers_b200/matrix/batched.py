@@ -27,6 +27,7 @@ from __future__ import annotations
 import logging
 import threading
 from concurrent.futures import ThreadPoolExecutor
+from types import SimpleNamespace
 from fractions import Fraction
 from typing import Any
 
@@ -134,6 +135,19 @@ _DC_CHUNK_ELEMS = int(_os.environ.get("OB200_EIGH_CHUNK_ELEMS", str(512 * 1024 *
 _DC_WORKSPACE_ARRAYS = 25
 # OB200_EIGH=library sends every factor larger than the Jacobi kernel's limit to the library eigensolver.
 _DC_ENABLED = _os.environ.get("OB200_EIGH", "native") != "library"
+# Host threads (each with its own stream) that drive the eigensolver on disjoint halves of the factors.
+_DC_LANES = int(_os.environ.get("OB200_EIGH_LANES", "2"))
+_lane_pools: dict[int, tuple[ThreadPoolExecutor, list[torch.cuda.Stream]]] = {}
+
+
+def _lane_pool(device: torch.device) -> tuple[ThreadPoolExecutor, list[torch.cuda.Stream]]:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _lane_pools:
+        _lane_pools[key] = (
+            ThreadPoolExecutor(max_workers=2, thread_name_prefix="ob200-eigh-lane"),
+            [torch.cuda.Stream(device=device) for _ in range(2)],
+        )
+    return _lane_pools[key]
 
 
 def native_eigh(
@@ -162,10 +176,55 @@ def native_eigh(
             size = 0
         chunks[-1].append(i)
         size += d2
+    device = mats[0].device
+    main = torch.cuda.current_stream(device)
+
+    def solve(group: list[int], stream: torch.cuda.Stream | None):
+        backend = NativeBackend(ext, device, status)
+        group_hints = [hints[i] for i in group] if hints is not None else None
+        if stream is None:
+            return backend, eigh_divide_and_conquer(backend, [mats[i] for i in group], hints=group_hints)
+        with torch.cuda.stream(stream):
+            lams, vecs, info = eigh_divide_and_conquer(backend, [mats[i] for i in group], hints=group_hints)
+            for t in (*lams, *vecs):
+                if t is not None:
+                    t.record_stream(main)  # allocated from this lane's pool, consumed on the caller's stream
+        return backend, (lams, vecs, info)
+
     for chunk in chunks:
-        backend = NativeBackend(ext, mats[chunk[0]].device, status)
-        chunk_hints = [hints[i] for i in chunk] if hints is not None else None
-        lams, vecs, info = eigh_divide_and_conquer(backend, [mats[i] for i in chunk], hints=chunk_hints)
+        # Two lanes: the host work of a round (launch tables, thousands of scratch views) is about
+        # a third of a refresh and the device idles meanwhile.  Each lane is a thread with its own
+        # stream driving half of the matrices; a lane blocked in a device read has released the
+        # interpreter lock, so the other lane's host work runs while this lane's kernels do.
+        lanes = [chunk[0::2], chunk[1::2]] if _DC_LANES > 1 and len(chunk) >= 8 else [chunk]
+        if len(lanes) == 1:
+            results = [solve(chunk, None)]
+        else:
+            from optimizers_b200.matrix.eigh_dc import prepare_test_matrix
+
+            prepare_test_matrix(ext, device, max(mats[i].shape[0] for i in chunk))  # shared by the lanes: made once
+            executor, streams = _lane_pool(device)
+            for st in streams:
+                st.wait_stream(main)
+            futures = [executor.submit(solve, lane, st) for lane, st in zip(lanes, streams)]
+            results = [f.result() for f in futures]
+            for st in streams:
+                main.wait_stream(st)
+        lams, vecs = [None] * len(chunk), [None] * len(chunk)
+        info = {"rounds": 0, "sign_computations": 0, "sign_cubes": 0.0, "one_sided_splits": 0, "failed": [], "reasons": {}}
+        leaves_retried, failed_in_finish = 0, []
+        position = {i: n for n, i in enumerate(chunk)}
+        for lane, (lane_backend, (lane_lams, lane_vecs, lane_info)) in zip(lanes, results, strict=True):
+            for r, i in enumerate(lane):
+                lams[position[i]], vecs[position[i]] = lane_lams[r], lane_vecs[r]
+            info["rounds"] = max(info["rounds"], lane_info["rounds"])
+            for key in ("sign_computations", "sign_cubes", "one_sided_splits"):
+                info[key] += lane_info[key]
+            info["failed"] += [position[lane[r]] for r in lane_info["failed"]]
+            info["reasons"].update({position[lane[r]]: why for r, why in lane_info["reasons"].items()})
+            leaves_retried += lane_backend.leaves_retried
+            failed_in_finish += [position[lane[r]] for r in lane_backend.failed_in_finish]
+        backend = SimpleNamespace(leaves_retried=leaves_retried, failed_in_finish=failed_in_finish)
         for i, lam, Q in zip(chunk, lams, vecs, strict=True):
             if lam is not None:
                 out[i] = (lam, Q)

@@ -34,6 +34,7 @@ from __future__ import annotations
 import logging
 import math
 import os
+import threading
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -462,6 +463,24 @@ def _mats(ext: Any, device: torch.device, shapes: list[tuple[int, int]], plain: 
 
 
 _OMEGA_CACHE: dict[tuple, _Mat] = {}
+_OMEGA_LOCK = threading.Lock()
+
+
+def prepare_test_matrix(ext: Any, device: torch.device, dmax: int, seed: int = 1234) -> _Mat:
+    """The random test matrix Omega^T (rows are the columns of Omega) as an operand pair, at least
+    ``dmax`` square; one per device and seed is kept, and a larger one serves smaller requests (the
+    solver only uses leading blocks).  Callers that run several solvers concurrently call this
+    first with the largest size so that the solvers find it made."""
+    key = (device.type, device.index, seed)
+    with _OMEGA_LOCK:
+        om = _OMEGA_CACHE.get(key)
+        if om is None or om.rows < dmax:
+            gen = torch.Generator(device="cpu").manual_seed(seed)
+            omega_t = torch.randn(dmax, dmax, generator=gen).to(device)
+            om = _Mat(dmax, dmax, device, plain=False)
+            ext.tf32_split(omega_t, om.hi, om.lo)
+            _OMEGA_CACHE[key] = om
+        return om
 
 
 
@@ -514,15 +533,7 @@ class NativeBackend:
     def begin(self, mats: list[Tensor]) -> list[Sub]:
         ext, dev = self.ext, self.device
         dmax = max(m.shape[0] for m in mats)
-        key = (dev.index, dmax, self._seed)
-        if key not in _OMEGA_CACHE:
-            _OMEGA_CACHE.clear()  # one test matrix per process is enough; sizes rarely change
-            gen = torch.Generator(device="cpu").manual_seed(self._seed)
-            omega_t = torch.randn(dmax, dmax, generator=gen).to(dev)  # rows are the columns of Omega
-            om = _Mat(dmax, dmax, dev, plain=False)
-            ext.tf32_split(omega_t, om.hi, om.lo)
-            _OMEGA_CACHE[key] = om
-        self._omega_t = _OMEGA_CACHE[key]
+        self._omega_t = prepare_test_matrix(ext, dev, dmax, self._seed)
         self.lams = [torch.zeros(m.shape[0], device=dev) for m in mats]
         self.vecs = [torch.zeros(m.shape[0], m.shape[0], device=dev) for m in mats]
         self.root_norms = torch.stack(torch._foreach_norm(list(mats))).cpu().tolist()
