@@ -29,7 +29,7 @@ from torch.distributed.tensor import DTensor
 from optimizers_b200.config import DDPDistributedConfig, DISTRIBUTED_CONFIG, PARAMS, ShampooRuntimeConfig
 from optimizers_b200.parallel.base import DistributorInterface
 from optimizers_b200.parallel.block_info import DTensorBlockInfo
-from optimizers_b200.parallel.dist_utils import allocate_zeros_on_owner, batched, shampoo_comm_profiler
+from optimizers_b200.parallel.dist_utils import allocate_zeros_on_owner, batched, get_device_mesh, shampoo_comm_profiler
 from optimizers_b200.utils.blocking import (
     compress_list,
     distribute_buffer_sizes,
@@ -112,6 +112,13 @@ class DDPDistributor(DistributorInterface):
         parent = dist_group if dist_group is not None else dist.group.WORLD
         all_ranks = dist.get_process_group_ranks(group=parent)
         self._owner_mesh_rows: tuple[tuple[int, ...], ...] = tuple(batched(all_ranks, self._group_size))
+        # Made here, on every rank, and not when the first state tensor is allocated: a rank that owns
+        # no block allocates no state, and a mesh (its process groups) created by the other ranks
+        # only never completes under NCCL with communicators bound at start-up
+        # (init_process_group(device_id=...)): measured as a hang of every rank.
+        device_type = self._param_group[PARAMS][0].device.type
+        mesh = get_device_mesh(device_type=device_type, mesh=self._owner_mesh_rows, mesh_dim_names=("replicate", "shard"))
+        mesh._get_all_submeshes(mesh_dim_name="replicate")  # type: ignore[attr-defined]
 
     # -- parameters may be DTensors (composable replicate()) ------------------------------------
     @torch.no_grad()
