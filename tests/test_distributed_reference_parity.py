@@ -140,6 +140,12 @@ def _ddp_corner_worker(rank, world, case):
         )
 
     opt = make(lib.DDPDistributedConfig(communication_dtype=torch.float32, num_trainers_per_group=world))
+    # Creating a mesh is collective.  Every rank, also one that owns no block and therefore never
+    # allocates state, must have created the owners' mesh by now (gloo tolerates a subset of ranks
+    # creating it later; NCCL with communicators bound at start-up hangs).
+    from optimizers_b200.parallel.dist_utils import get_device_mesh
+
+    assert get_device_mesh.cache_info().currsize >= 1
     g = torch.Generator().manual_seed(5)
     for step in range(5):
         x = torch.randn(8, 6, generator=g)

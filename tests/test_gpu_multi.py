@@ -14,14 +14,24 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(mode: str, nproc: int, out: str, port: int) -> None:
+def _run(mode: str, nproc: int, out: str, port: int, timeout: int = 300) -> None:
+    """Launch the worker on ``nproc`` GPUs.  The launcher gets its own process group so that a run
+    that exceeds the limit is ended together with its ranks (none survives to hold a GPU)."""
+    import signal
+
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
         "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_multi_gpu_worker.py"), mode, out,
     ]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+    try:
+        stdout, stderr = proc.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        stdout, stderr = proc.communicate()
+        raise AssertionError(f"worker {mode!r} exceeded {timeout} s\n" + stdout[-2000:] + stderr[-2000:]) from None
+    assert proc.returncode == 0, stdout[-3000:] + stderr[-3000:]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
