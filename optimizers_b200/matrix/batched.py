@@ -135,8 +135,11 @@ _DC_CHUNK_ELEMS = int(_os.environ.get("OB200_EIGH_CHUNK_ELEMS", str(512 * 1024 *
 _DC_WORKSPACE_ARRAYS = 25
 # OB200_EIGH=library sends every factor larger than the Jacobi kernel's limit to the library eigensolver.
 _DC_ENABLED = _os.environ.get("OB200_EIGH", "native") != "library"
-# Host threads (each with its own stream) that drive the eigensolver on disjoint halves of the factors.
-_DC_LANES = int(_os.environ.get("OB200_EIGH_LANES", "2"))
+# Host threads (each with its own stream) that drive the eigensolver on disjoint halves of the factors
+# (OB200_EIGH_LANES=2).  Off by default: measured on the factors of GPT-2 124M the refresh is bound by
+# the device once the scratch matrices are allocated per batch (1235 ms with two lanes, 1243 ms with
+# one), and a second stream doubles the allocator's cached pools.
+_DC_LANES = int(_os.environ.get("OB200_EIGH_LANES", "1"))
 _lane_pools: dict[int, tuple[ThreadPoolExecutor, list[torch.cuda.Stream]]] = {}
 
 
