@@ -181,6 +181,7 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
   float* a = jsm;                                // column j of A V at a + j * pitch
   float* v = jsm + kJacobiMaxN * kJacobiPitch;   // column j of V
   __shared__ int rotated;
+  __shared__ int significant;  // a rotation of the current sweep was well above the tolerance
   __shared__ float lam_s[kJacobiMaxN];
   const JacobiDesc d = descs[blockIdx.x];
   const int n = d.n;
@@ -221,9 +222,9 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
   }
 
   int sweep = 0;
-  bool converged = false;
+  bool converged = false, settled = false;
   for (; sweep < max_sweeps && !converged; ++sweep) {
-    if (threadIdx.x == 0) rotated = 0;
+    if (threadIdx.x == 0) rotated = significant = 0;
     __syncthreads();
     for (int r = 0; r < np - 1; ++r) {
       // Round r of the round-robin tournament: player np-1 stays, the others rotate.
@@ -265,12 +266,19 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
             vp[i] = c * vx - s * vy;
             vq[i] = s * vx + c * vy;
           }
-          if (lane == 0) rotated = 1;
+          if (lane == 0) {
+            rotated = 1;
+            if (fabsf(gamma) > 32.f * tol * sqrtf(alpha * beta)) significant = 1;
+          }
         }
       }
       __syncthreads();
     }
     converged = rotated == 0;
+    // Inner products of fp32 columns carry rounding noise of the order of the tolerance itself: a
+    // pair can hover around it for ever.  A last sweep all of whose rotations were within 32 times
+    // the tolerance has nothing left to remove.
+    settled = converged || significant == 0;
     __syncthreads();
   }
 
@@ -337,7 +345,7 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
     for (int i = warp; i < n; i += kWarps)
       for (int j = lane; j < n; j += 32) d.q[static_cast<long long>(i) * d.ldq + rank_of[j]] = v[j * kJacobiPitch + i];
   }
-  if (threadIdx.x == 0) sweeps_out[blockIdx.x] = converged ? sweep : max_sweeps + 1;
+  if (threadIdx.x == 0) sweeps_out[blockIdx.x] = settled ? sweep : max_sweeps + 1;
 }
 
 struct GpaScalars {
