@@ -252,7 +252,10 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
           beta += __shfl_xor_sync(0xffffffffu, beta, o);
           gamma += __shfl_xor_sync(0xffffffffu, gamma, o);
         }
-        if (fabsf(gamma) > tol * sqrtf(alpha * beta) && fabsf(gamma) > 1e-37f) {
+        // sqrt(alpha) * sqrt(beta), not sqrt(alpha * beta): for a leaf with entries of 1e-12 the
+        // product of the squared norms underflows to zero and every pair would rotate for ever.
+        const float scale = sqrtf(alpha) * sqrtf(beta);
+        if (fabsf(gamma) > tol * scale && fabsf(gamma) > 1e-37f) {
           const float zeta = (beta - alpha) / (2.f * gamma);
           const float t = copysignf(1.f, zeta) / (fabsf(zeta) + sqrtf(1.f + zeta * zeta));
           const float c = rsqrtf(1.f + t * t), s = c * t;
@@ -268,7 +271,7 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
           }
           if (lane == 0) {
             rotated = 1;
-            if (fabsf(gamma) > 32.f * tol * sqrtf(alpha * beta)) significant = 1;
+            if (fabsf(gamma) > 32.f * tol * scale) significant = 1;
           }
         }
       }

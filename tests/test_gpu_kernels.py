@@ -520,6 +520,24 @@ def test_native_engine_resumes_from_checkpoint(name):
         assert torch.allclose(p, q, rtol=1e-4, atol=1e-6), (p - q).abs().max()
 
 
+def test_jacobi_eigh_settles_on_a_tiny_scaled_matrix(ext):
+    """Entries of 1e-13 (a leaf deep in the null cluster of a factor): squared column norms are
+    1e-24, their product is below the smallest fp32 number, and a convergence test written with
+    sqrt(alpha * beta) never passes."""
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    n = 63
+    G = torch.randn(n, 2 * n, device=dev, dtype=torch.float64)
+    A = ((G @ G.T) / (2 * n) * 2e-13).float()
+    lams, qs, sweeps = ext.jacobi_eigh([A], 24, 2e-6)
+    torch.cuda.synchronize()
+    assert int(sweeps[0]) <= 24
+    ref = torch.linalg.eigvalsh(A.double())
+    assert (lams[0].double() - ref).abs().max().item() < 1e-5 * ref.abs().max().item()
+    Q = qs[0].double()
+    assert (Q.T @ Q - torch.eye(n, device=dev, dtype=torch.float64)).abs().max().item() < 1e-5
+
+
 @pytest.mark.parametrize("n", [1, 2, 7, 64, 100, 128])
 def test_jacobi_eigh_matches_lapack(ext, n):
     """Batched shared-memory Jacobi eigensolver against fp64 eigh: eigenvalues, orthogonality and
