@@ -124,3 +124,27 @@ def test_misleading_hint_costs_one_sign_computation_not_the_result():
     assert info["failed"] == []
     ref = torch.linalg.eigvalsh(A64)
     assert float((lams[0].double() - ref).abs().max()) <= 2e-6 * float(ref.abs().max())
+
+
+def test_second_sign_stage_takes_over_when_an_eigenvalue_sits_at_the_split_point():
+    """Eigenvalues 5e-7 of the spread away from the mean are not resolved by the first stage of the
+    sign iteration (it reaches about 5e-6): the projector fails the idempotency test and the
+    second stage finishes it, at the accuracy of the single long schedule."""
+    from optimizers_b200.matrix.eigh_dc import SIGN_STAGES
+
+    assert len(SIGN_STAGES) == 2
+    n = 200
+    gen = torch.Generator().manual_seed(11)
+    q, _ = torch.linalg.qr(torch.randn(n, n, dtype=torch.float64, generator=gen))
+    lam = torch.linspace(0.0, 1.0, n, dtype=torch.float64)
+    gap = 5e-7 * torch.linalg.norm(lam - 0.5)
+    lam[n // 2 - 1], lam[n // 2] = 0.5 - gap, 0.5 + gap  # a pair astride the first split point; the mean stays 0.5
+    A = ((q * lam) @ q.T)
+    backend = TorchBackend(torch.device("cpu"), torch.float64)
+    lams, vecs, info = eigh_divide_and_conquer(backend, [A])
+    assert info["failed"] == []
+    assert info["sign_stages"][1] >= 1, info["sign_stages"]
+    ref = torch.linalg.eigvalsh(A)
+    assert (lams[0] - ref).abs().max().item() < 1e-10
+    V = vecs[0]
+    assert (V.T @ V - torch.eye(n, dtype=torch.float64)).abs().max().item() < 1e-10
