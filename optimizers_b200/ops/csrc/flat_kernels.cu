@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
           }
           if (lane == 0) {
             rotated = 1;
-            if (fabsf(gamma) > 32.f * tol * scale) significant = 1;
+            if (fabsf(gamma) > 8.f * tol * scale) significant = 1;
           }
         }
       }
@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(kJacobiThreads) jacobi_eigh_kernel(const Jacob
     }
     converged = rotated == 0;
     // Inner products of fp32 columns carry rounding noise of the order of the tolerance itself: a
-    // pair can hover around it for ever.  A last sweep all of whose rotations were within 32 times
+    // pair can hover around it for ever.  A last sweep all of whose rotations were within 8 times
     // the tolerance has nothing left to remove.
     settled = converged || significant == 0;
     __syncthreads();
