@@ -627,15 +627,18 @@ class NativeBackend:
         ext, dev = self.ext, self.device
         om = self._omega_t
         qr_specs, g = [], []
+        # A Householder second pass only reads V1, the first rank rows of this pass's Q^T: the
+        # accumulation then produces those rows only.
+        head_only = self.range_passes > 1 and self.polish == "householder"
         Yts = _mats(ext, dev, [(s.rank, s.n) for s in subs], pair=False)  # rows: the columns of P Omega
-        Zts = _mats(ext, dev, [(s.n, s.n) for s in subs])
+        Zts = _mats(ext, dev, [(s.rank if head_only else s.n, s.n) for s in subs])
         for s, Yt, Zt in zip(subs, Yts, Zts, strict=True):
             k, n = s.rank, s.n
             P = s.extra.pop("P")
             s.extra["Qt"] = Zt
             g.append((om.hi, om.lo, P.hi, P.lo, Yt.plain, None, None, None, Yt.plain.stride(0), 0,
                       0, False, None, (0, 0, 0, 0, k, n, n)))
-            qr_specs.append((Yt.plain, n, k, Zt.plain, Zt.hi, Zt.lo))
+            qr_specs.append((Yt.plain, n, k, Zt.plain, Zt.hi, Zt.lo, k if head_only else n))
             s.extra["P_keep"] = P
         # the Omega view ends before its array along K unless n == dmax: K = n must then be a multiple of 32;
         # otherwise fall back to a sliced operand (its own tensor map)

@@ -898,14 +898,14 @@ void householder_qr(const std::vector<py::tuple>& specs) {
   TORCH_CHECK(!specs.empty(), "householder_qr: empty batch");
   struct Item {
     torch::Tensor ct, zt, zt_hi, zt_lo, vt, ttv, tv;
-    int n = 0, k = 0, npan = 0;
+    int n = 0, k = 0, npan = 0, q_rows = 0;
   };
   std::vector<Item> items(specs.size());
   int max_pan = 0;
   torch::Device device(torch::kCPU);
   for (size_t i = 0; i < specs.size(); ++i) {
     const py::tuple& s = specs[i];
-    TORCH_CHECK(s.size() == 6, "householder_qr spec must have 6 fields");
+    TORCH_CHECK(s.size() == 6 || s.size() == 7, "householder_qr spec must have 6 or 7 fields");
     Item& it = items[i];
     it.ct = s[0].cast<torch::Tensor>();
     it.n = s[1].cast<int>();
@@ -914,14 +914,17 @@ void householder_qr(const std::vector<py::tuple>& specs) {
     it.zt_hi = s[4].cast<torch::Tensor>();
     it.zt_lo = s[5].cast<torch::Tensor>();
     TORCH_CHECK(it.k >= 1 && it.k <= it.n, "householder_qr: need 1 <= k <= n");
+    // Optional 7th field: only the first q_rows rows of Q^T (the first q_rows columns of Q) are wanted.
+    it.q_rows = s.size() == 7 ? s[6].cast<int>() : it.n;
+    TORCH_CHECK(it.q_rows >= 1 && it.q_rows <= it.n, "householder_qr: need 1 <= q_rows <= n");
     TORCH_CHECK(it.n <= kReflectSmemFloats, "householder_qr: n too large for the row-tile kernel");
     TORCH_CHECK(it.ct.is_cuda() && it.ct.scalar_type() == torch::kFloat32 && it.ct.dim() == 2 && it.ct.stride(1) == 1 &&
                     it.ct.size(0) >= it.k && it.ct.size(1) == it.n,
                 "householder_qr: ct must be a [>= k, n] fp32 view");
     for (const torch::Tensor* t : {&it.zt, &it.zt_hi, &it.zt_lo}) {
       TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->dim() == 2 && t->stride(1) == 1 &&
-                      t->size(0) == it.n && t->size(1) == it.n && t->stride(0) == it.zt.stride(0),
-                  "householder_qr: zt arrays must be [n, n] fp32 views with one pitch");
+                      t->size(0) >= it.q_rows && t->size(1) == it.n && t->stride(0) == it.zt.stride(0),
+                  "householder_qr: zt arrays must be [>= q_rows, n] fp32 views with one pitch");
     }
     device = it.ct.device();
     it.npan = (it.k + kQrPanel - 1) / kQrPanel;
@@ -1007,9 +1010,10 @@ void householder_qr(const std::vector<py::tuple>& specs) {
     a.n = it.n;
     a.npan = it.npan;
     a.rows_per_tile = std::max(1, std::min(kReflectMaxRows, kReflectSmemFloats / it.n));
+    a.q_rows = it.q_rows;
     const int idx = static_cast<int>(accumulate.size());
     accumulate.push_back(a);
-    for (int row0 = 0; row0 < it.n; row0 += a.rows_per_tile) acc_tiles.push_back(make_int2(idx, row0));
+    for (int row0 = 0; row0 < it.q_rows; row0 += a.rows_per_tile) acc_tiles.push_back(make_int2(idx, row0));
   }
   auto d_panels = upload_bytes(panels.data(), panels.size() * sizeof(QrPanelDesc), device);
   auto d_reflect = upload_bytes(reflect.data(), reflect.size() * sizeof(ReflectDesc), device);

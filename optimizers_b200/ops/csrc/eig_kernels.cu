@@ -376,7 +376,7 @@ __global__ void __launch_bounds__(kReflectThreads, 2) accumulate_q_kernel(const 
     const int2 ref = tiles[tile];
     const AccumulateDesc d = descs[ref.x];
     const int row0 = ref.y, n = d.n;
-    const int R = min(d.rows_per_tile, n - row0);
+    const int R = min(d.rows_per_tile, d.q_rows - row0);
     const int first = min(d.npan - 1, (row0 + R - 1) / kQrPanel);  // last panel whose columns reach the tile's rows
     {
       const long long off = static_cast<long long>(first) * kQrPanel * d.ldw + first * kQrPanel;

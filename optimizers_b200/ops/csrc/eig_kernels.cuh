@@ -81,7 +81,8 @@ struct AccumulateDesc {
   const float* tv;
   int ldz, ldw, n, npan;
   int rows_per_tile;
-  int pad_[3];
+  int q_rows;  // only rows [0, q_rows) of Q^T are produced (the first q_rows columns of Q)
+  int pad_[2];
 };
 
 void launch_accumulate_q(const AccumulateDesc* descs, const int2* tiles, int num_tiles, cudaStream_t stream);

@@ -124,13 +124,15 @@ class FakeExt:
 
     def householder_qr(self, specs):
         self.calls.append("householder_qr")
-        for ct, n, k, zt, zt_hi, zt_lo in specs:
-            assert ct.shape == (k, n)
+        for spec in specs:
+            ct, n, k, zt, zt_hi, zt_lo = spec[:6]
+            q_rows = spec[6] if len(spec) == 7 else n  # only the first q_rows rows of Q^T are produced
+            assert ct.shape == (k, n) and zt.shape[0] >= q_rows
             Q, _ = torch.linalg.qr(ct.T.double(), mode="complete")
-            zt.copy_(Q.T.float())
+            zt[:q_rows].copy_(Q.T.float()[:q_rows])
             if zt_hi is not None:
-                zt_hi.copy_(zt)
-                zt_lo.zero_()
+                zt_hi[:q_rows].copy_(zt[:q_rows])
+                zt_lo[:q_rows].zero_()
 
     def jacobi_eigh_into(self, mats, qs, lams, transposed, max_sweeps, tol, shift_scale):
         for A, q, lam in zip(mats, qs, lams):

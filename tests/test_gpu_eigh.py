@@ -148,6 +148,24 @@ def test_householder_qr_matches_lapack(ext, n, k):
     assert float((Q[:, :k] @ R - Y.float().double()).abs().max()) < 2e-5 * float(Y.abs().max()) * n**0.5
 
 
+@pytest.mark.parametrize("n,k,rows", [(300, 77, 77), (513, 300, 5), (130, 64, 130)])
+def test_householder_qr_leading_rows_only(ext, n, k, rows):
+    """The optional seventh field asks for the first rows of Q^T only (what a second range pass
+    reads): same values as the full accumulation, nothing written behind them."""
+    torch.manual_seed(n + k + rows)
+    dev = torch.device("cuda")
+    Y = torch.randn(n, k, device=dev)
+    full = [torch.zeros(n, _pad4(n), device=dev)[:, :n] for _ in range(3)]
+    ext.householder_qr([(_padded(Y.T.contiguous()), n, k, *full)])
+    sentinel = -3.0e30
+    part = [torch.full((rows + 3, _pad4(n)), sentinel, device=dev) for _ in range(3)]
+    ext.householder_qr([(_padded(Y.T.contiguous()), n, k, *(p[:rows, :n] for p in part), rows)])
+    torch.cuda.synchronize()
+    for whole, some in zip(full, part):
+        assert torch.equal(some[:rows, :n], whole[:rows])
+        assert bool((some[rows:] == sentinel).all())
+
+
 def test_householder_qr_batch_of_mixed_shapes(ext):
     torch.manual_seed(2)
     dev = torch.device("cuda")
