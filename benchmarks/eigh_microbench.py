@@ -3,6 +3,8 @@ torch.linalg.eigh (cuSOLVER syevd, what the reference calls per factor) on a lis
 
     python benchmarks/eigh_microbench.py --sizes 2048:16,768:32 --spectrum gram
     python benchmarks/eigh_microbench.py --preset gpt2      # the factor sizes of GPT-2 124M at block 2048
+    python benchmarks/eigh_microbench.py --factors-from-bench 26 --skip-library --profile --host-profile
+                                                             # the factors of bench.py's model after 26 steps
 
 Prints one JSON line per arm: milliseconds (CUDA events, after one warm-up run, inputs larger than
 the L2), accuracy against fp64, and the work counters of the divide-and-conquer driver.
@@ -37,6 +39,34 @@ def gpt2_sizes() -> list[tuple[int, int]]:
     return sorted(counts.items(), reverse=True)
 
 
+def factors_of_the_bench_model(steps: int, dev: torch.device) -> list[torch.Tensor]:
+    """Train the model of ``bench.py`` (GPT-2 124M, this framework's optimizer, one GPU) for ``steps``
+    steps on synthetic tokens and return its unpacked Kronecker factors larger than 128."""
+    import bench
+    from optimizers_b200.models import GPT2, GPT2Config
+
+    torch.manual_seed(1234)
+    model = GPT2(GPT2Config(n_layer=12)).to(dev)
+    opt = bench.build_optimizer("ours", model, 1, argparse.Namespace(backend="native", gemm_mode="tf32x3", comm="p2p", layers=12), None)
+    for _ in range(steps):
+        tokens = torch.randint(0, bench.VOCAB, (16, 1025), device=dev)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model(tokens[:, :-1], tokens[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+    mats = []
+    for rec in opt._per_group_state_lists:
+        for kf in rec["shampoo_preconditioner_list"]._local_kronecker_factors_unwrapped:
+            for f in kf.factor_matrices:
+                A = kf.unpack(f)
+                if A.shape[0] > 128:
+                    mats.append(A.clone())
+    del opt, model
+    torch.cuda.empty_cache()
+    return mats
+
+
 def make(d: int, spectrum: str, gen: torch.Generator, dev: torch.device) -> torch.Tensor:
     if spectrum == "gram":  # a few hundred accumulated gradient outer products with decaying column scales
         G = torch.randn(d, 2 * d, device=dev, generator=gen) * torch.rand(2 * d, device=dev, generator=gen) ** 4
@@ -59,6 +89,9 @@ def main() -> None:
     ap.add_argument("--skip-library", action="store_true")
     ap.add_argument("--profile", action="store_true", help="also print the time per phase of the driver")
     ap.add_argument("--check", action="store_true", help="accuracy against fp64 eigh (slow)")
+    ap.add_argument("--factors-from-bench", type=int, default=0, metavar="STEPS",
+                    help="use the factors of bench.py's model after STEPS training steps instead of synthetic spectra")
+    ap.add_argument("--host-profile", action="store_true", help="also print a cProfile of the host side of one run")
     args = ap.parse_args()
     from optimizers_b200.matrix.eigh_dc import NativeBackend, eigh_divide_and_conquer
     from optimizers_b200.ops import build
@@ -67,7 +100,16 @@ def main() -> None:
     dev = torch.device("cuda")
     gen = torch.Generator(device=dev).manual_seed(0)
     sizes = gpt2_sizes() if args.preset == "gpt2" else [tuple(int(x) for x in s.split(":")) for s in args.sizes.split(",")]
-    mats = [make(d, args.spectrum, gen, dev) for d, count in sizes for _ in range(count)]
+    if args.factors_from_bench > 0:
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        mats = factors_of_the_bench_model(args.factors_from_bench, dev)
+        by_size: dict[int, int] = {}
+        for m in mats:
+            by_size[m.shape[0]] = by_size.get(m.shape[0], 0) + 1
+        sizes = sorted(by_size.items(), reverse=True)
+        args.spectrum = f"bench.py model after {args.factors_from_bench} steps"
+    else:
+        mats = [make(d, args.spectrum, gen, dev) for d, count in sizes for _ in range(count)]
     big = [m for m in mats if m.shape[0] > 128]
     total_bytes = sum(m.numel() * 4 for m in big)
 
@@ -108,6 +150,20 @@ def main() -> None:
         calls = backend.profile.pop("calls", [])
         print(json.dumps({"arm": "divide_and_conquer phases (ms, serialised)", **{k: round(v, 2) for k, v in backend.profile.items()}}), flush=True)
         print(json.dumps({"arm": "divide_and_conquer calls (phase, subproblems, mean size, ms)", "calls": calls}), flush=True)
+    if args.host_profile:
+        import cProfile
+        import io
+        import pstats
+
+        backend.profile = None
+        profiler = cProfile.Profile()
+        profiler.enable()
+        eigh_divide_and_conquer(backend, big)
+        torch.cuda.synchronize()
+        profiler.disable()
+        text = io.StringIO()
+        pstats.Stats(profiler, stream=text).sort_stats("tottime").print_stats(16)
+        print(text.getvalue(), flush=True)
     if not args.skip_library:
         ms_lib, _ = timed(lambda: [torch.linalg.eigh(m) for m in big])
         print(json.dumps({"arm": "torch.linalg.eigh loop", "ms": ms_lib, "matrices": len(big)}), flush=True)
