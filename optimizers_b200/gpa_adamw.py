@@ -296,11 +296,12 @@ class GPAAdamW(Optimizer):
                 weight_lr_power=group[WEIGHT_LR_POWER],
                 weight_sum_ref=shared[WEIGHT_SUM],
             )
-            c = float(c)
-
+            # In Schedule-Free mode ``c`` is a 0-dim tensor (weight / weight_sum), and the reference
+            # feeds it to ``lerp_`` and to ``1 - c`` as such: the torch path below does the same, to
+            # the bit; only the kernel takes it as a host scalar.
             if self._native_ok(params, zs):
                 ext, (table, chunks, n_chunks) = self._table(gi, params, grads, zs, ms, vs)
-                ext.gpa_adamw_step(table, n_chunks, chunks, float(lr), beta1, beta2, eps, bc1, bc2, wd, wd_on_y, c, mu_y)
+                ext.gpa_adamw_step(table, n_chunks, chunks, float(lr), beta1, beta2, eps, bc1, bc2, wd, wd_on_y, float(c), mu_y)
                 self.native_launches += 1
                 continue
 
