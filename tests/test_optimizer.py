@@ -364,3 +364,115 @@ def test_exports_cover_the_reference_surface():
         assert getattr(ob, n) is not None, n
     with pytest.raises(TypeError):
         ob.PreconditionerConfig()  # abstract
+
+
+def _more_options(lib):
+    R = reference()
+    momentum = (lib.shampoo_types.ClassicMomentumConfig if lib is R else lib.ClassicMomentumConfig)
+    return {
+        "l2_without_bias_correction": dict(
+            weight_decay=0.05, weight_decay_type=lib.WeightDecayType.L2, use_bias_correction=False,
+            grafting_config=lib.AdamPreconditionerConfig(beta2=0.99),
+        ),
+        "decoupled_sgd_graft_plain_momentum": dict(
+            weight_decay=0.03, weight_decay_type=lib.WeightDecayType.DECOUPLED, grafting_config=lib.SGDPreconditionerConfig(),
+            iterate_averaging_config=momentum(momentum=0.9, dampening=0.0, use_nesterov=False), betas=(0.0, 0.99),
+        ),
+        "no_grafting_beta2_one": dict(betas=(0.9, 1.0), epsilon=1e-6),
+        "rows_only": dict(
+            preconditioner_config=lib.RootInvShampooPreconditionerConfig(inverse_exponent_override={2: {0: 0.25, 1: 0.0}}),
+            grafting_config=lib.AdamPreconditionerConfig(beta2=0.99),
+        ),
+        "matrices_unpreconditioned": dict(
+            preconditioner_config=lib.RootInvShampooPreconditionerConfig(inverse_exponent_override={2: 0.0}),
+            grafting_config=lib.AdaGradPreconditionerConfig(),
+        ),
+        "eigendecomposed_columns_only": dict(
+            preconditioner_config=lib.EigendecomposedShampooPreconditionerConfig(inverse_exponent_override={2: {0: 0.0, 1: 0.5}}),
+            grafting_config=lib.AdamPreconditionerConfig(beta2=0.99),
+        ),
+        "coupled_higher_order": dict(
+            preconditioner_config=lib.RootInvShampooPreconditionerConfig(
+                amortized_computation_config=lib.CoupledHigherOrderConfig(rel_epsilon=1e-6, abs_epsilon=1e-10, order=3)
+            ),
+            grafting_config=lib.AdamPreconditionerConfig(beta2=0.99),
+        ),
+        "generalized_primal_averaging": dict(
+            iterate_averaging_config=lib.GeneralizedPrimalAveragingConfig(eval_interp_coeff=0.9, train_interp_coeff=0.7),
+            grafting_config=lib.AdamPreconditionerConfig(beta2=0.99), weight_decay=0.01,
+        ),
+    }
+
+
+@pytest.mark.skipif(not reference_available(), reason="reference not installed")
+@pytest.mark.parametrize("name", list(_more_options(ob)))
+def test_more_option_sets_match_reference_bitwise(name):
+    """Option sets beyond the family x extras grid: the other weight-decay types, no bias correction,
+    plain momentum, no grafting, dims switched off by an exponent of 0 (one side, or the whole
+    matrix), the coupled higher-order root, and primal averaging with visits to eval mode between
+    steps."""
+    R = reference()
+
+    def run(lib):
+        kw = dict(lr=0.02, betas=(0.9, 0.99), epsilon=1e-8, max_preconditioner_dim=5, precondition_frequency=2, start_preconditioning_step=2)
+        kw.update(_more_options(lib)[name])
+        model = _model()
+        opt = lib.DistributedShampoo(model.parameters(), **kw)
+        opt.train()
+        seen, losses = [], []
+        for step, (x, y) in enumerate(_batches(7)):
+            if name == "generalized_primal_averaging" and step in (3, 5):
+                opt.eval()
+                seen.append([p.detach().clone() for p in model.parameters()])
+                opt.train()
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(model(x), y)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        seen.append([p.detach().clone() for p in model.parameters()])
+        return seen, losses, opt
+
+    seen_ref, losses_ref, o_ref = run(R)
+    seen_our, losses_our, o_our = run(ob)
+    assert losses_ref == losses_our
+    for a_list, b_list in zip(seen_ref, seen_our, strict=True):
+        for a, b in zip(a_list, b_list):
+            assert torch.equal(a, b), (name, (a - b).abs().max().item())
+    _compare_state(o_ref.state_dict()["state"], o_our.state_dict()["state"])
+
+
+@pytest.mark.skipif(not reference_available(), reason="reference not installed")
+@pytest.mark.parametrize("family", ["root_inv", "soap", "eigendecomposed_kl", "root_inv_trace_scaling_override"])
+@pytest.mark.parametrize("max_dim", [3, 6, 64])
+def test_convolution_weights_match_reference_bitwise(family, max_dim):
+    """Order-4 weights: merged and blocked into tensors of order 1 to 4 depending on
+    ``max_preconditioner_dim`` (dims merged while their product fits, then split)."""
+    R = reference()
+
+    def run(lib):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(
+            torch.nn.Conv2d(2, 4, 3, padding=1), torch.nn.ReLU(), torch.nn.Conv2d(4, 3, (1, 3), padding=(0, 1)),
+            torch.nn.AdaptiveAvgPool2d(1), torch.nn.Flatten(), torch.nn.Linear(3, 3),
+        )
+        kw = dict(lr=0.02, betas=(0.9, 0.99), epsilon=1e-8, max_preconditioner_dim=max_dim, precondition_frequency=2,
+                  start_preconditioning_step=2, grafting_config=lib.AdamPreconditionerConfig(beta2=0.99), weight_decay=0.01)
+        kw.update(_families(lib)[family])
+        opt = lib.DistributedShampoo(model.parameters(), **kw)
+        g = torch.Generator().manual_seed(3)
+        losses = []
+        for _ in range(6):
+            x, y = torch.randn(8, 2, 5, 5, generator=g), torch.randint(0, 3, (8,), generator=g)
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(model(x), y)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        return model, opt, losses
+
+    m_ref, o_ref, l_ref = run(R)
+    m_our, o_our, l_our = run(ob)
+    assert l_ref == l_our
+    _assert_same_params(m_ref, m_our)
+    _compare_state(o_ref.state_dict()["state"], o_our.state_dict()["state"])
