@@ -40,9 +40,6 @@ from torch import Tensor
 
 from optimizers_b200.config import (
     AdaGradPreconditionerConfig,
-    BETA3,
-    BETAS,
-    ClassicMomentumConfig,
     DDPDistributedConfig,
     DISTRIBUTED_CONFIG,
     DISTRIBUTOR,
@@ -52,7 +49,6 @@ from optimizers_b200.config import (
     FILTERED_GRAD_LIST,
     GRAFTING_CONFIG,
     GRAFTING_PRECONDITIONER_LIST,
-    ITERATE_AVERAGING_CONFIG,
     LR_CPU_PINNED,
     MASKED_BLOCKED_GRADS,
     MOMENTUM_BUFFER_LIST,
@@ -64,13 +60,12 @@ from optimizers_b200.config import (
     RootInvShampooPreconditionerConfig,
     SGDPreconditionerConfig,
     SHAMPOO_PRECONDITIONER_LIST,
-    SingleDeviceDistributedConfig,
     TRAIN_MODE,
     WEIGHT_BUFFER_LIST,
     WeightDecayType,
 )
-from optimizers_b200.utils.blocking import compress_list, generate_pairwise_indices
 from optimizers_b200.utils import tracing
+from optimizers_b200.utils.blocking import compress_list
 
 logger: logging.Logger = logging.getLogger(__name__)
 
