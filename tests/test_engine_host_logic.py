@@ -1,0 +1,160 @@
+"""The native engine's orchestration on the CPU.
+
+``tests/fake_block_ext.py`` performs the engine's kernels with torch; the device-only pieces the
+engine touches besides (CUDA events, pinned memory, the capability check, the current stream) are
+replaced by inert stand-ins.  The engine then steps a model on the CPU and must agree with the
+torch step of the same optimizer: plans, tables, selectors, refresh and mirrors, weight decay,
+momentum, primal averaging and mode switches, dims switched off, gradients that go missing.
+"""
+
+import pytest
+import torch
+
+import optimizers_b200 as ob
+from fake_block_ext import FakeBlockExt
+
+
+class _Event:
+    def __init__(self, *args, **kwargs):
+        pass
+
+    def record(self, *args):
+        pass
+
+    def synchronize(self):
+        pass
+
+    def query(self):
+        return True
+
+    def wait(self, *args):
+        pass
+
+
+class _Stream(_Event):
+    def wait_event(self, *args):
+        pass
+
+    def wait_stream(self, *args):
+        pass
+
+
+@pytest.fixture
+def cpu_engine(monkeypatch):
+    """Make ``backend="native"`` build the engine for CPU parameters on top of the stand-in."""
+    import optimizers_b200.native_engine as engine_module
+    from optimizers_b200.ops import build
+
+    ext = FakeBlockExt()
+    monkeypatch.setattr(build, "load", lambda: ext)
+    monkeypatch.setattr(build, "available", lambda: True)
+    monkeypatch.setattr(
+        engine_module, "maybe_build_native_engine",
+        lambda optimizer, rec, group, cfg: None if cfg.backend == "torch" else engine_module.build_native_engine(optimizer, rec, group, cfg),
+    )
+    monkeypatch.setattr(torch.cuda, "Event", _Event)
+    monkeypatch.setattr(torch.cuda, "get_device_capability", lambda device=None: (10, 0))
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: _Stream())
+    monkeypatch.setattr(torch.Tensor, "pin_memory", lambda self, *args, **kwargs: self)
+    return ext
+
+
+def _model():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(torch.nn.Linear(20, 36), torch.nn.Tanh(), torch.nn.Linear(36, 12), torch.nn.Tanh(), torch.nn.Linear(12, 4))
+
+
+def _train(backend, steps=8, visit_eval_at=(), drop_grad_at=(), **kw):
+    # epsilon 1e-4: with a ridge of 1e-8 the inverse roots of these rank-deficient factors amplify the
+    # difference between two eigensolvers to 1e-4 in the parameters, which would hide a wrong plan
+    model = _model()
+    args = dict(lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3, start_preconditioning_step=3)
+    args.update(kw)
+    opt = ob.DistributedShampoo(model.parameters(), native_runtime_config=ob.NativeRuntimeConfig(backend=backend), **args)
+    opt.train()
+    g = torch.Generator().manual_seed(1)
+    seen = []
+    for step in range(steps):
+        if step in visit_eval_at:
+            opt.eval()
+            seen.append([p.detach().clone() for p in model.parameters()])
+            opt.train()
+        x, y = torch.randn(32, 20, generator=g), torch.randint(0, 4, (32,), generator=g)
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(x), y).backward()
+        if step in drop_grad_at:
+            list(model.parameters())[2].grad = None
+        opt.step()
+    seen.append([p.detach().clone() for p in model.parameters()])
+    return seen, opt
+
+
+def _configs():
+    return {
+        "adam_graft_weight_decay": dict(grafting_config=ob.AdamPreconditionerConfig(beta2=0.999, epsilon=1e-8), weight_decay=1e-2),
+        "no_grafting_unpacked": dict(preconditioner_config=ob.RootInvShampooPreconditionerConfig(use_symmetric_packing=False), beta3=0.8),
+        "sgd_graft_l2_nesterov": dict(
+            grafting_config=ob.SGDPreconditionerConfig(), weight_decay=1e-3, weight_decay_type=ob.WeightDecayType.L2,
+            iterate_averaging_config=ob.ClassicMomentumConfig(momentum=0.5, dampening=0.1, use_nesterov=True),
+        ),
+        "primal_averaging": dict(
+            grafting_config=ob.AdamPreconditionerConfig(), weight_decay=1e-2,
+            iterate_averaging_config=ob.GeneralizedPrimalAveragingConfig(eval_interp_coeff=0.9, train_interp_coeff=0.7),
+        ),
+        "eigendecomposed": dict(grafting_config=ob.AdaGradPreconditionerConfig(), preconditioner_config=ob.EigendecomposedShampooPreconditionerConfig()),
+        "kl_root_inverse": dict(grafting_config=ob.AdamPreconditionerConfig(), preconditioner_config=ob.RootInvKLShampooPreconditionerConfig()),
+        # Eigenvectors inside a (nearly) multiple eigenvalue are arbitrary, and the second moment lives in
+        # their basis: the factors (a bias of 16 entries gains one rank per step) get twenty steps to
+        # become full rank before the first refresh.
+        "eigenvalue_corrected": dict(
+            grafting_config=ob.AdamPreconditionerConfig(), preconditioner_config=ob.EigenvalueCorrectedShampooPreconditionerConfig(),
+            precondition_frequency=20, start_preconditioning_step=20, steps=24,
+        ),
+        "eigenvalue_corrected_qr": dict(
+            preconditioner_config=ob.EigenvalueCorrectedShampooPreconditionerConfig(
+                amortized_computation_config=ob.QREigendecompositionConfig(max_iterations=3)
+            ),
+            precondition_frequency=20, start_preconditioning_step=20, steps=26,
+        ),
+        "rows_only": dict(
+            grafting_config=ob.AdamPreconditionerConfig(),
+            preconditioner_config=ob.RootInvShampooPreconditionerConfig(inverse_exponent_override={2: {0: 0.25, 1: 0.0}}),
+        ),
+        "columns_only": dict(
+            grafting_config=ob.AdamPreconditionerConfig(),
+            preconditioner_config=ob.RootInvShampooPreconditionerConfig(inverse_exponent_override={2: {0: 0.0, 1: 0.5}}),
+        ),
+        "nothing_preconditioned": dict(
+            grafting_config=ob.AdamPreconditionerConfig(),
+            preconditioner_config=ob.RootInvShampooPreconditionerConfig(inverse_exponent_override={1: 0.0, 2: 0.0}),
+        ),
+        "coupled_newton": dict(
+            grafting_config=ob.AdamPreconditionerConfig(), epsilon=1e-4,
+            preconditioner_config=ob.RootInvShampooPreconditionerConfig(amortized_computation_config=ob.CoupledNewtonConfig(tolerance=1e-6)),
+        ),
+    }
+
+
+@pytest.mark.parametrize("name", list(_configs()))
+def test_engine_on_the_stand_in_matches_the_torch_step(cpu_engine, name):
+    kw = dict(_configs()[name])
+    steps = kw.pop("steps", 8)
+    visits = (4, 6) if name == "primal_averaging" else ()
+    want, _ = _train("torch", steps=steps, visit_eval_at=visits, **kw)
+    got, opt = _train("native", steps=steps, visit_eval_at=visits, **kw)
+    for rec in opt._per_group_state_lists:
+        assert rec["native_engine"] is not None
+        rec["native_engine"].check_status()
+    assert cpu_engine.gemm_launches > 0 or name == "nothing_preconditioned"
+    for a_list, b_list in zip(want, got, strict=True):
+        for a, b in zip(a_list, b_list):
+            loose = name.startswith("eigenvalue_corrected")  # eigenvectors react to the last bits of the factors
+            assert torch.allclose(a, b, rtol=1e-4, atol=2e-4 if loose else 2e-6), (name, (a - b).abs().max().item())
+
+
+def test_engine_with_a_gradient_that_goes_missing(cpu_engine):
+    kw = dict(grafting_config=ob.AdamPreconditionerConfig(), weight_decay=1e-2)
+    want, _ = _train("torch", drop_grad_at=(2, 5), **kw)
+    got, _ = _train("native", drop_grad_at=(2, 5), **kw)
+    for a, b in zip(want[-1], got[-1]):
+        assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (a - b).abs().max().item()
