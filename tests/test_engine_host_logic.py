@@ -39,24 +39,30 @@ class _Stream(_Event):
         pass
 
 
-@pytest.fixture
-def cpu_engine(monkeypatch):
-    """Make ``backend="native"`` build the engine for CPU parameters on top of the stand-in."""
+def install_cpu_engine(setattr_):
+    """Make ``backend="native"`` build the engine for CPU parameters on top of the stand-in.
+    ``setattr_(object, name, value)`` does the patching (pytest's monkeypatch, or plain ``setattr``
+    inside a spawned rank)."""
     import optimizers_b200.native_engine as engine_module
     from optimizers_b200.ops import build
 
     ext = FakeBlockExt()
-    monkeypatch.setattr(build, "load", lambda: ext)
-    monkeypatch.setattr(build, "available", lambda: True)
-    monkeypatch.setattr(
+    setattr_(build, "load", lambda: ext)
+    setattr_(build, "available", lambda: True)
+    setattr_(
         engine_module, "maybe_build_native_engine",
         lambda optimizer, rec, group, cfg: None if cfg.backend == "torch" else engine_module.build_native_engine(optimizer, rec, group, cfg),
     )
-    monkeypatch.setattr(torch.cuda, "Event", _Event)
-    monkeypatch.setattr(torch.cuda, "get_device_capability", lambda device=None: (10, 0))
-    monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: _Stream())
-    monkeypatch.setattr(torch.Tensor, "pin_memory", lambda self, *args, **kwargs: self)
+    setattr_(torch.cuda, "Event", _Event)
+    setattr_(torch.cuda, "get_device_capability", lambda device=None: (10, 0))
+    setattr_(torch.cuda, "current_stream", lambda device=None: _Stream())
+    setattr_(torch.Tensor, "pin_memory", lambda self, *args, **kwargs: self)
     return ext
+
+
+@pytest.fixture
+def cpu_engine(monkeypatch):
+    return install_cpu_engine(monkeypatch.setattr)
 
 
 def _model():
@@ -158,3 +164,63 @@ def test_engine_with_a_gradient_that_goes_missing(cpu_engine):
     got, _ = _train("native", drop_grad_at=(2, 5), **kw)
     for a, b in zip(want[-1], got[-1]):
         assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (a - b).abs().max().item()
+
+
+# ----------------------------------------------------------------------------------------------
+# The same under the DDP distributor, ranks as gloo processes
+# ----------------------------------------------------------------------------------------------
+def _ddp_worker(rank, world, case, backend):
+    import optimizers_b200 as lib
+
+    if backend == "native":
+        install_cpu_engine(setattr)
+    torch.manual_seed(0)
+    if case == "one_block":
+        # a single block: every rank but its owner is idle, and still gathers and applies
+        model = torch.nn.Sequential(torch.nn.Linear(12, 8, bias=False))
+    else:
+        model = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 8), torch.nn.Linear(8, 8))
+    comm = torch.bfloat16 if case == "bf16" else torch.float32
+    opt = lib.DistributedShampoo(
+        model.parameters(), lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3,
+        start_preconditioning_step=3, weight_decay=1e-2, grafting_config=lib.AdamPreconditionerConfig(),
+        distributed_config=lib.DDPDistributedConfig(
+            communication_dtype=comm, num_trainers_per_group=world, communicate_params=case == "communicate_params"
+        ),
+        native_runtime_config=lib.NativeRuntimeConfig(backend=backend),
+    )
+    if backend == "native":
+        assert all(rec["native_engine"] is not None for rec in opt._per_group_state_lists)
+    g = torch.Generator().manual_seed(5)
+    for step in range(7):
+        x = torch.randn(16, 12, generator=g)
+        opt.zero_grad(set_to_none=True)
+        if case == "dead_layer":
+            out = model[2](model[1](model[0](x)))  # the last layer never gets a gradient
+        else:
+            out = model(x)
+        out.square().mean().backward()
+        if case == "missing_grads" and step % 2 == 1:
+            list(model.parameters())[0].grad = None
+        opt.step()
+    return [p.detach().clone() for p in model.parameters()]
+
+
+@pytest.mark.parametrize(
+    "case,world", [("plain", 2), ("plain", 3), ("bf16", 2), ("communicate_params", 2), ("one_block", 3), ("dead_layer", 2), ("missing_grads", 2)]
+)
+def test_engine_under_ddp_matches_the_torch_step_on_every_rank(case, world):
+    """Block ownership, the send slots, the all-gather and the gathered apply of the engine under the
+    DDP distributor, with the communication dtypes of the benchmarks, idle ranks, a layer without
+    gradients and gradients that vanish on some steps: the same parameters as the torch step, on
+    every rank."""
+    from dist_utils_for_tests import run_distributed
+
+    want = run_distributed(_ddp_worker, world, case, "torch")
+    got = run_distributed(_ddp_worker, world, case, "native")
+    for ref_rank, twin_rank in zip(want, got, strict=True):
+        for a, b in zip(ref_rank, twin_rank, strict=True):
+            assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (case, (a - b).abs().max().item())
+    for other in got[1:]:
+        for a, b in zip(got[0], other):
+            assert torch.equal(a, b), "ranks diverged"
