@@ -224,3 +224,68 @@ def test_engine_under_ddp_matches_the_torch_step_on_every_rank(case, world):
     for other in got[1:]:
         for a, b in zip(got[0], other):
             assert torch.equal(a, b), "ranks diverged"
+
+
+# ----------------------------------------------------------------------------------------------
+# ... and under the sharded distributors
+# ----------------------------------------------------------------------------------------------
+def _sharded_worker(rank, world, strategy, backend):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy, fully_shard
+    from torch.distributed.tensor import DTensor
+
+    import optimizers_b200 as lib
+
+    if backend == "native":
+        install_cpu_engine(setattr)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 8), torch.nn.Tanh(), torch.nn.Linear(8, 4))
+    cpu = torch.device("cpu")
+    kind, _, assignment = strategy.partition(":")
+    extra = {} if not assignment else dict(param_assignment_strategy=lib.FSDPParamAssignmentStrategy[assignment])
+    if kind == "fsdp":
+        model = FSDP(model, use_orig_params=True, device_id=cpu)
+        cfg = lib.FSDPDistributedConfig(param_to_metadata=lib.compile_fsdp_parameter_metadata(model))
+    elif kind == "hsdp":
+        mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+        model = FSDP(model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True, device_id=cpu)
+        cfg = lib.HSDPDistributedConfig(param_to_metadata=lib.compile_fsdp_parameter_metadata(model), device_mesh=mesh)
+    elif kind == "fully_shard":
+        fully_shard(model, mesh=init_device_mesh("cpu", (world,)))
+        cfg = lib.FullyShardDistributedConfig(**extra)
+    else:
+        mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+        fully_shard(model, mesh=mesh)
+        cfg = lib.HybridShardDistributedConfig(device_mesh=mesh, **extra)
+    opt = lib.DistributedShampoo(
+        model.parameters(), lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=8, precondition_frequency=3,
+        start_preconditioning_step=3, weight_decay=1e-2, grafting_config=lib.AdamPreconditionerConfig(), distributed_config=cfg,
+        native_runtime_config=lib.NativeRuntimeConfig(backend=backend),
+    )
+    engines = [rec.get("native_engine") for rec in opt._per_group_state_lists]
+    g = torch.Generator().manual_seed(5)
+    for _ in range(7):
+        x, y = torch.randn(16, 12, generator=g), torch.randint(0, 4, (16,), generator=g)
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(x), y).backward()
+        opt.step()
+    local = [(p.to_local() if isinstance(p, DTensor) else p).detach().clone() for p in model.parameters()]
+    return local, [e is not None for e in engines]
+
+
+@pytest.mark.parametrize(
+    "strategy,world",
+    [("fsdp", 2), ("hsdp", 4), ("fully_shard", 2), ("fully_shard:ROUND_ROBIN", 2), ("fully_shard:REPLICATE", 2),
+     ("hybrid_shard", 4), ("hybrid_shard:ROUND_ROBIN", 4)],
+)
+def test_engine_under_the_sharded_distributors_matches_the_torch_step(strategy, world):
+    """Flat shards with recovered blocks (FSDP1 / HSDP1), dim-0 shards, the lossless variants' full
+    copies with their all-to-all write-back, and the replicate-group all-gather of the hybrid forms."""
+    from dist_utils_for_tests import run_distributed
+
+    want = run_distributed(_sharded_worker, world, strategy, "torch")
+    got = run_distributed(_sharded_worker, world, strategy, "native")
+    for (ref_rank, _), (twin_rank, engines) in zip(want, got, strict=True):
+        assert all(engines), "the engine was not built on every rank"
+        for a, b in zip(ref_rank, twin_rank, strict=True):
+            assert a.shape == b.shape and torch.allclose(a, b, rtol=1e-4, atol=2e-6), (strategy, (a - b).abs().max().item())
