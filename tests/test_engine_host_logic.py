@@ -289,3 +289,121 @@ def test_engine_under_the_sharded_distributors_matches_the_torch_step(strategy, 
         assert all(engines), "the engine was not built on every rank"
         for a, b in zip(ref_rank, twin_rank, strict=True):
             assert a.shape == b.shape and torch.allclose(a, b, rtol=1e-4, atol=2e-6), (strategy, (a - b).abs().max().item())
+
+
+# ----------------------------------------------------------------------------------------------
+# Convolution weights (order-3 blocks), checkpoints, mode switches across ranks
+# ----------------------------------------------------------------------------------------------
+def _conv_train(backend, **kw):
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(
+        torch.nn.Conv2d(4, 16, 3, padding=1, bias=False), torch.nn.ReLU(), torch.nn.Conv2d(16, 8, 3, padding=1),
+        torch.nn.AdaptiveAvgPool2d(1), torch.nn.Flatten(), torch.nn.Linear(8, 3),
+    )
+    args = dict(lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3,
+                start_preconditioning_step=3, grafting_config=ob.AdamPreconditionerConfig(), weight_decay=1e-2)
+    args.update(kw)
+    opt = ob.DistributedShampoo(model.parameters(), native_runtime_config=ob.NativeRuntimeConfig(backend=backend), **args)
+    g = torch.Generator().manual_seed(2)
+    for _ in range(7):
+        x, y = torch.randn(8, 4, 6, 6, generator=g), torch.randint(0, 3, (8,), generator=g)
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(x), y).backward()
+        opt.step()
+    return [p.detach().clone() for p in model.parameters()], opt
+
+
+@pytest.mark.parametrize("eigdec", [False, True])
+def test_engine_on_convolution_weights_matches_the_torch_step(cpu_engine, eigdec):
+    """(16, 4, 3, 3) and (8, 16, 3, 3) weights become order-3 tensors (out, in, kh * kw) with out and in
+    multiples of 4: the three mode unfoldings, the auxiliary descriptor of the second view and
+    the three chained products."""
+    kw = dict(preconditioner_config=ob.EigendecomposedShampooPreconditionerConfig()) if eigdec else {}
+    want, _ = _conv_train("torch", **kw)
+    got, opt = _conv_train("native", **kw)
+    engine = opt._per_group_state_lists[0]["native_engine"]
+    assert engine is not None and any(b.dims3 is not None for b in engine._blocks)
+    for a, b in zip(want, got):
+        assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (a - b).abs().max().item()
+
+
+def test_engine_resumes_from_a_checkpoint(cpu_engine):
+    """A fresh optimizer that loads the state of a running one continues exactly like it: the operand
+    mirrors of the inverse roots are rebuilt from the loaded state."""
+    import copy
+
+    kw = dict(grafting_config=ob.AdamPreconditionerConfig(), weight_decay=1e-2)
+
+    def build(model):
+        return ob.DistributedShampoo(
+            model.parameters(), lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3,
+            start_preconditioning_step=3, native_runtime_config=ob.NativeRuntimeConfig(backend="native"), **kw
+        )
+
+    def steps(model, opt, generator, count):
+        for _ in range(count):
+            x, y = torch.randn(32, 20, generator=generator), torch.randint(0, 4, (32,), generator=generator)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+
+    model = _model()
+    opt = build(model)
+    g = torch.Generator().manual_seed(1)
+    steps(model, opt, g, 5)
+    saved_model, saved_opt, saved_rng = copy.deepcopy(model.state_dict()), copy.deepcopy(opt.state_dict()), g.get_state()
+    steps(model, opt, g, 4)
+
+    resumed = _model()
+    resumed.load_state_dict(saved_model)
+    resumed_opt = build(resumed)
+    resumed_opt.load_state_dict(saved_opt)
+    g2 = torch.Generator()
+    g2.set_state(saved_rng)
+    steps(resumed, resumed_opt, g2, 4)
+    for a, b in zip(model.parameters(), resumed.parameters()):
+        assert torch.equal(a, b), (a - b).abs().max().item()
+
+
+def _gpa_ddp_worker(rank, world, backend):
+    import optimizers_b200 as lib
+
+    if backend == "native":
+        install_cpu_engine(setattr)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 8))
+    opt = lib.DistributedShampoo(
+        model.parameters(), lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3,
+        start_preconditioning_step=3, weight_decay=1e-2, grafting_config=lib.AdamPreconditionerConfig(),
+        iterate_averaging_config=lib.GeneralizedPrimalAveragingConfig(eval_interp_coeff=0.9, train_interp_coeff=0.7),
+        distributed_config=lib.DDPDistributedConfig(communication_dtype=torch.float32, num_trainers_per_group=world),
+        native_runtime_config=lib.NativeRuntimeConfig(backend=backend),
+    )
+    opt.train()
+    g = torch.Generator().manual_seed(5)
+    seen = []
+    for step in range(7):
+        if step in (4, 6):
+            opt.eval()
+            seen.append([p.detach().clone() for p in model.parameters()])
+            opt.train()
+        x = torch.randn(16, 12, generator=g)
+        opt.zero_grad()
+        model(x).square().mean().backward()
+        opt.step()
+    opt.eval()
+    seen.append([p.detach().clone() for p in model.parameters()])
+    return seen
+
+
+def test_engine_mode_switches_under_ddp_match_the_torch_step():
+    """train() / eval() of primal averaging with block ownership spread over ranks: every rank
+    switches every parameter (the owners' deltas travel through the all-gather buffer)."""
+    from dist_utils_for_tests import run_distributed
+
+    want = run_distributed(_gpa_ddp_worker, 2, "torch")
+    got = run_distributed(_gpa_ddp_worker, 2, "native")
+    for ref_rank, twin_rank in zip(want, got, strict=True):
+        for a_list, b_list in zip(ref_rank, twin_rank, strict=True):
+            for a, b in zip(a_list, b_list):
+                assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (a - b).abs().max().item()
