@@ -122,11 +122,14 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
 
 
 def _order3_ok(block: Tensor, pc: Any) -> bool:
-    """Order-3 blocks (a, b, c) run natively for root-inverse Shampoo when they are contiguous and
-    a, b are multiples of 4, so that every mode unfolding is an exact, 16-byte aligned 2-D view."""
+    """Order-3 blocks (a, b, c) run natively for root-inverse, eigendecomposed and eigenvalue-corrected
+    Shampoo when they are contiguous and a, b are multiples of 4, so that every mode unfolding is an
+    exact, 16-byte aligned 2-D view."""
     a, b, _ = block.shape
-    root_like = type(pc) in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig)  # not KL
-    return root_like and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
+    covered = type(pc) in (  # not KL
+        RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig, EigenvalueCorrectedShampooPreconditionerConfig
+    )
+    return covered and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
 
 
 def maybe_build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig):
@@ -188,6 +191,7 @@ class _Block:
         "m1", "v", "mom", "z", "g_hi", "g_lo", "gt_hi", "gt_lo", "f_hi", "f_lo", "tt_hi", "tt_lo", "p",
         "inv_hi", "inv_lo", "ev", "qt_hi", "qt_lo", "t2_hi", "t2_lo",
         "dims3", "view2d", "y_hi", "y_lo", "zt_hi", "zt_lo", "aux_g_hi", "aux_g_lo", "aux_gt_hi", "aux_gt_lo", "d1_hi", "d1_lo", "d2_hi", "d2_lo",
+        "e1_hi", "e1_lo", "e2_hi", "e2_lo",  # second set of chain intermediates (eigenvalue-corrected order-3: two chains per stage)
         "sel",  # per dim of the block: has a Kronecker factor (inverse_exponent_override 0 switches a dim off)
         "eig_hints",  # factor index -> eigenvalues found at the previous refresh (host tensor; steers the eigensolver)
     )
@@ -343,6 +347,7 @@ class NativeGroupEngine:
                 blocks.append(b)
                 continue
             b.aux_g_hi = b.aux_g_lo = b.aux_gt_hi = b.aux_gt_lo = b.d1_hi = b.d1_lo = b.d2_hi = b.d2_lo = None
+            b.e1_hi = b.e1_lo = b.e2_hi = b.e2_lo = None
             b.g_hi = zeros(b.m, b.n_pad) if need_g else None
             b.g_lo = zeros(b.m, b.n_pad) if need_g and self._split else None
             need_gt = right or self._soap
@@ -405,6 +410,17 @@ class NativeGroupEngine:
         b.inv_hi = [zeros(d, _pad4(d)) for d in b.dims3]
         b.inv_lo = [zeros(d, _pad4(d)) if sp else None for d in b.dims3]
         b.ev = b.qt_hi = b.qt_lo = b.t2_hi = b.t2_lo = None
+        b.e1_hi = b.e1_lo = b.e2_hi = b.e2_lo = None
+        if self._soap:
+            # The raw gradient is projected as well (second moment in the eigenbasis): it needs the
+            # (ab, c) operand form of G, the transposed eigenvector mirrors, and chain intermediates
+            # of its own, since it runs in the same launches as the chain of the filtered gradient.
+            b.g_hi, b.g_lo = pair(a * bb, _pad4(c))
+            b.ev = b.factors.corrected_eigenvalues
+            b.qt_hi = [zeros(d, _pad4(d)) for d in b.dims3]
+            b.qt_lo = [zeros(d, _pad4(d)) if sp else None for d in b.dims3]
+            b.e1_hi, b.e1_lo = pair(c, a * bb)
+            b.e2_hi, b.e2_lo = pair(bb, c * a)
 
     def _send_ptr(self, b: _Block) -> int:
         if not self._ddp or self._p2p:
@@ -626,10 +642,40 @@ class NativeGroupEngine:
         def _ab(a, b):
             return (a[0], a[1], b[0], b[1])
 
-        syrk, st_a, st_v, st_f, st_u1, st_u2 = [], [], [], [], [], []
+        syrk, st_a0, st_a, st_v, st_f, st_u0, st_u1, st_u2 = [], [], [], [], [], [], [], []
         pack_flag = F.FLAG_PACKED_C if self._packing else 0
         for b in blocks:
             fm = b.factors.factor_matrices
+            if b.dims3 is not None:
+                # Order-3 block (a, b, c): every product contracts the fastest index of the current
+                # layout and emits the new one slowest, (a,b,c) -> (c,a,b) -> (b,c,a) -> (a,b,c); the
+                # raw and the filtered gradient go through Q_c^T, Q_b^T, Q_a^T side by side, the
+                # scaled direction back through Q_c, Q_b, Q_a.
+                a, bb, c = b.dims3
+                lo = lambda t: t if split else None  # noqa: E731
+                xa = (b.aux_g_hi, lo(b.aux_g_lo))
+                xb = (b.aux_gt_hi.view(bb, c * a), lo(b.aux_gt_lo.view(bb, c * a) if split else None))
+                xc = (b.gt_hi, lo(b.gt_lo))
+                for x, factor, d in ((xa, fm[0], a), (xb, fm[1], bb), (xc, fm[2], c)):
+                    syrk.append((*_ab(x, x), factor, None, None, None, d, 0, pack_flag, self._packing))
+                q = [pair(b.inv_hi[k], b.inv_lo[k], d) for k, d in enumerate(b.dims3)]
+                qt = [pair(b.qt_hi[k], b.qt_lo[k], d) for k, d in enumerate(b.dims3)]
+                g3, f3 = pair(b.g_hi, b.g_lo, c), pair(b.f_hi, b.f_lo, c)
+
+                def as_rows(hi, lo_, rows, cols):
+                    return (hi.view(rows, cols), lo_.view(rows, cols) if lo_ is not None else None)
+
+                st_a0.append(chained(qt[2], g3, b.e1_hi, b.e1_lo))
+                st_a0.append(chained(qt[2], f3, b.d1_hi, b.d1_lo))
+                st_a.append(chained(qt[1], as_rows(b.e1_hi, b.e1_lo, c * a, bb), b.e2_hi, b.e2_lo))
+                st_a.append(chained(qt[1], as_rows(b.d1_hi, b.d1_lo, c * a, bb), b.d2_hi, b.d2_lo))
+                ev = b.ev.view(a, bb * c)
+                st_v.append((*_ab(qt[0], as_rows(b.e2_hi, b.e2_lo, bb * c, a)), ev, None, None, None, bb * c, 0, F.FLAG_SQUARE_ACC, False))
+                st_f.append((*_ab(qt[0], as_rows(b.d2_hi, b.d2_lo, bb * c, a)), b.p, None, None, None, bb * c, 0, 0, False))
+                st_u0.append(chained(q[2], f3, b.d1_hi, b.d1_lo))
+                st_u1.append(chained(q[1], as_rows(b.d1_hi, b.d1_lo, c * a, bb), b.d2_hi, b.d2_lo))
+                st_u2.append((*_ab(q[0], as_rows(b.d2_hi, b.d2_lo, bb * c, a)), b.p, None, None, self._norms[b.index, 1:2], bb * c, 0, F.FLAG_SUMSQ, False))
+                continue
             two_d = b.order == 2
             g = pair(b.g_hi, b.g_lo, b.n)
             gt = pair(b.gt_hi, b.gt_lo, b.m)
@@ -655,7 +701,9 @@ class NativeGroupEngine:
                 st_u2.append((*_ab(f, qr), b.p, None, None, sumsq, b.n, 0, F.FLAG_SUMSQ, False))
         self._syrk_plan = ext.build_gemm_plan(syrk)
         mk = lambda specs: ext.build_gemm_plan(specs) if specs else None  # noqa: E731
-        self._soap_plans = {"a": mk(st_a), "v": mk(st_v), "f": mk(st_f), "u1": mk(st_u1), "u2": mk(st_u2)}
+        self._soap_plans = {
+            "a0": mk(st_a0), "a": mk(st_a), "v": mk(st_v), "f": mk(st_f), "u0": mk(st_u0), "u1": mk(st_u1), "u2": mk(st_u2),
+        }
 
     def refresh_inverse_mirrors(self, blocks: list[_Block] | None = None) -> None:
         """Rebuild the full (hi, lo) operand copies of the inverse roots (or, for the
@@ -949,9 +997,10 @@ class NativeGroupEngine:
         ext, plans, split = self._ext, self._soap_plans, self._split
         run = lambda key, alpha=1.0, beta=0.0: ext.run_gemm_plan(*plans[key], alpha, beta, split, self._status)  # noqa: E731
         launches = 0
-        if plans["a"] is not None:
-            run("a")
-            launches += 1
+        for stage in ("a0", "a"):  # first stages of the projections: order-3 blocks only, then 2-D and order-3
+            if plans[stage] is not None:
+                run(stage)
+                launches += 1
         run("v", plist._weighting_factor, plist._beta2)
         launches += 1
         if graft_only:
@@ -960,9 +1009,10 @@ class NativeGroupEngine:
         blocks_t, tiles_t, n_tiles = self._table
         root = self._active_blocks[0].factors.roots[0]
         ext.eig_scale(blocks_t, tiles_t, n_tiles, float(plist._bias_correction2), 1.0 / root, plist._epsilon, split)
-        if plans["u1"] is not None:
-            run("u1")
-            launches += 1
+        for stage in ("u0", "u1"):
+            if plans[stage] is not None:
+                run(stage)
+                launches += 1
         run("u2")
         return launches + 3
 

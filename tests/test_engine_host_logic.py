@@ -294,7 +294,7 @@ def test_engine_under_the_sharded_distributors_matches_the_torch_step(strategy, 
 # ----------------------------------------------------------------------------------------------
 # Convolution weights (order-3 blocks), checkpoints, mode switches across ranks
 # ----------------------------------------------------------------------------------------------
-def _conv_train(backend, **kw):
+def _conv_train(backend, steps=7, **kw):
     torch.manual_seed(0)
     model = torch.nn.Sequential(
         torch.nn.Conv2d(4, 16, 3, padding=1, bias=False), torch.nn.ReLU(), torch.nn.Conv2d(16, 8, 3, padding=1),
@@ -305,12 +305,27 @@ def _conv_train(backend, **kw):
     args.update(kw)
     opt = ob.DistributedShampoo(model.parameters(), native_runtime_config=ob.NativeRuntimeConfig(backend=backend), **args)
     g = torch.Generator().manual_seed(2)
-    for _ in range(7):
+    for _ in range(steps):
         x, y = torch.randn(8, 4, 6, 6, generator=g), torch.randint(0, 3, (8,), generator=g)
         opt.zero_grad()
         torch.nn.functional.cross_entropy(model(x), y).backward()
         opt.step()
     return [p.detach().clone() for p in model.parameters()], opt
+
+
+def test_engine_on_convolution_weights_with_eigenvalue_correction(cpu_engine):
+    """Order-3 blocks under eigenvalue-corrected Shampoo: the raw and the filtered gradient are
+    projected through the three eigenbases side by side, the second moment is taken in the
+    eigenbasis, and the scaled direction goes back through the three bases.  The first refresh
+    waits until the factors have full rank (see the 2-D case above)."""
+    kw = dict(preconditioner_config=ob.EigenvalueCorrectedShampooPreconditionerConfig(), precondition_frequency=20,
+              start_preconditioning_step=20)
+    want, _ = _conv_train("torch", steps=24, **kw)
+    got, opt = _conv_train("native", steps=24, **kw)
+    engine = opt._per_group_state_lists[0]["native_engine"]
+    assert engine is not None and any(b.dims3 is not None for b in engine._blocks)
+    for a, b in zip(want, got):
+        assert torch.allclose(a, b, rtol=1e-4, atol=2e-5), (a - b).abs().max().item()
 
 
 @pytest.mark.parametrize("eigdec", [False, True])
