@@ -461,7 +461,9 @@ __global__ void __launch_bounds__(256) eig_scale_kernel(const BlockDesc* __restr
     const BlockDesc& b = blocks[ref.block];
     const int i0 = ref.ti * kTile, j = ref.tj * kWide + 4 * lane;
     const int cnt = b.n - j < 4 ? b.n - j : 4;
-    if (cnt <= 0) continue;
+    // The auxiliary descriptor of an order-3 block (its second 2-D view) carries no state: ev and p
+    // are null there.
+    if (cnt <= 0 || b.aux == 1 || b.ev == nullptr) continue;
     const bool vec = (b.n & 3) == 0 && aligned16(b.ev) && aligned16(b.p);
     float ev[4][4], p[4][4];
 #pragma unroll

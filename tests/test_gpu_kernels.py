@@ -477,6 +477,50 @@ def test_native_engine_order3_blocks_match_torch_step(graft):
     walk(results[0][1], results[1][1])
 
 
+def test_native_engine_order3_blocks_with_eigenvalue_correction_match_torch_step(monkeypatch):
+    """Order-3 blocks under eigenvalue-corrected Shampoo: raw and filtered gradient projected through
+    the three eigenbases side by side (second moment in the eigenbasis from the squared-EMA epilogue),
+    the scaled direction taken back through them.  The first refresh waits for twelve steps so that the
+    9 x 9 factor of the kernel window has distinct eigenvalues."""
+    import optimizers_b200.native_engine as engine_module
+    from optimizers_b200 import (
+        AdamPreconditionerConfig,
+        DistributedShampoo,
+        EigenvalueCorrectedShampooPreconditionerConfig,
+        NativeRuntimeConfig,
+    )
+
+    monkeypatch.setattr(engine_module, "_ORDER3_EIGENVALUE_CORRECTED", True)
+    results = []
+    for backend in ("torch", "native"):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(
+            torch.nn.Conv2d(64, 64, 3, padding=1, bias=False), torch.nn.ReLU(), torch.nn.Conv2d(64, 32, 3, padding=1),
+            torch.nn.AdaptiveAvgPool2d(1), torch.nn.Flatten(), torch.nn.Linear(32, 10),
+        ).cuda()
+        opt = DistributedShampoo(
+            model.parameters(), lr=1e-3, betas=(0.9, 0.999), epsilon=1e-6, max_preconditioner_dim=64,
+            precondition_frequency=12, start_preconditioning_step=12, weight_decay=1e-2,
+            grafting_config=AdamPreconditionerConfig(), preconditioner_config=EigenvalueCorrectedShampooPreconditionerConfig(),
+            native_runtime_config=NativeRuntimeConfig(backend=backend),
+        )
+        assert 3 in {b.dim() for b in opt._per_group_state_lists[0]["distributor"].local_blocked_params}
+        g = torch.Generator(device="cuda").manual_seed(1)
+        for _ in range(16):
+            x = torch.randn(16, 64, 8, 8, device="cuda", generator=g)
+            y = torch.randint(0, 10, (16,), device="cuda", generator=g)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+        if backend == "native":
+            eng = opt._per_group_state_lists[0]["native_engine"]
+            assert eng is not None and any(b.dims3 is not None for b in eng._blocks)
+            eng.check_status()
+        results.append([p.detach().clone() for p in model.parameters()])
+    for p, q in zip(*results):
+        assert torch.allclose(p, q, rtol=5e-3, atol=4e-3), (p - q).abs().max()
+
+
 @pytest.mark.parametrize("name", ["adam_graft", "soap_adam_graft", "eigendecomposed_adam_graft", "gpa"])
 def test_native_engine_resumes_from_checkpoint(name):
     """Train 5 steps, checkpoint (model + optimizer), train 4 more; a fresh model / optimizer loaded
