@@ -72,9 +72,6 @@ logger: logging.Logger = logging.getLogger(__name__)
 _GRAFT_NONE, _GRAFT_SGD, _GRAFT_ADAGRAD = 0, 1, 2
 
 
-_ORDER3_EIGENVALUE_CORRECTED = False  # see _order3_ok
-
-
 def _pad4(n: int) -> int:
     return (n + 3) // 4 * 4
 
@@ -125,17 +122,13 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
 
 
 def _order3_ok(block: Tensor, pc: Any) -> bool:
-    """Order-3 blocks (a, b, c) run natively for root-inverse and eigendecomposed Shampoo when they
-    are contiguous and a, b are multiples of 4, so that every mode unfolding is an exact, 16-byte
-    aligned 2-D view."""
+    """Order-3 blocks (a, b, c) run natively for root-inverse, eigendecomposed and eigenvalue-corrected
+    Shampoo when they are contiguous and a, b are multiples of 4, so that every mode unfolding is an
+    exact, 16-byte aligned 2-D view."""
     a, b, _ = block.shape
-    covered = type(pc) in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig)  # not KL
-    # Eigenvalue-corrected Shampoo on order-3 blocks: the plans exist (_build_soap_plans) and agree with
-    # the torch step when the kernels are replaced by their torch stand-ins, but the one run on a B200
-    # ended in a crash of the test process whose cause has not been found, so the path stays off
-    # unless asked for.
-    if _ORDER3_EIGENVALUE_CORRECTED and type(pc) is EigenvalueCorrectedShampooPreconditionerConfig:
-        covered = True
+    covered = type(pc) in (  # not KL
+        RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig, EigenvalueCorrectedShampooPreconditionerConfig
+    )
     return covered and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
 
 

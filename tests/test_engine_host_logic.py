@@ -313,14 +313,11 @@ def _conv_train(backend, steps=7, **kw):
     return [p.detach().clone() for p in model.parameters()], opt
 
 
-def test_engine_on_convolution_weights_with_eigenvalue_correction(cpu_engine, monkeypatch):
-    """Order-3 blocks under eigenvalue-corrected Shampoo (off by default, see ``_order3_ok``): the raw and the filtered gradient are
+def test_engine_on_convolution_weights_with_eigenvalue_correction(cpu_engine):
+    """Order-3 blocks under eigenvalue-corrected Shampoo: the raw and the filtered gradient are
     projected through the three eigenbases side by side, the second moment is taken in the
     eigenbasis, and the scaled direction goes back through the three bases.  The first refresh
     waits until the factors have full rank (see the 2-D case above)."""
-    import optimizers_b200.native_engine as engine_module
-
-    monkeypatch.setattr(engine_module, "_ORDER3_EIGENVALUE_CORRECTED", True)
     kw = dict(preconditioner_config=ob.EigenvalueCorrectedShampooPreconditionerConfig(), precondition_frequency=20,
               start_preconditioning_step=20)
     want, _ = _conv_train("torch", steps=24, **kw)

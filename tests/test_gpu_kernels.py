@@ -477,12 +477,11 @@ def test_native_engine_order3_blocks_match_torch_step(graft):
     walk(results[0][1], results[1][1])
 
 
-def test_native_engine_order3_blocks_with_eigenvalue_correction_match_torch_step(monkeypatch):
+def test_native_engine_order3_blocks_with_eigenvalue_correction_match_torch_step():
     """Order-3 blocks under eigenvalue-corrected Shampoo: raw and filtered gradient projected through
     the three eigenbases side by side (second moment in the eigenbasis from the squared-EMA epilogue),
     the scaled direction taken back through them.  The first refresh waits for twelve steps so that the
     9 x 9 factor of the kernel window has distinct eigenvalues."""
-    import optimizers_b200.native_engine as engine_module
     from optimizers_b200 import (
         AdamPreconditionerConfig,
         DistributedShampoo,
@@ -490,7 +489,6 @@ def test_native_engine_order3_blocks_with_eigenvalue_correction_match_torch_step
         NativeRuntimeConfig,
     )
 
-    monkeypatch.setattr(engine_module, "_ORDER3_EIGENVALUE_CORRECTED", True)
     results = []
     for backend in ("torch", "native"):
         torch.manual_seed(0)
