@@ -76,7 +76,8 @@ def _train(backend, steps=8, visit_eval_at=(), drop_grad_at=(), **kw):
     model = _model()
     args = dict(lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3, start_preconditioning_step=3)
     args.update(kw)
-    opt = ob.DistributedShampoo(model.parameters(), native_runtime_config=ob.NativeRuntimeConfig(backend=backend), **args)
+    runtime = ob.NativeRuntimeConfig(backend=backend, gemm_mode=args.pop("gemm_mode", "tf32x3"))
+    opt = ob.DistributedShampoo(model.parameters(), native_runtime_config=runtime, **args)
     opt.train()
     g = torch.Generator().manual_seed(1)
     seen = []
@@ -109,6 +110,9 @@ def _configs():
         ),
         "eigendecomposed": dict(grafting_config=ob.AdaGradPreconditionerConfig(), preconditioner_config=ob.EigendecomposedShampooPreconditionerConfig()),
         "kl_root_inverse": dict(grafting_config=ob.AdamPreconditionerConfig(), preconditioner_config=ob.RootInvKLShampooPreconditionerConfig()),
+        "kl_eigendecomposed": dict(preconditioner_config=ob.EigendecomposedKLShampooPreconditionerConfig()),
+        "single_pass_gemm_mode": dict(grafting_config=ob.AdamPreconditionerConfig(), gemm_mode="tf32"),
+        "rmsprop_graft_no_bias_correction": dict(grafting_config=ob.RMSpropPreconditionerConfig(beta2=0.95), use_bias_correction=False),
         # Eigenvectors inside a (nearly) multiple eigenvalue are arbitrary, and the second moment lives in
         # their basis: the factors (a bias of 16 entries gains one rank per step) get twenty steps to
         # become full rank before the first refresh.
