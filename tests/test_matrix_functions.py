@@ -152,3 +152,117 @@ def test_against_reference_matrix_functions():
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
         X = torch.randn(n, n + 5)
         assert torch.equal(mf.matrix_orthogonalization(X), rmf.matrix_orthogonalization(X))
+
+
+def _reference_pair():
+    from ref_oracle import reference, reference_available
+
+    if not reference_available():
+        pytest.skip("reference not installed")
+    R = reference()
+    from distributed_shampoo.preconditioner import matrix_functions as rmf
+
+    return R, rmf
+
+
+def _same(call_ours, call_theirs, label):
+    """Both return equal tensors (bit for bit), or both raise the same kind of error."""
+    try:
+        want = call_theirs()
+    except Exception as error:  # noqa: BLE001
+        with pytest.raises(type(error).__mro__[0] if type(error).__module__ == "builtins" else Exception):
+            call_ours()
+        return
+    got = call_ours()
+    want, got = (want if isinstance(want, tuple) else (want,)), (got if isinstance(got, tuple) else (got,))
+    assert len(want) == len(got), label
+    for a, b in zip(want, got):
+        assert a.shape == b.shape and a.dtype == b.dtype and torch.equal(a, b), (label, (a.double() - b.double()).abs().max().item())
+
+
+def _test_matrices():
+    gen = torch.Generator().manual_seed(9)
+    out = {}
+    G = torch.randn(12, 30, generator=gen)
+    out["full_rank"] = G @ G.T / 30
+    L = torch.randn(12, 3, generator=gen)
+    out["rank_3_of_12"] = L @ L.T
+    out["diagonal"] = torch.diag(torch.linspace(0.1, 3.0, 7))
+    out["one_by_one"] = torch.tensor([[2.5]])
+    out["tiny_scale"] = out["full_rank"] * 1e-20
+    out["with_negative_eigenvalue"] = out["full_rank"] - 0.5 * torch.eye(12)
+    out["float64"] = out["full_rank"].double()
+    return out
+
+
+def test_inverse_roots_against_reference_on_a_grid_of_configurations():
+    R, rmf = _reference_pair()
+    stabilities = [
+        (lambda L: L.PerturbationConfig(), "perturb_before"),
+        (lambda L: L.PerturbationConfig(perturb_before_computation=False), "perturb_after"),
+        (lambda L: L.PseudoInverseConfig(), "pseudo_inverse"),
+        (lambda L: L.PseudoInverseConfig(rank_atol=1e-6, rank_rtol=1e-4), "pseudo_inverse_tolerances"),
+    ]
+    import optimizers_b200.config as ours_lib
+    import distributed_shampoo.preconditioner.matrix_functions_types as theirs_lib
+
+    for name, A in _test_matrices().items():
+        for make_stability, stability_name in stabilities:
+            for retry in (True, False):
+                for root in (Fraction(2), Fraction(4), Fraction(3, 2), Fraction(1)):
+                    for epsilon in (0.0, 1e-6):
+                        ours = ours_lib.EigenConfig(rank_deficient_stability_config=make_stability(ours_lib), retry_double_precision=retry)
+                        theirs = theirs_lib.EigenConfig(rank_deficient_stability_config=make_stability(theirs_lib), retry_double_precision=retry)
+                        _same(
+                            lambda: mf.matrix_inverse_root(A, root, ours, epsilon=epsilon),
+                            lambda: rmf.matrix_inverse_root(A, root, theirs, epsilon=epsilon),
+                            (name, stability_name, retry, root, epsilon),
+                        )
+        for root in (Fraction(2), Fraction(4), Fraction(3, 2)):
+            for iterations, tolerance in ((100, 1e-6), (3, 1e-12)):
+                _same(
+                    lambda: mf.matrix_inverse_root(A, root, ours_lib.CoupledNewtonConfig(max_iterations=iterations, tolerance=tolerance), epsilon=1e-6),
+                    lambda: rmf.matrix_inverse_root(A, root, theirs_lib.CoupledNewtonConfig(max_iterations=iterations, tolerance=tolerance), epsilon=1e-6),
+                    (name, "newton", root, iterations),
+                )
+            for order in (2, 3, 4, 6):
+                kw = dict(rel_epsilon=1e-8, abs_epsilon=1e-12, order=order, max_iterations=40, tolerance=1e-8)
+                _same(
+                    lambda: mf.matrix_inverse_root(A, root, ours_lib.CoupledHigherOrderConfig(**kw)),
+                    lambda: rmf.matrix_inverse_root(A, root, theirs_lib.CoupledHigherOrderConfig(**kw)),
+                    (name, "higher_order", root, order),
+                )
+
+
+def test_eigendecompositions_and_orthogonalizations_against_reference_on_a_grid():
+    R, rmf = _reference_pair()
+    import optimizers_b200.config as ours_lib
+    import distributed_shampoo.preconditioner.matrix_functions_types as theirs_lib
+
+    gen = torch.Generator().manual_seed(4)
+    for name, A in _test_matrices().items():
+        n = A.shape[0]
+        estimate = torch.linalg.qr(torch.randn(n, n, generator=gen, dtype=A.dtype))[0]
+        for epsilon in (0.0, 1e-6):
+            for tolerance in (0.0, 1e-2):
+                for make, label in (
+                    (lambda L: L.EighEigendecompositionConfig(tolerance=tolerance), "eigh"),
+                    (lambda L: L.EighEigendecompositionConfig(tolerance=tolerance, retry_double_precision=False), "eigh_no_retry"),
+                    (lambda L: L.QREigendecompositionConfig(max_iterations=1, tolerance=tolerance), "qr_1"),
+                    (lambda L: L.QREigendecompositionConfig(max_iterations=5, tolerance=tolerance), "qr_5"),
+                ):
+                    for guess in (estimate, torch.eye(n, dtype=A.dtype)):
+                        _same(
+                            lambda: mf.matrix_eigendecomposition(A, epsilon, make(ours_lib), guess),
+                            lambda: rmf.matrix_eigendecomposition(A, epsilon, make(theirs_lib), guess),
+                            (name, label, epsilon, tolerance),
+                        )
+    for shape in ((5, 5), (4, 9), (9, 4), (1, 6)):
+        X = torch.randn(*shape, generator=gen)
+        for make, label in (
+            (lambda L: L.SVDOrthogonalizationConfig(), "svd"),
+            (lambda L: L.SVDOrthogonalizationConfig(scale_by_nuclear_norm=True), "svd_nuclear"),
+            (lambda L: L.NewtonSchulzOrthogonalizationConfig(), "newton_schulz"),
+            (lambda L: L.NewtonSchulzOrthogonalizationConfig(num_iterations=2, coefficients=(1.5, -0.5, 0.0)), "newton_schulz_cubic"),
+        ):
+            _same(lambda: mf.matrix_orthogonalization(X, make(ours_lib)), lambda: rmf.matrix_orthogonalization(X, make(theirs_lib)), (shape, label))
