@@ -476,3 +476,55 @@ def test_convolution_weights_match_reference_bitwise(family, max_dim):
     assert l_ref == l_our
     _assert_same_params(m_ref, m_our)
     _compare_state(o_ref.state_dict()["state"], o_our.state_dict()["state"])
+
+
+@pytest.mark.skipif(not reference_available(), reason="reference not installed")
+@pytest.mark.parametrize("scenario", ["lr_schedule_corrected_wd", "lr_schedule_schedule_free", "lr_schedule_primal_averaging", "two_groups_and_a_frozen_parameter"])
+def test_schedules_and_parameter_groups_match_reference_bitwise(scenario):
+    """The learning rate changes every step (warm-up, then decay), which feeds the corrected weight
+    decay, the Schedule-Free weights and the primal-averaging coefficients; and two parameter groups
+    with different preconditioners, one of them holding a frozen parameter."""
+    R = reference()
+
+    def run(lib):
+        model = _model()
+        momentum = lib.shampoo_types.ClassicMomentumConfig if lib is R else lib.ClassicMomentumConfig
+        kw = dict(lr=0.02, betas=(0.9, 0.99), epsilon=1e-8, max_preconditioner_dim=5, precondition_frequency=2, start_preconditioning_step=2,
+                  grafting_config=lib.AdamPreconditionerConfig(beta2=0.99))
+        params = list(model.parameters())
+        if scenario == "lr_schedule_corrected_wd":
+            kw.update(weight_decay=0.05, weight_decay_type=lib.WeightDecayType.CORRECTED,
+                      iterate_averaging_config=momentum(momentum=0.8, dampening=0.0, use_nesterov=True))
+            groups = params
+        elif scenario == "lr_schedule_schedule_free":
+            kw.update(iterate_averaging_config=lib.ScheduleFreeConfig(train_interp_coeff=0.9), weight_decay=0.01)
+            groups = params
+        elif scenario == "lr_schedule_primal_averaging":
+            kw.update(iterate_averaging_config=lib.GeneralizedPrimalAveragingConfig(eval_interp_coeff=0.95, train_interp_coeff=0.6))
+            groups = params
+        else:
+            params[1].requires_grad_(False)
+            groups = [
+                dict(params=params[:2], lr=0.01, preconditioner_config=lib.DefaultSOAPConfig),
+                dict(params=params[2:], weight_decay=0.02, max_preconditioner_dim=4),
+            ]
+        opt = lib.DistributedShampoo(groups, **kw)
+        opt.train()
+        losses = []
+        for step, (x, y) in enumerate(_batches(8)):
+            if scenario.startswith("lr_schedule"):
+                for group in opt.param_groups:
+                    group["lr"] = 0.02 * min(1.0, (step + 1) / 3) * (0.8 ** max(0, step - 3))
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(model(x), y)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        opt.eval()
+        return model, opt, losses
+
+    m_ref, o_ref, l_ref = run(R)
+    m_our, o_our, l_our = run(ob)
+    assert l_ref == l_our
+    _assert_same_params(m_ref, m_our)
+    _compare_state(o_ref.state_dict()["state"], o_our.state_dict()["state"])
