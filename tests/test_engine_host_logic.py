@@ -426,3 +426,41 @@ def test_engine_mode_switches_under_ddp_match_the_torch_step():
         for a_list, b_list in zip(ref_rank, twin_rank, strict=True):
             for a, b in zip(a_list, b_list):
                 assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (a - b).abs().max().item()
+
+
+@pytest.mark.parametrize("scenario", ["corrected_weight_decay_momentum", "schedule_free", "two_groups"])
+def test_engine_with_a_learning_rate_schedule_and_parameter_groups(cpu_engine, scenario):
+    """The learning rate is a device scalar refreshed every step: the corrected weight decay, the
+    Schedule-Free weights and the epilogue's ``-lr`` must follow a schedule; two groups get two engines."""
+
+    def run(backend):
+        model = _model()
+        params = list(model.parameters())
+        kw = dict(lr=2e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3,
+                  start_preconditioning_step=3, grafting_config=ob.AdamPreconditionerConfig())
+        groups = params
+        if scenario == "corrected_weight_decay_momentum":
+            kw.update(weight_decay=0.05, weight_decay_type=ob.WeightDecayType.CORRECTED,
+                      iterate_averaging_config=ob.ClassicMomentumConfig(momentum=0.8, dampening=0.0, use_nesterov=True))
+        elif scenario == "schedule_free":
+            kw.update(iterate_averaging_config=ob.ScheduleFreeConfig(train_interp_coeff=0.9), weight_decay=0.01)
+        else:
+            groups = [dict(params=params[:2], lr=1e-2), dict(params=params[2:], weight_decay=0.02, max_preconditioner_dim=8)]
+        opt = ob.DistributedShampoo(groups, native_runtime_config=ob.NativeRuntimeConfig(backend=backend), **kw)
+        opt.train()
+        g = torch.Generator().manual_seed(1)
+        for step in range(9):
+            for group in opt.param_groups:
+                group["lr"] = group["lr"] * (1.3 if step < 3 else 0.8)
+            x, y = torch.randn(32, 20, generator=g), torch.randint(0, 4, (32,), generator=g)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+        opt.eval()
+        return [p.detach().clone() for p in model.parameters()], opt
+
+    want, _ = run("torch")
+    got, opt = run("native")
+    assert all(rec["native_engine"] is not None for rec in opt._per_group_state_lists)
+    for a, b in zip(want, got):
+        assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (scenario, (a - b).abs().max().item())
