@@ -106,6 +106,14 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     for p in rec[DISTRIBUTOR]._get_params_or_grads():
         if p.dtype != torch.float32 or not p.is_contiguous() or type(p.detach()) is not Tensor:
             return "parameters (or their local shards) must be plain contiguous fp32 tensors"
+    # Dims switched off by an exponent of 0: decided from the configuration and the global block list,
+    # so that every rank of a group reaches the same verdict.
+    overrides = getattr(pc, "inverse_exponent_override", {}).values()
+    if any(0.0 in (o.values() if isinstance(o, dict) else (o,)) for o in overrides):
+        if type(pc) not in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig):
+            return "dims switched off by an exponent of 0 have a native step only under (eigendecomposed) root-inverse Shampoo"
+        if any(b.dim() > 2 for b in rec[DISTRIBUTOR]._global_blocked_params):
+            return "dims switched off by an exponent of 0 have no native step next to blocks of order 3"
     plist = rec[SHAMPOO_PRECONDITIONER_LIST]
     for block, sel in zip(
         rec[DISTRIBUTOR].local_blocked_params, plist._local_preconditioned_dims_selector_list, strict=True
@@ -116,7 +124,8 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
             return "blocks with unpreconditioned dims have a native step only for 1-D / 2-D blocks of (eigendecomposed) root-inverse Shampoo"
         if block.numel() == 0:
             return "empty blocks"
-    if any(b.dim() > 3 or b.numel() == 0 or (b.dim() == 3 and not b.is_contiguous()) for b in rec[DISTRIBUTOR]._global_blocked_params):
+    # The same verdict on every rank: ranks that disagreed would meet in different collectives.
+    if any(b.dim() > 3 or b.numel() == 0 or (b.dim() == 3 and not _order3_ok(b, pc)) for b in rec[DISTRIBUTOR]._global_blocked_params):
         return "a block of another rank has no native step"
     return None
 
