@@ -89,8 +89,9 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
         dtypes = (pc.factor_matrix_dtype, pc.factor_matrix_eigenvectors_dtype, pc.corrected_eigenvalues_dtype)
         if any(d != torch.float32 for d in dtypes):
             return "factor matrices, eigenvectors and corrected eigenvalues must be fp32"
-        roots = {kf.roots[0] for kf in rec[SHAMPOO_PRECONDITIONER_LIST]._local_kronecker_factors_unwrapped}
-        if len(roots) > 1:
+        # From the configuration and the global block list (the same on every rank), not from this rank's blocks.
+        orders = {b.dim() for b in rec[DISTRIBUTOR]._global_blocked_params}
+        if len({pc.inverse_exponent_override.get(order, 1 / 2) for order in orders}) > 1:
             return "eigenvalue-corrected Shampoo with different roots per tensor order has no native step yet"
     else:
         return f"preconditioner config {type(pc).__name__} has no native step yet"
