@@ -464,3 +464,75 @@ def test_engine_with_a_learning_rate_schedule_and_parameter_groups(cpu_engine, s
     assert all(rec["native_engine"] is not None for rec in opt._per_group_state_lists)
     for a, b in zip(want, got):
         assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (scenario, (a - b).abs().max().item())
+
+
+# ----------------------------------------------------------------------------------------------
+# The peer-memory paths, with shared memory standing in for NVLink peers
+# ----------------------------------------------------------------------------------------------
+def _p2p_worker(rank, world, case, mode):
+    import torch.distributed._symmetric_memory as symm_mem
+
+    import fake_peers
+    import optimizers_b200 as lib
+    import optimizers_b200.native_engine as engine_module
+    from optimizers_b200.ops import build
+
+    if mode != "torch":
+        install_cpu_engine(setattr)
+        ext = fake_peers.FakePeerExt()
+        build.load = lambda: ext
+        symm_mem.empty = fake_peers.symm_empty
+        symm_mem.rendezvous = fake_peers.symm_rendezvous
+        torch.cuda.synchronize = lambda device=None: None
+    torch.manual_seed(0)
+    if case == "one_block":
+        model = torch.nn.Sequential(torch.nn.Linear(12, 8, bias=False))
+    else:
+        model = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 8), torch.nn.Linear(8, 8))
+    pull = mode == "p2p_pull"
+    train_model = model if pull else torch.nn.parallel.DistributedDataParallel(model)
+    opt = lib.DistributedShampoo(
+        model.parameters(), lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3,
+        start_preconditioning_step=3, weight_decay=1e-2, grafting_config=lib.AdamPreconditionerConfig(),
+        distributed_config=lib.DDPDistributedConfig(
+            communication_dtype=torch.bfloat16 if case == "bf16" else torch.float32, num_trainers_per_group=world
+        ),
+        native_runtime_config=lib.NativeRuntimeConfig(
+            backend="torch" if mode == "torch" else "native", comm_path="nccl" if mode == "torch" else "p2p",
+            fuse_gradient_reduction=pull,
+        ),
+    )
+    if mode != "torch":
+        engine = opt._per_group_state_lists[0]["native_engine"]
+        assert engine is not None and engine._p2p and engine._pull == pull
+    g = torch.Generator().manual_seed(5)
+    for _ in range(7):
+        x = torch.randn(16, 12, generator=g)
+        shard = slice(rank * 16 // world, (rank + 1) * 16 // world)
+        opt.zero_grad(set_to_none=not pull)
+        loss = train_model(x[shard]).square().mean()
+        loss.backward()
+        opt.step()
+    if mode != "torch":
+        assert engine._arena.overrun_regions() == []
+        engine.check_status()
+    return [p.detach().clone() for p in model.parameters()]
+
+
+@pytest.mark.parametrize("mode", ["p2p_push", "p2p_pull"])
+@pytest.mark.parametrize("case,world", [("plain", 2), ("plain", 3), ("bf16", 2), ("one_block", 3)])
+def test_engine_peer_memory_paths_match_the_torch_step(case, world, mode):
+    """The all-gather by peer stores from the epilogue and the gradient reduction by peer loads in the
+    prologue (which replaces torch's DDP wrapper), with the engine's own barriers between them, over
+    memory shared between the ranks: the same parameters as the torch step under torch DDP, on every
+    rank, and the arena's guard regions intact."""
+    from dist_utils_for_tests import run_distributed
+
+    want = run_distributed(_p2p_worker, world, case, "torch")
+    got = run_distributed(_p2p_worker, world, case, mode)
+    for ref_rank, twin_rank in zip(want, got, strict=True):
+        for a, b in zip(ref_rank, twin_rank, strict=True):
+            assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (case, mode, (a - b).abs().max().item())
+    for other in got[1:]:
+        for a, b in zip(got[0], other):
+            assert torch.equal(a, b), "ranks diverged"
