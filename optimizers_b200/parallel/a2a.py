@@ -65,6 +65,9 @@ def _compute_param_chunk_sizes(params: tuple[DTensor, ...], group_size: int) -> 
 
 
 _default_comm_path = "nccl"
+# Device types whose memory the peer exchange can address from every rank.  Tests that stand in
+# shared host memory for NVLink peers add "cpu".
+_PEER_DEVICE_TYPES: tuple[str, ...] = ("cuda",)
 
 
 @contextlib.contextmanager
@@ -123,7 +126,7 @@ class AllToAllContext(abc.ABC):
         self._total_send_size, self._total_recv_size = sum(self._send_sizes), sum(self._recv_sizes)
         self._send_buffer = torch.empty(self._total_send_size, dtype=self._dtype, device=self._device)
         self._recv_buffer = torch.empty(self._total_recv_size, dtype=self._dtype, device=self._device)
-        self._p2p = (comm_path or _default_comm_path) == "p2p" and self._device.type == "cuda" and n > 1
+        self._p2p = (comm_path or _default_comm_path) == "p2p" and self._device.type in _PEER_DEVICE_TYPES and n > 1
         if self._p2p:
             self._setup_peer_exchange()
         self._send_list = _views(self._send_buffer, self._send_sizes)

@@ -361,10 +361,12 @@ class DistributedShampoo(Optimizer):
                 raise ValueError(f"Shampoo got an empty parameter group={group}")
             cls = self._select_distributor_class(group[DISTRIBUTED_CONFIG])
             nrc = self._native_runtime_config
-            on_gpu = group[PARAMS][0].device.type == "cuda"
             # The lossless distributors' exchange follows the native comm path (peer-memory pushes
             # instead of all_to_all) unless the torch back-end was asked for.
+            from optimizers_b200.parallel import a2a
             from optimizers_b200.parallel.a2a import exchange_comm_path
+
+            on_gpu = group[PARAMS][0].device.type in a2a._PEER_DEVICE_TYPES
 
             with exchange_comm_path(nrc.comm_path if (nrc.backend != "torch" and on_gpu) else "nccl"):
                 rec[DISTRIBUTOR] = cls(group, self._runtime_config)

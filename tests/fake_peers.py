@@ -70,8 +70,26 @@ def symm_rendezvous(tensor, group=None):
 
 class FakePeerExt(FakeBlockExt):
     def peer_barrier(self, local_flags, peer_flag_bases, my_rank, world, seq, status):
-        assert world == dist.get_world_size(), "the stand-in's barrier spans all ranks"
-        dist.barrier()
+        """The kernel's protocol: announce ``seq`` in slot ``my_rank`` of every member's flag array, then
+        wait until every slot of the local array has reached ``seq``; a wait that runs out sets the
+        peer-timeout bit of the status word instead of blocking for ever."""
+        import time
+
+        for base in peer_flag_bases.tolist():
+            _at(base + 4 * my_rank, 1, torch.int32)[0] = seq
+        deadline = time.monotonic() + 30.0
+        while bool((local_flags[:world] < seq).any()):
+            if time.monotonic() > deadline:
+                status[0] |= 4
+                return
+            time.sleep(0.0005)
+
+    def build_copy_table(self, specs, device_index):
+        return (list(specs), None, len(specs))
+
+    def peer_copy(self, specs, _chunks, _n):
+        for source, destination, nbytes in specs:
+            ctypes.memmove(destination, source, nbytes)
 
     def grad_prologue(self, blocks, tiles, n, grad_ptrs, l2, beta1, beta3, bc1, graft_kind, g_beta2, g_weight, g_bc2, g_eps,
                       write_split, status, num_grad_peers, grad_scale):

@@ -240,8 +240,22 @@ def _sharded_worker(rank, world, strategy, backend):
 
     import optimizers_b200 as lib
 
-    if backend == "native":
+    if backend != "torch":
         install_cpu_engine(setattr)
+    if backend == "native_p2p":
+        import torch.distributed._symmetric_memory as symm_mem
+
+        import fake_peers
+        from optimizers_b200.ops import build
+
+        import optimizers_b200.parallel.a2a as a2a
+
+        ext = fake_peers.FakePeerExt()
+        build.load = lambda: ext
+        symm_mem.empty = fake_peers.symm_empty
+        symm_mem.rendezvous = fake_peers.symm_rendezvous
+        torch.cuda.synchronize = lambda device=None: None
+        a2a._PEER_DEVICE_TYPES = ("cuda", "cpu")
     torch.manual_seed(0)
     model = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 8), torch.nn.Tanh(), torch.nn.Linear(8, 4))
     cpu = torch.device("cpu")
@@ -264,7 +278,9 @@ def _sharded_worker(rank, world, strategy, backend):
     opt = lib.DistributedShampoo(
         model.parameters(), lr=1e-2, betas=(0.9, 0.999), epsilon=1e-4, max_preconditioner_dim=8, precondition_frequency=3,
         start_preconditioning_step=3, weight_decay=1e-2, grafting_config=lib.AdamPreconditionerConfig(), distributed_config=cfg,
-        native_runtime_config=lib.NativeRuntimeConfig(backend=backend),
+        native_runtime_config=lib.NativeRuntimeConfig(
+            backend="torch" if backend == "torch" else "native", comm_path="p2p" if backend == "native_p2p" else "nccl"
+        ),
     )
     engines = [rec.get("native_engine") for rec in opt._per_group_state_lists]
     g = torch.Generator().manual_seed(5)
@@ -273,6 +289,17 @@ def _sharded_worker(rank, world, strategy, backend):
         opt.zero_grad()
         torch.nn.functional.cross_entropy(model(x), y).backward()
         opt.step()
+    if backend == "native_p2p":
+        for rec, engine in zip(opt._per_group_state_lists, engines):
+            d = rec["distributor"]
+            if getattr(d, "_gather_grads_ctx", None) is not None:  # lossless: the all-to-all contexts own the arenas
+                for ctx in (d._gather_grads_ctx, d._redistribute_ctx):
+                    if ctx._group_size > 1:
+                        assert ctx._p2p and ctx._arena.overrun_regions() == []
+                    ctx.check_status()
+            else:
+                assert engine._p2p and engine._arena.overrun_regions() == []
+            engine.check_status()
     local = [(p.to_local() if isinstance(p, DTensor) else p).detach().clone() for p in model.parameters()]
     return local, [e is not None for e in engines]
 
@@ -536,3 +563,19 @@ def test_engine_peer_memory_paths_match_the_torch_step(case, world, mode):
     for other in got[1:]:
         for a, b in zip(got[0], other):
             assert torch.equal(a, b), "ranks diverged"
+
+
+
+@pytest.mark.parametrize("strategy,world", [("hsdp", 4), ("hybrid_shard", 4), ("fully_shard:ROUND_ROBIN", 2), ("hybrid_shard:ROUND_ROBIN", 4)])
+def test_engine_peer_memory_paths_under_the_sharded_distributors(strategy, world):
+    """``comm_path="p2p"`` beyond plain DDP: the replicate groups of HSDP / hybrid shard gather the
+    directions by peer stores within their sub-group (the flag barrier spans that sub-group only), and
+    the lossless ROUND_ROBIN exchange moves gradients and parameters by grouped peer copies."""
+    from dist_utils_for_tests import run_distributed
+
+    want = run_distributed(_sharded_worker, world, strategy, "torch")
+    got = run_distributed(_sharded_worker, world, strategy, "native_p2p")
+    for (ref_rank, _), (twin_rank, engines) in zip(want, got, strict=True):
+        assert all(engines)
+        for a, b in zip(ref_rank, twin_rank, strict=True):
+            assert a.shape == b.shape and torch.allclose(a, b, rtol=1e-4, atol=2e-6), (strategy, (a - b).abs().max().item())
