@@ -69,6 +69,8 @@ def symm_rendezvous(tensor, group=None):
 
 
 class FakePeerExt(FakeBlockExt):
+    barrier_timeout = 30.0  # seconds a rank waits for the others before it reports the peer timeout
+
     def peer_barrier(self, local_flags, peer_flag_bases, my_rank, world, seq, status):
         """The kernel's protocol: announce ``seq`` in slot ``my_rank`` of every member's flag array, then
         wait until every slot of the local array has reached ``seq``; a wait that runs out sets the
@@ -77,7 +79,7 @@ class FakePeerExt(FakeBlockExt):
 
         for base in peer_flag_bases.tolist():
             _at(base + 4 * my_rank, 1, torch.int32)[0] = seq
-        deadline = time.monotonic() + 30.0
+        deadline = time.monotonic() + self.barrier_timeout
         while bool((local_flags[:world] < seq).any()):
             if time.monotonic() > deadline:
                 status[0] |= 4

@@ -579,3 +579,68 @@ def test_engine_peer_memory_paths_under_the_sharded_distributors(strategy, world
         assert all(engines)
         for a, b in zip(ref_rank, twin_rank, strict=True):
             assert a.shape == b.shape and torch.allclose(a, b, rtol=1e-4, atol=2e-6), (strategy, (a - b).abs().max().item())
+
+
+def _departing_rank_worker(rank, world):
+    import time
+
+    import torch.distributed._symmetric_memory as symm_mem
+
+    import fake_peers
+    import optimizers_b200 as lib
+    from optimizers_b200.ops import build
+
+    install_cpu_engine(setattr)
+    ext = fake_peers.FakePeerExt()
+    ext.barrier_timeout = 1.0
+    build.load = lambda: ext
+    symm_mem.empty = fake_peers.symm_empty
+    symm_mem.rendezvous = fake_peers.symm_rendezvous
+    torch.cuda.synchronize = lambda device=None: None
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 8))
+    opt = lib.DistributedShampoo(
+        model.parameters(), lr=1e-2, epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3, start_preconditioning_step=3,
+        grafting_config=lib.AdamPreconditionerConfig(),
+        distributed_config=lib.DDPDistributedConfig(communication_dtype=torch.float32, num_trainers_per_group=world),
+        native_runtime_config=lib.NativeRuntimeConfig(backend="native", comm_path="p2p", fuse_gradient_reduction=True),
+    )
+    engine = opt._per_group_state_lists[0]["native_engine"]
+    g = torch.Generator().manual_seed(5)
+
+    def step():
+        opt.zero_grad(set_to_none=False)
+        model(torch.randn(8, 12, generator=g)).square().mean().backward()
+        opt.step()
+
+    step()
+    step()
+    if rank == 1:
+        time.sleep(3.0)  # leaves between steps; stays alive until the other rank has given up waiting
+        return "left"
+    before = [p.detach().clone() for p in model.parameters()]
+    start = time.monotonic()
+    try:
+        step()  # the entry barrier runs out: the status word gets the peer-timeout bit
+        waited = time.monotonic() - start
+        engine.check_status()  # (a refresh step checks the word itself and raises from inside the step)
+    except RuntimeError as error:
+        waited = time.monotonic() - start
+        unchanged = all(torch.equal(a, b) for a, b in zip(before, model.parameters()))
+        return ("raised", str(error), waited, unchanged)
+    return ("silent", "", waited, False)
+
+
+def test_a_rank_that_leaves_is_reported_by_the_bounded_peer_wait():
+    """Failure made on the host: one rank stops stepping.  The other's flag wait runs out after its
+    limit, the status word carries the peer-timeout bit, ``check_status`` raises, and the parameters
+    were left as they were (the gathered apply skips its update when that bit is set)."""
+    from dist_utils_for_tests import run_distributed
+
+    results = run_distributed(_departing_rank_worker, 2)
+    assert results[1] == "left"
+    outcome, message, waited, unchanged = results[0]
+    assert outcome == "raised", results[0]
+    assert "peer" in message.lower()
+    assert 0.9 < waited < 10.0
+    assert unchanged
