@@ -133,3 +133,19 @@ class FakePeerExt(FakeBlockExt):
             for base in peer_bases:
                 _at(base + b.slot_offset, b.m * b.n, _DTYPES[send_dtype]).copy_(private[id(b)])
             b.send = 0
+
+    def run_gemm_plan_push(self, specs, _tiles, _n, alpha, beta, split, status, peer_bases, send_dtype):
+        """The last preconditioner product with the all-gather in its epilogue: the result, cast to
+        the communication dtype, goes to the block's slot in every rank's gather buffer (and its
+        squared norm to ``sumsq``); nothing is written locally."""
+        for spec in specs:
+            a_hi, a_lo, b_hi, b_lo, _c, _d_hi, _d_lo, sumsq, _ldc, _ldd, flags, _upper, push_offset = spec[:13]
+            assert flags & self.FLAG_PEER_PUSH and flags & self.FLAG_NO_C
+            A = a_hi + (a_lo if a_lo is not None else 0)
+            B = b_hi + (b_lo if b_lo is not None else 0)
+            out = alpha * (A.double() @ B.double().T).float()
+            if flags & self.FLAG_SUMSQ:
+                sumsq[0] += (out.double() ** 2).sum().float()
+            flat = out.reshape(-1).to(_DTYPES[send_dtype])
+            for base in peer_bases:
+                _at(base + push_offset, flat.numel(), _DTYPES[send_dtype]).copy_(flat)
