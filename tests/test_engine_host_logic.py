@@ -173,6 +173,19 @@ def test_engine_with_a_gradient_that_goes_missing(cpu_engine):
 # ----------------------------------------------------------------------------------------------
 # The same under the DDP distributor, ranks as gloo processes
 # ----------------------------------------------------------------------------------------------
+_reference_runs: dict = {}
+
+
+def _torch_reference(worker, world, *args):
+    """The torch-step run of a scenario, made once per session however many native forms are compared with it."""
+    from dist_utils_for_tests import run_distributed
+
+    key = (worker.__name__, world, args)
+    if key not in _reference_runs:
+        _reference_runs[key] = run_distributed(worker, world, *args, "torch")
+    return _reference_runs[key]
+
+
 def _ddp_worker(rank, world, case, backend):
     import optimizers_b200 as lib
 
@@ -220,7 +233,7 @@ def test_engine_under_ddp_matches_the_torch_step_on_every_rank(case, world):
     every rank."""
     from dist_utils_for_tests import run_distributed
 
-    want = run_distributed(_ddp_worker, world, case, "torch")
+    want = _torch_reference(_ddp_worker, world, case)
     got = run_distributed(_ddp_worker, world, case, "native")
     for ref_rank, twin_rank in zip(want, got, strict=True):
         for a, b in zip(ref_rank, twin_rank, strict=True):
@@ -314,7 +327,7 @@ def test_engine_under_the_sharded_distributors_matches_the_torch_step(strategy, 
     copies with their all-to-all write-back, and the replicate-group all-gather of the hybrid forms."""
     from dist_utils_for_tests import run_distributed
 
-    want = run_distributed(_sharded_worker, world, strategy, "torch")
+    want = _torch_reference(_sharded_worker, world, strategy)
     got = run_distributed(_sharded_worker, world, strategy, "native")
     for (ref_rank, _), (twin_rank, engines) in zip(want, got, strict=True):
         assert all(engines), "the engine was not built on every rank"
@@ -447,7 +460,7 @@ def test_engine_mode_switches_under_ddp_match_the_torch_step():
     switches every parameter (the owners' deltas travel through the all-gather buffer)."""
     from dist_utils_for_tests import run_distributed
 
-    want = run_distributed(_gpa_ddp_worker, 2, "torch")
+    want = _torch_reference(_gpa_ddp_worker, 2)
     got = run_distributed(_gpa_ddp_worker, 2, "native")
     for ref_rank, twin_rank in zip(want, got, strict=True):
         for a_list, b_list in zip(ref_rank, twin_rank, strict=True):
@@ -557,7 +570,7 @@ def test_engine_peer_memory_paths_match_the_torch_step(case, world, mode):
     rank, and the arena's guard regions intact."""
     from dist_utils_for_tests import run_distributed
 
-    want = run_distributed(_p2p_worker, world, case, "torch")
+    want = _torch_reference(_p2p_worker, world, case)
     got = run_distributed(_p2p_worker, world, case, mode)
     # The GEMM-epilogue form rounds the unscaled direction to the communication dtype and scales on
     # the receiving side; the other forms round the finished update: in bf16 they differ by its rounding.
@@ -578,7 +591,7 @@ def test_engine_peer_memory_paths_under_the_sharded_distributors(strategy, world
     the lossless ROUND_ROBIN exchange moves gradients and parameters by grouped peer copies."""
     from dist_utils_for_tests import run_distributed
 
-    want = run_distributed(_sharded_worker, world, strategy, "torch")
+    want = _torch_reference(_sharded_worker, world, strategy)
     got = run_distributed(_sharded_worker, world, strategy, "native_p2p")
     for (ref_rank, _), (twin_rank, engines) in zip(want, got, strict=True):
         assert all(engines)
