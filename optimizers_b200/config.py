@@ -660,7 +660,7 @@ class FullyShardDistributedConfig(DistributedConfig):
                 "num_sub_groups > 1 requires param_assignment_strategy != DEFAULT "
                 "(REPLICATE or ROUND_ROBIN); only the lossless FSDP/HSDP "
                 "distributors support param-group splitting. Got "
-                f"self.num_sub_groups={self.num_sub_groups}, self.param_assignment_strategy={self.param_assignment_strategy}."
+                f"self.num_sub_groups={self.num_sub_groups}, self.param_assignment_strategy={self.param_assignment_strategy!r}."
             )
 
 

@@ -352,7 +352,7 @@ class DistributedShampoo(Optimizer):
             case FullyShardDistributedConfig():
                 return P.FullyShardLosslessDistributor if lossless else P.FullyShardDistributor
             case _:
-                raise NotImplementedError(f"distributed_config={distributed_config} not supported!")
+                raise NotImplementedError(f"{distributed_config=} not supported!")
 
     @torch.no_grad()
     def _instantiate_distributor(self) -> None:
@@ -437,7 +437,7 @@ class DistributedShampoo(Optimizer):
                 block_list=blocks, preconditioner_config=cfg,
                 native_gemm_mode=None if nrc.backend == "torch" else nrc.gemm_mode,
             )
-        raise NotImplementedError(f"preconditioner_config={cfg} not supported!")
+        raise NotImplementedError(f"preconditioner_config={cfg!r} not supported!")
 
     @torch.no_grad()
     def _instantiate_shampoo_preconditioner_list(self) -> None:
@@ -522,7 +522,7 @@ class DistributedShampoo(Optimizer):
                     self.state[p][LR_SUM] = rec[LR_SUM]
             else:
                 raise NotImplementedError(
-                    f"group[ITERATE_AVERAGING_CONFIG]={cfg} is not supported! "
+                    f"group[ITERATE_AVERAGING_CONFIG]={cfg!r} is not supported! "
                     "Supported configs: ClassicMomentumConfig, GeneralizedPrimalAveragingConfig, ScheduleFreeConfig."
                 )
 
