@@ -167,3 +167,59 @@ def test_against_reference_utils():
         bins_a = B.greedy_bin_pack(sizes, 3, cost_fn=lambda x: x)
         bins_b = R.greedy_bin_pack(sizes, 3, cost_fn=lambda x: x)
         assert bins_a == bins_b
+
+
+def test_random_shapes_block_like_the_reference():
+    """Property test: for random parameter shapes, merge thresholds and block sizes, the merged
+    shape, the shapes and contents of the blocks and the split of a list of parameter groups agree
+    with the reference's ``utils/shampoo_utils.py``; so does the whole optimizer's block list
+    (``distributor/shampoo_distributor.py`` there), compared through the state keys."""
+    from hypothesis import given, settings, strategies as st
+
+    from ref_oracle import reference, reference_available
+
+    if not reference_available():
+        pytest.skip("reference not installed")
+    ref = reference()
+    from distributed_shampoo.utils import shampoo_utils as R
+
+    import optimizers_b200 as ob
+
+    shapes = st.lists(st.integers(1, 9), min_size=0, max_size=4).map(tuple)
+
+    @settings(max_examples=150, deadline=None)
+    @given(shape=shapes, threshold=st.integers(1, 200), target=st.sampled_from([1, 2, 3, math.inf]),
+           block=st.sampled_from([1, 2, 3, 5, 8, math.inf]))
+    def check(shape, threshold, target, block):
+        merged = B.merge_small_dims(shape, threshold, target)
+        assert merged == R.merge_small_dims(shape, threshold, target)
+        numel = math.prod(shape)
+        t = torch.arange(numel, dtype=torch.float32).reshape(merged)
+        mine, theirs = B.multi_dim_split(t, block), R.multi_dim_split(t, block)
+        assert len(mine) == len(theirs)
+        assert all(torch.equal(a, b) for a, b in zip(mine, theirs))
+
+    check()
+
+    @settings(max_examples=25, deadline=None)
+    @given(shape_list=st.lists(st.lists(st.integers(1, 7), min_size=1, max_size=3).map(tuple), min_size=1, max_size=4),
+           block=st.sampled_from([2, 3, 4, 8]), target=st.sampled_from([1, 2, math.inf]))
+    def check_optimizer(shape_list, block, target):
+        keys = []
+        for lib in (ref, ob):
+            params = [torch.nn.Parameter(torch.zeros(s)) for s in shape_list]
+            opt = lib.DistributedShampoo(
+                params, max_preconditioner_dim=block, precondition_frequency=1,
+                distributed_config=lib.SingleDeviceDistributedConfig(target_parameter_dimensionality=target),
+            )
+            for p in params:
+                p.grad = torch.ones_like(p)
+            opt.step()
+            state = opt.state_dict()["state"]
+            keys.append({
+                index: sorted((name, tuple(value["filtered_grad"].shape) if "filtered_grad" in value else ()) for name, value in entry.items() if name.startswith("block_"))
+                for index, entry in state.items()
+            })
+        assert keys[0] == keys[1]
+
+    check_optimizer()
