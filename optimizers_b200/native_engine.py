@@ -858,6 +858,54 @@ class NativeGroupEngine:
             self._arena.region("grads").zero_()
 
     # ------------------------------------------------------------------------------------------
+    # Observability
+    # ------------------------------------------------------------------------------------------
+    def memory_report(self) -> dict[str, int]:
+        """Bytes this group keeps on the device, by purpose; arrays that share storage (the search
+        direction in the place of G, chain intermediates in the place of G^T) are counted once.
+
+        ``state``: what a checkpoint holds (factors, inverse roots / eigenvectors, corrected
+        eigenvalues, filtered gradient, grafting and momentum buffers).  ``operands``: the tf32
+        (hi, lo) operand arrays of the gradient, its transpose, the filtered gradient and the chain
+        intermediates.  ``mirrors``: unpacked (hi, lo) copies of the inverse roots / eigenvectors
+        and their transposes.  ``exchange``: all-gather buffers or the peer-addressable arena."""
+        seen: set[tuple[int, int]] = set()
+
+        def total(tensors) -> int:
+            count = 0
+            for t in tensors:
+                if t is None:
+                    continue
+                key = (t.data_ptr(), t.numel() * t.element_size())
+                if key not in seen:
+                    seen.add(key)
+                    count += key[1]
+            return count
+
+        def tensors_of(obj) -> list[Tensor]:
+            found = []
+            for value in vars(obj).values():
+                for item in value if isinstance(value, (tuple, list)) else (value,):
+                    if isinstance(item, Tensor):
+                        found.append(item)
+            return found
+
+        report = {"state": 0, "operands": 0, "mirrors": 0, "exchange": 0}
+        operand_fields = [f for f in _Block.__slots__ if f.endswith(("_hi", "_lo")) and not f.startswith(("inv_", "qt_"))]
+        for b in self._blocks:
+            report["state"] += total([b.m1, b.v, b.mom, b.z, *tensors_of(b.factors)])
+            report["operands"] += total([getattr(b, f) for f in operand_fields] + [b.p])
+            for field in ("inv_hi", "inv_lo", "qt_hi", "qt_lo"):
+                report["mirrors"] += total(getattr(b, field) or [])
+        if self._p2p:
+            report["exchange"] = int(self._arena.nbytes)
+        elif self._ddp:
+            buffer = self._dist._global_dist_buffer
+            report["exchange"] = buffer.numel() * buffer.element_size()
+        report["total"] = sum(report.values())
+        return report
+
+    # ------------------------------------------------------------------------------------------
     # The step
     # ------------------------------------------------------------------------------------------
     def _raise_for(self, code: int) -> None:

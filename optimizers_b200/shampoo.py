@@ -548,6 +548,14 @@ class DistributedShampoo(Optimizer):
                 rec[CUDA_STREAM] = torch.cuda.Stream(device=group[PARAMS][0].device)
                 logger.info("param_group_%d: stream_id=%s", i, rec[CUDA_STREAM].stream_id)
 
+    def native_memory_report(self) -> list[dict[str, int] | None]:
+        """Per parameter group: the device bytes its sm_100a engine keeps, by purpose (see
+        ``NativeGroupEngine.memory_report``), or None where the group runs the torch step."""
+        return [
+            rec[NATIVE_ENGINE].memory_report() if rec.get(NATIVE_ENGINE) is not None else None
+            for rec, _ in self._groups()
+        ]
+
     # ------------------------------------------------------------------------------------------
     # Masking (blocks without a gradient drop out of every per-block list)
     # ------------------------------------------------------------------------------------------

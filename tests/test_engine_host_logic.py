@@ -662,3 +662,33 @@ def test_a_rank_that_leaves_is_reported_by_the_bounded_peer_wait():
     assert "peer" in message.lower()
     assert 0.9 < waited < 10.0
     assert unchanged
+
+
+@pytest.mark.parametrize("gemm_mode", ["tf32x3", "tf32"])
+def test_memory_report_counts_every_array_once(cpu_engine, gemm_mode):
+    """The engine's own account of its device memory: checked by hand for one 20 x 36 weight cut
+    into 16-wide blocks.  With split (hi, lo) operands a block m x n holds G, G^T and the filtered
+    gradient twice each (the direction and the chain intermediate live in G and G^T) and its two
+    inverse roots twice; a single-pass tf32 configuration holds half of that."""
+    torch.manual_seed(0)
+    layer = torch.nn.Linear(36, 20, bias=False)
+    opt = ob.DistributedShampoo(
+        layer.parameters(), lr=1e-2, epsilon=1e-4, max_preconditioner_dim=16, precondition_frequency=3,
+        native_runtime_config=ob.NativeRuntimeConfig(backend="native", gemm_mode=gemm_mode),
+    )
+    (report,) = opt.native_memory_report()
+    copies = 2 if gemm_mode == "tf32x3" else 1
+    pad = lambda n: (n + 3) // 4 * 4  # noqa: E731
+    operands = mirrors = state = 0
+    for m in (16, 4):
+        for n in (16, 16, 4):
+            operands += copies * 4 * (2 * m * pad(n) + n * pad(m))
+            mirrors += copies * 4 * (m * pad(m) + n * pad(n))
+            # packed factors and inverse roots, filtered gradient (no grafting, no momentum)
+            state += 4 * (2 * (m * (m + 1) // 2 + n * (n + 1) // 2) + m * n)
+    assert report["operands"] == operands
+    assert report["mirrors"] == mirrors
+    assert report["state"] == state
+    assert report["exchange"] == 0 and report["total"] == operands + mirrors + state
+    torch_only = ob.DistributedShampoo(layer.parameters(), native_runtime_config=ob.NativeRuntimeConfig(backend="torch"))
+    assert torch_only.native_memory_report() == [None]
