@@ -57,3 +57,62 @@ def test_combined_linear_matches_linear(bias):
     x = torch.randn(4, 5)
     torch.testing.assert_close(layer(x), ref(x))
     assert layer.combined_weight.shape == (3, 5 + int(bias))
+
+
+def test_quantized_tensor_list_workspace_warnings_and_edge_cases(caplog):
+    """Behaviours pinned by the reference's ``utils/tests/shampoo_quantization_test.py``, plus the
+    properties of this implementation: the in-place pair reuses one flat workspace, the copying
+    ``dequantize`` hands out fresh tensors."""
+    import logging
+
+    triples = [(torch.full((3, 2), float(i), dtype=torch.float16), None, None) for i in range(5)]
+    qlist = QuantizedTensorList(triples, torch.float16, torch.float64)
+    assert len(qlist) == 5 and len(qlist.compress((True, False, True, False, False))) == 2
+
+    with caplog.at_level(logging.WARNING):
+        qlist.quantize_()  # nothing to store yet
+    assert "Must first call dequantize_()" in caplog.text and not qlist.is_dequantized_stored()
+
+    qlist.dequantize_()
+    first = qlist.dequantized_value
+    assert all(t.dtype == torch.float64 for t in first)
+    # one flat allocation: the views follow each other in one storage
+    assert len({t.untyped_storage().data_ptr() for t in first}) == 1
+    caplog.clear()
+    with caplog.at_level(logging.WARNING):
+        qlist.dequantize_()
+    assert "already stored" in caplog.text
+    torch._foreach_add_(qlist.dequantized_value, 0.5)
+    caplog.clear()
+    with caplog.at_level(logging.WARNING):
+        qlist.quantize(tuple(torch.zeros(3, 2, dtype=torch.float64) for _ in range(5)))
+    assert "Existing stored dequantized values" in caplog.text
+    qlist.quantize_()
+    assert not qlist.is_dequantized_stored()
+    for i, t in enumerate(qlist.quantized_value):
+        assert t.dtype == torch.float16 and torch.equal(t, torch.full((3, 2), i + 0.5, dtype=torch.float16))
+    qlist.dequantize_()
+    assert qlist.dequantized_value[0].data_ptr() == first[0].data_ptr()  # the workspace is kept
+    qlist.quantize_()
+    fresh = qlist.dequantize()
+    assert fresh[0].data_ptr() != first[0].data_ptr() and torch.equal(fresh[2], torch.full((3, 2), 2.5, dtype=torch.float64))
+
+    same = QuantizedTensorList(triples, torch.float16, torch.float16)
+    assert same.dequantize() is same.quantized_value
+    with DequantizeQuantizedTensorListContext(same):
+        assert same.dequantized_value is same.quantized_value
+    assert not same.is_dequantized_stored()
+
+    assert len(QuantizedTensorList([], torch.float16)) == 0
+    with pytest.raises(TypeError, match="quantized_data must be"):
+        QuantizedTensorList([torch.zeros(2)], torch.float32)
+    with pytest.raises(AssertionError, match="is not supported"):
+        QuantizedTensorList(triples, torch.float16, torch.int8)
+    with pytest.raises(AssertionError):
+        QuantizedTensorList([(torch.zeros(2, dtype=torch.int8), torch.zeros(1), None)], torch.int8)
+    info = BlockInfo(param=torch.zeros(1), composable_block_ids=(0, "block_0"))
+    assert QuantizedTensor(torch.zeros(4, dtype=torch.int8), info).min_value is not None
+    with pytest.raises(NotImplementedError, match="Quantization for torch.int8"):
+        QuantizedTensor(torch.zeros(4, dtype=torch.int8), info).dequantize(torch.float32)
+    with pytest.raises(NotImplementedError):
+        QuantizedTensor(torch.zeros(4, dtype=torch.int8), info).quantize(torch.ones(4))
