@@ -35,6 +35,16 @@ def test_loss_metrics_window_and_lifetime():
         m.update(torch.tensor(v))
     assert float(m.window_loss) == pytest.approx(4.0) and float(m.lifetime_loss) == pytest.approx(3.0)
     m.log(); m.update_global_metrics(); m.log_global_metrics(); m.flush()
+    # a long stream against the plain definitions, across several turns of the ring
+    gen = torch.Generator().manual_seed(0)
+    values = (torch.rand(57, generator=gen) * 10).tolist()
+    for window in (1, 5, 100):
+        m = LossMetrics(window_size=window)
+        for i, v in enumerate(values, 1):
+            m.update(torch.tensor(v))
+            tail = values[max(0, i - window) : i]
+            assert float(m.window_loss) == pytest.approx(sum(tail) / len(tail), rel=1e-5)
+            assert float(m.lifetime_loss) == pytest.approx(sum(values[:i]) / i, rel=1e-5)
 
 
 def test_resolvers_and_strategies():
