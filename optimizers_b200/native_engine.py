@@ -76,6 +76,15 @@ def _pad4(n: int) -> int:
     return (n + 3) // 4 * 4
 
 
+# Configurations whose 2-D blocks may carry a factor on one dim only (the other switched off by an
+# exponent of 0): one-sided products.  Under KL-Shampoo such a block has no other dim to precondition
+# its Gram along, so its statistics are the plain ones.
+_ONE_SIDED_CONFIGS = (
+    RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig,
+    RootInvKLShampooPreconditionerConfig, EigendecomposedKLShampooPreconditionerConfig,
+)
+
+
 def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     pc = group[PRECONDITIONER_CONFIG]
     if type(pc) in (RootInvShampooPreconditionerConfig, RootInvKLShampooPreconditionerConfig):
@@ -111,8 +120,8 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     # so that every rank of a group reaches the same verdict.
     overrides = getattr(pc, "inverse_exponent_override", {}).values()
     if any(0.0 in (o.values() if isinstance(o, dict) else (o,)) for o in overrides):
-        if type(pc) not in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig):
-            return "dims switched off by an exponent of 0 have a native step only under (eigendecomposed) root-inverse Shampoo"
+        if type(pc) not in _ONE_SIDED_CONFIGS:
+            return "dims switched off by an exponent of 0 have no native step under eigenvalue-corrected Shampoo"
         if any(b.dim() > 2 for b in rec[DISTRIBUTOR]._global_blocked_params):
             return "dims switched off by an exponent of 0 have no native step next to blocks of order 3"
     plist = rec[SHAMPOO_PRECONDITIONER_LIST]
@@ -121,8 +130,8 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
     ):
         if block.dim() > 3 or (block.dim() == 3 and not _order3_ok(block, pc)):
             return f"block of order {block.dim()} and shape {tuple(block.shape)} has no native step yet"
-        if not all(sel) and (block.dim() > 2 or type(pc) not in (RootInvShampooPreconditionerConfig, EigendecomposedShampooPreconditionerConfig)):
-            return "blocks with unpreconditioned dims have a native step only for 1-D / 2-D blocks of (eigendecomposed) root-inverse Shampoo"
+        if not all(sel) and (block.dim() > 2 or type(pc) not in _ONE_SIDED_CONFIGS):
+            return "blocks with unpreconditioned dims have a native step only for 1-D / 2-D blocks of root-inverse, eigendecomposed and KL Shampoo"
         if block.numel() == 0:
             return "empty blocks"
     # The same verdict on every rank: ranks that disagreed would meet in different collectives.
@@ -368,7 +377,7 @@ class NativeGroupEngine:
             # The chain intermediate T^T [n, m_pad] takes over the memory of G^T, whose last reader
             # (the factor SYRK) has run before the first chain GEMM writes.
             b.y_hi = b.y_lo = b.zt_hi = b.zt_lo = None
-            if self._kl and two_d:
+            if self._kl and left and right:
                 # Y = G R^(-1/p) [m, n] and Z^T = G^T L^(-1/p) [n, m]: operands of the KL factor Grams.
                 b.y_hi, b.zt_hi = zeros(b.m, b.n_pad), zeros(b.n, b.m_pad)
                 if self._split:
@@ -568,7 +577,8 @@ class NativeGroupEngine:
             t_hi = t_lo = None
             if right:
                 t_hi, t_lo = op(b.gt_hi, b.n, b.m), (op(b.gt_lo, b.n, b.m) if self._split else None)
-            if two_d and self._kl:
+            if self._kl and left and right:
+                # (a block with a single factor has no other dim to precondition along: plain Gram)
                 # KL-Shampoo statistics: L <- Gram of G R^(-1/p), R <- Gram of L^(-1/p) G, with the
                 # current inverse roots (reference: shampoo_preconditioner_list.py:1945-2046).
                 a_hi, a_lo = op(b.g_hi, b.m, b.n), (op(b.g_lo, b.m, b.n) if sp else None)

@@ -138,6 +138,13 @@ def _configs():
             grafting_config=ob.AdamPreconditionerConfig(),
             preconditioner_config=ob.RootInvShampooPreconditionerConfig(inverse_exponent_override={1: 0.0, 2: 0.0}),
         ),
+        "kl_rows_only": dict(
+            grafting_config=ob.AdamPreconditionerConfig(),
+            preconditioner_config=ob.RootInvKLShampooPreconditionerConfig(inverse_exponent_override={2: {0: 0.5, 1: 0.0}}),
+        ),
+        "kl_columns_only_vectors_off": dict(
+            preconditioner_config=ob.EigendecomposedKLShampooPreconditionerConfig(inverse_exponent_override={1: 0.0, 2: {0: 0.0, 1: 0.5}}),
+        ),
         "coupled_newton": dict(
             grafting_config=ob.AdamPreconditionerConfig(), epsilon=1e-4,
             preconditioner_config=ob.RootInvShampooPreconditionerConfig(amortized_computation_config=ob.CoupledNewtonConfig(tolerance=1e-6)),
