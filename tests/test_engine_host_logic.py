@@ -591,7 +591,11 @@ def test_engine_peer_memory_paths_match_the_torch_step(case, world, mode):
 
 
 
-@pytest.mark.parametrize("strategy,world", [("hsdp", 4), ("hybrid_shard", 4), ("fully_shard:ROUND_ROBIN", 2), ("hybrid_shard:ROUND_ROBIN", 4)])
+@pytest.mark.parametrize(
+    "strategy,world",
+    # ("hsdp", 8) is the layout of the flagship benchmark on eight GPUs: replicate 2 x shard 4
+    [("hsdp", 4), ("hsdp", 8), ("hybrid_shard", 4), ("fully_shard:ROUND_ROBIN", 2), ("hybrid_shard:ROUND_ROBIN", 4)],
+)
 def test_engine_peer_memory_paths_under_the_sharded_distributors(strategy, world):
     """``comm_path="p2p"`` beyond plain DDP: the replicate groups of HSDP / hybrid shard gather the
     directions by peer stores within their sub-group (the flag barrier spans that sub-group only), and
