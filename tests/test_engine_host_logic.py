@@ -591,6 +591,22 @@ def test_engine_peer_memory_paths_match_the_torch_step(case, world, mode):
 
 
 
+def test_engine_peer_memory_paths_on_eight_ranks():
+    """The DDP arm of the flagship benchmark on eight GPUs: bf16 directions, gradients reduced by peer
+    loads in the prologue, directions gathered by peer stores, eight ranks sharing nine blocks (one rank
+    owns two)."""
+    from dist_utils_for_tests import run_distributed
+
+    want = _torch_reference(_p2p_worker, 8, "bf16")
+    got = run_distributed(_p2p_worker, 8, "bf16", "p2p_pull")
+    for ref_rank, twin_rank in zip(want, got, strict=True):
+        for a, b in zip(ref_rank, twin_rank, strict=True):
+            assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (a - b).abs().max().item()
+    for other in got[1:]:
+        for a, b in zip(got[0], other):
+            assert torch.equal(a, b), "ranks diverged"
+
+
 @pytest.mark.parametrize(
     "strategy,world",
     # ("hsdp", 8) is the layout of the flagship benchmark on eight GPUs: replicate 2 x shard 4
