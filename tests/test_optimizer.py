@@ -528,3 +528,39 @@ def test_schedules_and_parameter_groups_match_reference_bitwise(scenario):
     assert l_ref == l_our
     _assert_same_params(m_ref, m_our)
     _compare_state(o_ref.state_dict()["state"], o_our.state_dict()["state"])
+
+
+def test_cpu_mlp_configuration_of_the_baseline_matches_reference_bitwise():
+    """The CPU configuration that serves as the oracle: MLP 784-512-10, batch 64, 100 steps, lr 1e-3,
+    betas (0.9, 0.999), epsilon 1e-12, blocks of 256, refresh every 10 steps from step 10, Adam
+    grafting, root-inverse Shampoo by eigendecomposition.  Losses and parameters of all 100 steps
+    are identical to the reference's (``distributed_shampoo/distributed_shampoo.py``)."""
+    from ref_oracle import reference, reference_available
+
+    if not reference_available():
+        pytest.skip("reference not installed")
+
+    def run(lib):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 512), torch.nn.ReLU(), torch.nn.Linear(512, 10))
+        opt = lib.DistributedShampoo(
+            model.parameters(), lr=1e-3, betas=(0.9, 0.999), epsilon=1e-12, max_preconditioner_dim=256,
+            precondition_frequency=10, start_preconditioning_step=10,
+            grafting_config=lib.AdamPreconditionerConfig(beta2=0.999, epsilon=1e-8),
+            preconditioner_config=lib.DefaultShampooConfig,
+        )
+        g = torch.Generator().manual_seed(1)
+        losses = []
+        for _ in range(100):
+            x, y = torch.randn(64, 1, 28, 28, generator=g), torch.randint(0, 10, (64,), generator=g)
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(model(x), y)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        return losses, [p.detach().clone() for p in model.parameters()]
+
+    their_losses, their_params = run(reference())
+    my_losses, my_params = run(ob)
+    assert their_losses == my_losses
+    assert all(torch.equal(a, b) for a, b in zip(their_params, my_params, strict=True))
