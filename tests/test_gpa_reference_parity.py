@@ -102,3 +102,53 @@ def test_gpa_adamw_matches_the_reference_bitwise(name):
                 assert torch.equal(value, og[key]), key
             else:
                 assert value == og[key], (key, value, og[key])
+
+
+def _random_run(cls, averaging_types, seed):
+    """Hyperparameters, mode visits and learning-rate cuts drawn from ``seed``; the parameters seen
+    in eval mode along the way and at the end."""
+    import random
+
+    rng = random.Random(seed)
+    kw = dict(
+        lr=rng.choice([1e-3, 1e-2, 0.1, 1.0]), eps=rng.choice([1e-8, 1e-6]), beta1=rng.choice([0.0, 0.5, 0.9]),
+        beta2=rng.choice([0.9, 0.999]), weight_decay=rng.choice([0, 1e-2, 0.1]), use_wd_on_y=rng.random() < 0.5,
+        iterate_averaging_type=rng.choice(list(averaging_types)), train_interp_coeff=rng.choice([0.7, 0.9, 1.0]),
+        eval_interp_coeff=rng.choice([0.0, 0.9, 0.9967]), weight_pow_coeff=rng.choice([0.0, 1.0]),
+        weight_lr_power=rng.choice([0, 2]),
+    )
+    if rng.random() < 0.3:
+        kw["lr"] = torch.tensor(kw["lr"])
+    torch.manual_seed(seed)
+    model = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh(), torch.nn.Linear(8, 2))
+    opt = cls(model.parameters(), **kw)
+    opt.train()
+    g = torch.Generator().manual_seed(seed + 1)
+    seen = []
+    for _ in range(9):
+        if rng.random() < 0.3:
+            opt.eval()
+            seen.append([p.detach().clone() for p in model.parameters()])
+            opt.train()
+        if rng.random() < 0.2:
+            for group in opt.param_groups:
+                group["lr"] = group["lr"] * 0.5
+        x, y = torch.randn(16, 6, generator=g), torch.randn(16, 2, generator=g)
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(model(x), y).backward()
+        opt.step()
+    opt.eval()
+    seen.append([p.detach().clone() for p in model.parameters()])
+    return seen
+
+
+@needs_reference_gpa
+def test_random_hyperparameters_and_mode_visits_match_reference_bitwise():
+    their_module, their_types = _reference()
+    for seed in range(40):
+        want = _random_run(their_module.GPAAdamW, their_types.IterateAveragingType, seed)
+        got = _random_run(GPAAdamW, IterateAveragingType, seed)
+        assert len(want) == len(got)
+        for a_list, b_list in zip(want, got):
+            for a, b in zip(a_list, b_list, strict=True):
+                assert torch.equal(a, b), (seed, (a - b).abs().max().item())
