@@ -719,3 +719,24 @@ def test_memory_report_counts_every_array_once(cpu_engine, gemm_mode):
     assert report["exchange"] == 0 and report["total"] == operands + mirrors + state
     torch_only = ob.DistributedShampoo(layer.parameters(), native_runtime_config=ob.NativeRuntimeConfig(backend="torch"))
     assert torch_only.native_memory_report() == [None]
+
+
+def test_engine_keeps_the_filtered_gradient_apart_from_the_direction(cpu_engine):
+    """Without bias correction the reference's applied filtered gradient is the state tensor itself,
+    and with SGD grafting before preconditioning starts the search direction is that tensor too: its
+    in-place scaling by -lr ends up in the state (the torch step reproduces this, bit for bit).  The
+    engine's prologue writes the moving average and the direction to different arrays."""
+    stored = {}
+    for backend in ("torch", "native"):
+        p = torch.nn.Parameter(torch.zeros(3, 3))
+        opt = ob.DistributedShampoo(
+            [p], lr=0.1, betas=(0.9, 1.0), epsilon=1e-3, use_bias_correction=False, grafting_config=ob.SGDPreconditionerConfig(),
+            precondition_frequency=2, start_preconditioning_step=4, max_preconditioner_dim=16,
+            native_runtime_config=ob.NativeRuntimeConfig(backend=backend),
+        )
+        p.grad = torch.ones(3, 3)
+        opt.step()
+        stored[backend] = opt.state_dict()["state"][0]["block_0"]["filtered_grad"].flatten()[0].item()
+        assert p.flatten()[0].item() == pytest.approx(-0.01)  # the same update either way
+    assert stored["torch"] == pytest.approx(-0.01)  # the reference's write-through
+    assert stored["native"] == pytest.approx(0.1)  # the moving average of a gradient of 1 from 0
