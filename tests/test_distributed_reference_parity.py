@@ -200,3 +200,107 @@ def test_ddp_ranks_without_blocks_and_parameters_without_gradients(case, world):
     for params in run_distributed(_ddp_corner_worker, world, case):
         for a, b in zip(ref, params):
             assert torch.equal(a, b), (a - b).abs().max()
+
+
+def _random_options_worker(rank, world, strategy, seeds):
+    """For every seed: one random option set (see test_random_option_sets_parity) and random
+    distributor options, trained under ``strategy`` by the reference and by this library in the
+    same ranks; returns, per seed, both outcomes and whether the local parameters are identical."""
+    import logging
+    import math
+    import random
+    import sys
+
+    sys.path.insert(0, REF_DIR)
+    import distributed_shampoo as ref_lib
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy, fully_shard
+    from torch.distributed.tensor import DTensor
+
+    import optimizers_b200 as our_lib
+    import test_random_option_sets_parity as option_sets
+
+    logging.disable(logging.WARNING)
+    results = []
+    for seed in seeds:
+
+        def train(lib):
+            rng = random.Random(seed)
+            family, kw = option_sets._options(lib, rng)
+            if family == "spectral":  # needs whole matrices: not a distributor topic
+                return "skipped", None
+            if kw["max_preconditioner_dim"] == math.inf:
+                kw["max_preconditioner_dim"] = 8
+            torch.manual_seed(seed)
+            model = _model()
+            cpu = torch.device("cpu")
+            comm_dtype = rng.choice([torch.float32, torch.bfloat16])
+            if strategy == "ddp":
+                model = torch.nn.parallel.DistributedDataParallel(model)
+                cfg = lib.DDPDistributedConfig(
+                    communication_dtype=comm_dtype, num_trainers_per_group=rng.choice([-1, world]),
+                    communicate_params=rng.random() < 0.5,
+                )
+            elif strategy == "hsdp":
+                mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+                model = FSDP(model, device_mesh=mesh, sharding_strategy=ShardingStrategy.HYBRID_SHARD, use_orig_params=True, device_id=cpu)
+                cfg = lib.HSDPDistributedConfig(
+                    param_to_metadata=lib.compile_fsdp_parameter_metadata(model), device_mesh=mesh,
+                    communication_dtype=comm_dtype, communicate_params=rng.random() < 0.5,
+                )
+            elif strategy == "fully_shard_replicate":
+                fully_shard(model, mesh=init_device_mesh("cpu", (world,)))
+                cfg = lib.FullyShardDistributedConfig(
+                    param_assignment_strategy=lib.FSDPParamAssignmentStrategy.REPLICATE, num_sub_groups=rng.choice([1, 2])
+                )
+            else:
+                mesh = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("replicate", "shard"))
+                fully_shard(model, mesh=mesh)
+                cfg = lib.HybridShardDistributedConfig(device_mesh=mesh, communication_dtype=comm_dtype)
+            kw["distributed_config"] = cfg
+            try:
+                opt = lib.DistributedShampoo(model.parameters(), **kw)
+            except Exception as err:  # noqa: BLE001 - the kind and the text are what is compared
+                return f"constructor: {type(err).__name__}: {option_sets._strip(str(err))}", None
+            g = torch.Generator().manual_seed(seed + 1 + rank)
+            opt.train()
+            try:
+                for step in range(6):
+                    x, y = torch.randn(8, 12, generator=g), torch.randint(0, 5, (8,), generator=g)
+                    opt.zero_grad()
+                    torch.nn.functional.cross_entropy(model(x), y).backward()
+                    opt.step()
+                    if step == 3:
+                        opt.eval()
+                        opt.train()
+                opt.eval()
+            except Exception as err:  # noqa: BLE001
+                return f"step: {type(err).__name__}: {option_sets._strip(str(err))}", None
+            return "trained", [(p.to_local() if isinstance(p, DTensor) else p).detach().clone() for p in model.parameters()]
+
+        theirs, their_params = train(ref_lib)
+        dist.barrier()
+        mine, my_params = train(our_lib)
+        dist.barrier()
+        identical = their_params is None or all(
+            a.shape == b.shape and torch.equal(a, b) for a, b in zip(their_params, my_params, strict=True)
+        )
+        results.append((seed, theirs, mine, identical))
+    return results
+
+
+@needs_reference
+@pytest.mark.parametrize("strategy,world", [("ddp", 2), ("hsdp", 4), ("fully_shard_replicate", 2), ("hybrid_shard", 4)])
+def test_random_option_sets_under_distributors_match_reference_bitwise(strategy, world):
+    """Eight random option sets per strategy (with random communication dtype, parameter or
+    direction communication, group size, sub-groups): every rank ends with the reference's local
+    parameters, bit for bit, including a visit to eval mode."""
+    per_rank = run_distributed(_random_options_worker, world, strategy, list(range(8)))
+    trained = 0
+    for results in per_rank:
+        for seed, theirs, mine, identical in results:
+            assert theirs == mine, (strategy, seed, theirs, mine)
+            assert identical, (strategy, seed)
+            trained += theirs == "trained"
+    assert trained >= 5 * world
