@@ -180,17 +180,26 @@ def test_engine_with_a_gradient_that_goes_missing(cpu_engine):
 # ----------------------------------------------------------------------------------------------
 # The same under the DDP distributor, ranks as gloo processes
 # ----------------------------------------------------------------------------------------------
-_reference_runs: dict = {}
+_scenario_runs: dict = {}
 
 
-def _torch_reference(worker, world, *args):
-    """The torch-step run of a scenario, made once per session however many native forms are compared with it."""
+def _every_mode(rank, world, worker, args, modes):
+    """Inside one rank: the scenario under each mode in turn (the torch step first; the stand-ins a
+    native mode installs leave the torch step alone)."""
+    return {mode: worker(rank, world, *args, mode) for mode in modes}
+
+
+def _scenario(worker, world, args, modes):
+    """Per-rank results of ``worker(rank, world, *args, mode)`` for every mode, from one set of spawned
+    ranks per scenario however many tests look at it: starting the ranks costs more than the steps."""
     from dist_utils_for_tests import run_distributed
 
     key = (worker.__name__, world, args)
-    if key not in _reference_runs:
-        _reference_runs[key] = run_distributed(worker, world, *args, "torch")
-    return _reference_runs[key]
+    if key not in _scenario_runs:
+        per_rank = run_distributed(_every_mode, world, worker, args, modes)
+        _scenario_runs[key] = {mode: [rank_result[mode] for rank_result in per_rank] for mode in modes}
+    assert set(modes) <= set(_scenario_runs[key]), "a scenario is always asked for with the same modes"
+    return _scenario_runs[key]
 
 
 def _ddp_worker(rank, world, case, backend):
@@ -240,8 +249,8 @@ def test_engine_under_ddp_matches_the_torch_step_on_every_rank(case, world):
     every rank."""
     from dist_utils_for_tests import run_distributed
 
-    want = _torch_reference(_ddp_worker, world, case)
-    got = run_distributed(_ddp_worker, world, case, "native")
+    runs = _scenario(_ddp_worker, world, (case,), ("torch", "native"))
+    want, got = runs["torch"], runs["native"]
     for ref_rank, twin_rank in zip(want, got, strict=True):
         for a, b in zip(ref_rank, twin_rank, strict=True):
             assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (case, (a - b).abs().max().item())
@@ -253,6 +262,17 @@ def test_engine_under_ddp_matches_the_torch_step_on_every_rank(case, world):
 # ----------------------------------------------------------------------------------------------
 # ... and under the sharded distributors
 # ----------------------------------------------------------------------------------------------
+_P2P_SHARDED = [("hsdp", 4), ("hsdp", 8), ("hybrid_shard", 4), ("fully_shard:ROUND_ROBIN", 2), ("hybrid_shard:ROUND_ROBIN", 4)]
+
+
+def _sharded_modes(strategy, world):
+    """The torch step, the engine over the collectives and, where the strategy has one, the engine
+    over peer memory (the eight-rank layout is run for that form only)."""
+    if (strategy, world) == ("hsdp", 8):
+        return ("torch", "native_p2p")
+    return ("torch", "native", "native_p2p") if (strategy, world) in _P2P_SHARDED else ("torch", "native")
+
+
 def _sharded_worker(rank, world, strategy, backend):
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, ShardingStrategy, fully_shard
@@ -334,8 +354,8 @@ def test_engine_under_the_sharded_distributors_matches_the_torch_step(strategy, 
     copies with their all-to-all write-back, and the replicate-group all-gather of the hybrid forms."""
     from dist_utils_for_tests import run_distributed
 
-    want = _torch_reference(_sharded_worker, world, strategy)
-    got = run_distributed(_sharded_worker, world, strategy, "native")
+    runs = _scenario(_sharded_worker, world, (strategy,), _sharded_modes(strategy, world))
+    want, got = runs["torch"], runs["native"]
     for (ref_rank, _), (twin_rank, engines) in zip(want, got, strict=True):
         assert all(engines), "the engine was not built on every rank"
         for a, b in zip(ref_rank, twin_rank, strict=True):
@@ -467,8 +487,8 @@ def test_engine_mode_switches_under_ddp_match_the_torch_step():
     switches every parameter (the owners' deltas travel through the all-gather buffer)."""
     from dist_utils_for_tests import run_distributed
 
-    want = _torch_reference(_gpa_ddp_worker, 2)
-    got = run_distributed(_gpa_ddp_worker, 2, "native")
+    runs = _scenario(_gpa_ddp_worker, 2, (), ("torch", "native"))
+    want, got = runs["torch"], runs["native"]
     for ref_rank, twin_rank in zip(want, got, strict=True):
         for a_list, b_list in zip(ref_rank, twin_rank, strict=True):
             for a, b in zip(a_list, b_list):
@@ -577,8 +597,8 @@ def test_engine_peer_memory_paths_match_the_torch_step(case, world, mode):
     rank, and the arena's guard regions intact."""
     from dist_utils_for_tests import run_distributed
 
-    want = _torch_reference(_p2p_worker, world, case)
-    got = run_distributed(_p2p_worker, world, case, mode)
+    runs = _scenario(_p2p_worker, world, (case,), ("torch", "p2p_push", "p2p_pull", "p2p_gemm"))
+    want, got = runs["torch"], runs[mode]
     # The GEMM-epilogue form rounds the unscaled direction to the communication dtype and scales on
     # the receiving side; the other forms round the finished update: in bf16 they differ by its rounding.
     atol = 5e-4 if (case == "bf16" and mode == "p2p_gemm") else 2e-6
@@ -597,8 +617,8 @@ def test_engine_peer_memory_paths_on_eight_ranks():
     owns two)."""
     from dist_utils_for_tests import run_distributed
 
-    want = _torch_reference(_p2p_worker, 8, "bf16")
-    got = run_distributed(_p2p_worker, 8, "bf16", "p2p_pull")
+    runs = _scenario(_p2p_worker, 8, ("bf16",), ("torch", "p2p_pull"))
+    want, got = runs["torch"], runs["p2p_pull"]
     for ref_rank, twin_rank in zip(want, got, strict=True):
         for a, b in zip(ref_rank, twin_rank, strict=True):
             assert torch.allclose(a, b, rtol=1e-4, atol=2e-6), (a - b).abs().max().item()
@@ -609,8 +629,7 @@ def test_engine_peer_memory_paths_on_eight_ranks():
 
 @pytest.mark.parametrize(
     "strategy,world",
-    # ("hsdp", 8) is the layout of the flagship benchmark on eight GPUs: replicate 2 x shard 4
-    [("hsdp", 4), ("hsdp", 8), ("hybrid_shard", 4), ("fully_shard:ROUND_ROBIN", 2), ("hybrid_shard:ROUND_ROBIN", 4)],
+    _P2P_SHARDED,  # ("hsdp", 8) is the layout of the flagship benchmark on eight GPUs: replicate 2 x shard 4
 )
 def test_engine_peer_memory_paths_under_the_sharded_distributors(strategy, world):
     """``comm_path="p2p"`` beyond plain DDP: the replicate groups of HSDP / hybrid shard gather the
@@ -618,8 +637,8 @@ def test_engine_peer_memory_paths_under_the_sharded_distributors(strategy, world
     the lossless ROUND_ROBIN exchange moves gradients and parameters by grouped peer copies."""
     from dist_utils_for_tests import run_distributed
 
-    want = _torch_reference(_sharded_worker, world, strategy)
-    got = run_distributed(_sharded_worker, world, strategy, "native_p2p")
+    runs = _scenario(_sharded_worker, world, (strategy,), _sharded_modes(strategy, world))
+    want, got = runs["torch"], runs["native_p2p"]
     for (ref_rank, _), (twin_rank, engines) in zip(want, got, strict=True):
         assert all(engines)
         for a, b in zip(ref_rank, twin_rank, strict=True):
