@@ -155,3 +155,76 @@ def test_random_option_sets_match_reference_bitwise(first_seed):
         assert trained >= 6
     finally:
         logging.disable(logging.NOTSET)
+
+
+def _same_tree(a, b, path="state"):
+    """None when two state trees agree (keys, tensor shapes / dtypes / values, other leaves by
+    repr), else a description of the first difference."""
+    if isinstance(a, dict):
+        if set(map(str, a)) != set(map(str, b)):
+            return f"{path}: keys differ"
+        for key in a:
+            found = _same_tree(a[key], b[key], f"{path}/{key}")
+            if found:
+                return found
+        return None
+    if isinstance(a, torch.Tensor):
+        same = a.shape == b.shape and a.dtype == b.dtype and torch.equal(a, b)
+        return None if same else f"{path}: tensor differs"
+    return None if _strip(repr(a)) == _strip(repr(b)) else f"{path}: {a!r} against {b!r}"
+
+
+def test_checkpoints_of_random_option_sets_interchange_with_the_reference():
+    """For each option set: after four steps the two ``state_dict()["state"]`` trees are identical;
+    a fresh reference optimizer resumed from this library's checkpoint, and a fresh optimizer of
+    this library resumed from the reference's, continue exactly like the uninterrupted runs."""
+    import copy
+
+    logging.disable(logging.WARNING)
+
+    def make(lib, seed):
+        _, kw = _options(lib, random.Random(seed))
+        torch.manual_seed(seed)
+        model = torch.nn.Sequential(torch.nn.Linear(9, 12), torch.nn.Tanh(), torch.nn.Linear(12, 3, bias=False))
+        return model, lib.DistributedShampoo(model.parameters(), **kw)
+
+    def train(model, opt, data_seed, steps):
+        g = torch.Generator().manual_seed(data_seed)
+        opt.train()
+        for _ in range(steps):
+            x, y = torch.randn(8, 9, generator=g), torch.randint(0, 3, (8,), generator=g)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+
+    checked = 0
+    try:
+        for seed in range(100, 124):
+            try:
+                (their_model, theirs), (my_model, mine) = make(reference(), seed), make(ob, seed)
+                train(their_model, theirs, seed, 4)
+                train(my_model, mine, seed, 4)
+            except Exception:  # noqa: BLE001 - refused or failing option sets are the other tests' topic
+                continue
+            their_state, my_state = theirs.state_dict(), mine.state_dict()
+            assert _same_tree(their_state["state"], my_state["state"]) is None, seed
+            (their_model2, theirs2), (my_model2, mine2) = make(reference(), seed), make(ob, seed)
+            their_model2.load_state_dict(my_model.state_dict())
+            my_model2.load_state_dict(their_model.state_dict())
+            for fresh, source in ((theirs2, my_state), (mine2, their_state)):
+                checkpoint = fresh.state_dict()
+                checkpoint["state"] = copy.deepcopy(source["state"])
+                fresh.load_state_dict(checkpoint)
+            try:
+                runs = ((their_model, theirs), (my_model, mine), (their_model2, theirs2), (my_model2, mine2))
+                for model, opt in runs:
+                    train(model, opt, seed + 7, 3)
+            except Exception:  # noqa: BLE001
+                continue
+            for model, _ in runs[1:]:
+                for a, b in zip(their_model.parameters(), model.parameters(), strict=True):
+                    assert torch.equal(a, b), seed
+            checked += 1
+        assert checked >= 12
+    finally:
+        logging.disable(logging.NOTSET)
