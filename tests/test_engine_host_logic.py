@@ -759,3 +759,70 @@ def test_engine_keeps_the_filtered_gradient_apart_from_the_direction(cpu_engine)
         assert p.flatten()[0].item() == pytest.approx(-0.01)  # the same update either way
     assert stored["torch"] == pytest.approx(-0.01)  # the reference's write-through
     assert stored["native"] == pytest.approx(0.1)  # the moving average of a gradient of 1 from 0
+
+
+def test_engine_on_random_option_sets_matches_the_torch_step(cpu_engine):
+    """Thirty random option sets of the families whose result does not hinge on the choice of
+    eigenvectors inside a null space (root-inverse by eigendecomposition and by coupled Newton,
+    eigendecomposed, both KL forms), with random grafting, betas, weight decay, averaging, block
+    size, schedule, exponent overrides and GEMM mode: the engine ends where the torch step ends.
+    Option sets in which the reference lets the search direction write through to the
+    filtered-gradient state get bias correction switched on (the engine deliberately does not
+    reproduce that; see test_engine_keeps_the_filtered_gradient_apart_from_the_direction)."""
+    import logging
+    import math
+    import random
+
+    import test_random_option_sets_parity as option_sets
+
+    def train(backend, seed):
+        rng = random.Random(seed)
+        while True:
+            family, kw = option_sets._options(ob, rng)
+            if family in ("root_inv", "root_inv_newton", "eigendecomposed", "kl_root_inv", "kl_eigendecomposed"):
+                break
+        kw["epsilon"] = max(kw["epsilon"], 1e-3)
+        if kw["max_preconditioner_dim"] == math.inf:
+            kw["max_preconditioner_dim"] = 32
+        identity_blocks = getattr(kw["preconditioner_config"], "inverse_exponent_override", {}).get(1) == 0.0
+        if type(kw.get("grafting_config")).__name__ in ("SGDPreconditionerConfig", "NoneType") or identity_blocks:
+            kw["use_bias_correction"] = True
+        runtime = ob.NativeRuntimeConfig(backend=backend, gemm_mode=rng.choice(["tf32x3", "tf32"]))
+        torch.manual_seed(seed)
+        if rng.random() < 0.3:
+            model = torch.nn.Sequential(torch.nn.Conv2d(2, 4, 3), torch.nn.Flatten(), torch.nn.Linear(4 * 4 * 4, 3))
+            shape = (32, 2, 6, 6)
+        else:
+            model = torch.nn.Sequential(torch.nn.Linear(9, 12), torch.nn.Tanh(), torch.nn.Linear(12, 3, bias=False))
+            shape = (32, 9)
+        try:
+            opt = ob.DistributedShampoo(model.parameters(), native_runtime_config=runtime, **kw)
+        except RuntimeError:
+            return None  # not covered natively (backend="native" says so instead of falling back)
+        g = torch.Generator().manual_seed(seed + 1)
+        opt.train()
+        for step in range(7):
+            x, y = torch.randn(*shape, generator=g), torch.randint(0, 3, (shape[0],), generator=g)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+            if step == 4:
+                opt.eval()
+                opt.train()
+        opt.eval()
+        return [p.detach().clone() for p in model.parameters()]
+
+    logging.disable(logging.WARNING)
+    try:
+        compared = 0
+        for seed in range(30):
+            got = train("native", seed)
+            if got is None:
+                continue
+            want = train("torch", seed)
+            compared += 1
+            for a, b in zip(want, got, strict=True):
+                assert torch.allclose(a, b, rtol=1e-3, atol=1e-3 * float(a.abs().max())), (seed, (a - b).abs().max().item())
+        assert compared >= 15
+    finally:
+        logging.disable(logging.NOTSET)
