@@ -719,7 +719,9 @@ class NativeRuntimeConfig:
                they cover and the torch path otherwise; ``"torch"`` forces the torch path;
                ``"native"`` raises if a group cannot run natively.
     gemm_mode: ``"tf32x3"`` splits fp32 operands into two tf32 terms and issues three tensor-core
-               products (fp32-grade accuracy); ``"tf32"`` issues one.
+               products (fp32-grade accuracy); ``"tf32"`` issues one (relative error of a product
+               about 1e-3) and keeps one operand array instead of a (hi, lo) pair, which halves the
+               engine's operand arrays and mirrors (``DistributedShampoo.native_memory_report()``).
     comm_path: ``"nccl"`` uses ``torch.distributed`` collectives; ``"p2p"`` lets the kernels
                load/store peer memory directly over NVLink: the direction epilogue stores each
                block's search direction into every peer's gather buffer (all-gather fused into
