@@ -151,6 +151,9 @@ def _order3_ok(block: Tensor, pc: Any) -> bool:
     return covered and block.is_contiguous() and a % 4 == 0 and b % 4 == 0
 
 
+_FALLBACK_REASON = "native_engine_fallback_reason"  # key of the per-group record: why the group runs the torch step
+
+
 def maybe_build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, Any], cfg: NativeRuntimeConfig):
     """Return a native engine for the group, or ``None`` to use the torch step.
 
@@ -159,6 +162,7 @@ def maybe_build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[s
     if cfg.backend == "torch" or group[PARAMS][0].device.type != "cuda":
         if cfg.backend == "native":
             raise RuntimeError("native backend requested for a parameter group that is not on a CUDA device")
+        rec[_FALLBACK_REASON] = 'backend="torch" was requested' if cfg.backend == "torch" else "the parameters are not on a CUDA device"
         return None
     return build_native_engine(optimizer, rec, group, cfg)
 
@@ -171,6 +175,7 @@ def build_native_engine(optimizer: Any, rec: dict[str, Any], group: dict[str, An
         if cfg.backend == "native":
             raise RuntimeError(f"native backend requested but {reason}")
         logger.info("Parameter group uses the torch step: %s.", reason)
+        rec[_FALLBACK_REASON] = reason
         return None
     return NativeGroupEngine(optimizer, rec, group, cfg)
 

@@ -548,6 +548,15 @@ class DistributedShampoo(Optimizer):
                 rec[CUDA_STREAM] = torch.cuda.Stream(device=group[PARAMS][0].device)
                 logger.info("param_group_%d: stream_id=%s", i, rec[CUDA_STREAM].stream_id)
 
+    def native_coverage(self) -> list[str]:
+        """Per parameter group: ``"native"`` when its steps run on the sm_100a engine, else
+        ``"torch: <why>"`` (what ``backend="native"`` would have raised)."""
+        return [
+            "native" if rec.get(NATIVE_ENGINE) is not None
+            else f"torch: {rec.get('native_engine_fallback_reason', 'no engine was built')}"
+            for rec, _ in self._groups()
+        ]
+
     def native_memory_report(self) -> list[dict[str, int] | None]:
         """Per parameter group: the device bytes its sm_100a engine keeps, by purpose (see
         ``NativeGroupEngine.memory_report``), or None where the group runs the torch step."""

@@ -826,3 +826,31 @@ def test_engine_on_random_option_sets_matches_the_torch_step(cpu_engine):
         assert compared >= 15
     finally:
         logging.disable(logging.NOTSET)
+
+
+def test_native_coverage_names_the_reason_of_a_fallback(monkeypatch):
+    """``backend="auto"`` falls back silently; ``native_coverage()`` says per parameter group whether
+    the engine runs it and, if not, why (the text ``backend="native"`` would raise with)."""
+    import optimizers_b200.native_engine as engine_module
+    from optimizers_b200.ops import build
+
+    layer = torch.nn.Linear(6, 4)
+    assert ob.DistributedShampoo(layer.parameters()).native_coverage() == ["torch: the parameters are not on a CUDA device"]
+    forced = ob.DistributedShampoo(layer.parameters(), native_runtime_config=ob.NativeRuntimeConfig(backend="torch"))
+    assert forced.native_coverage() == ['torch: backend="torch" was requested']
+
+    # the engine's own decision, on CPU parameters through the stand-in of the extension
+    install_cpu_engine(monkeypatch.setattr)
+    monkeypatch.setattr(engine_module, "maybe_build_native_engine", engine_module.build_native_engine)
+    assert build.available()
+    covered = ob.DistributedShampoo(layer.parameters(), max_preconditioner_dim=8)
+    assert covered.native_coverage() == ["native"]
+    groups = [
+        {"params": [layer.weight]},
+        {"params": [layer.bias], "preconditioner_config": ob.DefaultSignDescentPreconditionerConfig},
+    ]
+    mixed = ob.DistributedShampoo(groups, max_preconditioner_dim=8)
+    first, second = mixed.native_coverage()
+    assert first == "native"
+    assert second == "torch: preconditioner config SignDescentPreconditionerConfig has no native step yet"
+    assert mixed.native_memory_report()[1] is None
