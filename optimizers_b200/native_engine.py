@@ -98,10 +98,6 @@ def _why_not_covered(rec: dict[str, Any], group: dict[str, Any]) -> str | None:
         dtypes = (pc.factor_matrix_dtype, pc.factor_matrix_eigenvectors_dtype, pc.corrected_eigenvalues_dtype)
         if any(d != torch.float32 for d in dtypes):
             return "factor matrices, eigenvectors and corrected eigenvalues must be fp32"
-        # From the configuration and the global block list (the same on every rank), not from this rank's blocks.
-        orders = {b.dim() for b in rec[DISTRIBUTOR]._global_blocked_params}
-        if len({pc.inverse_exponent_override.get(order, 1 / 2) for order in orders}) > 1:
-            return "eigenvalue-corrected Shampoo with different roots per tensor order has no native step yet"
     else:
         return f"preconditioner config {type(pc).__name__} has no native step yet"
     gc = group[GRAFTING_CONFIG]
@@ -540,6 +536,15 @@ class NativeGroupEngine:
             )
         self._table = ext.build_block_table(specs)
         if self._soap:
+            # The scaling between projection and unprojection takes one exponent per launch: blocks
+            # whose tensor order carries its own exponent override get a table of their own.
+            by_root: dict[float, list] = {}
+            for b, spec in zip(blocks, specs):
+                by_root.setdefault(float(b.factors.roots[0]), []).append(spec)
+            if len(by_root) == 1:
+                self._eig_tables = [(self._table, next(iter(by_root)))]
+            else:
+                self._eig_tables = [(ext.build_block_table(group), root) for root, group in by_root.items()]
             self._build_soap_plans(blocks)
             return
 
@@ -1079,15 +1084,14 @@ class NativeGroupEngine:
         if graft_only:
             return launches
         run("f")
-        blocks_t, tiles_t, n_tiles = self._table
-        root = self._active_blocks[0].factors.roots[0]
-        ext.eig_scale(blocks_t, tiles_t, n_tiles, float(plist._bias_correction2), 1.0 / root, plist._epsilon, split)
+        for (blocks_t, tiles_t, n_tiles), root in self._eig_tables:
+            ext.eig_scale(blocks_t, tiles_t, n_tiles, float(plist._bias_correction2), 1.0 / root, plist._epsilon, split)
         for stage in ("u0", "u1"):
             if plans[stage] is not None:
                 run(stage)
                 launches += 1
         run("u2")
-        return launches + 3
+        return launches + 2 + len(self._eig_tables)
 
     def _refresh(self, blocks: list[_Block]) -> None:
         """Amortised computation for the given blocks: batched native path for the eigen root

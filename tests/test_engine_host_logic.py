@@ -126,6 +126,11 @@ def _configs():
             ),
             precondition_frequency=20, start_preconditioning_step=20, steps=26,
         ),
+        "eigenvalue_corrected_exponent_per_order": dict(
+            grafting_config=ob.AdamPreconditionerConfig(),
+            preconditioner_config=ob.EigenvalueCorrectedShampooPreconditionerConfig(inverse_exponent_override={1: 1.0, 2: 0.25}),
+            precondition_frequency=20, start_preconditioning_step=20, steps=24,
+        ),
         "rows_only": dict(
             grafting_config=ob.AdamPreconditionerConfig(),
             preconditioner_config=ob.RootInvShampooPreconditionerConfig(inverse_exponent_override={2: {0: 0.25, 1: 0.0}}),
